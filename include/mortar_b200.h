@@ -1,0 +1,198 @@
+/*
+ * mortar_b200.h -- C ABI of libmortar_b200.so
+ *
+ * B200 (sm_100a) kernels for the MORTAR carved block-sparse ternary SwiGLU MLP.
+ * Every entry point takes plain pointers and sizes, returns 0 or a negative
+ * mortar_status, never throws, never synchronises the device and (unless stated)
+ * never allocates.  Device pointers are borrowed for the duration of the call;
+ * `stream` is a cudaStream_t passed as void*.
+ *
+ * Reference interfaces replaced (paths inside the reference project):
+ *   morph/kernels/triton/fused_decode_step.py:1465-1547  mortar_pack_strips / mortar_gemv
+ *   morph/kernels/triton/fused_decode_step.py:1883-1927  route_flags
+ *   morph/kernels/triton/fused_decode_step.py:293-321    rmsnorm_rows
+ *   morph/sparse/stk/backend/custom_ops.py:35-56         torch.ops.morph_stk.dds
+ *   morph/model/transformer.py:402-431                   _SwiGLUMortar.forward
+ *   morph/inference/deploy_quant.py:56-95,344-374        2-bit ternary pack
+ */
+#ifndef MORTAR_B200_H
+#define MORTAR_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum mortar_status {
+    MORTAR_OK = 0,
+    MORTAR_ERR_NULL = -1,          /* required pointer is NULL                         */
+    MORTAR_ERR_SHAPE = -2,         /* a dimension is zero, negative or not 16-aligned  */
+    MORTAR_ERR_ROWPTR = -3,        /* row pointer not monotone / wrong end value       */
+    MORTAR_ERR_COLIDX = -4,        /* column index out of range or not ascending       */
+    MORTAR_ERR_CODE = -5,          /* a 2-bit field holds the unused value 3           */
+    MORTAR_ERR_ALIGN = -6,         /* pointer not aligned as documented                */
+    MORTAR_ERR_DTYPE = -7,         /* unknown dtype / mode / plane count               */
+    MORTAR_ERR_CAPACITY = -8,      /* destination buffer or built-in limit too small   */
+    MORTAR_ERR_CUDA = -9,          /* a CUDA runtime call failed (see mortar_last_cuda_error) */
+    MORTAR_ERR_UNSUPPORTED = -10   /* combination not implemented                      */
+} mortar_status;
+
+typedef enum mortar_dtype { MORTAR_F32 = 0, MORTAR_BF16 = 1 } mortar_dtype;
+
+/* ---- canonical matrix format: tile-16 BCSR with 2-bit ternary codes ---------------
+ * W[out,in]; R = out/16 tile rows, C = in/16 tile columns.
+ *   row_ptr  int32[R+1]   CSR pointers over tile rows (empty rows allowed)
+ *   col_idx  uint16[nnz]  tile column of every kept tile, ascending inside a row
+ *   codes    uint8[nnz*64]  one 16x16 tile = 64 bytes, row-major, 4 codes per byte,
+ *                         element i of a byte in bits 2i..2i+1, stored value = code+1
+ *                         (the reference's flat pack at blocking 16,
+ *                         deploy_quant.py:56-71)
+ *   scale    fp32         per-matrix absmean scale (deploy_quant.py:81-95)
+ * This is what the reference's carve(blocking=16)+pack_mortar_ternary produce; a
+ * 128-block carve is the special case "8x8 groups of tiles all kept".
+ */
+
+/* ---- execution layout for the streaming kernels ("stream") ------------------------
+ * Built once on the host from the canonical format.  Tiles of one tile row are cut
+ * into groups of 8 (the last group of a row is padded with all-zero tiles that reuse
+ * a column the row already reads).  A group is 512 bytes: lane l of a warp owns the
+ * 16 bytes at offset 16*l, holding its tensor-core A-fragment codes for all 8 tiles,
+ * so a warp fetches a group with one coalesced 128-bit load per lane.
+ *   grp_ptr  int32[R+1]       groups per tile row (CSR)
+ *   grp_cols uint16[8*G]      tile column of each of the 8 slots of every group
+ *   grp_codes uint8[512*G]    fragment-ordered 2-bit codes
+ */
+typedef struct mortar_stream {
+    const void *grp_codes;   /* device, 16-byte aligned */
+    const void *grp_cols;    /* device, 16-byte aligned */
+    const int32_t *grp_ptr;  /* device */
+    int32_t n_groups;
+    int32_t tile_rows;       /* R = out_features/16 */
+    int32_t tile_cols;       /* C = in_features/16  */
+    float scale;
+} mortar_stream;
+
+const char *mortar_version(void);
+const char *mortar_status_string(int status);
+/* Text of the last CUDA error recorded by a call on this host thread ("" if none). */
+const char *mortar_last_cuda_error(void);
+
+/* ---- host-side packers and validators (no GPU work) ------------------------------- */
+
+/* Checks canonical metadata: row_ptr monotone from 0 to nnz, col_idx < C and strictly
+ * ascending inside a row, no 2-bit field equal to 3.  Replaces the asserts of
+ * morph/sparse/stk/backend/triton_kernels.py:25-29 and matrix.py:90-104. */
+int mortar_validate_bcsr(const int32_t *row_ptr, const uint16_t *col_idx, const uint8_t *codes,
+                         int32_t tile_rows, int32_t tile_cols, int64_t nnz);
+
+/* Number of 8-tile groups the stream layout of this matrix needs (negative = error). */
+int64_t mortar_stream_groups(const int32_t *row_ptr, int32_t tile_rows);
+
+/* Fills grp_ptr[R+1], grp_cols[8*G], grp_codes[512*G] (host buffers sized by
+ * mortar_stream_groups).  Counterpart of mortar_pack_strips,
+ * fused_decode_step.py:1465-1499. */
+int mortar_build_stream(const int32_t *row_ptr, const uint16_t *col_idx, const uint8_t *codes,
+                        int32_t tile_rows, int32_t tile_cols, int64_t nnz,
+                        int32_t *grp_ptr, uint16_t *grp_cols, uint8_t *grp_codes);
+
+/* Inverse of mortar_build_stream for round-trip checks: recovers canonical codes and
+ * column indices (padding slots dropped). */
+int mortar_unpack_stream(const int32_t *grp_ptr, const uint16_t *grp_cols, const uint8_t *grp_codes,
+                         const int32_t *row_ptr, int32_t tile_rows,
+                         uint16_t *col_idx, uint8_t *codes);
+
+/* Splits a reference BCSR with square blocks of `blocking` (a multiple of 16; 128 in
+ * the reference, block_sparse.py:874-899) and flat 2-bit codes into the canonical
+ * tile-16 format.  If drop_zero_tiles != 0, tiles whose 256 codes are all zero are
+ * omitted.  Two-pass: call with codes_out == NULL to obtain nnz16 in *nnz_out and the
+ * row pointers, then again with buffers. */
+int mortar_split_blocks(const int32_t *offsets, const int16_t *column_indices,
+                        const uint8_t *packed, int32_t block_rows, int32_t block_cols,
+                        int32_t blocking, int32_t drop_zero_tiles,
+                        int32_t *row_ptr_out, uint16_t *col_idx_out, uint8_t *codes_out,
+                        int64_t *nnz_out);
+
+/* ---- device entry points --------------------------------------------------------- */
+
+/* Activation planes.  The streaming kernels read activations as P bf16 "planes"
+ * [P][rows][ld] whose sum reproduces the source value: P=1 rounds to bf16 (the
+ * reference prefill dtype, block_sparse.py:947-955), P=3 is exact for fp32 (the
+ * reference decode dtype, engine.py:156-160), P=2 keeps 16 mantissa bits.
+ *
+ * mortar_act_prep: x[rows, cols] (f32 or bf16, row stride ldx elements) -> planes, with
+ * an optional RMSNorm in front (rms_weight fp32[cols] or NULL): (x*rsqrt(mean(x^2)+eps))*w
+ * in fp32, as rmsnorm_rows, fused_decode_step.py:293-321. */
+int mortar_act_prep(const void *x, int x_dtype, int64_t rows, int32_t cols, int64_t ldx,
+                    const float *rms_weight, float eps,
+                    void *planes, int32_t n_planes, int64_t plane_stride, int64_t ld_planes,
+                    void *stream);
+
+/* out_mode of mortar_linear */
+enum { MORTAR_OUT_F32 = 0, MORTAR_OUT_BF16 = 1, MORTAR_OUT_PLANES = 2 };
+/* flags of mortar_linear */
+enum {
+    MORTAR_FLAG_SWIGLU = 1,      /* rows [0,F) are gate, [F,2F) up; out[b, n] = silu(g)*u, F = R/2 */
+    MORTAR_FLAG_ROUND_BF16 = 2,  /* reproduce the reference's bf16 rounding points
+                                    (triton_kernels.py:226, transformer.py:405-427) */
+    MORTAR_FLAG_GATES_ON_INPUT = 4 /* non-SWIGLU call: `gates` describe the INPUT neurons
+                                    (the down projection); tile columns whose spanned
+                                    clusters are all gated to 0 are skipped (rows <= 8) */
+};
+
+/* y = act @ W^T for a stream-format matrix; replaces mortar_gemv
+ * (fused_decode_step.py:1502-1547) and, on token blocks, stk dds
+ * (custom_ops.py:35-56).
+ *   planes        bf16 [n_planes][rows][ld_planes]
+ *   out           MORTAR_OUT_F32: float [rows][ld_out]; MORTAR_OUT_BF16: bf16 [rows][ld_out];
+ *                 MORTAR_OUT_PLANES: bf16 [n_out_planes][rows][ld_out] (plane stride out_plane_stride)
+ *   gates         optional fp32 [rows][ld_gates] cluster gates (SWIGLU only), cluster =
+ *                 neuron / cluster_size (transformer.py:419-427); gate 0 forces an exact 0
+ *   row_act       optional int32 [rows][ld_row_act] flags per OUTPUT tile row (for SWIGLU: per
+ *                 hidden tile row): a tile row is skipped (zeros written) when the flag is 0 for
+ *                 every activation row of the launch block, fused_decode_step.py:1371-1381
+ *   col_act       optional int32 [rows][ld_col_act] flags per INPUT tile column,
+ *                 fused_decode_step.py:1386-1390 (honoured when rows <= 8)
+ */
+int mortar_linear(const mortar_stream *w, const void *planes, int32_t n_planes,
+                  int64_t plane_stride, int64_t ld_planes, int64_t rows,
+                  void *out, int32_t out_mode, int32_t n_out_planes, int64_t out_plane_stride,
+                  int64_t ld_out, int32_t flags,
+                  const float *gates, int64_t ld_gates, int32_t cluster_size,
+                  const int32_t *row_act, int64_t ld_row_act,
+                  const int32_t *col_act, int64_t ld_col_act,
+                  void *stream);
+
+/* gates[rows, n_clusters] -> activity flags, fused_decode_step.py:1883-1927: flag = 1 iff
+ * either spanned cluster (lo/hi index arrays, device int32) has gate > 0. */
+int mortar_route_flags(const float *gates, int64_t rows, int64_t ld_gates,
+                       const int32_t *row_lo, const int32_t *row_hi, int32_t n_row,
+                       const int32_t *col_lo, const int32_t *col_hi, int32_t n_col,
+                       int32_t *row_act, int64_t ld_row_act, int32_t *col_act, int64_t ld_col_act,
+                       void *stream);
+
+/* Bytes of caller-provided workspace mortar_mlp_decode / mortar_mlp_prefill need. */
+int64_t mortar_mlp_workspace_bytes(int64_t rows, int32_t d_model, int32_t d_ff, int32_t n_planes);
+
+/* One SwiGLU MLP application, the body of StaticDecodeEngine._mlp_fn
+ * (engine.py:936-986): [rmsnorm] -> gate_up (+silu(g)*u, *gates) -> down, fp32
+ * accumulation, scale applied after each sum.  x is f32 or bf16 [rows][ldx]; y is f32 or
+ * bf16 [rows][ldy].  n_planes selects the activation precision (3 = exact fp32 decode
+ * semantics, 1 = bf16).  gates optional fp32 [rows][ld_gates] with n_clusters equal
+ * contiguous clusters over d_ff; when given, hidden tile rows / down tile columns whose
+ * gates are all zero are skipped.  workspace: device, 256-byte aligned,
+ * mortar_mlp_workspace_bytes() bytes; contents are scratch.
+ * With MORTAR_FLAG_ROUND_BF16 in `flags` and n_planes == 1 the call reproduces the bf16
+ * rounding points of _SwiGLUMortar.forward under autocast (transformer.py:402-431). */
+int mortar_mlp_decode(const mortar_stream *gate_up, const mortar_stream *down,
+                      const void *x, int x_dtype, int64_t ldx, int64_t rows,
+                      const float *rms_weight, float eps,
+                      const float *gates, int64_t ld_gates, int32_t n_clusters,
+                      void *y, int y_dtype, int64_t ldy,
+                      int32_t n_planes, int32_t flags,
+                      void *workspace, int64_t workspace_bytes, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MORTAR_B200_H */

@@ -1,0 +1,14 @@
+"""B200-native (sm_100a) implementation of the MORTAR carved block-sparse ternary SwiGLU MLP.
+
+Layout: ``csrc/`` holds the CUDA kernels and the C ABI (declared in ``include/mortar_b200.h``
+at the repository root), ``format.py`` the matrix formats and converters, ``ops.py`` the
+torch-facing operators, ``modules.py`` the mirrors of the reference module API, ``synth.py``
+seeded synthetic layers for tests and benchmarks, ``build.py`` the nvcc build.
+"""
+from . import _lib  # noqa: F401
+from .format import MortarMatrix, StreamMatrix, ternary_quantize  # noqa: F401
+from . import ops, synth  # noqa: F401
+from .modules import MortarLinear, SwiGLUMortar  # noqa: F401
+
+__all__ = ["MortarMatrix", "StreamMatrix", "MortarLinear", "SwiGLUMortar", "ops", "synth",
+           "ternary_quantize"]

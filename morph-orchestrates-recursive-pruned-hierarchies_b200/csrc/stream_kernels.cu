@@ -1,0 +1,476 @@
+// Streaming kernels over the 8-tile-group layout: activation-plane preparation (with the
+// optional RMSNorm prologue), the block-sparse ternary linear / SwiGLU kernel used for
+// decode batches and as the generic token-block path, the routing-flag kernel, and the
+// fused per-MLP entry point.
+//
+// The linear kernel keeps the ternary tile as the A operand of mma.m16n8k16 (decoded from
+// 2-bit codes straight into registers) and 8 activation rows as the B operand, so one
+// fetch of a 64-byte tile serves every row of the batch.  Products are exact (+-x or 0 in
+// bf16), accumulation is fp32; the per-matrix scale multiplies the finished sum, as in the
+// reference combine step (morph/kernels/triton/fused_decode_step.py:1441-1459).
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cstdint>
+#include "common.h"
+
+namespace {
+
+constexpr int kWarpsPerCta = 4;
+constexpr int kMaxFlagCols = 4096;     // tile columns coverable by the column-activity bitmap
+
+struct LinearParams {
+    const uint4 *grp_codes;
+    const uint4 *grp_cols;
+    const int *grp_ptr;
+    int R, C;
+    float scale;
+    const uint32_t *planes;            // bf16 pairs
+    long long plane_stride_w;          // in 32-bit words
+    long long ld_w;                    // row stride in 32-bit words
+    int n_planes;
+    long long rows;
+    void *out;
+    int out_mode, n_out_planes;
+    long long out_plane_stride, ld_out;
+    int round_bf16;
+    const float *gates;
+    long long ld_gates;
+    int cluster_size;
+    int gates_on_input;
+    const int *row_act;
+    long long ld_row_act;
+    const int *col_act;
+    long long ld_col_act;
+    int units;                         // output tile rows (LINEAR) or hidden tile rows (SWIGLU)
+};
+
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                          uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Two 2-bit stored values (bits 2q and 16+2q of `word`) -> packed bf16 pair of codes.
+// 0x4300|s is the bf16 number 128+s; subtracting 129 leaves s-1 in {-1,0,+1} exactly.
+__device__ __forceinline__ uint32_t decode_pair(uint32_t word, int q) {
+    uint32_t v = ((word >> (2 * q)) & 0x00030003u) | 0x43004300u;
+    const uint32_t k129 = 0x43014301u;
+    __nv_bfloat162 r = __hsub2(*reinterpret_cast<__nv_bfloat162 *>(&v),
+                               *reinterpret_cast<const __nv_bfloat162 *>(&k129));
+    return *reinterpret_cast<uint32_t *>(&r);
+}
+
+__device__ __forceinline__ float round_bf16(float v) {
+    return __bfloat162float(__float2bfloat16_rn(v));
+}
+
+__device__ __forceinline__ void store_value(const LinearParams &p, long long row, long long col,
+                                            float v) {
+    if (p.out_mode == MORTAR_OUT_F32) {
+        reinterpret_cast<float *>(p.out)[row * p.ld_out + col] = v;
+    } else if (p.out_mode == MORTAR_OUT_BF16) {
+        reinterpret_cast<__nv_bfloat16 *>(p.out)[row * p.ld_out + col] = __float2bfloat16_rn(v);
+    } else {
+        __nv_bfloat16 *o = reinterpret_cast<__nv_bfloat16 *>(p.out) + row * p.ld_out + col;
+        float r = v;
+        for (int pl = 0; pl < p.n_out_planes; ++pl) {
+            __nv_bfloat16 h = __float2bfloat16_rn(r);
+            o[pl * p.out_plane_stride] = h;
+            r -= __bfloat162float(h);
+        }
+    }
+}
+
+// One CTA = 4 warps; WPR warps cooperate on one unit (a tile row, or for SWIGLU a hidden
+// tile row = gate row u and up row u+units), 4/WPR units per CTA.  blockIdx.y selects a
+// block of 8*NT activation rows.
+template <int NT, bool SWIGLU, int WPR>
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+bcsr_stream_kernel(const LinearParams p) {
+    constexpr int UPC = kWarpsPerCta / WPR;
+    constexpr int NACC = SWIGLU ? 2 : 1;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int unit_local = warp / WPR, sub = warp % WPR;
+    const int unit = blockIdx.x * UPC + unit_local;
+    const long long row0 = (long long)blockIdx.y * (8 * NT);
+    const int nrows = (int)min((long long)(8 * NT), p.rows - row0);
+
+    __shared__ float red[(WPR > 1) ? UPC * (WPR - 1) * NACC * NT * 4 * 32 : 1];
+    __shared__ unsigned char col_active[kMaxFlagCols];
+
+    // Column-activity bitmap for this block of rows (only built for small batches).
+    const bool use_cact = (p.col_act != nullptr) || (p.gates_on_input != 0);
+    if (use_cact) {
+        for (int c = threadIdx.x; c < p.C; c += blockDim.x) {
+            int any = 0;
+            if (p.col_act != nullptr) {
+                for (int b = 0; b < nrows; ++b) any |= p.col_act[(row0 + b) * p.ld_col_act + c];
+            } else {
+                const int lo = (c * 16) / p.cluster_size, hi = (c * 16 + 15) / p.cluster_size;
+                for (int b = 0; b < nrows; ++b)
+                    for (int k = lo; k <= hi; ++k)
+                        any |= (p.gates[(row0 + b) * p.ld_gates + k] > 0.f);
+            }
+            col_active[c] = (unsigned char)(any != 0);
+        }
+        __syncthreads();
+    }
+
+    const bool unit_valid = unit < p.units;
+    bool active = unit_valid;
+    if (unit_valid && (p.row_act != nullptr || (SWIGLU && p.gates != nullptr))) {
+        int any = 0;
+        for (int b = lane; b < nrows; b += 32) {
+            if (p.row_act != nullptr) {
+                any |= p.row_act[(row0 + b) * p.ld_row_act + unit];
+            } else {
+                const int lo = (unit * 16) / p.cluster_size, hi = (unit * 16 + 15) / p.cluster_size;
+                for (int k = lo; k <= hi; ++k) any |= (p.gates[(row0 + b) * p.ld_gates + k] > 0.f);
+            }
+        }
+        active = __any_sync(0xffffffffu, any != 0);
+    }
+
+    float acc[NACC][NT][4];
+#pragma unroll
+    for (int a = 0; a < NACC; ++a)
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[a][n][i] = 0.f;
+
+    if (active) {
+        const uint32_t *xb[NT];
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+            long long tok = row0 + n * 8 + g;
+            if (tok > p.rows - 1) tok = p.rows - 1;      // clamped rows compute discarded values
+            xb[n] = p.planes + tok * p.ld_w + t;
+        }
+        int done = 0;   // groups of earlier tile rows of this unit, keeps the round-robin going
+#pragma unroll
+        for (int a = 0; a < NACC; ++a) {
+            const int trow = unit + a * p.units;
+            const int gbeg = p.grp_ptr[trow], gend = p.grp_ptr[trow + 1];
+            int grp = gbeg + ((sub - done) % WPR + WPR) % WPR;
+            uint4 cw = make_uint4(0, 0, 0, 0), cl = make_uint4(0, 0, 0, 0);
+            if (grp < gend) {
+                cw = __ldg(p.grp_codes + (long long)grp * 32 + lane);
+                cl = __ldg(p.grp_cols + grp);
+            }
+            while (grp < gend) {
+                const int ngrp = grp + WPR;
+                uint4 ncw = cw, ncl = cl;
+                if (ngrp < gend) {
+                    ncw = __ldg(p.grp_codes + (long long)ngrp * 32 + lane);
+                    ncl = __ldg(p.grp_cols + ngrp);
+                }
+                const uint32_t cws[4] = {cw.x, cw.y, cw.z, cw.w};
+                const uint32_t cls[4] = {cl.x, cl.y, cl.z, cl.w};
+#pragma unroll
+                for (int s = 0; s < 8; ++s) {
+                    const uint32_t word = cws[s >> 1];
+                    const uint32_t col = (cls[s >> 1] >> (16 * (s & 1))) & 0xffffu;
+                    if (col == 0xffffu) break;                       // padding slots end a row
+                    if (use_cact && !col_active[col]) continue;
+                    uint32_t af[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) af[i] = decode_pair(word, (s & 1) * 4 + i);
+#pragma unroll
+                    for (int n = 0; n < NT; ++n) {
+                        const uint32_t *px = xb[n] + (long long)col * 8;
+                        for (int pl = 0; pl < p.n_planes; ++pl) {
+                            const uint32_t b0 = __ldg(px), b1 = __ldg(px + 4);
+                            mma_16816(acc[a][n], af, b0, b1);
+                            px += p.plane_stride_w;
+                        }
+                    }
+                }
+                cw = ncw; cl = ncl; grp = ngrp;
+            }
+            done += gend - gbeg;
+        }
+    }
+
+    if (WPR > 1) {
+        // fixed-order cross-warp sum: warps sub=1..WPR-1 publish, warp sub=0 adds in order
+        float *mine = red + ((unit_local * (WPR - 1) + (sub > 0 ? sub - 1 : 0)) * NACC * NT * 4) * 32;
+        if (sub > 0) {
+#pragma unroll
+            for (int a = 0; a < NACC; ++a)
+#pragma unroll
+                for (int n = 0; n < NT; ++n)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) mine[((a * NT + n) * 4 + i) * 32 + lane] = acc[a][n][i];
+        }
+        __syncthreads();
+        if (sub == 0) {
+            for (int w = 0; w < WPR - 1; ++w) {
+                const float *theirs = red + ((unit_local * (WPR - 1) + w) * NACC * NT * 4) * 32;
+#pragma unroll
+                for (int a = 0; a < NACC; ++a)
+#pragma unroll
+                    for (int n = 0; n < NT; ++n)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            acc[a][n][i] += theirs[((a * NT + n) * 4 + i) * 32 + lane];
+            }
+        }
+    }
+    if (sub != 0 || !unit_valid) return;
+
+    // Epilogue.  acc[.][n][0..3] = (neuron g, row 2t), (g, 2t+1), (g+8, 2t), (g+8, 2t+1).
+    const float scale = p.round_bf16 ? round_bf16(p.scale) : p.scale;
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const long long row = row0 + n * 8 + 2 * t + (i & 1);
+            if (row >= p.rows) continue;
+            const int neuron = unit * 16 + g + 8 * (i >> 1);
+            float v;
+            if (SWIGLU) {
+                float gv = scale * acc[0][n][i];
+                float uv = scale * acc[NACC - 1][n][i];
+                float gate = 1.f;
+                if (p.gates != nullptr) gate = p.gates[row * p.ld_gates + neuron / p.cluster_size];
+                if (p.round_bf16) {
+                    gv = round_bf16(gv);
+                    uv = round_bf16(uv);
+                    const float sg = round_bf16(gv / (1.f + expf(-gv)));
+                    v = round_bf16(sg * uv);
+                    if (p.gates != nullptr) v = round_bf16(v * round_bf16(gate));
+                } else {
+                    v = gv * (1.f / (1.f + expf(-gv))) * uv;
+                    if (p.gates != nullptr) v *= gate;
+                }
+                if (!active || (p.gates != nullptr && !(gate > 0.f))) v = 0.f;
+            } else {
+                v = scale * acc[0][n][i];
+                if (!active) v = 0.f;
+            }
+            store_value(p, row, neuron, v);
+        }
+    }
+}
+
+// x[rows, cols] -> bf16 planes, optional RMSNorm prologue.  One CTA per row.
+template <typename T>
+__global__ void __launch_bounds__(256)
+act_prep_kernel(const T *x, long long ldx, int cols, const float *rms_w, float eps,
+                __nv_bfloat16 *planes, int n_planes, long long plane_stride, long long ld_planes) {
+    const long long row = blockIdx.x;
+    const T *xr = x + row * ldx;
+    float inv = 1.f;
+    if (rms_w != nullptr) {
+        float ss = 0.f;
+        for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+            const float v = (float)xr[c];
+            ss += v * v;
+        }
+        __shared__ float part[8];
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
+        __syncthreads();
+        float tot = 0.f;
+        for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += part[w];
+        inv = 1.f / sqrtf(tot / (float)cols + eps);
+    }
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+        float v = (float)xr[c];
+        if (rms_w != nullptr) v = (v * inv) * rms_w[c];
+        __nv_bfloat16 *o = planes + row * ld_planes + c;
+        for (int pl = 0; pl < n_planes; ++pl) {
+            const __nv_bfloat16 h = __float2bfloat16_rn(v);
+            o[pl * plane_stride] = h;
+            v -= __bfloat162float(h);
+        }
+    }
+}
+
+__global__ void route_flags_kernel(const float *gates, long long ld_gates, const int *rlo,
+                                   const int *rhi, int n_row, const int *clo, const int *chi,
+                                   int n_col, int *ract, long long ld_ract, int *cact,
+                                   long long ld_cact) {
+    const long long b = blockIdx.x;
+    const float *gb = gates + b * ld_gates;
+    for (int i = threadIdx.x; i < n_row; i += blockDim.x)
+        ract[b * ld_ract + i] = (gb[rlo[i]] > 0.f) | (gb[rhi[i]] > 0.f);
+    for (int i = threadIdx.x; i < n_col; i += blockDim.x)
+        cact[b * ld_cact + i] = (gb[clo[i]] > 0.f) | (gb[chi[i]] > 0.f);
+}
+
+template <int NT, bool SWIGLU>
+int launch_wpr(const LinearParams &p, int wpr, dim3 grid_y, cudaStream_t st) {
+    const int upc = kWarpsPerCta / wpr;
+    dim3 grid((p.units + upc - 1) / upc, grid_y.x);
+    if (wpr == 4) bcsr_stream_kernel<NT, SWIGLU, 4><<<grid, kWarpsPerCta * 32, 0, st>>>(p);
+    else if (wpr == 2) bcsr_stream_kernel<NT, SWIGLU, 2><<<grid, kWarpsPerCta * 32, 0, st>>>(p);
+    else bcsr_stream_kernel<NT, SWIGLU, 1><<<grid, kWarpsPerCta * 32, 0, st>>>(p);
+    MORTAR_CUDA_CHECK(cudaGetLastError());
+    return MORTAR_OK;
+}
+
+template <bool SWIGLU>
+int launch_nt(const LinearParams &p, int wpr, cudaStream_t st) {
+    if (p.rows <= 8) return launch_wpr<1, SWIGLU>(p, wpr, dim3(1), st);
+    if (p.rows <= 16) return launch_wpr<2, SWIGLU>(p, wpr, dim3(1), st);
+    if (p.rows <= 32) return launch_wpr<4, SWIGLU>(p, wpr, dim3(1), st);
+    const long long blocks = (p.rows + 63) / 64;
+    if (blocks > 65535) return MORTAR_ERR_CAPACITY;
+    return launch_wpr<8, SWIGLU>(p, wpr, dim3((unsigned)blocks), st);
+}
+
+inline bool aligned(const void *ptr, size_t a) { return (reinterpret_cast<uintptr_t>(ptr) % a) == 0; }
+
+}  // namespace
+
+extern "C" int mortar_act_prep(const void *x, int x_dtype, int64_t rows, int32_t cols, int64_t ldx,
+                               const float *rms_weight, float eps, void *planes, int32_t n_planes,
+                               int64_t plane_stride, int64_t ld_planes, void *stream) {
+    if (!x || !planes) return MORTAR_ERR_NULL;
+    if (rows < 0 || cols <= 0 || ldx < cols || ld_planes < cols) return MORTAR_ERR_SHAPE;
+    if (n_planes < 1 || n_planes > 3) return MORTAR_ERR_DTYPE;
+    if (rows == 0) return MORTAR_OK;
+    if (rows > 0x7fffffffLL) return MORTAR_ERR_CAPACITY;
+    cudaStream_t st = (cudaStream_t)stream;
+    __nv_bfloat16 *pl = reinterpret_cast<__nv_bfloat16 *>(planes);
+    if (x_dtype == MORTAR_F32)
+        act_prep_kernel<float><<<(unsigned)rows, 256, 0, st>>>(
+            reinterpret_cast<const float *>(x), ldx, cols, rms_weight, eps, pl, n_planes,
+            plane_stride, ld_planes);
+    else if (x_dtype == MORTAR_BF16)
+        act_prep_kernel<__nv_bfloat16><<<(unsigned)rows, 256, 0, st>>>(
+            reinterpret_cast<const __nv_bfloat16 *>(x), ldx, cols, rms_weight, eps, pl, n_planes,
+            plane_stride, ld_planes);
+    else
+        return MORTAR_ERR_DTYPE;
+    MORTAR_CUDA_CHECK(cudaGetLastError());
+    return MORTAR_OK;
+}
+
+extern "C" int mortar_linear(const mortar_stream *w, const void *planes, int32_t n_planes,
+                             int64_t plane_stride, int64_t ld_planes, int64_t rows, void *out,
+                             int32_t out_mode, int32_t n_out_planes, int64_t out_plane_stride,
+                             int64_t ld_out, int32_t flags, const float *gates, int64_t ld_gates,
+                             int32_t cluster_size, const int32_t *row_act, int64_t ld_row_act,
+                             const int32_t *col_act, int64_t ld_col_act, void *stream) {
+    if (!w || !planes || !out || !w->grp_ptr) return MORTAR_ERR_NULL;
+    if (w->n_groups > 0 && (!w->grp_codes || !w->grp_cols)) return MORTAR_ERR_NULL;
+    if (w->tile_rows <= 0 || w->tile_cols <= 0 || w->tile_cols > 65534 || rows < 0)
+        return MORTAR_ERR_SHAPE;
+    if (n_planes < 1 || n_planes > 3) return MORTAR_ERR_DTYPE;
+    if (out_mode < MORTAR_OUT_F32 || out_mode > MORTAR_OUT_PLANES) return MORTAR_ERR_DTYPE;
+    if (out_mode == MORTAR_OUT_PLANES && (n_out_planes < 1 || n_out_planes > 3)) return MORTAR_ERR_DTYPE;
+    const bool swiglu = (flags & MORTAR_FLAG_SWIGLU) != 0;
+    if (swiglu && (w->tile_rows % 2)) return MORTAR_ERR_SHAPE;
+    const int units = swiglu ? w->tile_rows / 2 : w->tile_rows;
+    if (ld_planes < (int64_t)w->tile_cols * 16 || ld_out < (int64_t)units * 16) return MORTAR_ERR_SHAPE;
+    if (!aligned(planes, 4) || (ld_planes & 1) || (plane_stride & 1)) return MORTAR_ERR_ALIGN;
+    if (!aligned(w->grp_codes, 16) || !aligned(w->grp_cols, 16)) return MORTAR_ERR_ALIGN;
+    const bool gates_on_input = (flags & MORTAR_FLAG_GATES_ON_INPUT) != 0;
+    if (gates && cluster_size <= 0) return MORTAR_ERR_SHAPE;
+    if (gates && !swiglu && !gates_on_input) return MORTAR_ERR_UNSUPPORTED;
+    if (rows == 0) return MORTAR_OK;
+
+    LinearParams p;
+    p.grp_codes = reinterpret_cast<const uint4 *>(w->grp_codes);
+    p.grp_cols = reinterpret_cast<const uint4 *>(w->grp_cols);
+    p.grp_ptr = w->grp_ptr;
+    p.R = w->tile_rows; p.C = w->tile_cols; p.scale = w->scale;
+    p.planes = reinterpret_cast<const uint32_t *>(planes);
+    p.plane_stride_w = plane_stride / 2; p.ld_w = ld_planes / 2; p.n_planes = n_planes;
+    p.rows = rows;
+    p.out = out; p.out_mode = out_mode; p.n_out_planes = n_out_planes;
+    p.out_plane_stride = out_plane_stride; p.ld_out = ld_out;
+    p.round_bf16 = (flags & MORTAR_FLAG_ROUND_BF16) != 0;
+    p.gates = gates; p.ld_gates = ld_gates; p.cluster_size = cluster_size > 0 ? cluster_size : 1;
+    // activity bitmaps over input columns are only worth building for small batches
+    const bool small = rows <= 8 && w->tile_cols <= kMaxFlagCols;
+    p.gates_on_input = (gates_on_input && gates && small) ? 1 : 0;
+    p.row_act = row_act; p.ld_row_act = ld_row_act;
+    p.col_act = small ? col_act : nullptr; p.ld_col_act = ld_col_act;
+    if (!swiglu && !gates_on_input) p.gates = nullptr;
+    if (!swiglu && gates_on_input && !p.gates_on_input) p.gates = nullptr;
+    p.units = units;
+
+    const double avg = (double)w->n_groups / (double)units;   // groups per unit
+    const int wpr = avg >= 3.0 ? 4 : (avg >= 1.5 ? 2 : 1);
+    cudaStream_t st = (cudaStream_t)stream;
+    return swiglu ? launch_nt<true>(p, wpr, st) : launch_nt<false>(p, wpr, st);
+}
+
+extern "C" int mortar_route_flags(const float *gates, int64_t rows, int64_t ld_gates,
+                                  const int32_t *row_lo, const int32_t *row_hi, int32_t n_row,
+                                  const int32_t *col_lo, const int32_t *col_hi, int32_t n_col,
+                                  int32_t *row_act, int64_t ld_row_act, int32_t *col_act,
+                                  int64_t ld_col_act, void *stream) {
+    if (!gates || !row_lo || !row_hi || !col_lo || !col_hi || !row_act || !col_act) return MORTAR_ERR_NULL;
+    if (rows < 0 || n_row < 0 || n_col < 0) return MORTAR_ERR_SHAPE;
+    if (rows == 0) return MORTAR_OK;
+    if (rows > 0x7fffffffLL) return MORTAR_ERR_CAPACITY;
+    route_flags_kernel<<<(unsigned)rows, 128, 0, (cudaStream_t)stream>>>(
+        gates, ld_gates, row_lo, row_hi, n_row, col_lo, col_hi, n_col, row_act, ld_row_act, col_act,
+        ld_col_act);
+    MORTAR_CUDA_CHECK(cudaGetLastError());
+    return MORTAR_OK;
+}
+
+static inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
+
+extern "C" int64_t mortar_mlp_workspace_bytes(int64_t rows, int32_t d_model, int32_t d_ff,
+                                              int32_t n_planes) {
+    if (rows < 0 || d_model <= 0 || d_ff <= 0 || n_planes < 1 || n_planes > 3) return MORTAR_ERR_SHAPE;
+    return align_up((int64_t)n_planes * rows * d_model * 2, 256) +
+           align_up((int64_t)n_planes * rows * d_ff * 2, 256);
+}
+
+extern "C" int mortar_mlp_decode(const mortar_stream *gate_up, const mortar_stream *down,
+                                 const void *x, int x_dtype, int64_t ldx, int64_t rows,
+                                 const float *rms_weight, float eps, const float *gates,
+                                 int64_t ld_gates, int32_t n_clusters, void *y, int y_dtype,
+                                 int64_t ldy, int32_t n_planes, int32_t flags, void *workspace,
+                                 int64_t workspace_bytes, void *stream) {
+    if (!gate_up || !down || !x || !y || !workspace) return MORTAR_ERR_NULL;
+    if (x_dtype != MORTAR_F32 && x_dtype != MORTAR_BF16) return MORTAR_ERR_DTYPE;
+    if (y_dtype != MORTAR_F32 && y_dtype != MORTAR_BF16) return MORTAR_ERR_DTYPE;
+    if (n_planes < 1 || n_planes > 3) return MORTAR_ERR_DTYPE;
+    const int d_model = gate_up->tile_cols * 16;
+    if (gate_up->tile_rows % 2) return MORTAR_ERR_SHAPE;
+    const int d_ff = gate_up->tile_rows * 8;
+    if (down->tile_cols * 16 != d_ff || down->tile_rows * 16 != d_model) return MORTAR_ERR_SHAPE;
+    if (gates && (n_clusters <= 0 || d_ff % n_clusters)) return MORTAR_ERR_SHAPE;
+    if (!aligned(workspace, 256)) return MORTAR_ERR_ALIGN;
+    const int64_t need = mortar_mlp_workspace_bytes(rows, d_model, d_ff, n_planes);
+    if (need < 0) return (int)need;
+    if (workspace_bytes < need) return MORTAR_ERR_CAPACITY;
+    if (rows == 0) return MORTAR_OK;
+
+    char *ws = reinterpret_cast<char *>(workspace);
+    void *xp = ws;
+    void *hp = ws + align_up((int64_t)n_planes * rows * d_model * 2, 256);
+    const void *xin = xp;
+    int xin_planes = n_planes;
+    int64_t xin_stride = rows * (int64_t)d_model, xin_ld = d_model;
+    if (x_dtype == MORTAR_BF16 && rms_weight == nullptr && aligned(x, 4) && (ldx % 2) == 0) {
+        xin = x; xin_planes = 1; xin_stride = 0; xin_ld = ldx;       // bf16 input is already a plane
+    } else {
+        int rc = mortar_act_prep(x, x_dtype, rows, d_model, ldx, rms_weight, eps, xp, n_planes,
+                                 xin_stride, xin_ld, stream);
+        if (rc != MORTAR_OK) return rc;
+    }
+    const int cs = gates ? d_ff / n_clusters : 0;
+    const int rb = flags & MORTAR_FLAG_ROUND_BF16;
+    const int h_planes = rb ? 1 : n_planes;
+    int rc = mortar_linear(gate_up, xin, xin_planes, xin_stride, xin_ld, rows, hp, MORTAR_OUT_PLANES,
+                           h_planes, rows * (int64_t)d_ff, d_ff, MORTAR_FLAG_SWIGLU | rb, gates,
+                           ld_gates, cs, nullptr, 0, nullptr, 0, stream);
+    if (rc != MORTAR_OK) return rc;
+    return mortar_linear(down, hp, h_planes, rows * (int64_t)d_ff, d_ff, rows, y,
+                         y_dtype == MORTAR_F32 ? MORTAR_OUT_F32 : MORTAR_OUT_BF16, 0, 0, ldy,
+                         rb | (gates ? MORTAR_FLAG_GATES_ON_INPUT : 0), gates, ld_gates, cs, nullptr, 0, nullptr, 0, stream);
+}

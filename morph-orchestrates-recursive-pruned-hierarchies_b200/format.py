@@ -1,0 +1,275 @@
+"""Matrix formats of the MORTAR path and the converters between them.
+
+Canonical format (``MortarMatrix``): tile-16 BCSR with 2-bit ternary codes and one
+absmean scale per matrix -- byte-identical to what the reference's
+``carve(blocking=16)`` + ``pack_mortar_ternary`` produce
+(morph/model/layers/block_sparse.py:874-899, morph/inference/deploy_quant.py:56-95,
+344-374).  Execution layout (``StreamMatrix``): the 8-tile-group stream the kernels read,
+built by the native packer; counterpart of ``mortar_pack_strips``
+(morph/kernels/triton/fused_decode_step.py:1465-1499).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional
+
+import numpy as np
+import torch
+
+from . import _lib
+
+TILE = 16
+
+
+def ternary_quantize(w: torch.Tensor, threshold: float = 0.5):
+    """Per-tensor symmetric ternarisation in fp32: scale = mean|w| (clamped at 1e-8) over
+    the values handed in, code = sign(w/scale) where |w/scale| > threshold.  Same rule as
+    deploy_quant.py:81-95; callers pass kept tiles only (deploy_quant.py:356-358)."""
+    wf = w.detach().float()
+    scale = wf.abs().mean().clamp(min=1e-8)
+    wn = wf / scale
+    q = (torch.sign(wn) * (wn.abs() > threshold)).to(torch.int8)
+    return q, float(scale)
+
+
+def pack_codes_2bit(codes: np.ndarray) -> np.ndarray:
+    """int8 codes (last dim a multiple of 4) -> bytes, 4 per byte, stored value = code+1,
+    element i of a byte in bits 2i..2i+1 (deploy_quant.py:56-71)."""
+    u = (np.asarray(codes).astype(np.int16) + 1).astype(np.uint8)
+    u = u.reshape(*u.shape[:-1], u.shape[-1] // 4, 4)
+    return (u[..., 0] | (u[..., 1] << 2) | (u[..., 2] << 4) | (u[..., 3] << 6)).astype(np.uint8)
+
+
+def unpack_codes_2bit(packed: np.ndarray) -> np.ndarray:
+    p = np.asarray(packed, dtype=np.uint8)
+    u = (p[..., None] >> np.array([0, 2, 4, 6], dtype=np.uint8)) & 3
+    return (u.reshape(*p.shape[:-1], p.shape[-1] * 4).astype(np.int8) - 1)
+
+
+def _ptr(a: np.ndarray):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+@dataclass
+class MortarMatrix:
+    """Canonical tile-16 BCSR ternary matrix W[out, in] (host, numpy)."""
+    out_features: int
+    in_features: int
+    row_ptr: np.ndarray      # int32 [R+1]
+    col_idx: np.ndarray      # uint16 [nnz]
+    codes: np.ndarray        # uint8 [nnz, 64]
+    scale: float
+
+    @property
+    def tile_rows(self) -> int:
+        return self.out_features // TILE
+
+    @property
+    def tile_cols(self) -> int:
+        return self.in_features // TILE
+
+    @property
+    def nnz(self) -> int:
+        return int(self.col_idx.shape[0])
+
+    @property
+    def density(self) -> float:
+        return self.nnz / float(self.tile_rows * self.tile_cols)
+
+    def validate(self) -> None:
+        """Raises ValueError on malformed metadata (non-monotone row pointers, column index
+        out of range or unsorted, unused code value)."""
+        if self.out_features <= 0 or self.in_features <= 0 or self.out_features % TILE \
+                or self.in_features % TILE:
+            raise ValueError(f"features [{self.out_features},{self.in_features}] must be positive "
+                             f"multiples of {TILE}")
+        if self.row_ptr.dtype != np.int32 or self.col_idx.dtype != np.uint16 \
+                or self.codes.dtype != np.uint8:
+            raise ValueError("row_ptr must be int32, col_idx uint16, codes uint8")
+        if self.row_ptr.shape != (self.tile_rows + 1,) or self.codes.shape != (self.nnz, 64):
+            raise ValueError("row_ptr / codes have the wrong shape for these features")
+        rp = np.ascontiguousarray(self.row_ptr)
+        ci = np.ascontiguousarray(self.col_idx)
+        cd = np.ascontiguousarray(self.codes)
+        _lib.check(_lib.lib().mortar_validate_bcsr(_ptr(rp), _ptr(ci), _ptr(cd), self.tile_rows,
+                                                   self.tile_cols, self.nnz), "mortar_validate_bcsr")
+
+    # ---- constructors -------------------------------------------------------------
+    @staticmethod
+    def from_codes(codes: np.ndarray, tile_mask: Optional[np.ndarray], scale: float) -> "MortarMatrix":
+        """Dense int8 code matrix [out, in] + bool tile mask [R, C] (None = keep every tile)."""
+        codes = np.asarray(codes, dtype=np.int8)
+        O, I = codes.shape
+        R, Cc = O // TILE, I // TILE
+        if tile_mask is None:
+            tile_mask = np.ones((R, Cc), dtype=bool)
+        tile_mask = np.asarray(tile_mask, dtype=bool)
+        rows, cols = np.nonzero(tile_mask)                      # row-major: sorted by row, then col
+        row_ptr = np.zeros(R + 1, dtype=np.int32)
+        np.cumsum(tile_mask.sum(axis=1), out=row_ptr[1:])
+        tiles = codes.reshape(R, TILE, Cc, TILE).transpose(0, 2, 1, 3)[rows, cols]   # [nnz,16,16]
+        packed = pack_codes_2bit(tiles.reshape(-1, TILE * TILE))
+        m = MortarMatrix(O, I, row_ptr, cols.astype(np.uint16), np.ascontiguousarray(packed),
+                         float(scale))
+        m.validate()
+        return m
+
+    @staticmethod
+    def from_weight(w: torch.Tensor, tile_mask: Optional[torch.Tensor], threshold: float = 0.5):
+        """Masked-dense weight -> canonical matrix, ternarising the KEPT values only with the
+        deploy rule (the composition carve + pack_mortar_ternary of the reference)."""
+        O, I = w.shape
+        R, Cc = O // TILE, I // TILE
+        if tile_mask is None:
+            tile_mask = torch.ones(R, Cc, dtype=torch.bool)
+        tm = tile_mask.cpu().bool()
+        rows, cols = tm.nonzero(as_tuple=True)
+        tiles = w.detach().cpu().reshape(R, TILE, Cc, TILE).permute(0, 2, 1, 3)[rows, cols]
+        q, scale = ternary_quantize(tiles, threshold)
+        dense = torch.zeros(R, Cc, TILE, TILE, dtype=torch.int8)
+        dense[rows, cols] = q
+        dense = dense.permute(0, 2, 1, 3).reshape(O, I)
+        return MortarMatrix.from_codes(dense.numpy(), tm.numpy(), scale)
+
+    @staticmethod
+    def from_reference_bcsr(offsets, column_indices, packed, scale: float, blocking: int,
+                            out_features: int, in_features: int,
+                            drop_zero_tiles: bool = False) -> "MortarMatrix":
+        """Reference carved+packed storage (``mortar_offsets`` int32, ``mortar_column_indices``
+        int16, ``mortar_packed`` uint8 flat 2-bit over [nnz, blk, blk], ``mortar_scale``) at
+        any blocking that is a multiple of 16 -> canonical tiles (each block becomes
+        (blk/16)^2 tiles)."""
+        off = np.ascontiguousarray(np.asarray(offsets, dtype=np.int32))
+        ci = np.ascontiguousarray(np.asarray(column_indices, dtype=np.int16))
+        pk = np.ascontiguousarray(np.asarray(packed, dtype=np.uint8))
+        Rb, Cb = out_features // blocking, in_features // blocking
+        if off.shape != (Rb + 1,):
+            raise ValueError("offsets length does not match out_features / blocking")
+        nnzb = int(off[-1])
+        if ci.shape[0] != nnzb or pk.shape[0] < nnzb * blocking * blocking // 4:
+            raise ValueError("column_indices / packed shorter than offsets[-1] blocks")
+        L = _lib.lib()
+        tpb = blocking // TILE
+        row_ptr = np.zeros(Rb * tpb + 1, dtype=np.int32)
+        nnz = C.c_int64(0)
+        _lib.check(L.mortar_split_blocks(_ptr(off), _ptr(ci), _ptr(pk), Rb, Cb, blocking,
+                                         int(drop_zero_tiles), _ptr(row_ptr), None, None,
+                                         C.byref(nnz)), "mortar_split_blocks")
+        col_idx = np.zeros(nnz.value, dtype=np.uint16)
+        codes = np.zeros((nnz.value, 64), dtype=np.uint8)
+        _lib.check(L.mortar_split_blocks(_ptr(off), _ptr(ci), _ptr(pk), Rb, Cb, blocking,
+                                         int(drop_zero_tiles), _ptr(row_ptr), _ptr(col_idx),
+                                         _ptr(codes), C.byref(nnz)), "mortar_split_blocks")
+        m = MortarMatrix(out_features, in_features, row_ptr, col_idx, codes, float(scale))
+        m.validate()
+        return m
+
+    @staticmethod
+    def from_reference_cms(cms, drop_zero_tiles: bool = False) -> "MortarMatrix":
+        """A carved reference ``CMSBlockLinear`` (``MortarLinear._cms``): packed
+        (``mortar_packed``/``mortar_scale``, deploy_quant.py:361-365) or still holding
+        ``mortar_data`` (block_sparse.py:783-799), which is ternarised with the deploy rule."""
+        if not getattr(cms, "_mortar", False):
+            raise ValueError("layer is not carved: call carve() first, or use from_weight with "
+                             "its _prune_mask")
+        blk = int(cms._mortar_blocking)
+        if hasattr(cms, "mortar_packed"):
+            packed = cms.mortar_packed.detach().cpu().numpy()
+            scale = float(cms.mortar_scale)
+        else:
+            q, scale = ternary_quantize(cms.mortar_data.data)
+            packed = pack_codes_2bit(q.cpu().numpy().reshape(-1, 4)).reshape(-1)
+        return MortarMatrix.from_reference_bcsr(
+            cms.mortar_offsets.detach().cpu().numpy(), cms.mortar_column_indices.detach().cpu().numpy(),
+            packed, scale, blk, cms.out_features, cms.in_features, drop_zero_tiles)
+
+    # ---- views ----------------------------------------------------------------------
+    def to_dense_codes(self) -> np.ndarray:
+        """int8 [out, in] with zeros in pruned tiles."""
+        R, Cc = self.tile_rows, self.tile_cols
+        tiles = unpack_codes_2bit(self.codes).reshape(self.nnz, TILE, TILE)
+        rows = np.repeat(np.arange(R), np.diff(self.row_ptr))
+        dense = np.zeros((R, Cc, TILE, TILE), dtype=np.int8)
+        dense[rows, self.col_idx.astype(np.int64)] = tiles
+        return dense.transpose(0, 2, 1, 3).reshape(self.out_features, self.in_features)
+
+    def tile_mask(self) -> np.ndarray:
+        R, Cc = self.tile_rows, self.tile_cols
+        m = np.zeros((R, Cc), dtype=bool)
+        rows = np.repeat(np.arange(R), np.diff(self.row_ptr))
+        m[rows, self.col_idx.astype(np.int64)] = True
+        return m
+
+    def algorithmic_bytes(self) -> int:
+        """Bytes a kernel must read to use this matrix once: 64 per tile of codes, 2 per tile of
+        column index, 4 per row pointer, 4 of scale."""
+        return 64 * self.nnz + 2 * self.nnz + 4 * (self.tile_rows + 1) + 4
+
+    def build_stream_host(self):
+        """(grp_ptr int32[R+1], grp_cols uint16[8G], grp_codes uint8[512G]) on the host."""
+        L = _lib.lib()
+        rp = np.ascontiguousarray(self.row_ptr)
+        ci = np.ascontiguousarray(self.col_idx)
+        cd = np.ascontiguousarray(self.codes)
+        G = L.mortar_stream_groups(_ptr(rp), self.tile_rows)
+        if G < 0:
+            _lib.check(int(G), "mortar_stream_groups")
+        grp_ptr = np.zeros(self.tile_rows + 1, dtype=np.int32)
+        grp_cols = np.zeros(max(G, 1) * 8, dtype=np.uint16)
+        grp_codes = np.zeros(max(G, 1) * 512, dtype=np.uint8)
+        _lib.check(L.mortar_build_stream(_ptr(rp), _ptr(ci), _ptr(cd), self.tile_rows, self.tile_cols,
+                                         self.nnz, _ptr(grp_ptr), _ptr(grp_cols), _ptr(grp_codes)),
+                   "mortar_build_stream")
+        return grp_ptr, grp_cols, grp_codes, int(G)
+
+    def to_stream(self, device="cuda") -> "StreamMatrix":
+        grp_ptr, grp_cols, grp_codes, G = self.build_stream_host()
+        return StreamMatrix(self.out_features, self.in_features, self.scale, G, self.nnz,
+                            torch.from_numpy(grp_ptr).to(device),
+                            torch.from_numpy(grp_cols.view(np.int16)).to(device),
+                            torch.from_numpy(grp_codes).to(device),
+                            self.algorithmic_bytes())
+
+
+def unpack_stream_host(grp_ptr, grp_cols, grp_codes, row_ptr, tile_rows):
+    """Inverse of build_stream_host -> (col_idx uint16[nnz], codes uint8[nnz,64])."""
+    nnz = int(row_ptr[-1])
+    col_idx = np.zeros(nnz, dtype=np.uint16)
+    codes = np.zeros((nnz, 64), dtype=np.uint8)
+    rp = np.ascontiguousarray(row_ptr, dtype=np.int32)
+    _lib.check(_lib.lib().mortar_unpack_stream(_ptr(np.ascontiguousarray(grp_ptr)),
+                                               _ptr(np.ascontiguousarray(grp_cols)),
+                                               _ptr(np.ascontiguousarray(grp_codes)), _ptr(rp),
+                                               tile_rows, _ptr(col_idx), _ptr(codes)),
+               "mortar_unpack_stream")
+    return col_idx, codes
+
+
+class StreamMatrix:
+    """Device-resident execution layout of one matrix.  Owns its torch tensors; the C struct
+    handed to the library borrows their pointers."""
+
+    def __init__(self, out_features, in_features, scale, n_groups, nnz, grp_ptr, grp_cols,
+                 grp_codes, algorithmic_bytes):
+        self.out_features, self.in_features = int(out_features), int(in_features)
+        self.scale, self.n_groups, self.nnz = float(scale), int(n_groups), int(nnz)
+        self.grp_ptr, self.grp_cols, self.grp_codes = grp_ptr, grp_cols, grp_codes
+        self.algorithmic_bytes = int(algorithmic_bytes)
+        self._c = None
+
+    @property
+    def device(self):
+        return self.grp_ptr.device
+
+    def to(self, device) -> "StreamMatrix":
+        return StreamMatrix(self.out_features, self.in_features, self.scale, self.n_groups, self.nnz,
+                            self.grp_ptr.to(device), self.grp_cols.to(device),
+                            self.grp_codes.to(device), self.algorithmic_bytes)
+
+    def c_struct(self) -> _lib.Stream:
+        if self._c is None:
+            self._c = _lib.Stream(self.grp_codes.data_ptr(), self.grp_cols.data_ptr(),
+                                  self.grp_ptr.data_ptr(), self.n_groups,
+                                  self.out_features // TILE, self.in_features // TILE, self.scale)
+        return self._c

@@ -1,0 +1,294 @@
+"""Torch-facing operators of the MORTAR path.  Every function launches the hand-written
+sm_100a kernels through the C ABI on the current CUDA stream; CPU tensors are rejected
+(there is no fallback, as with the reference's CUDA-only ``morph_stk::dds`` op,
+morph/sparse/stk/backend/custom_ops.py:35).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import _lib
+from .format import TILE, MortarMatrix, StreamMatrix
+
+_launches = 0      # kernels launched by this module (bench.py reports it)
+
+
+def launch_count() -> int:
+    return _launches
+
+
+def _stream_ptr() -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _require_cuda(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise NotImplementedError(
+            f"{name} is on {t.device}: the MORTAR operators are CUDA-only (sm_100a), no CPU path")
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return _lib.F32
+    if t.dtype == torch.bfloat16:
+        return _lib.BF16
+    raise ValueError(f"unsupported dtype {t.dtype}: expected float32 or bfloat16")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _rows2d(x: torch.Tensor, features: int, name: str) -> torch.Tensor:
+    if x.shape[-1] != features:
+        raise ValueError(f"{name} has last dim {x.shape[-1]}, expected {features}")
+    x2 = x.reshape(-1, features)
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    return x2
+
+
+def act_prep(x: torch.Tensor, n_planes: int = 3, rms_weight: Optional[torch.Tensor] = None,
+             eps: float = 1e-6) -> torch.Tensor:
+    """x[rows, cols] -> bf16 planes [n_planes, rows, cols] whose sum is x (after the optional
+    RMSNorm (x*rsqrt(mean x^2+eps))*w, fused_decode_step.py:293-321)."""
+    global _launches
+    _require_cuda(x, "x")
+    x2 = _rows2d(x, x.shape[-1], "x")
+    rows, cols = x2.shape
+    planes = torch.empty(n_planes, rows, cols, device=x.device, dtype=torch.bfloat16)
+    w = None
+    if rms_weight is not None:
+        w = rms_weight.to(device=x.device, dtype=torch.float32).contiguous()
+    _lib.check(_lib.lib().mortar_act_prep(_ptr(x2), _dtype_code(x2), rows, cols, x2.stride(0), _ptr(w),
+                                          float(eps), _ptr(planes), n_planes, rows * cols, cols,
+                                          _stream_ptr()), "mortar_act_prep")
+    _launches += 1
+    return planes
+
+
+def linear_planes(w: StreamMatrix, planes: torch.Tensor, *, swiglu: bool = False,
+                  out_dtype: torch.dtype = torch.float32, out_planes: int = 0,
+                  round_bf16: bool = False, gates: Optional[torch.Tensor] = None,
+                  cluster_size: int = 0, gates_on_input: bool = False,
+                  row_act: Optional[torch.Tensor] = None, col_act: Optional[torch.Tensor] = None):
+    """Block-sparse ternary linear on activation planes [P, rows, in]: returns [rows, out]
+    (or [rows, out/2] = silu(gate)*up with ``swiglu``), as float32/bfloat16 or, with
+    ``out_planes`` > 0, as planes [out_planes, rows, n]."""
+    global _launches
+    _require_cuda(planes, "planes")
+    if planes.dim() != 3 or planes.dtype != torch.bfloat16 or not planes.is_contiguous():
+        raise ValueError("planes must be a contiguous bfloat16 tensor [P, rows, in_features]")
+    P, rows, cols = planes.shape
+    if cols != w.in_features:
+        raise ValueError(f"planes have {cols} columns, matrix expects {w.in_features}")
+    n_out = w.out_features // 2 if swiglu else w.out_features
+    dev = planes.device
+    if out_planes:
+        out = torch.empty(out_planes, rows, n_out, device=dev, dtype=torch.bfloat16)
+        mode = _lib.OUT_PLANES
+    elif out_dtype == torch.float32:
+        out = torch.empty(rows, n_out, device=dev, dtype=torch.float32)
+        mode = _lib.OUT_F32
+    elif out_dtype == torch.bfloat16:
+        out = torch.empty(rows, n_out, device=dev, dtype=torch.bfloat16)
+        mode = _lib.OUT_BF16
+    else:
+        raise ValueError(f"unsupported out_dtype {out_dtype}")
+    flags = (_lib.FLAG_SWIGLU if swiglu else 0) | (_lib.FLAG_ROUND_BF16 if round_bf16 else 0) \
+        | (_lib.FLAG_GATES_ON_INPUT if gates_on_input else 0)
+    if gates is not None:
+        gates = gates.to(device=dev, dtype=torch.float32).reshape(rows, -1).contiguous()
+    for name, a in (("row_act", row_act), ("col_act", col_act)):
+        if a is not None and (a.dtype != torch.int32 or a.dim() != 2 or a.shape[0] != rows
+                              or a.stride(1) != 1):
+            raise ValueError(f"{name} must be int32 [rows, n] with unit inner stride")
+    st = w.c_struct()
+    _lib.check(_lib.lib().mortar_linear(
+        C.byref(st), _ptr(planes), P, rows * cols, cols, rows, _ptr(out), mode, out_planes,
+        rows * n_out, n_out, flags, _ptr(gates), gates.stride(0) if gates is not None else 0,
+        int(cluster_size), _ptr(row_act), row_act.stride(0) if row_act is not None else 0,
+        _ptr(col_act), col_act.stride(0) if col_act is not None else 0, _stream_ptr()),
+        "mortar_linear")
+    _launches += 1
+    return out
+
+
+def linear(x: torch.Tensor, w: StreamMatrix, *, n_planes: Optional[int] = None,
+           out_dtype: Optional[torch.dtype] = None, round_bf16: Optional[bool] = None) -> torch.Tensor:
+    """y = x @ W^T for x[..., in]; the drop-in for ``CMSBlockLinear._forward_mortar``
+    (block_sparse.py:921-970).  bf16 input -> bf16 output with the reference's rounding;
+    fp32 input -> fp32 output computed from exact 3-plane activations."""
+    _require_cuda(x, "x")
+    lead = x.shape[:-1]
+    x2 = _rows2d(x, w.in_features, "x")
+    is_bf16 = x2.dtype == torch.bfloat16
+    if n_planes is None:
+        n_planes = 1 if is_bf16 else 3
+    if out_dtype is None:
+        out_dtype = x2.dtype
+    if round_bf16 is None:
+        round_bf16 = is_bf16
+    if is_bf16 and x2.is_contiguous():
+        planes = x2.unsqueeze(0)
+    else:
+        planes = act_prep(x2, n_planes)
+    y = linear_planes(w, planes, out_dtype=out_dtype, round_bf16=round_bf16)
+    return y.reshape(*lead, w.out_features)
+
+
+_workspaces: dict = {}
+
+
+def _workspace(device, nbytes: int) -> torch.Tensor:
+    key = (device.type, device.index)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 20), device=device, dtype=torch.uint8)
+        _workspaces[key] = ws
+    return ws
+
+
+def mlp_decode(x: torch.Tensor, gate_up: StreamMatrix, down: StreamMatrix, *,
+               rms_weight: Optional[torch.Tensor] = None, eps: float = 1e-6,
+               gates: Optional[torch.Tensor] = None, n_clusters: int = 0,
+               n_planes: int = 3, round_bf16: bool = False,
+               out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None,
+               workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One SwiGLU MLP application for a block of rows: [rmsnorm] -> gate_up -> silu(g)*u
+    [*gates] -> down.  Mirrors StaticDecodeEngine._mlp_fn (morph/inference/engine.py:936-986)
+    with ``n_planes=3`` (fp32 semantics) and ``_SwiGLUMortar.forward`` under autocast
+    (morph/model/transformer.py:402-431) with ``n_planes=1, round_bf16=True``."""
+    global _launches
+    _require_cuda(x, "x")
+    d_model, d_ff = gate_up.in_features, gate_up.out_features // 2
+    lead = x.shape[:-1]
+    x2 = _rows2d(x, d_model, "x")
+    rows = x2.shape[0]
+    if out_dtype is None:
+        out_dtype = x2.dtype
+    if out is None:
+        out = torch.empty(rows, d_model, device=x.device, dtype=out_dtype)
+    elif out.shape[-1] != d_model or out.numel() != rows * d_model or out.stride(-1) != 1:
+        raise ValueError("out has the wrong shape")
+    out2 = out.reshape(rows, d_model)
+    L = _lib.lib()
+    need = L.mortar_mlp_workspace_bytes(rows, d_model, d_ff, n_planes)
+    if need < 0:
+        _lib.check(int(need), "mortar_mlp_workspace_bytes")
+    if workspace is None:
+        workspace = _workspace(x.device, need)
+    w = None
+    if rms_weight is not None:
+        w = rms_weight.to(device=x.device, dtype=torch.float32).contiguous()
+    g = None
+    if gates is not None:
+        g = gates.to(device=x.device, dtype=torch.float32).reshape(rows, -1).contiguous()
+        if g.shape[1] != n_clusters:
+            raise ValueError(f"gates have {g.shape[1]} clusters, n_clusters={n_clusters}")
+    gu, dn = gate_up.c_struct(), down.c_struct()
+    _lib.check(L.mortar_mlp_decode(
+        C.byref(gu), C.byref(dn), _ptr(x2), _dtype_code(x2), x2.stride(0), rows, _ptr(w), float(eps),
+        _ptr(g), g.stride(0) if g is not None else 0, int(n_clusters), _ptr(out2), _dtype_code(out2),
+        out2.stride(0), int(n_planes), _lib.FLAG_ROUND_BF16 if round_bf16 else 0,
+        _ptr(workspace), workspace.numel(), _stream_ptr()), "mortar_mlp_decode")
+    direct = x2.dtype == torch.bfloat16 and rms_weight is None and x2.stride(0) % 2 == 0 \
+        and x2.data_ptr() % 4 == 0
+    _launches += 2 if direct else 3
+    return out.reshape(*lead, d_model)
+
+
+def mlp_prefill(x: torch.Tensor, gate_up: StreamMatrix, down: StreamMatrix, *,
+                gates: Optional[torch.Tensor] = None, n_clusters: int = 0,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``_SwiGLUMortar.forward`` for a block of tokens in the reference's autocast dtype:
+    bf16 operands, fp32 accumulation, bf16 rounding after gate_up, silu, the product, the
+    gate multiply and down (transformer.py:402-431; triton_kernels.py:203-226)."""
+    xb = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
+    return mlp_decode(xb, gate_up, down, gates=gates, n_clusters=n_clusters, n_planes=1,
+                      round_bf16=True, out_dtype=torch.bfloat16, out=out)
+
+
+def route_flags(gates: torch.Tensor, rlo: torch.Tensor, rhi: torch.Tensor, clo: torch.Tensor,
+                chi: torch.Tensor, ract: torch.Tensor, cact: torch.Tensor) -> None:
+    """Same contract as the reference ``route_flags`` (fused_decode_step.py:1913-1927): gates
+    [B, n_clusters] fp32; rlo/rhi [NR], clo/chi [NC] int32 cluster spans; ract [B, NR] /
+    cact [B, NC] int32 outputs (may be sliced views of a wider scratch)."""
+    global _launches
+    _require_cuda(gates, "gates")
+    B = gates.shape[0]
+    _lib.check(_lib.lib().mortar_route_flags(
+        _ptr(gates), B, gates.stride(0), _ptr(rlo), _ptr(rhi), rlo.numel(), _ptr(clo), _ptr(chi),
+        clo.numel(), _ptr(ract), ract.stride(0), _ptr(cact), cact.stride(0), _stream_ptr()),
+        "mortar_route_flags")
+    _launches += 1
+
+
+def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """fp32 RMSNorm over the last dim (fused_decode_step.py:305-321), evaluated by the
+    activation-prep kernel and re-assembled from its three exact planes."""
+    planes = act_prep(x, 3, rms_weight=weight, eps=eps)
+    return planes.float().sum(0).reshape(x.shape)
+
+
+# ---- reference-signature shims ---------------------------------------------------------
+
+class MortarPack:
+    """What ``mortar_pack_strips`` returns here: the stream-format matrix plus the block size
+    the caller's activity flags are expressed in."""
+
+    def __init__(self, stream: StreamMatrix, matrix: MortarMatrix, flag_blocking: int):
+        self.stream, self.matrix, self.flag_blocking = stream, matrix, int(flag_blocking)
+        self.out_features = matrix.out_features
+
+
+def mortar_pack_strips(cms, device="cuda") -> MortarPack:
+    """Counterpart of the reference ``mortar_pack_strips(cms)`` (fused_decode_step.py:1465):
+    converts a carved+packed ``CMSBlockLinear`` into this library's stream layout."""
+    m = MortarMatrix.from_reference_cms(cms)
+    return MortarPack(m.to_stream(device), m, int(cms._mortar_blocking))
+
+
+def _expand_flags(act: Optional[torch.Tensor], blocking: int, first_half: bool):
+    if act is None:
+        return None
+    if act.dim() == 1:
+        act = act.unsqueeze(0)
+    if first_half:
+        act = act[:, : act.shape[1] // 2]
+    rep = blocking // TILE
+    if rep > 1:
+        act = act.repeat_interleave(rep, dim=1)
+    return act.to(torch.int32).contiguous()
+
+
+def mortar_gemv(x: torch.Tensor, pack: MortarPack, swiglu_x: bool = False, swiglu_out: bool = False,
+                row_act: Optional[torch.Tensor] = None, col_act: Optional[torch.Tensor] = None,
+                gates: Optional[torch.Tensor] = None, cluster_size: int = 0) -> torch.Tensor:
+    """Same signature and result as the reference ``mortar_gemv``
+    (fused_decode_step.py:1502-1547): x [B, I] fp32 -> [B, O] fp32, or [B, O/2] =
+    silu(g)*u (x cluster gate) with ``swiglu_out``; ``swiglu_x`` takes the packed [B, 2F]
+    gate_up output and forms silu(g)*u on load.  Activity flags are per block of the
+    pack's original blocking, [B, n_blocks] or [n_blocks]."""
+    if swiglu_x and swiglu_out:
+        raise AssertionError("swiglu_x and swiglu_out are mutually exclusive")
+    _require_cuda(x, "x")
+    xf = x.float()
+    if swiglu_x:
+        F_ = xf.shape[-1] // 2
+        g, u = xf[..., :F_], xf[..., F_:]
+        xf = g * torch.sigmoid(g) * u
+    planes = act_prep(xf.reshape(-1, xf.shape[-1]), 3)
+    B = planes.shape[1]
+    ra = _expand_flags(row_act, pack.flag_blocking, first_half=swiglu_out)
+    ca = _expand_flags(col_act, pack.flag_blocking, first_half=False)
+    if ra is not None and ra.shape[0] == 1 and B > 1:
+        ra = ra.expand(B, -1).contiguous()
+    if ca is not None and ca.shape[0] == 1 and B > 1:
+        ca = ca.expand(B, -1).contiguous()
+    return linear_planes(pack.stream, planes, swiglu=swiglu_out, out_dtype=torch.float32,
+                         gates=gates if swiglu_out else None, cluster_size=cluster_size,
+                         row_act=ra, col_act=ca)

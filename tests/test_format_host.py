@@ -1,0 +1,200 @@
+"""Host logic: canonical format, stream layout round trips, converters from the reference's
+storage, metadata validation, and the C-ABI export list.  No GPU."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+import mortar_b200 as mb
+from conftest import GOLDEN_CASES, ROOT, load_golden
+from oracle import mortar_oracle as orc
+
+fmt = mb.format if hasattr(mb, "format") else None
+from importlib import import_module
+fmt = import_module(mb.__name__ + ".format")
+_lib = mb._lib
+
+
+def test_abi_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "mortar_b200.h")).read()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    declared = set(re.findall(r"\b(mortar_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations parsed"
+    handle = ctypes.CDLL(_lib.LIB_PATH)
+    for name in sorted(declared):
+        assert hasattr(handle, name), f"{name} declared in the header but not exported"
+    assert declared == set(_lib.exported_symbols())
+
+
+def test_status_strings_and_version():
+    L = _lib.lib()
+    assert b"sm_100a" in L.mortar_version()
+    assert L.mortar_status_string(0) == b"ok"
+    for code in range(-10, 0):
+        assert L.mortar_status_string(code) != b"unknown status"
+
+
+@pytest.mark.parametrize("case", GOLDEN_CASES)
+def test_from_reference_storage_matches_reference_codes(case):
+    g = load_golden(case)
+    d_model, d_ff, blk, ncls = (int(v) for v in g["meta"])
+    for tag, (O, I) in (("gu", (2 * d_ff, d_model)), ("dn", (d_model, d_ff))):
+        m = mb.MortarMatrix.from_reference_bcsr(g[f"{tag}_offsets"], g[f"{tag}_column_indices"],
+                                                g[f"{tag}_packed"], float(g[f"{tag}_scale"]), blk, O, I)
+        # dense code matrix rebuilt from the reference's own (unpacked) codes and indices
+        ref = orc.mortar_dense(torch.from_numpy(g[f"{tag}_codes"]), torch.ones(()),
+                               torch.from_numpy(g[f"{tag}_row_indices"]),
+                               torch.from_numpy(g[f"{tag}_column_indices"]), O, I, False)
+        np.testing.assert_array_equal(m.to_dense_codes(), ref.numpy().astype(np.int8))
+        assert m.nnz == g[f"{tag}_codes"].shape[0] * (blk // 16) ** 2
+        if blk == 16:   # canonical format IS the reference's flat pack at blocking 16
+            np.testing.assert_array_equal(m.codes.reshape(-1), g[f"{tag}_packed"])
+            np.testing.assert_array_equal(m.row_ptr, g[f"{tag}_offsets"])
+            np.testing.assert_array_equal(m.col_idx, g[f"{tag}_column_indices"].astype(np.uint16))
+        md = mb.MortarMatrix.from_reference_bcsr(g[f"{tag}_offsets"], g[f"{tag}_column_indices"],
+                                                 g[f"{tag}_packed"], float(g[f"{tag}_scale"]), blk, O, I,
+                                                 drop_zero_tiles=True)
+        np.testing.assert_array_equal(md.to_dense_codes(), m.to_dense_codes())
+        assert md.nnz <= m.nnz
+
+
+@pytest.mark.parametrize("case", GOLDEN_CASES)
+def test_from_weight_reproduces_reference_lifecycle(case):
+    """topk mask + ternarise-kept-values == the reference's prune -> carve -> pack."""
+    g = load_golden(case)
+    d_model, d_ff, blk, ncls = (int(v) for v in g["meta"])
+    if blk != 16:
+        pytest.skip("tile-granular selection only")
+    from conftest import bf16_from_bits
+    for tag in ("gu", "dn"):
+        w = bf16_from_bits(g[f"w_{tag}_bf16"]).float()
+        mask = mb.synth.topk_l2_mask(w, 0.25)
+        np.testing.assert_array_equal(mask.numpy(), g[f"{tag}_prune_mask"])
+        m = mb.MortarMatrix.from_weight(w, mask)
+        np.testing.assert_array_equal(m.codes.reshape(-1), g[f"{tag}_packed"])
+        assert np.float32(m.scale) == g[f"{tag}_scale"]
+
+
+def test_stream_round_trip_ragged_and_empty_rows():
+    rng = np.random.default_rng(5)
+    R, C = 37, 29
+    mask = rng.random((R, C)) < 0.3
+    mask[3] = False            # empty row
+    mask[4] = True             # full row (29 tiles: 3 full groups + 5)
+    mask[5, :] = False; mask[5, 7] = True
+    codes = rng.integers(-1, 2, size=(R * 16, C * 16)).astype(np.int8)
+    m = mb.MortarMatrix.from_codes(codes, mask, 0.5)
+    gp, gc, gcd, G = m.build_stream_host()
+    assert G == sum(-(-int(n) // 8) for n in np.diff(m.row_ptr))
+    assert gp[3 + 1] == gp[3]
+    ci, cd = fmt.unpack_stream_host(gp, gc, gcd, m.row_ptr, m.tile_rows)
+    np.testing.assert_array_equal(ci, m.col_idx)
+    np.testing.assert_array_equal(cd, m.codes)
+    # padding slots carry the sentinel column and all-zero codes
+    cols = gc.reshape(-1, 8)
+    words = gcd.view(np.uint32).reshape(-1, 32, 4)
+    for r in range(R):
+        n = int(m.row_ptr[r + 1] - m.row_ptr[r])
+        if n % 8:
+            last = gp[r + 1] - 1
+            assert (cols[last, n % 8:] == 0xFFFF).all()
+            for s in range(n % 8, 8):
+                fields = (words[last, :, s >> 1] >> (16 * 0)) if False else words[last, :, s >> 1]
+                shift = 8 * (s & 1)
+                lo = (fields >> shift) & 0xFF
+                hi = (fields >> (16 + shift)) & 0xFF
+                assert (lo == 0x55).all() and (hi == 0x55).all()
+    masked = codes.reshape(R, 16, C, 16) * mask[:, None, :, None]
+    np.testing.assert_array_equal(m.to_dense_codes(), masked.reshape(R * 16, C * 16))
+
+
+def test_fragment_layout_matches_mma_operand_order():
+    """Lane (g,t) of a warp must find, in register i, the codes of tile elements
+    (g + 8*(i&1), 2t + 8*(i>>1)) and (.., +1): the m16n8k16 A-fragment order."""
+    codes = np.zeros((16, 16), dtype=np.int8)
+    codes[3, 5] = 1      # g=3, t=2, low row, left half, odd column -> reg 0, high field
+    codes[11, 12] = -1   # g=3, upper row, right half, t=2, even column -> reg 3, low field
+    m = mb.MortarMatrix.from_codes(codes, None, 1.0)
+    gp, gc, gcd, G = m.build_stream_host()
+    words = gcd.view(np.uint32).reshape(G, 32, 4)
+    lane = 3 * 4 + 2
+    w = int(words[0, lane, 0])
+    assert (w >> (2 * 0 + 16)) & 3 == 2          # stored 2 = code +1
+    assert (w >> (2 * 3)) & 3 == 0               # stored 0 = code -1
+    w_other = np.delete(words[0, :, 0], lane)
+    assert (w_other == 0x55555555).all()
+
+
+def _good():
+    mask = np.array([[1, 0, 1], [0, 1, 1]], dtype=bool)
+    codes = np.ones((32, 48), dtype=np.int8)
+    return mb.MortarMatrix.from_codes(codes, mask, 1.0)
+
+
+def test_validation_rejects_malformed_metadata():
+    m = _good(); m.row_ptr = m.row_ptr.copy(); m.row_ptr[1] = 3; m.row_ptr[2] = 2
+    with pytest.raises(ValueError, match="row pointer"):
+        m.validate()
+    m = _good(); m.row_ptr = m.row_ptr.copy(); m.row_ptr[-1] = 3
+    with pytest.raises(ValueError, match="row pointer"):
+        m.validate()
+    m = _good(); m.col_idx = m.col_idx.copy(); m.col_idx[0] = 3
+    with pytest.raises(ValueError, match="column index"):
+        m.validate()
+    m = _good(); m.col_idx = m.col_idx.copy(); m.col_idx[[0, 1]] = m.col_idx[[1, 0]]
+    with pytest.raises(ValueError, match="column index"):
+        m.validate()
+    m = _good(); m.codes = m.codes.copy(); m.codes[1, 7] = 0b00001100
+    with pytest.raises(ValueError, match="2-bit"):
+        m.validate()
+    m = _good(); m.col_idx = m.col_idx.astype(np.int32)
+    with pytest.raises(ValueError, match="uint16"):
+        m.validate()
+    with pytest.raises(ValueError):
+        mb.MortarMatrix(30, 48, np.zeros(3, np.int32), np.zeros(0, np.uint16),
+                        np.zeros((0, 64), np.uint8), 1.0).validate()
+
+
+def test_split_blocks_rejects_bad_input():
+    g = load_golden("mlp_blk128_d256")
+    off = g["gu_offsets"].copy(); off[2] = off[1] - 1
+    with pytest.raises(ValueError):
+        mb.MortarMatrix.from_reference_bcsr(off, g["gu_column_indices"], g["gu_packed"], 1.0, 128, 1024, 256)
+    ci = g["gu_column_indices"].copy(); ci[0] = 9
+    with pytest.raises(ValueError):
+        mb.MortarMatrix.from_reference_bcsr(g["gu_offsets"], ci, g["gu_packed"], 1.0, 128, 1024, 256)
+    with pytest.raises(ValueError):
+        mb.MortarMatrix.from_reference_bcsr(g["gu_offsets"], g["gu_column_indices"], g["gu_packed"][:100],
+                                            1.0, 128, 1024, 256)
+
+
+def test_cpu_tensors_are_rejected_loudly():
+    m = _good()
+    with pytest.raises(NotImplementedError, match="CUDA-only"):
+        mb.ops.act_prep(torch.zeros(2, 48))
+
+
+def test_synth_generators_shapes_and_densities():
+    gen = torch.Generator().manual_seed(1)
+    u = mb.synth.uniform_mask(128, 352, 0.125, gen)
+    assert int(u.sum()) == round(0.125 * 128 * 352)
+    for rho in (0.125, 0.25, 0.5):
+        z = mb.synth.zipf_row_mask(128, 352, rho, gen)
+        assert abs(float(z.float().mean()) - rho) < 0.02
+        # one contiguous run per row
+        for r in range(0, 128, 17):
+            idx = z[r].nonzero().flatten()
+            if len(idx):
+                assert int(idx[-1] - idx[0]) + 1 == len(idx)
+    L = mb.synth.make_layer(768, 2048, 0.25, seed=100)
+    assert L.gate_up.nnz == 3072 and L.down.nnz == 1536
+    assert L.gate_up.algorithmic_bytes() + L.down.algorithmic_bytes() + 0 == 305360 - 0
+    gates = mb.synth.make_gates(5, L, 128, 32, seed=3)
+    assert int((gates > 0).sum(-1).max()) == 31
+    np.testing.assert_allclose(gates.sum(-1).numpy(), 32, rtol=1e-5)
+    # oracle's gate rule agrees
+    lg = torch.randn(4, 16)
+    np.testing.assert_array_equal(mb.synth.remoe_gates(lg, 4).numpy(), orc.remoe_gates(lg, 4).numpy())

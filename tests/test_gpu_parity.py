@@ -1,0 +1,263 @@
+"""Parity of the CUDA path (through the C ABI) against the CPU oracle and the golden
+fixtures.  Needs a B200."""
+import numpy as np
+import pytest
+import torch
+
+import mortar_b200 as mb
+from conftest import GOLDEN_CASES, bf16_from_bits, load_golden
+from oracle import mortar_oracle as orc
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+# fp32 (decode) semantics: reassociation noise only
+F32_TOL = 1e-5
+# bf16 (prefill) semantics: the official tolerance of the path ...
+BF16_RTOL, BF16_ATOL = 1e-2, 1e-3
+
+
+def _ulp_diff_bf16(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """distance in bf16 representable steps (monotone integer mapping of the bit pattern)"""
+    def key(t):
+        i = t.contiguous().view(torch.int16).to(torch.int32) & 0xFFFF
+        return torch.where(i >= 0x8000, 0x8000 - i, i)
+    return (key(a) - key(b)).abs()
+
+
+def _assert_bf16_close(y: torch.Tensor, ref: torch.Tensor):
+    """... and the internal gate: a handful of one-step flips where an fp32 sum lands on a
+    rounding boundary, nothing larger."""
+    y, ref = y.cpu().reshape(-1), ref.cpu().reshape(-1)
+    torch.testing.assert_close(y.float(), ref.float(), rtol=BF16_RTOL, atol=BF16_ATOL)
+    d = _ulp_diff_bf16(y, ref)
+    assert int(d.max()) <= 2, f"max bf16 step distance {int(d.max())}"
+    assert float((d > 0).float().mean()) < 0.02, f"{float((d > 0).float().mean()):.4f} of outputs differ"
+
+
+def _oracle_meta(m):
+    rows = np.repeat(np.arange(m.tile_rows), np.diff(m.row_ptr))
+    codes = torch.from_numpy(
+        np.ascontiguousarray(orc.unpack_ternary(m.codes.reshape(-1), m.nnz * 256).reshape(m.nnz, 16, 16)))
+    meta = (torch.from_numpy(rows), torch.from_numpy(m.col_idx.astype(np.int64)),
+            m.out_features, m.in_features)
+    return codes, meta
+
+
+def _decode_oracle(x, layer, gates=None, ncls=0, rms_w=None):
+    cg, mg = _oracle_meta(layer.gate_up)
+    cd, md = _oracle_meta(layer.down)
+    return orc.swiglu_mlp_decode(x.float(), cg, torch.tensor(layer.gate_up.scale), mg, cd,
+                                 torch.tensor(layer.down.scale), md, gates, ncls, rms_w)
+
+
+def _dense(m, bf16_scale=True):
+    c, meta = _oracle_meta(m)
+    return orc.mortar_dense(c, torch.tensor(m.scale), meta[0], meta[1], meta[2], meta[3], bf16_scale)
+
+
+@pytest.fixture(scope="module")
+def local_layer():
+    L = mb.synth.make_layer(768, 2048, 0.25, seed=100)
+    return L, L.gate_up.to_stream(DEV), L.down.to_stream(DEV)
+
+
+@pytest.mark.parametrize("B", [1, 3, 8, 13, 64])
+@pytest.mark.parametrize("in_dtype", [torch.bfloat16, torch.float32])
+def test_mlp_decode_fp32_semantics(local_layer, B, in_dtype):
+    L, gu, dn = local_layer
+    x = mb.synth.make_activations(B, 768, seed=B).to(in_dtype)
+    y = mb.ops.mlp_decode(x.to(DEV), gu, dn, n_planes=3, out_dtype=torch.float32)
+    ref = _decode_oracle(x, L)
+    assert float((y.cpu() - ref).abs().max()) <= F32_TOL * float(ref.abs().max())
+
+
+@pytest.mark.parametrize("B", [1, 8, 64])
+def test_mlp_decode_rmsnorm_and_gates(local_layer, B):
+    L, gu, dn = local_layer
+    gen = torch.Generator().manual_seed(77 + B)
+    x = torch.randn(B, 768, generator=gen) * 3.0
+    rms_w = 1.0 + 0.1 * torch.randn(768, generator=gen)
+    ncls, k = 16, 8
+    gates = mb.synth.make_gates(B, L, ncls, k, seed=5 + B)
+    y = mb.ops.mlp_decode(x.to(DEV), gu, dn, rms_weight=rms_w.to(DEV), eps=1e-6, gates=gates.to(DEV),
+                          n_clusters=ncls, n_planes=3)
+    ref = _decode_oracle(x, L, gates, ncls, rms_w)
+    assert float((y.cpu() - ref).abs().max()) <= F32_TOL * float(ref.abs().max())
+    # fine-grained groups (one 16-neuron group per tile, k-1 = 31 of 128 active)
+    gates = mb.synth.make_gates(B, L, 128, 32, seed=9 + B)
+    y = mb.ops.mlp_decode(x.to(DEV), gu, dn, rms_weight=rms_w.to(DEV), gates=gates.to(DEV),
+                          n_clusters=128, n_planes=3)
+    ref = _decode_oracle(x, L, gates, 128, rms_w)
+    assert float((y.cpu() - ref).abs().max()) <= F32_TOL * float(ref.abs().max())
+
+
+@pytest.mark.parametrize("rows", [5, 64, 200])
+def test_mlp_prefill_bf16_rounding_points(local_layer, rows):
+    L, gu, dn = local_layer
+    x = mb.synth.make_activations(rows, 768, seed=3 * rows)
+    y = mb.ops.mlp_prefill(x.to(DEV), gu, dn)
+    assert y.dtype == torch.bfloat16
+    ref = orc.swiglu_mlp(x.float(), _dense(L.gate_up), _dense(L.down), dtype=torch.bfloat16)
+    _assert_bf16_close(y, ref)
+    gates = mb.synth.make_gates(rows, L, 16, 8, seed=rows)
+    y = mb.ops.mlp_prefill(x.to(DEV), gu, dn, gates=gates.to(DEV), n_clusters=16)
+    ref = orc.swiglu_mlp(x.float(), _dense(L.gate_up), _dense(L.down), gates, 16, dtype=torch.bfloat16)
+    _assert_bf16_close(y, ref)
+
+
+@pytest.mark.parametrize("case", GOLDEN_CASES)
+def test_golden_fixtures_through_reference_storage(case):
+    """Reference storage (offsets / column_indices / mortar_packed / scale at blocking 16 and
+    128) -> converter -> kernels, against outputs the reference itself produced."""
+    g = load_golden(case)
+    d_model, d_ff, blk, ncls = (int(v) for v in g["meta"])
+    mats = {}
+    for tag, (O, I) in (("gu", (2 * d_ff, d_model)), ("dn", (d_model, d_ff))):
+        mats[tag] = mb.MortarMatrix.from_reference_bcsr(
+            g[f"{tag}_offsets"], g[f"{tag}_column_indices"], g[f"{tag}_packed"],
+            float(g[f"{tag}_scale"]), blk, O, I).to_stream(DEV)
+    x = bf16_from_bits(g["x_bf16"])
+    lead = x.shape[:-1]
+    # bf16 (prefill) semantics vs the reference's autocast outputs
+    y = mb.ops.mlp_prefill(x.to(DEV), mats["gu"], mats["dn"])
+    _assert_bf16_close(y, bf16_from_bits(g["y_bf16"]))
+    gates = torch.from_numpy(g["gates_autocast"])
+    y = mb.ops.mlp_prefill(x.to(DEV), mats["gu"], mats["dn"], gates=gates.to(DEV), n_clusters=ncls)
+    _assert_bf16_close(y, bf16_from_bits(g["y_routed_bf16"]))
+    # fp32 semantics vs the reference's fp32 outputs: the reference folds bf16(scale) into the
+    # weights, the decode algebra multiplies by the fp32 scale after the sum, so the two agree
+    # to bf16-scale precision (2^-9 relative per matrix).
+    y32 = mb.ops.mlp_decode(x.float().to(DEV), mats["gu"], mats["dn"], n_planes=3).cpu()
+    ref = torch.from_numpy(g["y_fp32"])
+    assert float((y32 - ref).abs().max()) <= 1.5e-2 * float(ref.abs().max())
+    gates = torch.from_numpy(g["gates_fp32"])
+    y32 = mb.ops.mlp_decode(x.float().to(DEV), mats["gu"], mats["dn"], gates=gates.to(DEV),
+                            n_clusters=ncls, n_planes=3).cpu()
+    ref = torch.from_numpy(g["y_routed_fp32"])
+    assert float((y32 - ref).abs().max()) <= 1.5e-2 * float(ref.abs().max())
+    # rmsnorm prologue vs the reference RMSNorm module
+    xn = mb.ops.rmsnorm_rows(torch.from_numpy(g["x_raw"]).to(DEV), torch.from_numpy(g["rms_weight"]).to(DEV), 1e-6)
+    np.testing.assert_allclose(xn.cpu().numpy(), g["x_normed"], rtol=3e-6, atol=1e-7)
+
+
+@pytest.mark.parametrize("case", GOLDEN_CASES)
+def test_mortar_gemv_shim_matches_reference_algebra(case):
+    """The reference-signature shim against the restatement of the reference's two decode
+    kernels on ITS strip layout and work list, flags at the reference's block granularity."""
+    g = load_golden(case)
+    d_model, d_ff, blk, ncls = (int(v) for v in g["meta"])
+
+    class FakeCms:      # the attributes mortar_pack_strips reads from a packed CMSBlockLinear
+        pass
+    packs, sps = {}, {}
+    for tag, (O, I) in (("gu", (2 * d_ff, d_model)), ("dn", (d_model, d_ff))):
+        c = FakeCms()
+        c._mortar, c._mortar_blocking = True, blk
+        c.mortar_packed = torch.from_numpy(g[f"{tag}_packed"])
+        c.mortar_scale = torch.tensor(float(g[f"{tag}_scale"]))
+        c.mortar_offsets = torch.from_numpy(g[f"{tag}_offsets"])
+        c.mortar_column_indices = torch.from_numpy(g[f"{tag}_column_indices"])
+        c.out_features, c.in_features = O, I
+        packs[tag] = mb.ops.mortar_pack_strips(c, DEV)
+        sps[tag] = orc.pack_strips(g[f"{tag}_codes"], g[f"{tag}_column_indices"], g[f"{tag}_offsets"],
+                                   g[f"{tag}_scale"])
+    x = torch.from_numpy(g["x_normed"]).reshape(-1, d_model)[:4].contiguous()
+    gates = g["gates_fp32"].reshape(-1, ncls)[:4]
+    cs = d_ff // ncls
+    rlo, rhi, clo, chi = orc.cluster_spans(d_ff, ncls, blk)
+    ract_o, cact_o = orc.route_flags(gates, rlo, rhi, clo, chi)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+    ract = torch.zeros(4, 512, dtype=torch.int32, device=DEV)[:, :len(rlo)]
+    cact = torch.zeros(4, 512, dtype=torch.int32, device=DEV)[:, :len(clo)]
+    mb.ops.route_flags(t(gates), t(rlo), t(rhi), t(clo), t(chi), ract, cact)
+    np.testing.assert_array_equal(ract.cpu().numpy(), ract_o)
+    np.testing.assert_array_equal(cact.cpu().numpy(), cact_o)
+    # unrouted
+    h = mb.ops.mortar_gemv(x.to(DEV), packs["gu"], swiglu_out=True)
+    y = mb.ops.mortar_gemv(h, packs["dn"])
+    ho = orc.mortar_gemv(x.numpy(), sps["gu"], swiglu_out=True)
+    yo = orc.mortar_gemv(ho, sps["dn"])
+    assert np.abs(h.cpu().numpy() - ho).max() <= F32_TOL * np.abs(ho).max()
+    assert np.abs(y.cpu().numpy() - yo).max() <= F32_TOL * np.abs(yo).max()
+    # routed, with gather flags
+    h = mb.ops.mortar_gemv(x.to(DEV), packs["gu"], swiglu_out=True, row_act=ract, gates=t(gates),
+                           cluster_size=cs)
+    y = mb.ops.mortar_gemv(h, packs["dn"], col_act=cact)
+    ho = orc.mortar_gemv(x.numpy(), sps["gu"], swiglu_out=True, row_act=ract_o, gates=gates, cluster_size=cs)
+    yo = orc.mortar_gemv(ho, sps["dn"], col_act=cact_o)
+    assert np.abs(h.cpu().numpy() - ho).max() <= F32_TOL * np.abs(ho).max()
+    assert np.abs(y.cpu().numpy() - yo).max() <= F32_TOL * np.abs(yo).max()
+    # legacy swiglu-on-load form
+    gu_full = mb.ops.mortar_gemv(x.to(DEV), packs["gu"])
+    y2 = mb.ops.mortar_gemv(gu_full, packs["dn"], swiglu_x=True)
+    yo2 = orc.mortar_gemv(orc.mortar_gemv(x.numpy(), sps["gu"], swiglu_out=True), sps["dn"])
+    assert np.abs(y2.cpu().numpy() - yo2).max() <= 2 * F32_TOL * np.abs(yo2).max()
+
+
+def test_linear_edge_topologies():
+    """empty rows, a single tile, a full row, ragged tails; every batch remainder."""
+    rng = np.random.default_rng(11)
+    R, C = 19, 21
+    mask = rng.random((R, C)) < 0.3
+    mask[0] = False
+    mask[1] = True
+    mask[2] = False; mask[2, 20] = True
+    codes = rng.integers(-1, 2, size=(R * 16, C * 16)).astype(np.int8)
+    m = mb.MortarMatrix.from_codes(codes, mask, 0.37)
+    s = m.to_stream(DEV)
+    W = torch.from_numpy(m.to_dense_codes()).float()
+    for rows in (1, 2, 7, 8, 9, 16, 31, 33, 64, 65, 130):
+        x = torch.randn(rows, C * 16, generator=torch.Generator().manual_seed(rows))
+        y = mb.ops.linear(x.to(DEV), s)
+        ref = (x.double() @ W.double().T * np.float32(0.37)).float()
+        assert float((y.cpu() - ref).abs().max()) <= F32_TOL * float(ref.abs().max())
+        assert float(y[:, :16].abs().max()) == 0.0      # the empty tile row yields exact zeros
+    assert mb.ops.linear(torch.zeros(0, C * 16, device=DEV), s).shape == (0, R * 16)
+    with pytest.raises(ValueError):
+        mb.ops.linear(torch.zeros(2, C * 16 + 16, device=DEV), s)
+
+
+def test_linear_is_linear_and_exact_on_integers():
+    """size-independent properties: integer-valued activations make every partial sum exact,
+    so the kernel must agree with integer arithmetic bit for bit."""
+    L = mb.synth.make_layer(2048, 5632, 0.25, seed=200)
+    s = L.gate_up.to_stream(DEV)
+    gen = torch.Generator().manual_seed(4)
+    xi = torch.randint(-8, 9, (40, 2048), generator=gen).float()
+    y = mb.ops.linear_planes(s, xi.to(torch.bfloat16).unsqueeze(0).to(DEV), out_dtype=torch.float32)
+    Wc = torch.from_numpy(L.gate_up.to_dense_codes()).to(DEV).float()
+    exact = (xi.to(DEV) @ Wc.T)                     # integer sums below 2^24: exact in fp32
+    assert torch.equal(y, exact * np.float32(L.gate_up.scale))
+
+
+@pytest.mark.parametrize("mask", ["uniform", "zipf_rows"])
+@pytest.mark.parametrize("density", [0.125, 0.5, 1.0])
+def test_topology_sweep_cloud_shape(mask, density):
+    """density / topology sweep on the cloud-shape MLP against a dense evaluation of the same
+    codes on the GPU (row-clustered Zipf masks have empty and very long rows)."""
+    L = mb.synth.make_layer(2048, 5632, density, seed=300, mask=mask)
+    gu, dn = L.gate_up.to_stream(DEV), L.down.to_stream(DEV)
+    x = mb.synth.make_activations(96, 2048, seed=1).to(DEV)
+    y = mb.ops.mlp_decode(x, gu, dn, n_planes=3, out_dtype=torch.float32)
+    Wg = torch.from_numpy(L.gate_up.to_dense_codes()).to(DEV).double()
+    Wd = torch.from_numpy(L.down.to_dense_codes()).to(DEV).double()
+    gu_ = (x.double() @ Wg.T) * float(np.float32(L.gate_up.scale))
+    g_, u_ = gu_.chunk(2, dim=-1)
+    ref = ((g_ * torch.sigmoid(g_) * u_) @ Wd.T) * float(np.float32(L.down.scale))
+    assert float((y.double() - ref).abs().max()) <= 2e-5 * float(ref.abs().max())
+
+
+def test_module_mirror_matches_ops(local_layer):
+    L, gu, dn = local_layer
+    mlp = mb.SwiGLUMortar(L.gate_up, L.down, device=DEV)
+    x = mb.synth.make_activations(4 * 9, 768, seed=8).reshape(4, 9, 768).to(DEV)
+    y = mlp(x)
+    assert y.shape == (4, 9, 768) and y.dtype == torch.bfloat16
+    assert torch.equal(y.reshape(-1, 768), mb.ops.mlp_prefill(x.reshape(-1, 768), gu, dn))
+    y32 = mlp(x.float(), iter_idx=3)
+    assert y32.dtype == torch.float32
+    lin = mlp.down
+    assert lin.is_compact and lin.bias is None and abs(lin.get_density() - 0.25) < 1e-6
+    with pytest.raises(AssertionError):
+        lin.carve()
