@@ -1,0 +1,487 @@
+"""Benchmark of the MORTAR sparse-MLP hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Headline workload (N=1 and every N): the decode stack of the default 3+6xT+3 layout --
+12 independent ternary MLP layers (d_model 768, d_ff 2048, 25% tile density, seeds
+100..111), 42 MLP applications per token in engine order, 64 tokens per GPU per step.  One
+step = one decode step of the whole stack: x <- x + MLP_i(rmsnorm_i(x)) for the 42
+applications (the residual add makes the chain data-dependent; attention between the
+applications is not part of this path).  `value` = tokens/s with inputs resident in HBM,
+`e2e` = the same through pinned host buffers with the copies inside the timed region.
+Between timed steps a 256 MiB buffer is written to flush L2.  The JSON line also carries
+batch 1 / 8 decode and cloud-shape prefill measurements, each with its own roofline.
+
+Under torchrun (N>1) every rank runs the same stack on its own GPU with its own 64 tokens
+(weights replicated, no collective on the data path); the aggregate is all tokens over
+the slowest rank's device time.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+LOCAL = dict(d_model=768, d_ff=2048, prelude=3, core=6, coda=3, T=6, seed0=100)
+CLOUD = dict(d_model=2048, d_ff=5632, prelude=4, core=8, coda=4, T=8, seed0=200)
+DENSITY = 0.25
+DECODE_BATCH = 64
+PREFILL_TOKENS = 16384
+L2_FLUSH_BYTES = 256 << 20
+
+
+def site_order(cfg) -> list[int]:
+    """Layer index of every MLP application of one token, in the order of
+    StaticDecodeEngine's site list (morph/inference/engine.py:207-213)."""
+    p, c, d, T = cfg["prelude"], cfg["core"], cfg["coda"], cfg["T"]
+    return (list(range(p)) + [p + i for _ in range(T) for i in range(c)]
+            + [p + c + i for i in range(d)])
+
+
+def peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        d["source"] = "measured"
+        return d
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+            "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append(line.strip())
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            f = [t.strip() for t in s.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0])); mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def max_over_ranks(ms: float, device) -> float:
+    """Whole-job time of a timed region = the slowest rank's summed device time."""
+    t = torch.tensor([ms], device=device, dtype=torch.float64)
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def job_throughput(units_per_rank: int, world: int, slowest_ms: float) -> float:
+    """Units processed by all ranks (weak scaling: the same count on each) per second."""
+    return units_per_rank * world / (slowest_ms * 1e-3)
+
+
+# ---------------------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------------------
+
+class Stack:
+    """Device-resident layers of one configuration."""
+
+    def __init__(self, cfg, mb, device):
+        self.cfg = cfg
+        n_layers = cfg["prelude"] + cfg["core"] + cfg["coda"]
+        self.layers = [mb.synth.make_layer(cfg["d_model"], cfg["d_ff"], DENSITY, seed=cfg["seed0"] + i)
+                       for i in range(n_layers)]
+        self.gu = [L.gate_up.to_stream(device) for L in self.layers]
+        self.dn = [L.down.to_stream(device) for L in self.layers]
+        gen = torch.Generator().manual_seed(cfg["seed0"] + 999)
+        self.rms = [(1.0 + 0.05 * torch.randn(cfg["d_model"], generator=gen)).to(device)
+                    for _ in range(n_layers)]
+        self.order = site_order(cfg)
+        self.matrix_bytes = [L.gate_up.algorithmic_bytes() + L.down.algorithmic_bytes()
+                             for L in self.layers]
+        self.tiles = [L.gate_up.nnz + L.down.nnz for L in self.layers]
+
+    def algorithmic_bytes_per_step(self, batch: int) -> int:
+        """per application: codes + column indices + row pointers + scales of both matrices,
+        plus the bf16 activations in and out (2*d*batch*2 bytes)."""
+        d = self.cfg["d_model"]
+        return sum(self.matrix_bytes[i] + batch * 2 * d * 2 for i in self.order)
+
+    def useful_flops_per_token(self) -> int:
+        return sum(2 * 256 * self.tiles[i] for i in self.order)
+
+
+def decode_step(mb, stack: Stack, x: torch.Tensor, ws: torch.Tensor) -> None:
+    """x [B, d] fp32 residual carrier, updated in place through the 42 applications."""
+    for i in stack.order:
+        mb.ops.mlp_decode(x, stack.gu[i], stack.dn[i], rms_weight=stack.rms[i], eps=1e-6,
+                          n_planes=3, out=x, accumulate=True, workspace=ws)
+
+
+def prefill_pass(mb, stack: Stack, x: torch.Tensor, y: torch.Tensor, ws: torch.Tensor) -> None:
+    """x [N, d] bf16 token block through every application of the stack (bf16 semantics, the
+    reference's rounding points); every application reads the same normalised block."""
+    for i in stack.order:
+        mb.ops.mlp_decode(x, stack.gu[i], stack.dn[i], n_planes=1, round_bf16=True,
+                          out_dtype=torch.bfloat16, out=y, workspace=ws)
+
+
+def time_steps(fn, steps: int, warmup: int, flush: torch.Tensor | None, pre=None, post=None):
+    """Runs `fn` warmup+steps times; returns per-step device milliseconds (CUDA events on the
+    current stream).  `pre`/`post` run inside the timed window (the host copies of the
+    end-to-end measurement); the L2 flush runs outside it."""
+    times = []
+    for it in range(warmup + steps):
+        if flush is not None:
+            flush.fill_(float(it & 7))
+        s = torch.cuda.Event(enable_timing=True)
+        e = torch.cuda.Event(enable_timing=True)
+        s.record()
+        if pre is not None:
+            pre()
+        fn()
+        if post is not None:
+            post()
+        e.record()
+        e.synchronize()
+        if it >= warmup:
+            times.append(s.elapsed_time(e))
+    return times
+
+
+def capture(fn):
+    """CUDA graph of `fn` (one warm call first so lazy allocations are outside the capture)."""
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        fn()
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            fn()
+    torch.cuda.current_stream().wait_stream(stream)
+    return g
+
+
+def run_decode(mb, stack: Stack, batch: int, steps: int, warmup: int, flush, device, seed: int):
+    d = stack.cfg["d_model"]
+    x0 = mb.synth.make_activations(batch, d, seed=seed, dtype=torch.float32)
+    x = x0.to(device)
+    ws = torch.empty(mb._lib.lib().mortar_mlp_workspace_bytes(batch, d, stack.cfg["d_ff"], 3) + 256,
+                     device=device, dtype=torch.uint8)
+    n0 = mb.ops.launch_count()
+    g = capture(lambda: decode_step(mb, stack, x, ws))
+    launches_per_step = (mb.ops.launch_count() - n0) // 2
+    xin = x0.to(device)
+
+    def reset():
+        x.copy_(xin)          # same input every step (outside the timed window)
+
+    # device-resident
+    t_dev = []
+    for it in range(warmup + steps):
+        reset()
+        t = time_steps(g.replay, 1, 0, flush)
+        if it >= warmup:
+            t_dev += t
+    # end to end through pinned host memory
+    hx = x0.clone().pin_memory()
+    hy = torch.empty_like(hx).pin_memory()
+    t_e2e = time_steps(g.replay, steps, warmup, flush,
+                       pre=lambda: x.copy_(hx, non_blocking=True),
+                       post=lambda: hy.copy_(x, non_blocking=True))
+    # warm L2 (no flush), for reference
+    reset()
+    t_warm = time_steps(g.replay, steps, warmup, None)
+    return dict(batch=batch, t_dev=t_dev, t_e2e=t_e2e, t_warm=t_warm,
+                launches_per_step=launches_per_step, h2d=hx.numel() * 4, d2h=hy.numel() * 4,
+                checksum=float(hy.double().abs().sum()))
+
+
+def kernel_only(mb, stack: Stack, batch: int, reps: int, device):
+    """Average duration of one launch of the block-sparse streaming kernel (the dominant
+    kernel): gate_up and down launches of every application back to back, activations already
+    in plane form, CUDA events around the whole run."""
+    d, f = stack.cfg["d_model"], stack.cfg["d_ff"]
+    xp = mb.ops.act_prep(mb.synth.make_activations(batch, d, seed=5, dtype=torch.float32).to(device), 3)
+    hp = torch.empty(3, batch, f, device=device, dtype=torch.bfloat16)
+    y = torch.empty(batch, d, device=device, dtype=torch.float32)
+    L = mb._lib.lib()
+    import ctypes as C
+
+    def one(i):
+        gu, dn = stack.gu[i].c_struct(), stack.dn[i].c_struct()
+        st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        mb._lib.check(L.mortar_linear(C.byref(gu), C.c_void_p(xp.data_ptr()), 3, batch * d, d, batch,
+                                      C.c_void_p(hp.data_ptr()), 2, 3, batch * f, f, 1, None, 0, 0,
+                                      None, 0, None, 0, st), "mortar_linear")
+        mb._lib.check(L.mortar_linear(C.byref(dn), C.c_void_p(hp.data_ptr()), 3, batch * f, f, batch,
+                                      C.c_void_p(y.data_ptr()), 0, 0, 0, d, 0, None, 0, 0,
+                                      None, 0, None, 0, st), "mortar_linear")
+
+    def step():
+        for i in stack.order:
+            one(i)
+    g = capture(step)
+    t = time_steps(g.replay, reps, 3, None)
+    launches = 2 * len(stack.order)
+    return statistics.mean(t) / launches * 1e3     # microseconds per launch
+
+
+def cpu_reference_decode(batch: int, budget_s: float, cfg=LOCAL):
+    """The reference's CPU path for this MLP (dense reconstruction of the effective weights
+    + F.linear, fp32, all host threads; morph/inference/engine.py:74-84 and
+    morph/model/transformer.py:402-431) on the same stack, for a bounded number of steps."""
+    from oracle import mortar_oracle as orc
+    import mortar_b200 as mb
+    import numpy as np
+    torch.set_num_threads(os.cpu_count() or 1)
+    n_layers = cfg["prelude"] + cfg["core"] + cfg["coda"]
+    dense = []
+    for i in range(n_layers):
+        L = mb.synth.make_layer(cfg["d_model"], cfg["d_ff"], DENSITY, seed=cfg["seed0"] + i)
+        ws = []
+        for m in (L.gate_up, L.down):
+            rows = np.repeat(np.arange(m.tile_rows), np.diff(m.row_ptr))
+            codes = torch.from_numpy(np.ascontiguousarray(
+                orc.unpack_ternary(m.codes.reshape(-1), m.nnz * 256).reshape(m.nnz, 16, 16)))
+            ws.append(orc.mortar_dense(codes, torch.tensor(m.scale), torch.from_numpy(rows),
+                                       torch.from_numpy(m.col_idx.astype(np.int64)),
+                                       m.out_features, m.in_features, bf16_weights=False))
+        dense.append(ws)
+    gen = torch.Generator().manual_seed(cfg["seed0"] + 999)
+    rms = [(1.0 + 0.05 * torch.randn(cfg["d_model"], generator=gen)) for _ in range(n_layers)]
+    order = site_order(cfg)
+    x0 = mb.synth.make_activations(batch, cfg["d_model"], seed=1, dtype=torch.float32)
+
+    def step():
+        x = x0.clone()
+        for i in order:
+            xn = orc.rmsnorm_rows(x, rms[i], 1e-6)
+            x = x + orc.swiglu_mlp(xn, dense[i][0], dense[i][1])
+        return x
+    step()
+    times = []
+    t_start = time.perf_counter()
+    while len(times) < 3 or (time.perf_counter() - t_start < budget_s and len(times) < 200):
+        t0 = time.perf_counter()
+        step()
+        times.append(time.perf_counter() - t0)
+    return dict(ms_per_step=1e3 * min(times), steps=len(times), cores=torch.get_num_threads(),
+                tokens_per_s=batch / min(times))
+
+
+def run_ours(args, rank, world, local_rank):
+    import mortar_b200 as mb
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    pk = peaks()
+    stack = Stack(LOCAL, mb, device)
+    flush = torch.empty(L2_FLUSH_BYTES, device=device, dtype=torch.uint8)
+    steps, warmup = args.steps, max(args.warmup, 3)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    sync_all()
+    with ClockSampler(local_rank) as clk:
+        main = run_decode(mb, stack, DECODE_BATCH, steps, warmup, flush, device, seed=1 + rank)
+    sync_all()
+
+    def agg(times_ms):
+        return max_over_ranks(sum(times_ms), device)
+
+    tot_dev, tot_e2e, tot_warm = agg(main["t_dev"]), agg(main["t_e2e"]), agg(main["t_warm"])
+    tokens = DECODE_BATCH * steps * world
+    value = job_throughput(DECODE_BATCH * steps, world, tot_dev)
+    e2e = job_throughput(DECODE_BATCH * steps, world, tot_e2e)
+
+    extra = {}
+    roof = None
+    cpu = None
+    if rank == 0:
+        us_launch = kernel_only(mb, stack, DECODE_BATCH, max(steps, 10), device)
+        alg = stack.algorithmic_bytes_per_step(DECODE_BATCH) / (2 * len(stack.order))
+        achieved = alg / (us_launch * 1e-6) / 1e9
+        roof = {"bound": "hbm", "kernel": "bcsr_stream_kernel (gate_up+SwiGLU and down launches)",
+                "achieved": round(achieved, 2), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "frac": round(achieved / pk["hbm_gbs"], 5), "peak_source": pk["source"],
+                "us_per_launch": round(us_launch, 3),
+                "algorithmic_bytes_per_launch": int(alg),
+                "traffic": TRAFFIC_BYTES_PER_LAUNCH,
+                "note": "weights of the whole stack (3.6 MB) are L2-resident between launches: "
+                        "this configuration is latency-bound, not HBM-bound"}
+        if world == 1 and not args.quick:
+            for b in (1, 8):
+                r = run_decode(mb, stack, b, steps, warmup, flush, device, seed=11 + b)
+                extra[f"decode_b{b}"] = {
+                    "tokens_per_s": round(b * steps / (sum(r["t_dev"]) * 1e-3), 1),
+                    "e2e_tokens_per_s": round(b * steps / (sum(r["t_e2e"]) * 1e-3), 1),
+                    "ms_per_step": round(statistics.mean(r["t_dev"]), 4),
+                    "hbm_frac_algorithmic": round(stack.algorithmic_bytes_per_step(b)
+                                                  / (statistics.mean(r["t_dev"]) * 1e-3) / 1e9
+                                                  / pk["hbm_gbs"], 5)}
+            extra["prefill_cloud"] = run_prefill(mb, device, pk, flush)
+        if world == 1:
+            c = cpu_reference_decode(DECODE_BATCH, budget_s=12.0)
+            cpu = {"value": round(c["tokens_per_s"], 1), "unit": "tokens/s", "cores": c["cores"],
+                   "kind": "port",
+                   "sample": f"{c['steps']} decode steps of the same 42-application stack at batch "
+                             f"{DECODE_BATCH}, fp32 dense reconstruction + F.linear, best step"}
+    if rank != 0:
+        return
+    ms_per_step = tot_dev / steps
+    line = {
+        "metric": "MORTAR MLP tokens/s (decode stack, 42 MLP applications per token)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": steps,
+        "warmup": warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16 planes x ternary, fp32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": "decode stack 3+6x6+3 (configs[1]): d_model 768, d_ff 2048, 12 "
+                               "ternary layers at 25% 16x16-tile density, 42 applications/token",
+                   "batch_per_gpu": DECODE_BATCH, "l2": "256 MiB flush between timed steps",
+                   "graph": "one CUDA graph per decode step", "parallelism": f"dp{world} (token shards, replicated weights, no collective)"},
+        "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": main["h2d"],
+                "d2h_bytes_per_step": main["d2h"]},
+        "gpu_launches": main["launches_per_step"] * steps,
+        "warm_l2_tokens_per_s": round(tokens / (tot_warm * 1e-3), 1),
+        "clocks": clk.summary(),
+        "roofline": roof,
+        "cpu_baseline": cpu,
+        "checksum": main["checksum"],
+    }
+    line.update(extra)
+    print(json.dumps(line), flush=True)
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of bcsr_stream_kernel, from the ncu
+# capture summarised in profiles/ (cold caches under ncu; null until a capture exists)
+TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def run_prefill(mb, device, pk, flush, tokens: int = PREFILL_TOKENS, reps: int = 2):
+    """Cloud-shape prefill (configs[2]): 16 layers, 72 applications, 16384 tokens, bf16."""
+    stack = Stack(CLOUD, mb, device)
+    d, f = CLOUD["d_model"], CLOUD["d_ff"]
+    x = mb.synth.make_activations(tokens, d, seed=7).to(device)
+    y = torch.empty_like(x)
+    ws = torch.empty(mb._lib.lib().mortar_mlp_workspace_bytes(tokens, d, f, 1) + 256, device=device,
+                     dtype=torch.uint8)
+    fn = lambda: prefill_pass(mb, stack, x, y, ws)
+    t = time_steps(fn, reps, 1, flush)
+    ms = statistics.mean(t)
+    flops = stack.useful_flops_per_token() * tokens
+    tf = flops / (ms * 1e-3) / 1e12
+    return {"tokens_per_s": round(tokens / (ms * 1e-3), 1), "ms_per_pass": round(ms, 3),
+            "applications": len(stack.order), "tokens": tokens,
+            "useful_tflops": round(tf, 2),
+            "tensor_frac_of_bf16_peak": round(tf / pk["bf16_tflops_sustained"], 5),
+            "peak_source": pk["source"]}
+
+
+# ---------------------------------------------------------------------------------------
+# reference arm: the reference's CPU path on the host cores
+# ---------------------------------------------------------------------------------------
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    steps, warmup = args.steps, max(args.warmup, 1)
+    c = cpu_reference_decode(DECODE_BATCH, budget_s=min(60.0, 2.0 * (steps + warmup)))
+    line = {
+        "impl": "reference",
+        "metric": "MORTAR MLP tokens/s (decode stack, 42 MLP applications per token)",
+        "value": round(c["tokens_per_s"], 1), "unit": "tokens/s", "n_gpus": world, "steps": steps,
+        "warmup": warmup, "ms_per_step": round(c["ms_per_step"], 3), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "decode stack 3+6x6+3 (configs[1]): d_model 768, d_ff 2048, 12 "
+                               "ternary layers at 25% 16x16-tile density, 42 applications/token",
+                   "batch_per_gpu": DECODE_BATCH},
+        "cpu_baseline": {"value": round(c["tokens_per_s"], 1), "unit": "tokens/s", "cores": c["cores"],
+                         "kind": "port",
+                         "sample": f"{c['steps']} decode steps at batch {DECODE_BATCH}, dense "
+                                   f"reconstruction + F.linear fp32 (the reference's CPU path; its "
+                                   f"carved kernels are CUDA/Triton-only), best step"},
+        "e2e": {"value": round(c["tokens_per_s"], 1), "unit": "tokens/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--quick", action="store_true", help="headline measurement only")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_ours(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

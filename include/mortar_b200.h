@@ -135,9 +135,13 @@ enum {
     MORTAR_FLAG_SWIGLU = 1,      /* rows [0,F) are gate, [F,2F) up; out[b, n] = silu(g)*u, F = R/2 */
     MORTAR_FLAG_ROUND_BF16 = 2,  /* reproduce the reference's bf16 rounding points
                                     (triton_kernels.py:226, transformer.py:405-427) */
-    MORTAR_FLAG_GATES_ON_INPUT = 4 /* non-SWIGLU call: `gates` describe the INPUT neurons
+    MORTAR_FLAG_GATES_ON_INPUT = 4, /* non-SWIGLU call: `gates` describe the INPUT neurons
                                     (the down projection); tile columns whose spanned
                                     clusters are all gated to 0 are skipped (rows <= 8) */
+    MORTAR_FLAG_ACCUMULATE = 8   /* out += result (MORTAR_OUT_F32 / MORTAR_OUT_BF16): the caller's
+                                    residual carrier receives the MLP output directly, the
+                                    add the reference performs after the MLP
+                                    (morph/model/hyper_connections.py:182-229) */
 };
 
 /* y = act @ W^T for a stream-format matrix; replaces mortar_gemv
@@ -183,7 +187,9 @@ int64_t mortar_mlp_workspace_bytes(int64_t rows, int32_t d_model, int32_t d_ff, 
  * gates are all zero are skipped.  workspace: device, 256-byte aligned,
  * mortar_mlp_workspace_bytes() bytes; contents are scratch.
  * With MORTAR_FLAG_ROUND_BF16 in `flags` and n_planes == 1 the call reproduces the bf16
- * rounding points of _SwiGLUMortar.forward under autocast (transformer.py:402-431). */
+ * rounding points of _SwiGLUMortar.forward under autocast (transformer.py:402-431).
+ * With MORTAR_FLAG_ACCUMULATE, y += MLP(x) (x and y may be the same buffer: x is fully
+ * consumed by the first stage before y is written). */
 int mortar_mlp_decode(const mortar_stream *gate_up, const mortar_stream *down,
                       const void *x, int x_dtype, int64_t ldx, int64_t rows,
                       const float *rms_weight, float eps,

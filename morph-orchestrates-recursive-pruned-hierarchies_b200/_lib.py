@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(PKG, "libmortar_b200.so")
 OK = 0
 F32, BF16 = 0, 1
 OUT_F32, OUT_BF16, OUT_PLANES = 0, 1, 2
-FLAG_SWIGLU, FLAG_ROUND_BF16, FLAG_GATES_ON_INPUT = 1, 2, 4
+FLAG_SWIGLU, FLAG_ROUND_BF16, FLAG_GATES_ON_INPUT, FLAG_ACCUMULATE = 1, 2, 4, 8
 
 _SHAPE_ERRORS = {-2, -3, -4, -5, -6, -7, -8}
 

@@ -33,6 +33,7 @@ struct LinearParams {
     int out_mode, n_out_planes;
     long long out_plane_stride, ld_out;
     int round_bf16;
+    int accumulate;
     const float *gates;
     long long ld_gates;
     int cluster_size;
@@ -70,9 +71,11 @@ __device__ __forceinline__ float round_bf16(float v) {
 __device__ __forceinline__ void store_value(const LinearParams &p, long long row, long long col,
                                             float v) {
     if (p.out_mode == MORTAR_OUT_F32) {
-        reinterpret_cast<float *>(p.out)[row * p.ld_out + col] = v;
+        float *o = reinterpret_cast<float *>(p.out) + row * p.ld_out + col;
+        *o = p.accumulate ? *o + v : v;
     } else if (p.out_mode == MORTAR_OUT_BF16) {
-        reinterpret_cast<__nv_bfloat16 *>(p.out)[row * p.ld_out + col] = __float2bfloat16_rn(v);
+        __nv_bfloat16 *o = reinterpret_cast<__nv_bfloat16 *>(p.out) + row * p.ld_out + col;
+        *o = __float2bfloat16_rn(p.accumulate ? __bfloat162float(*o) + v : v);
     } else {
         __nv_bfloat16 *o = reinterpret_cast<__nv_bfloat16 *>(p.out) + row * p.ld_out + col;
         float r = v;
@@ -87,10 +90,13 @@ __device__ __forceinline__ void store_value(const LinearParams &p, long long row
 // One CTA = 4 warps; WPR warps cooperate on one unit (a tile row, or for SWIGLU a hidden
 // tile row = gate row u and up row u+units), 4/WPR units per CTA.  blockIdx.y selects a
 // block of 8*NT activation rows.
-template <int NT, bool SWIGLU, int WPR>
+template <int NT, int P, bool SWIGLU, int WPR>
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
 bcsr_stream_kernel(const LinearParams p) {
     constexpr int UPC = kWarpsPerCta / WPR;
+    // tile slots whose activation fragments are fetched together before any of them is
+    // consumed, so the loads overlap instead of each waiting behind the previous MMA
+    constexpr int SB = (16 / (NT * P) >= 8) ? 8 : (16 / (NT * P) >= 4) ? 4 : (16 / (NT * P) >= 2) ? 2 : 1;
     constexpr int NACC = SWIGLU ? 2 : 1;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -172,21 +178,41 @@ bcsr_stream_kernel(const LinearParams p) {
                 const uint32_t cws[4] = {cw.x, cw.y, cw.z, cw.w};
                 const uint32_t cls[4] = {cl.x, cl.y, cl.z, cl.w};
 #pragma unroll
-                for (int s = 0; s < 8; ++s) {
-                    const uint32_t word = cws[s >> 1];
-                    const uint32_t col = (cls[s >> 1] >> (16 * (s & 1))) & 0xffffu;
-                    if (col == 0xffffu) break;                       // padding slots end a row
-                    if (use_cact && !col_active[col]) continue;
-                    uint32_t af[4];
+                for (int s0 = 0; s0 < 8; s0 += SB) {
+                    uint32_t bf[SB][NT][P][2];
+                    bool live[SB];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) af[i] = decode_pair(word, (s & 1) * 4 + i);
+                    for (int ss = 0; ss < SB; ++ss) {
+                        const int s = s0 + ss;
+                        const uint32_t col = (cls[s >> 1] >> (16 * (s & 1))) & 0xffffu;
+                        live[ss] = (col != 0xffffu);                 // padding slots end a row
+                        if (use_cact && live[ss]) live[ss] = col_active[col] != 0;
+                        if (live[ss]) {
 #pragma unroll
-                    for (int n = 0; n < NT; ++n) {
-                        const uint32_t *px = xb[n] + (long long)col * 8;
-                        for (int pl = 0; pl < p.n_planes; ++pl) {
-                            const uint32_t b0 = __ldg(px), b1 = __ldg(px + 4);
-                            mma_16816(acc[a][n], af, b0, b1);
-                            px += p.plane_stride_w;
+                            for (int n = 0; n < NT; ++n) {
+                                const uint32_t *px = xb[n] + (long long)col * 8;
+#pragma unroll
+                                for (int pl = 0; pl < P; ++pl) {
+                                    bf[ss][n][pl][0] = __ldg(px);
+                                    bf[ss][n][pl][1] = __ldg(px + 4);
+                                    px += p.plane_stride_w;
+                                }
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int ss = 0; ss < SB; ++ss) {
+                        const int s = s0 + ss;
+                        if (live[ss]) {
+                            const uint32_t word = cws[s >> 1];
+                            uint32_t af[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) af[i] = decode_pair(word, (s & 1) * 4 + i);
+#pragma unroll
+                            for (int n = 0; n < NT; ++n)
+#pragma unroll
+                                for (int pl = 0; pl < P; ++pl)
+                                    mma_16816(acc[a][n], af, bf[ss][n][pl][0], bf[ss][n][pl][1]);
                         }
                     }
                 }
@@ -304,25 +330,31 @@ __global__ void route_flags_kernel(const float *gates, long long ld_gates, const
         cact[b * ld_cact + i] = (gb[clo[i]] > 0.f) | (gb[chi[i]] > 0.f);
 }
 
-template <int NT, bool SWIGLU>
-int launch_wpr(const LinearParams &p, int wpr, dim3 grid_y, cudaStream_t st) {
+template <int NT, int P, bool SWIGLU>
+int launch_wpr(const LinearParams &p, int wpr, unsigned grid_y, cudaStream_t st) {
     const int upc = kWarpsPerCta / wpr;
-    dim3 grid((p.units + upc - 1) / upc, grid_y.x);
-    if (wpr == 4) bcsr_stream_kernel<NT, SWIGLU, 4><<<grid, kWarpsPerCta * 32, 0, st>>>(p);
-    else if (wpr == 2) bcsr_stream_kernel<NT, SWIGLU, 2><<<grid, kWarpsPerCta * 32, 0, st>>>(p);
-    else bcsr_stream_kernel<NT, SWIGLU, 1><<<grid, kWarpsPerCta * 32, 0, st>>>(p);
+    dim3 grid((p.units + upc - 1) / upc, grid_y);
+    if (wpr == 4) bcsr_stream_kernel<NT, P, SWIGLU, 4><<<grid, kWarpsPerCta * 32, 0, st>>>(p);
+    else if (wpr == 2) bcsr_stream_kernel<NT, P, SWIGLU, 2><<<grid, kWarpsPerCta * 32, 0, st>>>(p);
+    else bcsr_stream_kernel<NT, P, SWIGLU, 1><<<grid, kWarpsPerCta * 32, 0, st>>>(p);
     MORTAR_CUDA_CHECK(cudaGetLastError());
     return MORTAR_OK;
 }
 
-template <bool SWIGLU>
+template <int P, bool SWIGLU>
 int launch_nt(const LinearParams &p, int wpr, cudaStream_t st) {
-    if (p.rows <= 8) return launch_wpr<1, SWIGLU>(p, wpr, dim3(1), st);
-    if (p.rows <= 16) return launch_wpr<2, SWIGLU>(p, wpr, dim3(1), st);
-    if (p.rows <= 32) return launch_wpr<4, SWIGLU>(p, wpr, dim3(1), st);
-    const long long blocks = (p.rows + 63) / 64;
+    if (p.rows <= 8) return launch_wpr<1, P, SWIGLU>(p, wpr, 1, st);
+    if (p.rows <= 16) return launch_wpr<2, P, SWIGLU>(p, wpr, 1, st);
+    const long long blocks = (p.rows + 31) / 32;
     if (blocks > 65535) return MORTAR_ERR_CAPACITY;
-    return launch_wpr<8, SWIGLU>(p, wpr, dim3((unsigned)blocks), st);
+    return launch_wpr<4, P, SWIGLU>(p, wpr, (unsigned)blocks, st);
+}
+
+template <bool SWIGLU>
+int launch_planes(const LinearParams &p, int wpr, cudaStream_t st) {
+    if (p.n_planes == 1) return launch_nt<1, SWIGLU>(p, wpr, st);
+    if (p.n_planes == 2) return launch_nt<2, SWIGLU>(p, wpr, st);
+    return launch_nt<3, SWIGLU>(p, wpr, st);
 }
 
 inline bool aligned(const void *ptr, size_t a) { return (reinterpret_cast<uintptr_t>(ptr) % a) == 0; }
@@ -388,6 +420,8 @@ extern "C" int mortar_linear(const mortar_stream *w, const void *planes, int32_t
     p.out = out; p.out_mode = out_mode; p.n_out_planes = n_out_planes;
     p.out_plane_stride = out_plane_stride; p.ld_out = ld_out;
     p.round_bf16 = (flags & MORTAR_FLAG_ROUND_BF16) != 0;
+    p.accumulate = (flags & MORTAR_FLAG_ACCUMULATE) != 0;
+    if (p.accumulate && out_mode == MORTAR_OUT_PLANES) return MORTAR_ERR_UNSUPPORTED;
     p.gates = gates; p.ld_gates = ld_gates; p.cluster_size = cluster_size > 0 ? cluster_size : 1;
     // activity bitmaps over input columns are only worth building for small batches
     const bool small = rows <= 8 && w->tile_cols <= kMaxFlagCols;
@@ -401,7 +435,7 @@ extern "C" int mortar_linear(const mortar_stream *w, const void *planes, int32_t
     const double avg = (double)w->n_groups / (double)units;   // groups per unit
     const int wpr = avg >= 3.0 ? 4 : (avg >= 1.5 ? 2 : 1);
     cudaStream_t st = (cudaStream_t)stream;
-    return swiglu ? launch_nt<true>(p, wpr, st) : launch_nt<false>(p, wpr, st);
+    return swiglu ? launch_planes<true>(p, wpr, st) : launch_planes<false>(p, wpr, st);
 }
 
 extern "C" int mortar_route_flags(const float *gates, int64_t rows, int64_t ld_gates,
@@ -472,5 +506,5 @@ extern "C" int mortar_mlp_decode(const mortar_stream *gate_up, const mortar_stre
     if (rc != MORTAR_OK) return rc;
     return mortar_linear(down, hp, h_planes, rows * (int64_t)d_ff, d_ff, rows, y,
                          y_dtype == MORTAR_F32 ? MORTAR_OUT_F32 : MORTAR_OUT_BF16, 0, 0, ldy,
-                         rb | (gates ? MORTAR_FLAG_GATES_ON_INPUT : 0), gates, ld_gates, cs, nullptr, 0, nullptr, 0, stream);
+                         rb | (flags & MORTAR_FLAG_ACCUMULATE) | (gates ? MORTAR_FLAG_GATES_ON_INPUT : 0), gates, ld_gates, cs, nullptr, 0, nullptr, 0, stream);
 }

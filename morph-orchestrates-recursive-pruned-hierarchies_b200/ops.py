@@ -60,6 +60,8 @@ def act_prep(x: torch.Tensor, n_planes: int = 3, rms_weight: Optional[torch.Tens
     x2 = _rows2d(x, x.shape[-1], "x")
     rows, cols = x2.shape
     planes = torch.empty(n_planes, rows, cols, device=x.device, dtype=torch.bfloat16)
+    if rows == 0:
+        return planes
     w = None
     if rms_weight is not None:
         w = rms_weight.to(device=x.device, dtype=torch.float32).contiguous()
@@ -98,6 +100,8 @@ def linear_planes(w: StreamMatrix, planes: torch.Tensor, *, swiglu: bool = False
         mode = _lib.OUT_BF16
     else:
         raise ValueError(f"unsupported out_dtype {out_dtype}")
+    if rows == 0:
+        return out
     flags = (_lib.FLAG_SWIGLU if swiglu else 0) | (_lib.FLAG_ROUND_BF16 if round_bf16 else 0) \
         | (_lib.FLAG_GATES_ON_INPUT if gates_on_input else 0)
     if gates is not None:
@@ -157,11 +161,13 @@ def mlp_decode(x: torch.Tensor, gate_up: StreamMatrix, down: StreamMatrix, *,
                gates: Optional[torch.Tensor] = None, n_clusters: int = 0,
                n_planes: int = 3, round_bf16: bool = False,
                out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None,
+               accumulate: bool = False,
                workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One SwiGLU MLP application for a block of rows: [rmsnorm] -> gate_up -> silu(g)*u
     [*gates] -> down.  Mirrors StaticDecodeEngine._mlp_fn (morph/inference/engine.py:936-986)
     with ``n_planes=3`` (fp32 semantics) and ``_SwiGLUMortar.forward`` under autocast
-    (morph/model/transformer.py:402-431) with ``n_planes=1, round_bf16=True``."""
+    (morph/model/transformer.py:402-431) with ``n_planes=1, round_bf16=True``.  With
+    ``accumulate`` the result is added into ``out`` (the residual carrier)."""
     global _launches
     _require_cuda(x, "x")
     d_model, d_ff = gate_up.in_features, gate_up.out_features // 2
@@ -171,10 +177,14 @@ def mlp_decode(x: torch.Tensor, gate_up: StreamMatrix, down: StreamMatrix, *,
     if out_dtype is None:
         out_dtype = x2.dtype
     if out is None:
+        if accumulate:
+            raise ValueError("accumulate needs an `out` tensor to add into")
         out = torch.empty(rows, d_model, device=x.device, dtype=out_dtype)
     elif out.shape[-1] != d_model or out.numel() != rows * d_model or out.stride(-1) != 1:
         raise ValueError("out has the wrong shape")
     out2 = out.reshape(rows, d_model)
+    if rows == 0:
+        return out.reshape(*lead, d_model)
     L = _lib.lib()
     need = L.mortar_mlp_workspace_bytes(rows, d_model, d_ff, n_planes)
     if need < 0:
@@ -193,7 +203,8 @@ def mlp_decode(x: torch.Tensor, gate_up: StreamMatrix, down: StreamMatrix, *,
     _lib.check(L.mortar_mlp_decode(
         C.byref(gu), C.byref(dn), _ptr(x2), _dtype_code(x2), x2.stride(0), rows, _ptr(w), float(eps),
         _ptr(g), g.stride(0) if g is not None else 0, int(n_clusters), _ptr(out2), _dtype_code(out2),
-        out2.stride(0), int(n_planes), _lib.FLAG_ROUND_BF16 if round_bf16 else 0,
+        out2.stride(0), int(n_planes),
+        (_lib.FLAG_ROUND_BF16 if round_bf16 else 0) | (_lib.FLAG_ACCUMULATE if accumulate else 0),
         _ptr(workspace), workspace.numel(), _stream_ptr()), "mortar_mlp_decode")
     direct = x2.dtype == torch.bfloat16 and rms_weight is None and x2.stride(0) % 2 == 0 \
         and x2.data_ptr() % 4 == 0

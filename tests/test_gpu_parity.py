@@ -17,22 +17,19 @@ F32_TOL = 1e-5
 BF16_RTOL, BF16_ATOL = 1e-2, 1e-3
 
 
-def _ulp_diff_bf16(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
-    """distance in bf16 representable steps (monotone integer mapping of the bit pattern)"""
-    def key(t):
-        i = t.contiguous().view(torch.int16).to(torch.int32) & 0xFFFF
-        return torch.where(i >= 0x8000, 0x8000 - i, i)
-    return (key(a) - key(b)).abs()
-
-
 def _assert_bf16_close(y: torch.Tensor, ref: torch.Tensor):
-    """... and the internal gate: a handful of one-step flips where an fp32 sum lands on a
-    rounding boundary, nothing larger."""
-    y, ref = y.cpu().reshape(-1), ref.cpu().reshape(-1)
-    torch.testing.assert_close(y.float(), ref.float(), rtol=BF16_RTOL, atol=BF16_ATOL)
-    d = _ulp_diff_bf16(y, ref)
-    assert int(d.max()) <= 2, f"max bf16 step distance {int(d.max())}"
-    assert float((d > 0).float().mean()) < 0.02, f"{float((d > 0).float().mean()):.4f} of outputs differ"
+    """... and the internal gate: an output may differ from the oracle only where an fp32 sum
+    landed on a bf16 rounding boundary -- by at most two bf16 steps of its own magnitude, or
+    (for outputs that cancel to nearly zero) by 4e-3 of the output RMS, the size of one-step
+    flips of a few hidden activations -- and only a small fraction of outputs may differ."""
+    y, ref = y.cpu().reshape(-1).float(), ref.cpu().reshape(-1).float()
+    torch.testing.assert_close(y, ref, rtol=BF16_RTOL, atol=BF16_ATOL)
+    rms = float(ref.pow(2).mean().sqrt())
+    bound = torch.maximum(ref.abs() * 2.0 ** -7, torch.full_like(ref, 4e-3 * rms))
+    excess = ((y - ref).abs() - bound).max()
+    assert float(excess) <= 0, f"error exceeds two bf16 steps by {float(excess):.3e} (rms {rms:.3e})"
+    frac = float((y != ref).float().mean())
+    assert frac < 0.02, f"{frac:.4f} of outputs differ"
 
 
 def _oracle_meta(m):
