@@ -198,6 +198,66 @@ int mortar_mlp_decode(const mortar_stream *gate_up, const mortar_stream *down,
                       int32_t n_planes, int32_t flags,
                       void *workspace, int64_t workspace_bytes, void *stream);
 
+/* ---- prefill: tcgen05 / tensor-memory path --------------------------------------------
+ * Execution layout for blocks of 128 activation rows ("panel schedule"), built once on the
+ * host from the canonical format.  A panel is 16 tile rows that share tensor memory (for a
+ * gate_up matrix: 8 gate rows and the 8 matching up rows); a chunk is 4 tile columns (64
+ * features).  Inside a (panel, chunk) cell tiles are ordered by column then row; vertically
+ * adjacent tiles of one column form a run that a single MMA of N = 16*len covers.
+ *   tiles          uint8[64*n_tiles]    canonical tile codes in schedule order
+ *   runs           uint32[4*n_runs]     {A offset, B offset, accumulator column | accumulate<<31,
+ *                                        instruction descriptor} per run
+ *   cell_tile_ptr  int32[n_panels*n_chunks+1], cell_run_ptr likewise
+ *   panel_mask     uint32[n_panels]     bit l set iff local row l of the panel holds a tile
+ */
+typedef struct mortar_sched {
+    const void *tiles;             /* device, 16-byte aligned */
+    const void *runs;              /* device, 16-byte aligned */
+    const int32_t *cell_tile_ptr;  /* device */
+    const int32_t *cell_run_ptr;   /* device */
+    const uint32_t *panel_mask;    /* device */
+    int64_t n_tiles;
+    int64_t n_runs;
+    int32_t n_panels;
+    int32_t n_chunks;
+    int32_t tile_rows;
+    int32_t tile_cols;
+    int32_t swiglu;                /* 1: rows [0,R/2) gate, [R/2,R) up, output = silu(g)*u */
+    float scale;
+} mortar_sched;
+
+/* Sizes of the schedule of a matrix (host).  swiglu selects the gate/up row pairing. */
+int mortar_sched_sizes(const int32_t *row_ptr, const uint16_t *col_idx, int32_t tile_rows,
+                       int32_t tile_cols, int32_t swiglu, int64_t *n_tiles, int64_t *n_runs,
+                       int32_t *n_panels, int32_t *n_chunks);
+
+/* Fills host buffers sized by mortar_sched_sizes. */
+int mortar_build_sched(const int32_t *row_ptr, const uint16_t *col_idx, const uint8_t *codes,
+                       int32_t tile_rows, int32_t tile_cols, int64_t nnz, int32_t swiglu,
+                       uint8_t *tiles, uint32_t *runs, int32_t *cell_tile_ptr,
+                       int32_t *cell_run_ptr, uint32_t *panel_mask);
+
+/* out[rows, n] (bf16) = x[rows, in] (bf16) @ W^T with the reference's prefill arithmetic:
+ * bf16 operands, fp32 accumulation in tensor memory, the bf16-rounded scale applied to the
+ * sum and the result rounded to bf16 (triton_kernels.py:203-226); for a swiglu schedule
+ * additionally silu, the product and the optional cluster-gate multiply, each rounded to
+ * bf16 (transformer.py:402-431).  Replaces stk dds on token blocks (custom_ops.py:35-56).
+ * x and out: 16-byte aligned, row strides multiples of 8 elements. */
+int mortar_linear_tc(const mortar_sched *w, const void *x, int64_t ldx, int64_t rows,
+                     void *out, int64_t ld_out, const float *gates, int64_t ld_gates,
+                     int32_t cluster_size, void *stream);
+
+/* _SwiGLUMortar.forward on a block of tokens (transformer.py:402-431) as two launches of the
+ * kernel above.  workspace: device, 256-byte aligned, rows*d_ff*2 bytes (the hidden block). */
+int mortar_mlp_prefill(const mortar_sched *gate_up, const mortar_sched *down, const void *x,
+                       int64_t ldx, int64_t rows, const float *gates, int64_t ld_gates,
+                       int32_t n_clusters, void *y, int64_t ldy, void *workspace,
+                       int64_t workspace_bytes, void *stream);
+
+/* Reads (and optionally clears) the error word the prefill kernel sets when one of its
+ * bounded barrier waits expires: 0 = none, 1..4 = the waiting role.  Synchronises. */
+int mortar_prefill_error(int32_t *code, int32_t reset);
+
 #ifdef __cplusplus
 }
 #endif

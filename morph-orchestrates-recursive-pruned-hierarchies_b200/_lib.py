@@ -32,6 +32,15 @@ class Stream(C.Structure):
                 ("scale", C.c_float)]
 
 
+class Sched(C.Structure):
+    """mirror of `mortar_sched`"""
+    _fields_ = [("tiles", C.c_void_p), ("runs", C.c_void_p), ("cell_tile_ptr", C.c_void_p),
+                ("cell_run_ptr", C.c_void_p), ("panel_mask", C.c_void_p),
+                ("n_tiles", C.c_int64), ("n_runs", C.c_int64), ("n_panels", C.c_int32),
+                ("n_chunks", C.c_int32), ("tile_rows", C.c_int32), ("tile_cols", C.c_int32),
+                ("swiglu", C.c_int32), ("scale", C.c_float)]
+
+
 _lib = None
 
 _i32, _i64, _f32, _vp = C.c_int32, C.c_int64, C.c_float, C.c_void_p
@@ -54,6 +63,12 @@ _SIGNATURES = {
     "mortar_mlp_decode": (C.c_int, [C.POINTER(Stream), C.POINTER(Stream), _vp, C.c_int, _i64, _i64, _vp,
                                     _f32, _vp, _i64, _i32, _vp, C.c_int, _i64, _i32, _i32, _vp, _i64,
                                     _vp]),
+    "mortar_sched_sizes": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp]),
+    "mortar_build_sched": (C.c_int, [_vp, _vp, _vp, _i32, _i32, _i64, _i32, _vp, _vp, _vp, _vp, _vp]),
+    "mortar_linear_tc": (C.c_int, [C.POINTER(Sched), _vp, _i64, _i64, _vp, _i64, _vp, _i64, _i32, _vp]),
+    "mortar_mlp_prefill": (C.c_int, [C.POINTER(Sched), C.POINTER(Sched), _vp, _i64, _i64, _vp, _i64,
+                                     _i32, _vp, _i64, _vp, _i64, _vp]),
+    "mortar_prefill_error": (C.c_int, [_vp, _i32]),
 }
 
 # entry points added by later translation units; bound when present in the header list

@@ -6,6 +6,10 @@
 
 #define MORTAR_VERSION_STRING "mortar_b200 0.1 (sm_100a)"
 
+// Geometry of the prefill panel schedule (shared by the host builder and the kernel).
+#define MORTAR_PANEL_ROWS 16   // tile rows per panel = 256 fp32 accumulator columns of tensor memory
+#define MORTAR_CHUNK_COLS 4    // tile columns per chunk = 64 features = one 128-byte swizzle row
+
 // Records the text of a failed CUDA runtime call for mortar_last_cuda_error().
 void mortar_set_cuda_error(const char *what, const char *msg);
 

@@ -223,6 +223,10 @@ class MortarMatrix:
                    "mortar_build_stream")
         return grp_ptr, grp_cols, grp_codes, int(G)
 
+    def to_sched(self, swiglu: bool, device="cuda") -> "SchedMatrix":
+        """Prefill (tcgen05) execution layout; `swiglu` pairs gate rows with up rows."""
+        return SchedMatrix(self, swiglu, device)
+
     def to_stream(self, device="cuda") -> "StreamMatrix":
         grp_ptr, grp_cols, grp_codes, G = self.build_stream_host()
         return StreamMatrix(self.out_features, self.in_features, self.scale, G, self.nnz,
@@ -230,6 +234,63 @@ class MortarMatrix:
                             torch.from_numpy(grp_cols.view(np.int16)).to(device),
                             torch.from_numpy(grp_codes).to(device),
                             self.algorithmic_bytes())
+
+
+PANEL_ROWS, CHUNK_COLS = 16, 4
+
+
+def build_sched_host(m: "MortarMatrix", swiglu: bool):
+    """Host arrays of the prefill panel schedule of `m` (see ``mortar_sched`` in the header)."""
+    L = _lib.lib()
+    rp = np.ascontiguousarray(m.row_ptr)
+    ci = np.ascontiguousarray(m.col_idx)
+    cd = np.ascontiguousarray(m.codes)
+    nt, nr = C.c_int64(0), C.c_int64(0)
+    npan, nch = C.c_int32(0), C.c_int32(0)
+    _lib.check(L.mortar_sched_sizes(_ptr(rp), _ptr(ci), m.tile_rows, m.tile_cols, int(swiglu),
+                                    C.byref(nt), C.byref(nr), C.byref(npan), C.byref(nch)),
+               "mortar_sched_sizes")
+    cells = npan.value * nch.value
+    tiles = np.zeros((max(nt.value, 1), 64), dtype=np.uint8)
+    runs = np.zeros((max(nr.value, 1), 4), dtype=np.uint32)
+    ctp = np.zeros(cells + 1, dtype=np.int32)
+    crp = np.zeros(cells + 1, dtype=np.int32)
+    mask = np.zeros(npan.value, dtype=np.uint32)
+    _lib.check(L.mortar_build_sched(_ptr(rp), _ptr(ci), _ptr(cd), m.tile_rows, m.tile_cols, m.nnz,
+                                    int(swiglu), _ptr(tiles), _ptr(runs), _ptr(ctp), _ptr(crp),
+                                    _ptr(mask)), "mortar_build_sched")
+    return dict(tiles=tiles, runs=runs, cell_tile_ptr=ctp, cell_run_ptr=crp, panel_mask=mask,
+                n_tiles=nt.value, n_runs=nr.value, n_panels=npan.value, n_chunks=nch.value)
+
+
+class SchedMatrix:
+    """Device-resident prefill schedule of one matrix (owns its tensors)."""
+
+    def __init__(self, m: "MortarMatrix", swiglu: bool, device="cuda"):
+        h = build_sched_host(m, swiglu)
+        self.out_features, self.in_features = m.out_features, m.in_features
+        self.swiglu, self.scale, self.nnz = bool(swiglu), float(m.scale), m.nnz
+        self.n_tiles, self.n_runs = h["n_tiles"], h["n_runs"]
+        self.n_panels, self.n_chunks = h["n_panels"], h["n_chunks"]
+        self.tiles = torch.from_numpy(h["tiles"]).to(device)
+        self.runs = torch.from_numpy(h["runs"].view(np.int32)).to(device)
+        self.cell_tile_ptr = torch.from_numpy(h["cell_tile_ptr"]).to(device)
+        self.cell_run_ptr = torch.from_numpy(h["cell_run_ptr"]).to(device)
+        self.panel_mask = torch.from_numpy(h["panel_mask"].view(np.int32)).to(device)
+        self._c = None
+
+    @property
+    def n_out(self) -> int:
+        return self.out_features // 2 if self.swiglu else self.out_features
+
+    def c_struct(self) -> _lib.Sched:
+        if self._c is None:
+            self._c = _lib.Sched(self.tiles.data_ptr(), self.runs.data_ptr(),
+                                 self.cell_tile_ptr.data_ptr(), self.cell_run_ptr.data_ptr(),
+                                 self.panel_mask.data_ptr(), self.n_tiles, self.n_runs, self.n_panels,
+                                 self.n_chunks, self.out_features // TILE, self.in_features // TILE,
+                                 int(self.swiglu), self.scale)
+        return self._c
 
 
 def unpack_stream_host(grp_ptr, grp_cols, grp_codes, row_ptr, tile_rows):

@@ -11,7 +11,7 @@ from typing import Optional
 import torch
 
 from . import _lib
-from .format import TILE, MortarMatrix, StreamMatrix
+from .format import TILE, MortarMatrix, SchedMatrix, StreamMatrix
 
 _launches = 0      # kernels launched by this module (bench.py reports it)
 
@@ -221,6 +221,81 @@ def mlp_prefill(x: torch.Tensor, gate_up: StreamMatrix, down: StreamMatrix, *,
     xb = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
     return mlp_decode(xb, gate_up, down, gates=gates, n_clusters=n_clusters, n_planes=1,
                       round_bf16=True, out_dtype=torch.bfloat16, out=out)
+
+
+def linear_tc(x: torch.Tensor, w: SchedMatrix, *, gates: Optional[torch.Tensor] = None,
+              cluster_size: int = 0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Tensor-memory (tcgen05) block-sparse linear for token blocks: bf16 x[rows, in] ->
+    bf16 [rows, out] (or [rows, out/2] = silu(gate)*up for a swiglu schedule), with the
+    reference's prefill rounding (stk dds, triton_kernels.py:203-226)."""
+    global _launches
+    _require_cuda(x, "x")
+    if x.dtype != torch.bfloat16:
+        raise ValueError("linear_tc takes bfloat16 activations")
+    lead = x.shape[:-1]
+    x2 = _rows2d(x, w.in_features, "x")
+    rows = x2.shape[0]
+    if x2.stride(0) % 8 or x2.data_ptr() % 16:
+        x2 = x2.contiguous()
+    n_out = w.n_out
+    if out is None:
+        out = torch.empty(rows, n_out, device=x.device, dtype=torch.bfloat16)
+    out2 = out.reshape(rows, n_out)
+    if rows == 0:
+        return out.reshape(*lead, n_out)
+    g = None
+    if gates is not None:
+        g = gates.to(device=x.device, dtype=torch.float32).reshape(rows, -1).contiguous()
+    st = w.c_struct()
+    _lib.check(_lib.lib().mortar_linear_tc(C.byref(st), _ptr(x2), x2.stride(0), rows, _ptr(out2),
+                                           out2.stride(0), _ptr(g), g.stride(0) if g is not None else 0,
+                                           int(cluster_size), _stream_ptr()), "mortar_linear_tc")
+    _launches += 1
+    return out.reshape(*lead, n_out)
+
+
+def mlp_prefill_tc(x: torch.Tensor, gate_up: SchedMatrix, down: SchedMatrix, *,
+                   gates: Optional[torch.Tensor] = None, n_clusters: int = 0,
+                   out: Optional[torch.Tensor] = None,
+                   workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``_SwiGLUMortar.forward`` on a token block through the tcgen05 kernels: bf16 in, bf16
+    out, the reference's autocast rounding points (transformer.py:402-431)."""
+    global _launches
+    _require_cuda(x, "x")
+    xb = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
+    d_model, d_ff = gate_up.in_features, gate_up.out_features // 2
+    lead = xb.shape[:-1]
+    x2 = _rows2d(xb, d_model, "x")
+    rows = x2.shape[0]
+    if x2.stride(0) % 8 or x2.data_ptr() % 16:
+        x2 = x2.contiguous()
+    if out is None:
+        out = torch.empty(rows, d_model, device=x.device, dtype=torch.bfloat16)
+    out2 = out.reshape(rows, d_model)
+    if rows == 0:
+        return out.reshape(*lead, d_model)
+    need = rows * d_ff * 2
+    if workspace is None:
+        workspace = _workspace(x.device, need)
+    g = None
+    if gates is not None:
+        g = gates.to(device=x.device, dtype=torch.float32).reshape(rows, -1).contiguous()
+        if g.shape[1] != n_clusters:
+            raise ValueError(f"gates have {g.shape[1]} clusters, n_clusters={n_clusters}")
+    gu, dn = gate_up.c_struct(), down.c_struct()
+    _lib.check(_lib.lib().mortar_mlp_prefill(
+        C.byref(gu), C.byref(dn), _ptr(x2), x2.stride(0), rows, _ptr(g),
+        g.stride(0) if g is not None else 0, int(n_clusters), _ptr(out2), out2.stride(0),
+        _ptr(workspace), workspace.numel(), _stream_ptr()), "mortar_mlp_prefill")
+    _launches += 2
+    return out.reshape(*lead, d_model)
+
+
+def prefill_error(reset: bool = True) -> int:
+    """Error word of the tcgen05 kernel (0 = none; synchronises the device)."""
+    code = C.c_int32(0)
+    _lib.check(_lib.lib().mortar_prefill_error(C.byref(code), int(reset)), "mortar_prefill_error")
+    return code.value
 
 
 def route_flags(gates: torch.Tensor, rlo: torch.Tensor, rhi: torch.Tensor, clo: torch.Tensor,

@@ -198,3 +198,56 @@ def test_synth_generators_shapes_and_densities():
     # oracle's gate rule agrees
     lg = torch.randn(4, 16)
     np.testing.assert_array_equal(mb.synth.remoe_gates(lg, 4).numpy(), orc.remoe_gates(lg, 4).numpy())
+
+
+@pytest.mark.parametrize("swiglu", [False, True])
+def test_prefill_schedule_covers_every_tile_once(swiglu):
+    """Rebuild the dense code matrix from the panel schedule: every kept tile appears exactly
+    once, at the accumulator column and activation offset its run record names; the first
+    MMA into an accumulator row overwrites, later ones accumulate; runs are vertical."""
+    rng = np.random.default_rng(3)
+    R, C = (40, 23) if not swiglu else (48, 23)
+    mask = rng.random((R, C)) < 0.35
+    mask[5] = False
+    mask[6] = True
+    codes = rng.integers(-1, 2, size=(R * 16, C * 16)).astype(np.int8)
+    m = mb.MortarMatrix.from_codes(codes, mask, 1.0)
+    h = fmt.build_sched_host(m, swiglu)
+    P, CC = fmt.PANEL_ROWS, fmt.CHUNK_COLS
+    units = R // 2 if swiglu else R
+    per_panel = P // 2 if swiglu else P
+    assert h["n_panels"] == -(-units // per_panel) and h["n_chunks"] == -(-C // CC)
+    assert h["n_tiles"] == m.nnz
+    dense = np.zeros_like(codes)
+    seen = np.zeros((R, C), dtype=int)
+    tiles = fmt.unpack_codes_2bit(h["tiles"]).reshape(-1, 16, 16)
+    for p in range(h["n_panels"]):
+        touched = 0
+        for ch in range(h["n_chunks"]):
+            cell = p * h["n_chunks"] + ch
+            t0 = h["cell_tile_ptr"][cell]
+            for r in range(h["cell_run_ptr"][cell], h["cell_run_ptr"][cell + 1]):
+                a_off, b_off, d, idesc = (int(v) for v in h["runs"][r])
+                n = ((idesc >> 17) & 0x3F) << 3
+                assert (idesc >> 24) & 0x1F == 8 and n % 16 == 0 and 16 <= n <= 256
+                cl, first, l0, acc = a_off // 2, b_off // 32, (d & 0xFFFF) // 16, d >> 31
+                for k in range(n // 16):
+                    l = l0 + k
+                    assert ((touched >> l) & 1) == acc
+                    if swiglu:
+                        half = P // 2
+                        trow = p * half + l if l < half else R // 2 + p * half + (l - half)
+                    else:
+                        trow = p * P + l
+                    col = ch * CC + cl
+                    dense[trow * 16:(trow + 1) * 16, col * 16:(col + 1) * 16] = tiles[t0 + first + k]
+                    seen[trow, col] += 1
+                for k in range(n // 16):
+                    touched |= 1 << (l0 + k)
+        assert touched == int(h["panel_mask"][p])
+    np.testing.assert_array_equal(seen, mask.astype(int))
+    np.testing.assert_array_equal(dense, m.to_dense_codes())
+    # a fully dense matrix fuses each column of a panel into a single N=256 run
+    md = mb.MortarMatrix.from_codes(codes[:32 * 16] if not swiglu else codes[:32 * 16], None, 1.0)
+    hd = fmt.build_sched_host(md, swiglu)
+    assert hd["n_runs"] == hd["n_panels"] * C
