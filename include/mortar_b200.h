@@ -202,40 +202,48 @@ int mortar_mlp_decode(const mortar_stream *gate_up, const mortar_stream *down,
  * Execution layout for blocks of 128 activation rows ("panel schedule"), built once on the
  * host from the canonical format.  A panel is 16 tile rows that share tensor memory (for a
  * gate_up matrix: 8 gate rows and the 8 matching up rows); a chunk is 4 tile columns (64
- * features).  Inside a (panel, chunk) cell tiles are ordered by column then row; vertically
- * adjacent tiles of one column form a run that a single MMA of N = 16*len covers.
- *   tiles          uint8[64*n_tiles]    canonical tile codes in schedule order
- *   runs           uint32[4*n_runs]     {A offset, B offset, accumulator column | accumulate<<31,
- *                                        instruction descriptor} per run
- *   cell_tile_ptr  int32[n_panels*n_chunks+1], cell_run_ptr likewise
- *   panel_mask     uint32[n_panels]     bit l set iff local row l of the panel holds a tile
+ * features).  The kept tiles of a (panel, chunk) cell are ordered by column then row;
+ * vertically adjacent tiles of one column form a run that a single MMA of N = 16*len covers.
+ * A step is the part of a cell that fits one stage of the kernel (at most 48 tiles); empty
+ * cells produce no step.
+ *   tiles           uint8[64*n_tiles]  canonical tile codes in schedule order
+ *   runs            uint32[4*n_runs]   {A offset, B offset, accumulator column | accumulate<<31,
+ *                                       instruction descriptor} per run
+ *   panel_step_ptr  int32[n_panels+1]  steps of every panel
+ *   step_tile_ptr   int32[n_steps+1], step_run_ptr int32[n_steps+1]
+ *   step_chunk      uint32[n_steps]    chunk index | reuses-previous-chunk<<30 | last-on-chunk<<31
+ *   panel_mask      uint32[n_panels]   bit l set iff local row l of the panel holds a tile
  */
 typedef struct mortar_sched {
-    const void *tiles;             /* device, 16-byte aligned */
-    const void *runs;              /* device, 16-byte aligned */
-    const int32_t *cell_tile_ptr;  /* device */
-    const int32_t *cell_run_ptr;   /* device */
-    const uint32_t *panel_mask;    /* device */
+    const void *tiles;              /* device, 16-byte aligned */
+    const void *runs;               /* device, 16-byte aligned */
+    const int32_t *panel_step_ptr;  /* device */
+    const int32_t *step_tile_ptr;   /* device */
+    const int32_t *step_run_ptr;    /* device */
+    const uint32_t *step_chunk;     /* device */
+    const uint32_t *panel_mask;     /* device */
     int64_t n_tiles;
     int64_t n_runs;
+    int64_t n_steps;
     int32_t n_panels;
-    int32_t n_chunks;
+    int32_t max_panel_steps;        /* largest step count of any panel (kernel limit: 512) */
     int32_t tile_rows;
     int32_t tile_cols;
-    int32_t swiglu;                /* 1: rows [0,R/2) gate, [R/2,R) up, output = silu(g)*u */
+    int32_t swiglu;                 /* 1: rows [0,R/2) gate, [R/2,R) up, output = silu(g)*u */
     float scale;
 } mortar_sched;
 
 /* Sizes of the schedule of a matrix (host).  swiglu selects the gate/up row pairing. */
 int mortar_sched_sizes(const int32_t *row_ptr, const uint16_t *col_idx, int32_t tile_rows,
                        int32_t tile_cols, int32_t swiglu, int64_t *n_tiles, int64_t *n_runs,
-                       int32_t *n_panels, int32_t *n_chunks);
+                       int64_t *n_steps, int32_t *n_panels);
 
 /* Fills host buffers sized by mortar_sched_sizes. */
 int mortar_build_sched(const int32_t *row_ptr, const uint16_t *col_idx, const uint8_t *codes,
                        int32_t tile_rows, int32_t tile_cols, int64_t nnz, int32_t swiglu,
-                       uint8_t *tiles, uint32_t *runs, int32_t *cell_tile_ptr,
-                       int32_t *cell_run_ptr, uint32_t *panel_mask);
+                       uint8_t *tiles, uint32_t *runs, int32_t *panel_step_ptr,
+                       int32_t *step_tile_ptr, int32_t *step_run_ptr, uint32_t *step_chunk,
+                       uint32_t *panel_mask);
 
 /* out[rows, n] (bf16) = x[rows, in] (bf16) @ W^T with the reference's prefill arithmetic:
  * bf16 operands, fp32 accumulation in tensor memory, the bf16-rounded scale applied to the

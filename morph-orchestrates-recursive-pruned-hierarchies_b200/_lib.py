@@ -34,11 +34,12 @@ class Stream(C.Structure):
 
 class Sched(C.Structure):
     """mirror of `mortar_sched`"""
-    _fields_ = [("tiles", C.c_void_p), ("runs", C.c_void_p), ("cell_tile_ptr", C.c_void_p),
-                ("cell_run_ptr", C.c_void_p), ("panel_mask", C.c_void_p),
-                ("n_tiles", C.c_int64), ("n_runs", C.c_int64), ("n_panels", C.c_int32),
-                ("n_chunks", C.c_int32), ("tile_rows", C.c_int32), ("tile_cols", C.c_int32),
-                ("swiglu", C.c_int32), ("scale", C.c_float)]
+    _fields_ = [("tiles", C.c_void_p), ("runs", C.c_void_p), ("panel_step_ptr", C.c_void_p),
+                ("step_tile_ptr", C.c_void_p), ("step_run_ptr", C.c_void_p),
+                ("step_chunk", C.c_void_p), ("panel_mask", C.c_void_p),
+                ("n_tiles", C.c_int64), ("n_runs", C.c_int64), ("n_steps", C.c_int64),
+                ("n_panels", C.c_int32), ("max_panel_steps", C.c_int32), ("tile_rows", C.c_int32),
+                ("tile_cols", C.c_int32), ("swiglu", C.c_int32), ("scale", C.c_float)]
 
 
 _lib = None
@@ -64,7 +65,8 @@ _SIGNATURES = {
                                     _f32, _vp, _i64, _i32, _vp, C.c_int, _i64, _i32, _i32, _vp, _i64,
                                     _vp]),
     "mortar_sched_sizes": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp]),
-    "mortar_build_sched": (C.c_int, [_vp, _vp, _vp, _i32, _i32, _i64, _i32, _vp, _vp, _vp, _vp, _vp]),
+    "mortar_build_sched": (C.c_int, [_vp, _vp, _vp, _i32, _i32, _i64, _i32, _vp, _vp, _vp, _vp, _vp, _vp,
+                                     _vp]),
     "mortar_linear_tc": (C.c_int, [C.POINTER(Sched), _vp, _i64, _i64, _vp, _i64, _vp, _i64, _i32, _vp]),
     "mortar_mlp_prefill": (C.c_int, [C.POINTER(Sched), C.POINTER(Sched), _vp, _i64, _i64, _vp, _i64,
                                      _i32, _vp, _i64, _vp, _i64, _vp]),

@@ -2,11 +2,14 @@
 // the 5th-generation tensor cores (tcgen05.mma, accumulators in tensor memory).
 //
 // One CTA owns 128 rows of the activation matrix and one panel of 16 weight tile rows, whose
-// 256 fp32 accumulator columns live in tensor memory.  It walks the panel's non-empty chunks
-// (64 input features each) through a 2-stage shared-memory ring:
-//   warp 1        issues the TMA load of the [128 x 64] bf16 activation chunk (128-byte swizzle)
-//   warps 2..5    expand the chunk's 2-bit tile codes into bf16 B tiles (K-major, no swizzle),
-//                 stage the chunk's MMA run records, and later run the epilogue
+// 256 fp32 accumulator columns live in tensor memory.  It walks the panel's schedule steps
+// (each: one 64-feature activation chunk and up to 48 weight tiles) through two rings:
+//   warp 1        issues the TMA loads of the [128 x 64] bf16 activation chunks (128-byte
+//                 swizzle) into a 3-stage ring, ahead of their use
+//   warps 2..5    expand each step's 2-bit tile codes into bf16 B tiles (K-major, no swizzle)
+//                 in a 2-stage ring, stage the step's MMA run records, and later run the
+//                 epilogue; code words of the next step are fetched before the current one
+//                 is expanded
 //   warp 0        issues one tcgen05.mma per run (M=128, N=16*len, K=16) and commits
 // The epilogue reads the accumulators with tcgen05.ld, applies the per-matrix scale, the
 // reference's bf16 rounding points, SwiGLU and the cluster gates, and stores bf16 rows.
@@ -22,28 +25,31 @@ namespace {
 
 constexpr int kPanelRows = MORTAR_PANEL_ROWS;
 constexpr int kChunkCols = MORTAR_CHUNK_COLS;
-constexpr int kStages = 2;
+constexpr int kAStages = 3;                                  // activation-chunk ring
+constexpr int kBStages = 2;                                  // expanded-tile ring
 constexpr int kRows = 128;                                   // activation rows per CTA (MMA M)
 constexpr int kAStage = kRows * 128;                         // 16 KB
-constexpr int kMaxTiles = kPanelRows * kChunkCols;           // 64 tiles per (panel, chunk)
-constexpr int kBStage = kMaxTiles * 512;                     // 32 KB
-constexpr int kRunStage = kMaxTiles * 16;                    // 1 KB
+constexpr int kStepTiles = MORTAR_STEP_TILES;                // tiles per step
+constexpr int kBStage = kStepTiles * 512;                    // 24 KB
+constexpr int kRunStage = kStepTiles * 16;                   // run records of one step
 constexpr int kTmemCols = kPanelRows * 16;                   // 256
 constexpr int kThreads = 192;
 constexpr int kDecodeThreads = 128;
-constexpr int kSmemBytes = kStages * (kAStage + kBStage + kRunStage) + 1024 /*align*/ + 128 /*barriers*/;
+constexpr int kWordsPerThread = kStepTiles * 16 / kDecodeThreads;   // code words a decoder expands per step
+constexpr int kSmemBytes = kAStages * kAStage + kBStages * (kBStage + kRunStage) + 1024 /*align*/ + 128 /*barriers*/;
 constexpr uint32_t kWaitLimit = 1u << 22;
-constexpr int kMaxChunks = 1024;                             // in_features <= 65536
+constexpr int kMaxSteps = 512;                               // steps of one panel held in shared memory
 
 __device__ int g_prefill_error;   // first error recorded by any CTA (0 = none)
 
 struct PrefillParams {
     const uint32_t *tiles;        // [n_tiles][16] words of canonical 2-bit codes
     const uint4 *runs;            // [n_runs]
-    const int *cell_tile_ptr;     // [n_panels*n_chunks + 1]
-    const int *cell_run_ptr;
+    const int *panel_step_ptr;    // [n_panels + 1]
+    const int *step_tile_ptr;     // [n_steps + 1]
+    const int *step_run_ptr;      // [n_steps + 1]
+    const uint32_t *step_chunk;   // [n_steps] chunk | reuse<<30 | last<<31
     const uint32_t *panel_mask;   // [n_panels] rows that received at least one tile
-    int n_chunks;
     int swiglu;
     int total_units;              // output tile rows (LINEAR) or hidden tile rows (SWIGLU)
     long long rows;
@@ -140,30 +146,40 @@ __global__ void __launch_bounds__(kThreads, 2)
 prefill_panel_kernel(const __grid_constant__ CUtensorMap tmap_x, const PrefillParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t *sA = smem;                                   // kStages x 16 KB, 1024-byte aligned
-    uint8_t *sB = sA + kStages * kAStage;                 // kStages x 32 KB
-    uint4 *sRuns = reinterpret_cast<uint4 *>(sB + kStages * kBStage);   // kStages x 64 records
-    uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(sRuns) + kStages * kRunStage);
-    // bars[0..1] full, bars[2..3] empty, bars[4] accumulators ready
+    uint8_t *sA = smem;                                   // kAStages x 16 KB, 1024-byte aligned
+    uint8_t *sB = sA + kAStages * kAStage;                // kBStages x 24 KB
+    uint4 *sRuns = reinterpret_cast<uint4 *>(sB + kBStages * kBStage);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(sRuns) + kBStages * kRunStage);
+    uint64_t *a_full = bars, *a_empty = bars + kAStages;
+    uint64_t *b_full = bars + 2 * kAStages, *b_empty = b_full + kBStages;
+    uint64_t *acc_full = b_empty + kBStages;
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
-    __shared__ int tptr[kMaxChunks + 1], rptr[kMaxChunks + 1];   // this panel's cell pointers
+    __shared__ int s_tile[kMaxSteps + 1], s_run[kMaxSteps + 1];   // this panel's step pointers
+    __shared__ uint32_t s_chunk[kMaxSteps];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int panel = blockIdx.x;
     const long long row0 = (long long)blockIdx.y * kRows;
-    for (int i = threadIdx.x; i <= p.n_chunks; i += kThreads) {
-        tptr[i] = p.cell_tile_ptr[(long long)panel * p.n_chunks + i];
-        rptr[i] = p.cell_run_ptr[(long long)panel * p.n_chunks + i];
+    const int step0 = p.panel_step_ptr[panel];
+    const int n_steps = p.panel_step_ptr[panel + 1] - step0;
+    for (int i = threadIdx.x; i <= n_steps; i += kThreads) {
+        s_tile[i] = p.step_tile_ptr[step0 + i];
+        s_run[i] = p.step_run_ptr[step0 + i];
+        if (i < n_steps) s_chunk[i] = p.step_chunk[step0 + i];
     }
 
     if (threadIdx.x == 0) {
         abort_s = 0;
-        for (int s = 0; s < kStages; ++s) {
-            mbar_init(smem_u32(&bars[s]), kDecodeThreads + 1);
-            mbar_init(smem_u32(&bars[kStages + s]), 1);
+        for (int s = 0; s < kAStages; ++s) {
+            mbar_init(smem_u32(&a_full[s]), 1);
+            mbar_init(smem_u32(&a_empty[s]), 1);
         }
-        mbar_init(smem_u32(&bars[2 * kStages]), 1);
+        for (int s = 0; s < kBStages; ++s) {
+            mbar_init(smem_u32(&b_full[s]), kDecodeThreads);
+            mbar_init(smem_u32(&b_empty[s]), 1);
+        }
+        mbar_init(smem_u32(acc_full), 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == 0) {
@@ -179,84 +195,102 @@ prefill_panel_kernel(const __grid_constant__ CUtensorMap tmap_x, const PrefillPa
 
     if (warp == 0) {
         // ---------------- MMA issue ----------------
-        int it = 0;
+        int a_it = -1;                                     // activation chunks consumed so far - 1
         bool ok = true;
-        for (int c = 0; c < p.n_chunks && ok; ++c) {
-            const int r0 = rptr[c], r1 = rptr[c + 1];
-            if (r1 == r0) continue;
-            const int s = it % kStages;
-            const uint32_t ph = (it / kStages) & 1;
-            ok = mbar_wait(smem_u32(&bars[s]), ph, abort_flag, 1);
+        for (int i = 0; i < n_steps && ok; ++i) {
+            const uint32_t ck = s_chunk[i];
+            const int bs = i % kBStages;
+            if (!(ck & 0x40000000u)) {                     // this step starts a new activation chunk
+                ++a_it;
+                ok = mbar_wait(smem_u32(&a_full[a_it % kAStages]), (a_it / kAStages) & 1, abort_flag, 1);
+                if (!ok) break;
+            }
+            ok = mbar_wait(smem_u32(&b_full[bs]), (i / kBStages) & 1, abort_flag, 5);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             if (lane == 0) {
-                const uint64_t a0 = make_smem_desc(smem_u32(sA + s * kAStage), 16, 1024, 2);
-                const uint64_t b0 = make_smem_desc(smem_u32(sB + s * kBStage), 128, 256, 0);
-                const uint4 *rr = sRuns + s * kMaxTiles;
-                for (int r = 0; r < r1 - r0; ++r) {
+                const int as = a_it % kAStages;
+                const uint64_t a0 = make_smem_desc(smem_u32(sA + as * kAStage), 16, 1024, 2);
+                const uint64_t b0 = make_smem_desc(smem_u32(sB + bs * kBStage), 128, 256, 0);
+                const uint4 *rr = sRuns + bs * kStepTiles;
+                const int nrun = s_run[i + 1] - s_run[i];
+                for (int r = 0; r < nrun; ++r) {
                     const uint4 q = rr[r];
                     tc_mma(tmem + (q.z & 0xffffu), a0 + q.x, b0 + q.y, q.w, q.z >> 31);
                 }
-                tc_commit(smem_u32(&bars[kStages + s]));      // stage reusable once these MMAs retire
+                tc_commit(smem_u32(&b_empty[bs]));         // B stage reusable once these MMAs retire
+                if (ck & 0x80000000u) tc_commit(smem_u32(&a_empty[as]));   // last step on this chunk
             }
             __syncwarp();
-            ++it;
         }
         if (lane == 0) {
-            if (ok && it > 0) tc_commit(smem_u32(&bars[2 * kStages]));
-            else mbar_arrive(smem_u32(&bars[2 * kStages]));
+            if (ok && n_steps > 0) tc_commit(smem_u32(acc_full));
+            else mbar_arrive(smem_u32(acc_full));
         }
     } else if (warp == 1) {
         // ---------------- TMA producer ----------------
-        int it = 0;
-        for (int c = 0; c < p.n_chunks; ++c) {
-            if (rptr[c + 1] == rptr[c]) continue;
-            const int s = it % kStages;
-            const uint32_t ph = (it / kStages) & 1;
-            if (!mbar_wait(smem_u32(&bars[kStages + s]), ph ^ 1u, abort_flag, 2)) break;
+        int a_it = 0;
+        for (int i = 0; i < n_steps; ++i) {
+            const uint32_t ck = s_chunk[i];
+            if (ck & 0x40000000u) continue;
+            const int as = a_it % kAStages;
+            if (!mbar_wait(smem_u32(&a_empty[as]), ((a_it / kAStages) & 1) ^ 1u, abort_flag, 2)) break;
             if (lane == 0) {
-                const uint32_t bar = smem_u32(&bars[s]);
+                const uint32_t bar = smem_u32(&a_full[as]);
                 mbar_arrive_expect_tx(bar, kAStage);
                 asm volatile(
                     "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
                     "[%0], [%1, {%2, %3}], [%4];\n"
-                    ::"r"(smem_u32(sA + s * kAStage)), "l"(&tmap_x), "r"(c * kChunkCols * 16),
-                      "r"((int)row0), "r"(bar) : "memory");
+                    ::"r"(smem_u32(sA + as * kAStage)), "l"(&tmap_x),
+                      "r"((int)(ck & 0xffffffu) * kChunkCols * 16), "r"((int)row0), "r"(bar) : "memory");
             }
             __syncwarp();
-            ++it;
+            ++a_it;
         }
     } else {
         // ---------------- tile decode ----------------
         const int td = threadIdx.x - 64;
-        int it = 0;
         bool ok = true;
-        for (int c = 0; c < p.n_chunks && ok; ++c) {
-            const int r0 = rptr[c], r1 = rptr[c + 1];
-            if (r1 == r0) continue;
-            const int t0 = tptr[c], t1 = tptr[c + 1];
-            const int s = it % kStages;
-            const uint32_t ph = (it / kStages) & 1;
-            ok = mbar_wait(smem_u32(&bars[kStages + s]), ph ^ 1u, abort_flag, 3);
+        uint32_t cur[kWordsPerThread], nxt[kWordsPerThread];
+        uint4 cur_run = make_uint4(0, 0, 0, 0), nxt_run = make_uint4(0, 0, 0, 0);
+        auto fetch = [&](int i, uint32_t (&w)[kWordsPerThread], uint4 &run) {
+            const int t0 = s_tile[i], items = (s_tile[i + 1] - t0) * 16;
+#pragma unroll
+            for (int k = 0; k < kWordsPerThread; ++k) {
+                const int item = td + k * kDecodeThreads;
+                w[k] = item < items ? __ldg(p.tiles + (long long)t0 * 16 + item) : 0u;
+            }
+            if (td < s_run[i + 1] - s_run[i]) run = __ldg(p.runs + s_run[i] + td);
+        };
+        if (n_steps > 0) fetch(0, cur, cur_run);
+        for (int i = 0; i < n_steps && ok; ++i) {
+            if (i + 1 < n_steps) fetch(i + 1, nxt, nxt_run);
+            const int bs = i % kBStages;
+            ok = mbar_wait(smem_u32(&b_empty[bs]), ((i / kBStages) & 1) ^ 1u, abort_flag, 3);
             if (!ok) break;
-            if (td < r1 - r0) sRuns[s * kMaxTiles + td] = __ldg(p.runs + r0 + td);
-            uint8_t *bdst = sB + s * kBStage;
-            const int items = (t1 - t0) * 16;                  // (tile, row) pairs
-            for (int item = td; item < items; item += kDecodeThreads) {
-                const int tile = item >> 4, row = item & 15;
-                const uint32_t w = __ldg(p.tiles + (long long)(t0 + tile) * 16 + row);
-                uint4 lo, hi;
-                expand_row(w, lo, hi);
-                uint8_t *d = bdst + tile * 512 + (row >> 3) * 256 + (row & 7) * 16;
-                *reinterpret_cast<uint4 *>(d) = lo;            // features 0..7 of the tile column
-                *reinterpret_cast<uint4 *>(d + 128) = hi;      // features 8..15
+            if (td < s_run[i + 1] - s_run[i]) sRuns[bs * kStepTiles + td] = cur_run;
+            uint8_t *bdst = sB + bs * kBStage;
+            const int items = (s_tile[i + 1] - s_tile[i]) * 16;        // (tile, row) pairs
+#pragma unroll
+            for (int k = 0; k < kWordsPerThread; ++k) {
+                const int item = td + k * kDecodeThreads;
+                if (item < items) {
+                    const int tile = item >> 4, row = item & 15;
+                    uint4 lo, hi;
+                    expand_row(cur[k], lo, hi);
+                    uint8_t *d = bdst + tile * 512 + (row >> 3) * 256 + (row & 7) * 16;
+                    *reinterpret_cast<uint4 *>(d) = lo;        // features 0..7 of the tile column
+                    *reinterpret_cast<uint4 *>(d + 128) = hi;  // features 8..15
+                }
             }
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-            mbar_arrive(smem_u32(&bars[s]));
-            ++it;
+            mbar_arrive(smem_u32(&b_full[bs]));
+#pragma unroll
+            for (int k = 0; k < kWordsPerThread; ++k) cur[k] = nxt[k];
+            cur_run = nxt_run;
         }
         // ---------------- epilogue ----------------
-        if (ok) ok = mbar_wait(smem_u32(&bars[2 * kStages]), 0, abort_flag, 4);
+        if (ok) ok = mbar_wait(smem_u32(acc_full), 0, abort_flag, 4);
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const int q = warp & 3;                            // tensor-memory lane quadrant of this warp
@@ -338,7 +372,9 @@ inline bool aligned_to(const void *ptr, size_t a) { return (reinterpret_cast<uin
 extern "C" int mortar_linear_tc(const mortar_sched *w, const void *x, int64_t ldx, int64_t rows,
                                 void *out, int64_t ld_out, const float *gates, int64_t ld_gates,
                                 int32_t cluster_size, void *stream) {
-    if (!w || !x || !out || !w->cell_tile_ptr || !w->cell_run_ptr || !w->panel_mask) return MORTAR_ERR_NULL;
+    if (!w || !x || !out || !w->panel_step_ptr || !w->step_tile_ptr || !w->step_run_ptr ||
+        !w->step_chunk || !w->panel_mask)
+        return MORTAR_ERR_NULL;
     if (w->n_tiles > 0 && (!w->tiles || !w->runs)) return MORTAR_ERR_NULL;
     if (w->tile_rows <= 0 || w->tile_cols <= 0 || rows < 0) return MORTAR_ERR_SHAPE;
     const int K = w->tile_cols * 16;
@@ -346,7 +382,7 @@ extern "C" int mortar_linear_tc(const mortar_sched *w, const void *x, int64_t ld
     if (ldx < K || ld_out < (int64_t)units * 16) return MORTAR_ERR_SHAPE;
     if (!aligned_to(x, 16) || (ldx % 8) || !aligned_to(out, 16) || (ld_out % 8)) return MORTAR_ERR_ALIGN;
     if (gates && (cluster_size <= 0 || !w->swiglu)) return MORTAR_ERR_SHAPE;
-    if (w->n_chunks > kMaxChunks) return MORTAR_ERR_CAPACITY;
+    if (w->max_panel_steps > kMaxSteps) return MORTAR_ERR_CAPACITY;
     if (rows == 0) return MORTAR_OK;
     const int64_t row_blocks = (rows + kRows - 1) / kRows;
     if (row_blocks > 65535) return MORTAR_ERR_CAPACITY;
@@ -376,10 +412,11 @@ extern "C" int mortar_linear_tc(const mortar_sched *w, const void *x, int64_t ld
     PrefillParams p;
     p.tiles = reinterpret_cast<const uint32_t *>(w->tiles);
     p.runs = reinterpret_cast<const uint4 *>(w->runs);
-    p.cell_tile_ptr = w->cell_tile_ptr;
-    p.cell_run_ptr = w->cell_run_ptr;
+    p.panel_step_ptr = w->panel_step_ptr;
+    p.step_tile_ptr = w->step_tile_ptr;
+    p.step_run_ptr = w->step_run_ptr;
+    p.step_chunk = w->step_chunk;
     p.panel_mask = w->panel_mask;
-    p.n_chunks = w->n_chunks;
     p.swiglu = w->swiglu;
     p.total_units = units;
     p.rows = rows;

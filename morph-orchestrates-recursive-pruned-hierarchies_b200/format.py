@@ -236,7 +236,7 @@ class MortarMatrix:
                             self.algorithmic_bytes())
 
 
-PANEL_ROWS, CHUNK_COLS = 16, 4
+PANEL_ROWS, CHUNK_COLS, STEP_TILES = 16, 4, 48
 
 
 def build_sched_host(m: "MortarMatrix", swiglu: bool):
@@ -245,22 +245,25 @@ def build_sched_host(m: "MortarMatrix", swiglu: bool):
     rp = np.ascontiguousarray(m.row_ptr)
     ci = np.ascontiguousarray(m.col_idx)
     cd = np.ascontiguousarray(m.codes)
-    nt, nr = C.c_int64(0), C.c_int64(0)
-    npan, nch = C.c_int32(0), C.c_int32(0)
+    nt, nr, ns = C.c_int64(0), C.c_int64(0), C.c_int64(0)
+    npan = C.c_int32(0)
     _lib.check(L.mortar_sched_sizes(_ptr(rp), _ptr(ci), m.tile_rows, m.tile_cols, int(swiglu),
-                                    C.byref(nt), C.byref(nr), C.byref(npan), C.byref(nch)),
+                                    C.byref(nt), C.byref(nr), C.byref(ns), C.byref(npan)),
                "mortar_sched_sizes")
-    cells = npan.value * nch.value
     tiles = np.zeros((max(nt.value, 1), 64), dtype=np.uint8)
     runs = np.zeros((max(nr.value, 1), 4), dtype=np.uint32)
-    ctp = np.zeros(cells + 1, dtype=np.int32)
-    crp = np.zeros(cells + 1, dtype=np.int32)
+    psp = np.zeros(npan.value + 1, dtype=np.int32)
+    stp = np.zeros(ns.value + 1, dtype=np.int32)
+    srp = np.zeros(ns.value + 1, dtype=np.int32)
+    sch = np.zeros(max(ns.value, 1), dtype=np.uint32)
     mask = np.zeros(npan.value, dtype=np.uint32)
     _lib.check(L.mortar_build_sched(_ptr(rp), _ptr(ci), _ptr(cd), m.tile_rows, m.tile_cols, m.nnz,
-                                    int(swiglu), _ptr(tiles), _ptr(runs), _ptr(ctp), _ptr(crp),
-                                    _ptr(mask)), "mortar_build_sched")
-    return dict(tiles=tiles, runs=runs, cell_tile_ptr=ctp, cell_run_ptr=crp, panel_mask=mask,
-                n_tiles=nt.value, n_runs=nr.value, n_panels=npan.value, n_chunks=nch.value)
+                                    int(swiglu), _ptr(tiles), _ptr(runs), _ptr(psp), _ptr(stp),
+                                    _ptr(srp), _ptr(sch), _ptr(mask)), "mortar_build_sched")
+    return dict(tiles=tiles, runs=runs, panel_step_ptr=psp, step_tile_ptr=stp, step_run_ptr=srp,
+                step_chunk=sch, panel_mask=mask, n_tiles=nt.value, n_runs=nr.value,
+                n_steps=ns.value, n_panels=npan.value,
+                max_panel_steps=int(np.diff(psp).max()) if npan.value else 0)
 
 
 class SchedMatrix:
@@ -270,13 +273,16 @@ class SchedMatrix:
         h = build_sched_host(m, swiglu)
         self.out_features, self.in_features = m.out_features, m.in_features
         self.swiglu, self.scale, self.nnz = bool(swiglu), float(m.scale), m.nnz
-        self.n_tiles, self.n_runs = h["n_tiles"], h["n_runs"]
-        self.n_panels, self.n_chunks = h["n_panels"], h["n_chunks"]
-        self.tiles = torch.from_numpy(h["tiles"]).to(device)
-        self.runs = torch.from_numpy(h["runs"].view(np.int32)).to(device)
-        self.cell_tile_ptr = torch.from_numpy(h["cell_tile_ptr"]).to(device)
-        self.cell_run_ptr = torch.from_numpy(h["cell_run_ptr"]).to(device)
-        self.panel_mask = torch.from_numpy(h["panel_mask"].view(np.int32)).to(device)
+        self.n_tiles, self.n_runs, self.n_steps = h["n_tiles"], h["n_runs"], h["n_steps"]
+        self.n_panels, self.max_panel_steps = h["n_panels"], h["max_panel_steps"]
+        t = lambda a: torch.from_numpy(a).to(device)
+        self.tiles = t(h["tiles"])
+        self.runs = t(h["runs"].view(np.int32))
+        self.panel_step_ptr = t(h["panel_step_ptr"])
+        self.step_tile_ptr = t(h["step_tile_ptr"])
+        self.step_run_ptr = t(h["step_run_ptr"])
+        self.step_chunk = t(h["step_chunk"].view(np.int32))
+        self.panel_mask = t(h["panel_mask"].view(np.int32))
         self._c = None
 
     @property
@@ -286,10 +292,11 @@ class SchedMatrix:
     def c_struct(self) -> _lib.Sched:
         if self._c is None:
             self._c = _lib.Sched(self.tiles.data_ptr(), self.runs.data_ptr(),
-                                 self.cell_tile_ptr.data_ptr(), self.cell_run_ptr.data_ptr(),
-                                 self.panel_mask.data_ptr(), self.n_tiles, self.n_runs, self.n_panels,
-                                 self.n_chunks, self.out_features // TILE, self.in_features // TILE,
-                                 int(self.swiglu), self.scale)
+                                 self.panel_step_ptr.data_ptr(), self.step_tile_ptr.data_ptr(),
+                                 self.step_run_ptr.data_ptr(), self.step_chunk.data_ptr(),
+                                 self.panel_mask.data_ptr(), self.n_tiles, self.n_runs, self.n_steps,
+                                 self.n_panels, self.max_panel_steps, self.out_features // TILE,
+                                 self.in_features // TILE, int(self.swiglu), self.scale)
         return self._c
 
 

@@ -201,36 +201,47 @@ def test_synth_generators_shapes_and_densities():
 
 
 @pytest.mark.parametrize("swiglu", [False, True])
-def test_prefill_schedule_covers_every_tile_once(swiglu):
+@pytest.mark.parametrize("density", [0.35, 1.0])
+def test_prefill_schedule_covers_every_tile_once(swiglu, density):
     """Rebuild the dense code matrix from the panel schedule: every kept tile appears exactly
     once, at the accumulator column and activation offset its run record names; the first
-    MMA into an accumulator row overwrites, later ones accumulate; runs are vertical."""
+    MMA into an accumulator row overwrites, later ones accumulate; runs are vertical; steps
+    hold at most 48 tiles and only the first step on a chunk fetches it."""
     rng = np.random.default_rng(3)
     R, C = (40, 23) if not swiglu else (48, 23)
-    mask = rng.random((R, C)) < 0.35
-    mask[5] = False
-    mask[6] = True
+    mask = rng.random((R, C)) < density
+    if density < 1.0:
+        mask[5] = False
+        mask[6] = True
     codes = rng.integers(-1, 2, size=(R * 16, C * 16)).astype(np.int8)
     m = mb.MortarMatrix.from_codes(codes, mask, 1.0)
     h = fmt.build_sched_host(m, swiglu)
     P, CC = fmt.PANEL_ROWS, fmt.CHUNK_COLS
     units = R // 2 if swiglu else R
     per_panel = P // 2 if swiglu else P
-    assert h["n_panels"] == -(-units // per_panel) and h["n_chunks"] == -(-C // CC)
+    assert h["n_panels"] == -(-units // per_panel)
     assert h["n_tiles"] == m.nnz
     dense = np.zeros_like(codes)
     seen = np.zeros((R, C), dtype=int)
     tiles = fmt.unpack_codes_2bit(h["tiles"]).reshape(-1, 16, 16)
     for p in range(h["n_panels"]):
         touched = 0
-        for ch in range(h["n_chunks"]):
-            cell = p * h["n_chunks"] + ch
-            t0 = h["cell_tile_ptr"][cell]
-            for r in range(h["cell_run_ptr"][cell], h["cell_run_ptr"][cell + 1]):
+        prev_chunk, prev_last = -1, True
+        for st in range(h["panel_step_ptr"][p], h["panel_step_ptr"][p + 1]):
+            ck = int(h["step_chunk"][st])
+            ch, reuse, last = ck & 0xFFFFFF, (ck >> 30) & 1, (ck >> 31) & 1
+            assert reuse == (0 if prev_last else 1)
+            assert ch == prev_chunk if reuse else ch > prev_chunk
+            prev_chunk, prev_last = ch, bool(last)
+            t0 = h["step_tile_ptr"][st]
+            n_in_step = h["step_tile_ptr"][st + 1] - t0
+            assert 0 < n_in_step <= fmt.STEP_TILES
+            for r in range(h["step_run_ptr"][st], h["step_run_ptr"][st + 1]):
                 a_off, b_off, d, idesc = (int(v) for v in h["runs"][r])
                 n = ((idesc >> 17) & 0x3F) << 3
                 assert (idesc >> 24) & 0x1F == 8 and n % 16 == 0 and 16 <= n <= 256
                 cl, first, l0, acc = a_off // 2, b_off // 32, (d & 0xFFFF) // 16, d >> 31
+                assert first + n // 16 <= n_in_step
                 for k in range(n // 16):
                     l = l0 + k
                     assert ((touched >> l) & 1) == acc
@@ -244,10 +255,10 @@ def test_prefill_schedule_covers_every_tile_once(swiglu):
                     seen[trow, col] += 1
                 for k in range(n // 16):
                     touched |= 1 << (l0 + k)
+        assert prev_last
         assert touched == int(h["panel_mask"][p])
     np.testing.assert_array_equal(seen, mask.astype(int))
     np.testing.assert_array_equal(dense, m.to_dense_codes())
-    # a fully dense matrix fuses each column of a panel into a single N=256 run
-    md = mb.MortarMatrix.from_codes(codes[:32 * 16] if not swiglu else codes[:32 * 16], None, 1.0)
-    hd = fmt.build_sched_host(md, swiglu)
-    assert hd["n_runs"] == hd["n_panels"] * C
+    if density == 1.0 and not swiglu:
+        # a full panel fuses each of its columns into a single N=256 run
+        assert int(((h["runs"][:, 3] >> 17) & 0x3F).max()) == 32
