@@ -103,12 +103,17 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo, 
            ((uint64_t)((sbo >> 4) & 0x3fffu) << 32) | (1ull << 46) | ((uint64_t)layout << 61);
 }
 
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                       uint32_t idesc, uint32_t accumulate) {
+// Descriptors are passed as (low, high) words: only the low word (start address) changes
+// between MMAs of a step, so the issuing lane does 32-bit adds only.
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                       uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
-        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+        "{\n.reg .pred p;\n.reg .b64 da, db;\n"
+        "setp.ne.b32 p, %6, 0;\n"
+        "mov.b64 da, {%1, %2};\n"
+        "mov.b64 db, {%3, %4};\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate));
 }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
@@ -212,11 +217,20 @@ prefill_panel_kernel(const __grid_constant__ CUtensorMap tmap_x, const PrefillPa
                 const int as = a_it % kAStages;
                 const uint64_t a0 = make_smem_desc(smem_u32(sA + as * kAStage), 16, 1024, 2);
                 const uint64_t b0 = make_smem_desc(smem_u32(sB + bs * kBStage), 128, 256, 0);
+                const uint32_t a_lo = (uint32_t)a0, a_hi = (uint32_t)(a0 >> 32);
+                const uint32_t b_lo = (uint32_t)b0, b_hi = (uint32_t)(b0 >> 32);
                 const uint4 *rr = sRuns + bs * kStepTiles;
                 const int nrun = s_run[i + 1] - s_run[i];
-                for (int r = 0; r < nrun; ++r) {
-                    const uint4 q = rr[r];
-                    tc_mma(tmem + (q.z & 0xffffu), a0 + q.x, b0 + q.y, q.w, q.z >> 31);
+                for (int r = 0; r < nrun; r += 4) {
+                    // fetch four run records, then issue: the loads do not wait behind the MMAs
+                    uint4 q[4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) q[k] = rr[min(r + k, nrun - 1)];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        if (r + k < nrun)
+                            tc_mma(tmem + (q[k].z & 0xffffu), a_lo + q[k].x, a_hi, b_lo + q[k].y, b_hi,
+                                   q[k].w, q[k].z >> 31);
                 }
                 tc_commit(smem_u32(&b_empty[bs]));         // B stage reusable once these MMAs retire
                 if (ck & 0x80000000u) tc_commit(smem_u32(&a_empty[as]));   // last step on this chunk
