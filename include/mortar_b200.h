@@ -204,29 +204,28 @@ int mortar_mlp_decode(const mortar_stream *gate_up, const mortar_stream *down,
  * gate_up matrix: 8 gate rows and the 8 matching up rows); a chunk is 4 tile columns (64
  * features).  The kept tiles of a (panel, chunk) cell are ordered by column then row;
  * vertically adjacent tiles of one column form a run that a single MMA of N = 16*len covers.
- * A step is the part of a cell that fits one stage of the kernel (at most 48 tiles); empty
- * cells produce no step.
- *   tiles           uint8[64*n_tiles]  canonical tile codes in schedule order
- *   runs            uint32[4*n_runs]   {A offset, B offset, accumulator column | accumulate<<31,
- *                                       instruction descriptor} per run
- *   panel_step_ptr  int32[n_panels+1]  steps of every panel
- *   step_tile_ptr   int32[n_steps+1], step_run_ptr int32[n_steps+1]
- *   step_chunk      uint32[n_steps]    chunk index | reuses-previous-chunk<<30 | last-on-chunk<<31
- *   panel_mask      uint32[n_panels]   bit l set iff local row l of the panel holds a tile
+ * A step is the part of a cell that fits one stage of the kernel (at most 32 tiles); empty
+ * cells produce no step.  Each step is one contiguous record, staged by one bulk copy:
+ *   [ n_tiles, n_runs, meta, 0 ][ n_runs x {A offset, B offset, accumulator column |
+ *     accumulate<<31, instruction descriptor} ][ n_tiles x 64 bytes of canonical tile codes ]
+ *   meta = chunk index | reuses-previous-chunk<<30 | last-on-chunk<<31
+ *   step_data       uint8[16*data_units]  the records
+ *   step_off        uint32[n_steps+1]     record offsets in 16-byte units
+ *   step_meta       uint32[n_steps]       copy of every record's meta word
+ *   panel_step_ptr  int32[n_panels+1]     steps of every panel
+ *   panel_mask      uint32[n_panels]      bit l set iff local row l of the panel holds a tile
  */
 typedef struct mortar_sched {
-    const void *tiles;              /* device, 16-byte aligned */
-    const void *runs;               /* device, 16-byte aligned */
+    const void *step_data;          /* device, 16-byte aligned */
+    const uint32_t *step_off;       /* device */
+    const uint32_t *step_meta;      /* device */
     const int32_t *panel_step_ptr;  /* device */
-    const int32_t *step_tile_ptr;   /* device */
-    const int32_t *step_run_ptr;    /* device */
-    const uint32_t *step_chunk;     /* device */
     const uint32_t *panel_mask;     /* device */
     int64_t n_tiles;
     int64_t n_runs;
     int64_t n_steps;
+    int64_t data_units;
     int32_t n_panels;
-    int32_t max_panel_steps;        /* largest step count of any panel (kernel limit: 512) */
     int32_t tile_rows;
     int32_t tile_cols;
     int32_t swiglu;                 /* 1: rows [0,R/2) gate, [R/2,R) up, output = silu(g)*u */
@@ -236,14 +235,13 @@ typedef struct mortar_sched {
 /* Sizes of the schedule of a matrix (host).  swiglu selects the gate/up row pairing. */
 int mortar_sched_sizes(const int32_t *row_ptr, const uint16_t *col_idx, int32_t tile_rows,
                        int32_t tile_cols, int32_t swiglu, int64_t *n_tiles, int64_t *n_runs,
-                       int64_t *n_steps, int32_t *n_panels);
+                       int64_t *n_steps, int32_t *n_panels, int64_t *data_units);
 
 /* Fills host buffers sized by mortar_sched_sizes. */
 int mortar_build_sched(const int32_t *row_ptr, const uint16_t *col_idx, const uint8_t *codes,
                        int32_t tile_rows, int32_t tile_cols, int64_t nnz, int32_t swiglu,
-                       uint8_t *tiles, uint32_t *runs, int32_t *panel_step_ptr,
-                       int32_t *step_tile_ptr, int32_t *step_run_ptr, uint32_t *step_chunk,
-                       uint32_t *panel_mask);
+                       uint8_t *step_data, uint32_t *step_off, uint32_t *step_meta,
+                       int32_t *panel_step_ptr, uint32_t *panel_mask);
 
 /* out[rows, n] (bf16) = x[rows, in] (bf16) @ W^T with the reference's prefill arithmetic:
  * bf16 operands, fp32 accumulation in tensor memory, the bf16-rounded scale applied to the

@@ -34,11 +34,10 @@ class Stream(C.Structure):
 
 class Sched(C.Structure):
     """mirror of `mortar_sched`"""
-    _fields_ = [("tiles", C.c_void_p), ("runs", C.c_void_p), ("panel_step_ptr", C.c_void_p),
-                ("step_tile_ptr", C.c_void_p), ("step_run_ptr", C.c_void_p),
-                ("step_chunk", C.c_void_p), ("panel_mask", C.c_void_p),
+    _fields_ = [("step_data", C.c_void_p), ("step_off", C.c_void_p), ("step_meta", C.c_void_p),
+                ("panel_step_ptr", C.c_void_p), ("panel_mask", C.c_void_p),
                 ("n_tiles", C.c_int64), ("n_runs", C.c_int64), ("n_steps", C.c_int64),
-                ("n_panels", C.c_int32), ("max_panel_steps", C.c_int32), ("tile_rows", C.c_int32),
+                ("data_units", C.c_int64), ("n_panels", C.c_int32), ("tile_rows", C.c_int32),
                 ("tile_cols", C.c_int32), ("swiglu", C.c_int32), ("scale", C.c_float)]
 
 
@@ -64,9 +63,8 @@ _SIGNATURES = {
     "mortar_mlp_decode": (C.c_int, [C.POINTER(Stream), C.POINTER(Stream), _vp, C.c_int, _i64, _i64, _vp,
                                     _f32, _vp, _i64, _i32, _vp, C.c_int, _i64, _i32, _i32, _vp, _i64,
                                     _vp]),
-    "mortar_sched_sizes": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp]),
-    "mortar_build_sched": (C.c_int, [_vp, _vp, _vp, _i32, _i32, _i64, _i32, _vp, _vp, _vp, _vp, _vp, _vp,
-                                     _vp]),
+    "mortar_sched_sizes": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp]),
+    "mortar_build_sched": (C.c_int, [_vp, _vp, _vp, _i32, _i32, _i64, _i32, _vp, _vp, _vp, _vp, _vp]),
     "mortar_linear_tc": (C.c_int, [C.POINTER(Sched), _vp, _i64, _i64, _vp, _i64, _vp, _i64, _i32, _vp]),
     "mortar_mlp_prefill": (C.c_int, [C.POINTER(Sched), C.POINTER(Sched), _vp, _i64, _i64, _vp, _i64,
                                      _i32, _vp, _i64, _vp, _i64, _vp]),

@@ -1,20 +1,24 @@
 // Prefill kernel: block-sparse ternary linear / SwiGLU over blocks of 128 activation rows on
 // the 5th-generation tensor cores (tcgen05.mma, accumulators in tensor memory).
 //
-// One CTA owns 128 rows of the activation matrix and one panel of 16 weight tile rows, whose
-// 256 fp32 accumulator columns live in tensor memory.  It walks the panel's schedule steps
-// (each: one 64-feature activation chunk and up to 48 weight tiles) through two rings:
-//   warp 1        issues the TMA loads of the [128 x 64] bf16 activation chunks (128-byte
-//                 swizzle) into a 3-stage ring, ahead of their use
-//   warps 2..5    expand each step's 2-bit tile codes into bf16 B tiles (K-major, no swizzle)
-//                 in a 2-stage ring, stage the step's MMA run records, and later run the
-//                 epilogue; code words of the next step are fetched before the current one
-//                 is expanded
-//   warp 0        issues one tcgen05.mma per run (M=128, N=16*len, K=16) and commits
-// The epilogue reads the accumulators with tcgen05.ld, applies the per-matrix scale, the
-// reference's bf16 rounding points, SwiGLU and the cluster gates, and stores bf16 rows.
-// Every mbarrier wait is bounded; on expiry the CTA records an error code and unwinds
-// (tensor memory is released on every path).
+// Persistent: one CTA per SM loops over work items.  An item is 128 activation rows x a PAIR
+// of panels (2 x 16 weight tile rows); each panel has its own pipeline ("pipe") and its own
+// 256 fp32 accumulator columns in tensor memory, and both pipes consume the same stream of
+// activation chunks, so an activation chunk is fetched once for 32 tile rows.
+// Warp roles (19 warps):
+//   warps 0..7    epilogue (4 per pipe): tcgen05.ld, per-matrix scale, the reference's bf16
+//                 rounding points, SwiGLU, cluster gates, bf16 stores
+//   warps 8, 9    MMA issue, one per pipe: one tcgen05.mma per run (M=128, N=16*len, K=16),
+//                 tcgen05.commit to hand stages back (two issuers: a single thread issues
+//                 an MMA with fresh descriptors every ~120 clk, the tensor pipe accepts one
+//                 every ~45 clk)
+//   warp 10       TMA producer: per activation chunk one tiled [128 x 64] bf16 load (128-byte
+//                 swizzle) into a 4-stage ring; per schedule step of either pipe one bulk copy
+//                 of the step record (run records + packed 2-bit codes) into a 6-stage ring
+//   warps 11..18  decode (4 per pipe): expand the staged 2-bit codes into bf16 B tiles
+//                 (K-major, no swizzle) in a 3-stage ring
+// Every mbarrier wait is bounded; on expiry the CTA records an error code, every role unwinds
+// and tensor memory is released.
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
@@ -25,37 +29,49 @@ namespace {
 
 constexpr int kPanelRows = MORTAR_PANEL_ROWS;
 constexpr int kChunkCols = MORTAR_CHUNK_COLS;
-constexpr int kAStages = 3;                                  // activation-chunk ring
-constexpr int kBStages = 2;                                  // expanded-tile ring
-constexpr int kRows = 128;                                   // activation rows per CTA (MMA M)
+constexpr int kStepTiles = MORTAR_STEP_TILES;                // 32 tiles per step
+constexpr int kPipes = 2;                                    // panels executed side by side per item
+constexpr int kAStages = 4;                                  // activation-chunk ring (shared)
+constexpr int kBStages = 3;                                  // expanded-tile ring, per pipe
+constexpr int kRawStages = 6;                                // step-record ring, per pipe
+constexpr int kRows = 128;                                   // activation rows per item (MMA M)
 constexpr int kAStage = kRows * 128;                         // 16 KB
-constexpr int kStepTiles = MORTAR_STEP_TILES;                // tiles per step
-constexpr int kBStage = kStepTiles * 512;                    // 24 KB
-constexpr int kRunStage = kStepTiles * 16;                   // run records of one step
-constexpr int kTmemCols = kPanelRows * 16;                   // 256
-constexpr int kThreads = 192;
-constexpr int kDecodeThreads = 128;
-constexpr int kWordsPerThread = kStepTiles * 16 / kDecodeThreads;   // code words a decoder expands per step
-constexpr int kSmemBytes = kAStages * kAStage + kBStages * (kBStage + kRunStage) + 1024 /*align*/ + 128 /*barriers*/;
+constexpr int kBTiles = kStepTiles * 512;                    // 16 KB of expanded tiles
+constexpr int kBStage = kBTiles + (kStepTiles + 1) * 16;     // + the step's run records and header
+constexpr int kRawStage = 16 + kStepTiles * 16 + kStepTiles * 64;   // 2576 B: header, runs, codes
+constexpr int kRawStride = 2688;                             // stage pitch (multiple of 128)
+constexpr int kAccCols = kPanelRows * 16;                    // 256 accumulator columns per pipe
+constexpr int kTmemCols = kPipes * kAccCols;                 // 512
+constexpr int kDecodeThreads = 128;                          // per pipe
+constexpr int kEpilogueWarps = 4 * kPipes;
+constexpr int kEpilogueThreads = 32 * kEpilogueWarps;
+constexpr int kMmaWarp0 = kEpilogueWarps;                    // warps 8, 9
+constexpr int kTmaWarp = kMmaWarp0 + kPipes;                 // warp 10
+constexpr int kDecodeWarp0 = kTmaWarp + 1;                   // warps 11..18
+constexpr int kThreads = 32 * (kDecodeWarp0 + 4 * kPipes);   // 608
+constexpr int kWordsPerThread = kStepTiles * 16 / kDecodeThreads;   // 4 code words per decoder per step
+constexpr int kNumBars = 2 * kAStages + kPipes * (2 * kBStages + 2 * kRawStages) + 2;
+constexpr int kSmemBytes = kAStages * kAStage + kPipes * (kBStages * kBStage + kRawStages * kRawStride) +
+                           kNumBars * 8 + 1024 /*align*/;
 constexpr uint32_t kWaitLimit = 1u << 22;
-constexpr int kMaxSteps = 512;                               // steps of one panel held in shared memory
+static_assert(kRawStage <= kRawStride, "raw stage pitch too small");
 
 __device__ int g_prefill_error;   // first error recorded by any CTA (0 = none)
 
 struct PrefillParams {
-    const uint32_t *tiles;        // [n_tiles][16] words of canonical 2-bit codes
-    const uint4 *runs;            // [n_runs]
+    const uint8_t *step_data;     // step records
+    const uint32_t *step_off;     // [n_steps + 1], 16-byte units
+    const uint32_t *step_meta;    // [n_steps] chunk | reuse<<30 | last<<31
     const int *panel_step_ptr;    // [n_panels + 1]
-    const int *step_tile_ptr;     // [n_steps + 1]
-    const int *step_run_ptr;      // [n_steps + 1]
-    const uint32_t *step_chunk;   // [n_steps] chunk | reuse<<30 | last<<31
     const uint32_t *panel_mask;   // [n_panels] rows that received at least one tile
+    int n_panels;
+    int n_items;                  // n_panels * row blocks
     int swiglu;
     int total_units;              // output tile rows (LINEAR) or hidden tile rows (SWIGLU)
     long long rows;
     __nv_bfloat16 *out;
     long long ld_out;
-    float scale;                  // already rounded to bf16 when rounding is emulated
+    float scale;                  // per-matrix scale rounded to bf16
     const float *gates;
     long long ld_gates;
     int cluster_size;
@@ -64,7 +80,6 @@ struct PrefillParams {
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return (uint32_t)__cvta_generic_to_shared(p);
 }
-
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
 }
@@ -97,6 +112,20 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     return false;
 }
 
+// Same, for roles that run ahead of the critical path: backs off between polls so the
+// spinning warp does not take issue slots from the warps doing work.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                                  int code) {
+    for (uint32_t i = 0; i < kWaitLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(64);
+        if ((i & 255u) == 255u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicCAS(&g_prefill_error, 0, code);
+    return false;
+}
+
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo,
                                                    uint32_t layout) {
     return (uint64_t)((addr >> 4) & 0x3fffu) | ((uint64_t)((lbo >> 4) & 0x3fffu) << 16) |
@@ -119,14 +148,18 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
                  ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+// 32 accumulator columns of this thread's tensor-memory lane; waits for the data.
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
         "tcgen05.wait::ld.sync.aligned;\n"
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
           "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-          "=r"(r[14]), "=r"(r[15])
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr) : "memory");
 }
 
@@ -147,47 +180,48 @@ __device__ __forceinline__ void expand_row(uint32_t w, uint4 &lo, uint4 &hi) {
     hi = make_uint4(out[4], out[5], out[6], out[7]);
 }
 
-__global__ void __launch_bounds__(kThreads, 2)
+// One output value of the epilogue with the reference's rounding points.
+__device__ __forceinline__ float finish(const PrefillParams &p, float acc_a, float acc_b, bool live_a,
+                                        bool live_b, float gate, bool gated) {
+    float g = live_a ? rbf(p.scale * acc_a) : 0.f;
+    if (!p.swiglu) return g;
+    const float u = live_b ? rbf(p.scale * acc_b) : 0.f;
+    const float sg = rbf(__fdividef(g, 1.f + __expf(-g)));
+    float hv = rbf(sg * u);
+    if (gated) hv = gate > 0.f ? rbf(hv * rbf(gate)) : 0.f;
+    return hv;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
 prefill_panel_kernel(const __grid_constant__ CUtensorMap tmap_x, const PrefillParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t *sA = smem;                                   // kAStages x 16 KB, 1024-byte aligned
-    uint8_t *sB = sA + kAStages * kAStage;                // kBStages x 24 KB
-    uint4 *sRuns = reinterpret_cast<uint4 *>(sB + kBStages * kBStage);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(sRuns) + kBStages * kRunStage);
-    uint64_t *a_full = bars, *a_empty = bars + kAStages;
-    uint64_t *b_full = bars + 2 * kAStages, *b_empty = b_full + kBStages;
-    uint64_t *acc_full = b_empty + kBStages;
+    uint8_t *sA = smem;                                          // kAStages x 16 KB, 1024-byte aligned
+    uint8_t *sB = sA + kAStages * kAStage;                       // kPipes x kBStages x 16 KB
+    uint8_t *sRaw = sB + kPipes * kBStages * kBStage;            // kPipes x kRawStages x kRawStride
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sRaw + kPipes * kRawStages * kRawStride);
+    uint64_t *a_full = bars, *a_empty = a_full + kAStages;
+    uint64_t *b_full = a_empty + kAStages;                       // [pipe][stage]
+    uint64_t *b_empty = b_full + kPipes * kBStages;
+    uint64_t *raw_full = b_empty + kPipes * kBStages;
+    uint64_t *raw_empty = raw_full + kPipes * kRawStages;
+    uint64_t *acc_full = raw_empty + kPipes * kRawStages, *acc_empty = acc_full + 1;
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
-    __shared__ int s_tile[kMaxSteps + 1], s_run[kMaxSteps + 1];   // this panel's step pointers
-    __shared__ uint32_t s_chunk[kMaxSteps];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int panel = blockIdx.x;
-    const long long row0 = (long long)blockIdx.y * kRows;
-    const int step0 = p.panel_step_ptr[panel];
-    const int n_steps = p.panel_step_ptr[panel + 1] - step0;
-    for (int i = threadIdx.x; i <= n_steps; i += kThreads) {
-        s_tile[i] = p.step_tile_ptr[step0 + i];
-        s_run[i] = p.step_run_ptr[step0 + i];
-        if (i < n_steps) s_chunk[i] = p.step_chunk[step0 + i];
-    }
+    const int n_super = p.n_panels / kPipes;                     // panel pairs
 
     if (threadIdx.x == 0) {
         abort_s = 0;
-        for (int s = 0; s < kAStages; ++s) {
-            mbar_init(smem_u32(&a_full[s]), 1);
-            mbar_init(smem_u32(&a_empty[s]), 1);
-        }
-        for (int s = 0; s < kBStages; ++s) {
-            mbar_init(smem_u32(&b_full[s]), kDecodeThreads);
-            mbar_init(smem_u32(&b_empty[s]), 1);
-        }
-        mbar_init(smem_u32(acc_full), 1);
+        for (int s = 0; s < kAStages; ++s) { mbar_init(smem_u32(&a_full[s]), 1); mbar_init(smem_u32(&a_empty[s]), kPipes); }
+        for (int s = 0; s < kPipes * kBStages; ++s) { mbar_init(smem_u32(&b_full[s]), kDecodeThreads); mbar_init(smem_u32(&b_empty[s]), 1); }
+        for (int s = 0; s < kPipes * kRawStages; ++s) { mbar_init(smem_u32(&raw_full[s]), 1); mbar_init(smem_u32(&raw_empty[s]), kDecodeThreads); }
+        mbar_init(smem_u32(acc_full), kPipes);
+        mbar_init(smem_u32(acc_empty), kEpilogueThreads);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    if (warp == 0) {
+    if (warp == kMmaWarp0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
                      ::"r"(smem_u32(&tmem_base_s)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
@@ -198,162 +232,251 @@ prefill_panel_kernel(const __grid_constant__ CUtensorMap tmap_x, const PrefillPa
     const uint32_t tmem = tmem_base_s;
     volatile int *abort_flag = &abort_s;
 
-    if (warp == 0) {
-        // ---------------- MMA issue ----------------
-        int a_it = -1;                                     // activation chunks consumed so far - 1
+    if (warp < kEpilogueWarps) {
+        // ---------------- epilogue: warps 0..3 drain pipe 0, warps 4..7 pipe 1 ----------------
+        const int q = warp & 3;                                       // tensor-memory lane quadrant
+        const int pipe = warp >> 2;
+        int it = 0;
         bool ok = true;
-        for (int i = 0; i < n_steps && ok; ++i) {
-            const uint32_t ck = s_chunk[i];
-            const int bs = i % kBStages;
-            if (!(ck & 0x40000000u)) {                     // this step starts a new activation chunk
-                ++a_it;
-                ok = mbar_wait(smem_u32(&a_full[a_it % kAStages]), (a_it / kAStages) & 1, abort_flag, 1);
-                if (!ok) break;
-            }
-            ok = mbar_wait(smem_u32(&b_full[bs]), (i / kBStages) & 1, abort_flag, 5);
-            if (!ok) break;
-            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            if (lane == 0) {
-                const int as = a_it % kAStages;
-                const uint64_t a0 = make_smem_desc(smem_u32(sA + as * kAStage), 16, 1024, 2);
-                const uint64_t b0 = make_smem_desc(smem_u32(sB + bs * kBStage), 128, 256, 0);
-                const uint32_t a_lo = (uint32_t)a0, a_hi = (uint32_t)(a0 >> 32);
-                const uint32_t b_lo = (uint32_t)b0, b_hi = (uint32_t)(b0 >> 32);
-                const uint4 *rr = sRuns + bs * kStepTiles;
-                const int nrun = s_run[i + 1] - s_run[i];
-                for (int r = 0; r < nrun; r += 4) {
-                    // fetch four run records, then issue: the loads do not wait behind the MMAs
-                    uint4 q[4];
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) q[k] = rr[min(r + k, nrun - 1)];
-#pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        if (r + k < nrun)
-                            tc_mma(tmem + (q[k].z & 0xffffu), a_lo + q[k].x, a_hi, b_lo + q[k].y, b_hi,
-                                   q[k].w, q[k].z >> 31);
-                }
-                tc_commit(smem_u32(&b_empty[bs]));         // B stage reusable once these MMAs retire
-                if (ck & 0x80000000u) tc_commit(smem_u32(&a_empty[as]));   // last step on this chunk
-            }
-            __syncwarp();
-        }
-        if (lane == 0) {
-            if (ok && n_steps > 0) tc_commit(smem_u32(acc_full));
-            else mbar_arrive(smem_u32(acc_full));
-        }
-    } else if (warp == 1) {
-        // ---------------- TMA producer ----------------
-        int a_it = 0;
-        for (int i = 0; i < n_steps; ++i) {
-            const uint32_t ck = s_chunk[i];
-            if (ck & 0x40000000u) continue;
-            const int as = a_it % kAStages;
-            if (!mbar_wait(smem_u32(&a_empty[as]), ((a_it / kAStages) & 1) ^ 1u, abort_flag, 2)) break;
-            if (lane == 0) {
-                const uint32_t bar = smem_u32(&a_full[as]);
-                mbar_arrive_expect_tx(bar, kAStage);
-                asm volatile(
-                    "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
-                    "[%0], [%1, {%2, %3}], [%4];\n"
-                    ::"r"(smem_u32(sA + as * kAStage)), "l"(&tmap_x),
-                      "r"((int)(ck & 0xffffffu) * kChunkCols * 16), "r"((int)row0), "r"(bar) : "memory");
-            }
-            __syncwarp();
-            ++a_it;
-        }
-    } else {
-        // ---------------- tile decode ----------------
-        const int td = threadIdx.x - 64;
-        bool ok = true;
-        uint32_t cur[kWordsPerThread], nxt[kWordsPerThread];
-        uint4 cur_run = make_uint4(0, 0, 0, 0), nxt_run = make_uint4(0, 0, 0, 0);
-        auto fetch = [&](int i, uint32_t (&w)[kWordsPerThread], uint4 &run) {
-            const int t0 = s_tile[i], items = (s_tile[i + 1] - t0) * 16;
-#pragma unroll
-            for (int k = 0; k < kWordsPerThread; ++k) {
-                const int item = td + k * kDecodeThreads;
-                w[k] = item < items ? __ldg(p.tiles + (long long)t0 * 16 + item) : 0u;
-            }
-            if (td < s_run[i + 1] - s_run[i]) run = __ldg(p.runs + s_run[i] + td);
-        };
-        if (n_steps > 0) fetch(0, cur, cur_run);
-        for (int i = 0; i < n_steps && ok; ++i) {
-            if (i + 1 < n_steps) fetch(i + 1, nxt, nxt_run);
-            const int bs = i % kBStages;
-            ok = mbar_wait(smem_u32(&b_empty[bs]), ((i / kBStages) & 1) ^ 1u, abort_flag, 3);
-            if (!ok) break;
-            if (td < s_run[i + 1] - s_run[i]) sRuns[bs * kStepTiles + td] = cur_run;
-            uint8_t *bdst = sB + bs * kBStage;
-            const int items = (s_tile[i + 1] - s_tile[i]) * 16;        // (tile, row) pairs
-#pragma unroll
-            for (int k = 0; k < kWordsPerThread; ++k) {
-                const int item = td + k * kDecodeThreads;
-                if (item < items) {
-                    const int tile = item >> 4, row = item & 15;
-                    uint4 lo, hi;
-                    expand_row(cur[k], lo, hi);
-                    uint8_t *d = bdst + tile * 512 + (row >> 3) * 256 + (row & 7) * 16;
-                    *reinterpret_cast<uint4 *>(d) = lo;        // features 0..7 of the tile column
-                    *reinterpret_cast<uint4 *>(d + 128) = hi;  // features 8..15
-                }
-            }
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-            mbar_arrive(smem_u32(&b_full[bs]));
-#pragma unroll
-            for (int k = 0; k < kWordsPerThread; ++k) cur[k] = nxt[k];
-            cur_run = nxt_run;
-        }
-        // ---------------- epilogue ----------------
-        if (ok) ok = mbar_wait(smem_u32(acc_full), 0, abort_flag, 4);
-        if (ok) {
-            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            const int q = warp & 3;                            // tensor-memory lane quadrant of this warp
-            const long long row = row0 + q * 32 + lane;
+        const int units = p.swiglu ? kPanelRows / 2 : kPanelRows;
+        for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++it) {
+            const int panel = (item % n_super) * kPipes + pipe;
+            const long long row = (long long)(item / n_super) * kRows + q * 32 + lane;
             const bool in_range = row < p.rows;
-            const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16);
             const uint32_t mask = p.panel_mask[panel];
-            const int units = p.swiglu ? kPanelRows / 2 : kPanelRows;
-            for (int j = 0; j < units; ++j) {
-                uint32_t a[16], b[16];
-                tc_ld16(taddr + j * 16, a);
-                if (p.swiglu) tc_ld16(taddr + (units + j) * 16, b);
-                const bool live_a = (mask >> j) & 1u;
-                const bool live_b = p.swiglu ? ((mask >> (units + j)) & 1u) : true;
+            ok = mbar_wait_relaxed(smem_u32(acc_full), it & 1, abort_flag, 8);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const uint32_t taddr = tmem + pipe * kAccCols + ((uint32_t)(q * 32) << 16);
+            const bool gated = p.swiglu && p.gates != nullptr && in_range;
+            for (int j = 0; j < units; j += 2) {                      // two output tile columns at a time
+                uint32_t a[32], b[32];
+                tc_ld32(taddr + j * 16, a);
+                if (p.swiglu) tc_ld32(taddr + (units + j) * 16, b);
                 const long long col0 = ((long long)panel * units + j) * 16;
-                uint32_t packed[8];
+                uint32_t packed[16];
 #pragma unroll
-                for (int e = 0; e < 16; e += 2) {
+                for (int e = 0; e < 32; e += 2) {
                     float v[2];
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
-                        float g = live_a ? rbf(p.scale * __uint_as_float(a[e + h])) : 0.f;
-                        if (p.swiglu) {
-                            const float u = live_b ? rbf(p.scale * __uint_as_float(b[e + h])) : 0.f;
-                            const float sg = rbf(g / (1.f + expf(-g)));
-                            float hv = rbf(sg * u);
-                            if (p.gates != nullptr && in_range) {
-                                const float gt = p.gates[row * p.ld_gates + (col0 + e + h) / p.cluster_size];
-                                hv = gt > 0.f ? rbf(hv * rbf(gt)) : 0.f;
-                            }
-                            g = hv;
-                        }
-                        v[h] = g;
+                        const int jj = j + ((e + h) >> 4);
+                        const bool live_a = (mask >> jj) & 1u;
+                        const bool live_b = p.swiglu ? ((mask >> (units + jj)) & 1u) : true;
+                        float gate = 1.f;
+                        if (gated) gate = p.gates[row * p.ld_gates + (col0 + e + h) / p.cluster_size];
+                        v[h] = finish(p, __uint_as_float(a[e + h]), p.swiglu ? __uint_as_float(b[e + h]) : 0.f,
+                                      live_a, live_b, gate, gated);
                     }
                     __nv_bfloat162 pr = __floats2bfloat162_rn(v[0], v[1]);
                     packed[e >> 1] = *reinterpret_cast<uint32_t *>(&pr);
                 }
-                if (in_range && panel * units + j < p.total_units) {
+                if (in_range) {
                     uint4 *dst = reinterpret_cast<uint4 *>(p.out + row * p.ld_out + col0);
-                    dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                    dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                    if (panel * units + j < p.total_units) {
+                        dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                        dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                    }
+                    if (panel * units + j + 1 < p.total_units) {
+                        dst[2] = make_uint4(packed[8], packed[9], packed[10], packed[11]);
+                        dst[3] = make_uint4(packed[12], packed[13], packed[14], packed[15]);
+                    }
                 }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            mbar_arrive(smem_u32(acc_empty));                         // accumulators drained
+        }
+    } else if (warp == kMmaWarp0 || warp == kMmaWarp0 + 1) {
+        // ---------------- MMA issue, one warp per pipe ----------------
+        const int pipe = warp - kMmaWarp0;
+        uint64_t *bf = b_full + pipe * kBStages, *be = b_empty + pipe * kBStages;
+        const uint8_t *bbase = sB + pipe * kBStages * kBStage;
+        const uint32_t acc = tmem + pipe * kAccCols;
+        int g = 0, ga = -1, it = 0;
+        bool ok = true;
+        for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++it) {
+            const int panel = (item % n_super) * kPipes + pipe;
+            const int n_steps = p.panel_step_ptr[panel + 1] - p.panel_step_ptr[panel];
+            ok = mbar_wait_relaxed(smem_u32(acc_empty), (it & 1) ^ 1u, abort_flag, 9);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            for (int i = 0; i < n_steps; ++i, ++g) {
+                const int bs = g % kBStages;
+                // the decoders publish the step (tiles, header, run records) in the B stage
+                ok = mbar_wait(smem_u32(&bf[bs]), (g / kBStages) & 1, abort_flag, 3);
+                if (!ok) break;
+                const uint8_t *rec = bbase + bs * kBStage + kBTiles;
+                const uint4 hdr = *reinterpret_cast<const uint4 *>(rec + kStepTiles * 16);
+                if (!(hdr.z & 0x40000000u)) {              // this step starts a new activation chunk
+                    ++ga;
+                    ok = mbar_wait(smem_u32(&a_full[ga % kAStages]), (ga / kAStages) & 1, abort_flag, 2);
+                    if (!ok) break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                if (lane == 0) {
+                    const int as = ga % kAStages;
+                    const uint64_t a0 = make_smem_desc(smem_u32(sA + as * kAStage), 16, 1024, 2);
+                    const uint64_t b0 = make_smem_desc(smem_u32(bbase + bs * kBStage), 128, 256, 0);
+                    const uint32_t a_lo = (uint32_t)a0, a_hi = (uint32_t)(a0 >> 32);
+                    const uint32_t b_lo = (uint32_t)b0, b_hi = (uint32_t)(b0 >> 32);
+                    const uint4 *rr = reinterpret_cast<const uint4 *>(rec);
+                    const int nrun = (int)hdr.y;
+                    for (int r = 0; r < nrun; r += 4) {
+                        // fetch four run records, then issue: the loads do not wait behind the MMAs
+                        uint4 qv[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) qv[k] = rr[min(r + k, nrun - 1)];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            if (r + k < nrun)
+                                tc_mma(acc + (qv[k].z & 0xffffu), a_lo + qv[k].x, a_hi, b_lo + qv[k].y, b_hi,
+                                       qv[k].w, qv[k].z >> 31);
+                    }
+                    tc_commit(smem_u32(&be[bs]));          // B stage reusable once these MMAs retire
+                    if (hdr.z & 0x80000000u) tc_commit(smem_u32(&a_empty[as]));   // last step on this chunk
+                }
+                __syncwarp();
+            }
+            if (!ok) break;
+            if (lane == 0) {
+                if (n_steps > 0) tc_commit(smem_u32(acc_full));
+                else mbar_arrive(smem_u32(acc_full));
+            }
+            __syncwarp();
+        }
+    } else if (warp == kTmaWarp) {
+        // ---------------- TMA producer: activation chunks + both pipes' step records ----------------
+        int g[kPipes] = {0, 0};
+        int ga = 0;
+        bool ok = true;
+        for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
+            const int panel0 = (item % n_super) * kPipes;
+            const int row0 = (item / n_super) * kRows;
+            int cur[kPipes], end[kPipes], base[kPipes];
+            uint32_t o0[kPipes], o1[kPipes], mt[kPipes];
+#pragma unroll
+            for (int k = 0; k < kPipes; ++k) {
+                cur[k] = p.panel_step_ptr[panel0 + k];
+                end[k] = p.panel_step_ptr[panel0 + k + 1];
+                base[k] = -64;
+                o0[k] = o1[k] = mt[k] = 0;
+            }
+            // both panels list the same chunks; walk them chunk by chunk
+            while (cur[0] < end[0] && ok) {
+                bool first = true;
+#pragma unroll
+                for (int k = 0; k < kPipes; ++k) {
+                    bool last = false;
+                    while (!last && cur[k] < end[k] && ok) {
+                        if (cur[k] >= base[k] + 32) {            // refill this pipe's metadata batch
+                            base[k] = cur[k];
+                            const int i = base[k] + lane;
+                            o0[k] = o1[k] = mt[k] = 0;
+                            if (i < end[k]) {
+                                o0[k] = __ldg(p.step_off + i);
+                                o1[k] = __ldg(p.step_off + i + 1);
+                                mt[k] = __ldg(p.step_meta + i);
+                            }
+                        }
+                        const int sl = cur[k] - base[k];
+                        const uint32_t so0 = __shfl_sync(0xffffffffu, o0[k], sl);
+                        const uint32_t so1 = __shfl_sync(0xffffffffu, o1[k], sl);
+                        const uint32_t sm = __shfl_sync(0xffffffffu, mt[k], sl);
+                        if (k == 0 && first) {                   // new activation chunk
+                            const int as = ga % kAStages;
+                            ok = mbar_wait_relaxed(smem_u32(&a_empty[as]), ((ga / kAStages) & 1) ^ 1u, abort_flag, 5);
+                            if (!ok) break;
+                            if (lane == 0) {
+                                const uint32_t bar = smem_u32(&a_full[as]);
+                                mbar_arrive_expect_tx(bar, kAStage);
+                                asm volatile(
+                                    "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+                                    "[%0], [%1, {%2, %3}], [%4];\n"
+                                    ::"r"(smem_u32(sA + as * kAStage)), "l"(&tmap_x),
+                                      "r"((int)(sm & 0xffffffu) * kChunkCols * 16), "r"(row0), "r"(bar) : "memory");
+                            }
+                            ++ga;
+                            first = false;
+                        }
+                        const int rs = g[k] % kRawStages;
+                        ok = mbar_wait_relaxed(smem_u32(&raw_empty[k * kRawStages + rs]),
+                                               ((g[k] / kRawStages) & 1) ^ 1u, abort_flag, 4);
+                        if (!ok) break;
+                        if (lane == 0) {
+                            const uint32_t bar = smem_u32(&raw_full[k * kRawStages + rs]);
+                            const uint32_t bytes = (so1 - so0) * 16u;
+                            mbar_arrive_expect_tx(bar, bytes);
+                            asm volatile(
+                                "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                                ::"r"(smem_u32(sRaw + (k * kRawStages + rs) * kRawStride)),
+                                  "l"(p.step_data + (size_t)so0 * 16), "r"(bytes), "r"(bar) : "memory");
+                        }
+                        __syncwarp();
+                        last = (sm & 0x80000000u) != 0;
+                        ++g[k];
+                        ++cur[k];
+                    }
+                }
+            }
+        }
+    } else {
+        // ---------------- tile decode: warps 11..14 pipe 0, 15..18 pipe 1 ----------------
+        const int pipe = (warp - kDecodeWarp0) >> 2;
+        const int td = threadIdx.x - (kDecodeWarp0 + 4 * pipe) * 32;
+        uint64_t *bf = b_full + pipe * kBStages, *be = b_empty + pipe * kBStages;
+        uint64_t *rf = raw_full + pipe * kRawStages, *re = raw_empty + pipe * kRawStages;
+        const uint8_t *raw = sRaw + pipe * kRawStages * kRawStride;
+        uint8_t *bbase = sB + pipe * kBStages * kBStage;
+        int g = 0;
+        bool ok = true;
+        for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
+            const int panel = (item % n_super) * kPipes + pipe;
+            const int n_steps = p.panel_step_ptr[panel + 1] - p.panel_step_ptr[panel];
+            for (int i = 0; i < n_steps; ++i, ++g) {
+                const int rs = g % kRawStages, bs = g % kBStages;
+                ok = mbar_wait_relaxed(smem_u32(&rf[rs]), (g / kRawStages) & 1, abort_flag, 6);
+                if (!ok) break;
+                const uint8_t *rec = raw + rs * kRawStride;
+                const uint4 hdr = *reinterpret_cast<const uint4 *>(rec);
+                const uint32_t *words = reinterpret_cast<const uint32_t *>(rec + 16 + hdr.y * 16);
+                const int items = (int)hdr.x * 16;                    // (tile, row) pairs
+                uint32_t w[kWordsPerThread];
+#pragma unroll
+                for (int k = 0; k < kWordsPerThread; ++k) {
+                    const int idx = td + k * kDecodeThreads;
+                    w[k] = idx < items ? words[idx] : 0u;
+                }
+                // the MMA warp reads the header and run records from the B stage, so the raw
+                // stage is free as soon as the decoders hold its contents in registers
+                uint4 run = make_uint4(0, 0, 0, 0);
+                if (td < (int)hdr.y) run = *reinterpret_cast<const uint4 *>(rec + 16 + td * 16);
+                mbar_arrive(smem_u32(&re[rs]));                       // codes and runs are in registers
+                ok = mbar_wait_relaxed(smem_u32(&be[bs]), ((g / kBStages) & 1) ^ 1u, abort_flag, 7);
+                if (!ok) break;
+                uint8_t *bdst = bbase + bs * kBStage;
+                if (td < (int)hdr.y) *reinterpret_cast<uint4 *>(bdst + kBTiles + td * 16) = run;
+                if (td == kDecodeThreads - 1) *reinterpret_cast<uint4 *>(bdst + kBTiles + kStepTiles * 16) = hdr;
+#pragma unroll
+                for (int k = 0; k < kWordsPerThread; ++k) {
+                    const int idx = td + k * kDecodeThreads;
+                    if (idx < items) {
+                        const int tile = idx >> 4, row = idx & 15;
+                        uint4 lo, hi;
+                        expand_row(w[k], lo, hi);
+                        uint8_t *d = bdst + tile * 512 + (row >> 3) * 256 + (row & 7) * 16;
+                        *reinterpret_cast<uint4 *>(d) = lo;           // features 0..7 of the tile column
+                        *reinterpret_cast<uint4 *>(d + 128) = hi;     // features 8..15
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                mbar_arrive(smem_u32(&bf[bs]));
             }
         }
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
-    if (warp == 0) {
+    if (warp == kMmaWarp0) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(kTmemCols) : "memory");
     }
 }
@@ -386,20 +509,20 @@ inline bool aligned_to(const void *ptr, size_t a) { return (reinterpret_cast<uin
 extern "C" int mortar_linear_tc(const mortar_sched *w, const void *x, int64_t ldx, int64_t rows,
                                 void *out, int64_t ld_out, const float *gates, int64_t ld_gates,
                                 int32_t cluster_size, void *stream) {
-    if (!w || !x || !out || !w->panel_step_ptr || !w->step_tile_ptr || !w->step_run_ptr ||
-        !w->step_chunk || !w->panel_mask)
-        return MORTAR_ERR_NULL;
-    if (w->n_tiles > 0 && (!w->tiles || !w->runs)) return MORTAR_ERR_NULL;
-    if (w->tile_rows <= 0 || w->tile_cols <= 0 || rows < 0) return MORTAR_ERR_SHAPE;
+    if (!w || !x || !out || !w->panel_step_ptr || !w->panel_mask) return MORTAR_ERR_NULL;
+    if (w->n_steps > 0 && (!w->step_data || !w->step_off || !w->step_meta)) return MORTAR_ERR_NULL;
+    if (w->tile_rows <= 0 || w->tile_cols <= 0 || w->n_panels <= 0 || rows < 0) return MORTAR_ERR_SHAPE;
     const int K = w->tile_cols * 16;
     const int units = w->swiglu ? w->tile_rows / 2 : w->tile_rows;
     if (ldx < K || ld_out < (int64_t)units * 16) return MORTAR_ERR_SHAPE;
     if (!aligned_to(x, 16) || (ldx % 8) || !aligned_to(out, 16) || (ld_out % 8)) return MORTAR_ERR_ALIGN;
+    if (!aligned_to(w->step_data, 16)) return MORTAR_ERR_ALIGN;
     if (gates && (cluster_size <= 0 || !w->swiglu)) return MORTAR_ERR_SHAPE;
-    if (w->max_panel_steps > kMaxSteps) return MORTAR_ERR_CAPACITY;
     if (rows == 0) return MORTAR_OK;
     const int64_t row_blocks = (rows + kRows - 1) / kRows;
-    if (row_blocks > 65535) return MORTAR_ERR_CAPACITY;
+    if (w->n_panels % kPipes) return MORTAR_ERR_SHAPE;          // the builder pads to pairs
+    const int64_t n_items = row_blocks * (w->n_panels / kPipes);
+    if (n_items > 0x7fffffffLL || rows > 0x7fffffffLL) return MORTAR_ERR_CAPACITY;
 
     EncodeTiledFn encode;
     int rc = get_encode_fn(&encode);
@@ -417,20 +540,25 @@ extern "C" int mortar_linear_tc(const mortar_sched *w, const void *x, int64_t ld
         return MORTAR_ERR_CUDA;
     }
 
-    static bool attr_set = false;
-    if (!attr_set) {
+    int dev = 0;
+    MORTAR_CUDA_CHECK(cudaGetDevice(&dev));
+    static int sm_count[64] = {0};
+    static bool attr_set[64] = {false};
+    if (dev < 0 || dev >= 64) return MORTAR_ERR_CAPACITY;
+    if (!attr_set[dev]) {
+        MORTAR_CUDA_CHECK(cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev));
         MORTAR_CUDA_CHECK(cudaFuncSetAttribute(prefill_panel_kernel,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-        attr_set = true;
+        attr_set[dev] = true;
     }
     PrefillParams p;
-    p.tiles = reinterpret_cast<const uint32_t *>(w->tiles);
-    p.runs = reinterpret_cast<const uint4 *>(w->runs);
+    p.step_data = reinterpret_cast<const uint8_t *>(w->step_data);
+    p.step_off = w->step_off;
+    p.step_meta = w->step_meta;
     p.panel_step_ptr = w->panel_step_ptr;
-    p.step_tile_ptr = w->step_tile_ptr;
-    p.step_run_ptr = w->step_run_ptr;
-    p.step_chunk = w->step_chunk;
     p.panel_mask = w->panel_mask;
+    p.n_panels = w->n_panels;
+    p.n_items = (int)n_items;
     p.swiglu = w->swiglu;
     p.total_units = units;
     p.rows = rows;
@@ -440,7 +568,7 @@ extern "C" int mortar_linear_tc(const mortar_sched *w, const void *x, int64_t ld
     p.gates = gates;
     p.ld_gates = ld_gates;
     p.cluster_size = cluster_size > 0 ? cluster_size : 1;
-    dim3 grid((unsigned)w->n_panels, (unsigned)row_blocks);
+    const unsigned grid = (unsigned)(n_items < sm_count[dev] ? n_items : sm_count[dev]);
     prefill_panel_kernel<<<grid, kThreads, kSmemBytes, (cudaStream_t)stream>>>(tmap, p);
     MORTAR_CUDA_CHECK(cudaGetLastError());
     return MORTAR_OK;

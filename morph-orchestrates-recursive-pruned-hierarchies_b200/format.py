@@ -236,7 +236,7 @@ class MortarMatrix:
                             self.algorithmic_bytes())
 
 
-PANEL_ROWS, CHUNK_COLS, STEP_TILES = 16, 4, 48
+PANEL_ROWS, CHUNK_COLS, STEP_TILES = 16, 4, 32
 
 
 def build_sched_host(m: "MortarMatrix", swiglu: bool):
@@ -245,25 +245,22 @@ def build_sched_host(m: "MortarMatrix", swiglu: bool):
     rp = np.ascontiguousarray(m.row_ptr)
     ci = np.ascontiguousarray(m.col_idx)
     cd = np.ascontiguousarray(m.codes)
-    nt, nr, ns = C.c_int64(0), C.c_int64(0), C.c_int64(0)
+    nt, nr, ns, du = C.c_int64(0), C.c_int64(0), C.c_int64(0), C.c_int64(0)
     npan = C.c_int32(0)
     _lib.check(L.mortar_sched_sizes(_ptr(rp), _ptr(ci), m.tile_rows, m.tile_cols, int(swiglu),
-                                    C.byref(nt), C.byref(nr), C.byref(ns), C.byref(npan)),
-               "mortar_sched_sizes")
-    tiles = np.zeros((max(nt.value, 1), 64), dtype=np.uint8)
-    runs = np.zeros((max(nr.value, 1), 4), dtype=np.uint32)
+                                    C.byref(nt), C.byref(nr), C.byref(ns), C.byref(npan),
+                                    C.byref(du)), "mortar_sched_sizes")
+    data = np.zeros(max(du.value, 1) * 16, dtype=np.uint8)
+    off = np.zeros(ns.value + 1, dtype=np.uint32)
+    meta = np.zeros(max(ns.value, 1), dtype=np.uint32)
     psp = np.zeros(npan.value + 1, dtype=np.int32)
-    stp = np.zeros(ns.value + 1, dtype=np.int32)
-    srp = np.zeros(ns.value + 1, dtype=np.int32)
-    sch = np.zeros(max(ns.value, 1), dtype=np.uint32)
     mask = np.zeros(npan.value, dtype=np.uint32)
     _lib.check(L.mortar_build_sched(_ptr(rp), _ptr(ci), _ptr(cd), m.tile_rows, m.tile_cols, m.nnz,
-                                    int(swiglu), _ptr(tiles), _ptr(runs), _ptr(psp), _ptr(stp),
-                                    _ptr(srp), _ptr(sch), _ptr(mask)), "mortar_build_sched")
-    return dict(tiles=tiles, runs=runs, panel_step_ptr=psp, step_tile_ptr=stp, step_run_ptr=srp,
-                step_chunk=sch, panel_mask=mask, n_tiles=nt.value, n_runs=nr.value,
-                n_steps=ns.value, n_panels=npan.value,
-                max_panel_steps=int(np.diff(psp).max()) if npan.value else 0)
+                                    int(swiglu), _ptr(data), _ptr(off), _ptr(meta), _ptr(psp),
+                                    _ptr(mask)), "mortar_build_sched")
+    return dict(step_data=data, step_off=off, step_meta=meta, panel_step_ptr=psp, panel_mask=mask,
+                n_tiles=nt.value, n_runs=nr.value, n_steps=ns.value, n_panels=npan.value,
+                data_units=du.value)
 
 
 class SchedMatrix:
@@ -274,14 +271,12 @@ class SchedMatrix:
         self.out_features, self.in_features = m.out_features, m.in_features
         self.swiglu, self.scale, self.nnz = bool(swiglu), float(m.scale), m.nnz
         self.n_tiles, self.n_runs, self.n_steps = h["n_tiles"], h["n_runs"], h["n_steps"]
-        self.n_panels, self.max_panel_steps = h["n_panels"], h["max_panel_steps"]
+        self.n_panels, self.data_units = h["n_panels"], h["data_units"]
         t = lambda a: torch.from_numpy(a).to(device)
-        self.tiles = t(h["tiles"])
-        self.runs = t(h["runs"].view(np.int32))
+        self.step_data = t(h["step_data"])
+        self.step_off = t(h["step_off"].view(np.int32))
+        self.step_meta = t(h["step_meta"].view(np.int32))
         self.panel_step_ptr = t(h["panel_step_ptr"])
-        self.step_tile_ptr = t(h["step_tile_ptr"])
-        self.step_run_ptr = t(h["step_run_ptr"])
-        self.step_chunk = t(h["step_chunk"].view(np.int32))
         self.panel_mask = t(h["panel_mask"].view(np.int32))
         self._c = None
 
@@ -291,11 +286,10 @@ class SchedMatrix:
 
     def c_struct(self) -> _lib.Sched:
         if self._c is None:
-            self._c = _lib.Sched(self.tiles.data_ptr(), self.runs.data_ptr(),
-                                 self.panel_step_ptr.data_ptr(), self.step_tile_ptr.data_ptr(),
-                                 self.step_run_ptr.data_ptr(), self.step_chunk.data_ptr(),
+            self._c = _lib.Sched(self.step_data.data_ptr(), self.step_off.data_ptr(),
+                                 self.step_meta.data_ptr(), self.panel_step_ptr.data_ptr(),
                                  self.panel_mask.data_ptr(), self.n_tiles, self.n_runs, self.n_steps,
-                                 self.n_panels, self.max_panel_steps, self.out_features // TILE,
+                                 self.data_units, self.n_panels, self.out_features // TILE,
                                  self.in_features // TILE, int(self.swiglu), self.scale)
         return self._c
 

@@ -219,25 +219,32 @@ def test_prefill_schedule_covers_every_tile_once(swiglu, density):
     P, CC = fmt.PANEL_ROWS, fmt.CHUNK_COLS
     units = R // 2 if swiglu else R
     per_panel = P // 2 if swiglu else P
-    assert h["n_panels"] == -(-units // per_panel)
+    assert h["n_panels"] == (-(-units // per_panel) + 1) // 2 * 2     # padded to panel pairs
     assert h["n_tiles"] == m.nnz
     dense = np.zeros_like(codes)
     seen = np.zeros((R, C), dtype=int)
-    tiles = fmt.unpack_codes_2bit(h["tiles"]).reshape(-1, 16, 16)
+    data = h["step_data"]
+    n_tiles_seen = 0
     for p in range(h["n_panels"]):
         touched = 0
         prev_chunk, prev_last = -1, True
         for st in range(h["panel_step_ptr"][p], h["panel_step_ptr"][p + 1]):
-            ck = int(h["step_chunk"][st])
+            rec = data[int(h["step_off"][st]) * 16:int(h["step_off"][st + 1]) * 16]
+            hdr = rec[:16].view(np.uint32)
+            n_in_step, n_runs, ck = int(hdr[0]), int(hdr[1]), int(hdr[2])
+            assert ck == int(h["step_meta"][st]) and hdr[3] == 0
+            assert len(rec) == 16 + 16 * n_runs + 64 * n_in_step
             ch, reuse, last = ck & 0xFFFFFF, (ck >> 30) & 1, (ck >> 31) & 1
             assert reuse == (0 if prev_last else 1)
             assert ch == prev_chunk if reuse else ch > prev_chunk
             prev_chunk, prev_last = ch, bool(last)
-            t0 = h["step_tile_ptr"][st]
-            n_in_step = h["step_tile_ptr"][st + 1] - t0
-            assert 0 < n_in_step <= fmt.STEP_TILES
-            for r in range(h["step_run_ptr"][st], h["step_run_ptr"][st + 1]):
-                a_off, b_off, d, idesc = (int(v) for v in h["runs"][r])
+            assert 0 <= n_in_step <= fmt.STEP_TILES
+            assert n_in_step > 0 or (n_runs == 0 and last and not reuse)      # mirror step of the partner
+            n_tiles_seen += n_in_step
+            runs = rec[16:16 + 16 * n_runs].view(np.uint32).reshape(n_runs, 4)
+            tiles = fmt.unpack_codes_2bit(rec[16 + 16 * n_runs:].reshape(n_in_step, 64)).reshape(-1, 16, 16)
+            for r in range(n_runs):
+                a_off, b_off, d, idesc = (int(v) for v in runs[r])
                 n = ((idesc >> 17) & 0x3F) << 3
                 assert (idesc >> 24) & 0x1F == 8 and n % 16 == 0 and 16 <= n <= 256
                 cl, first, l0, acc = a_off // 2, b_off // 32, (d & 0xFFFF) // 16, d >> 31
@@ -251,14 +258,22 @@ def test_prefill_schedule_covers_every_tile_once(swiglu, density):
                     else:
                         trow = p * P + l
                     col = ch * CC + cl
-                    dense[trow * 16:(trow + 1) * 16, col * 16:(col + 1) * 16] = tiles[t0 + first + k]
+                    dense[trow * 16:(trow + 1) * 16, col * 16:(col + 1) * 16] = tiles[first + k]
                     seen[trow, col] += 1
                 for k in range(n // 16):
                     touched |= 1 << (l0 + k)
         assert prev_last
         assert touched == int(h["panel_mask"][p])
+        # both panels of a pair list the same chunks
+        def chunks(pp):
+            return [int(h["step_meta"][st]) & 0xFFFFFF
+                    for st in range(h["panel_step_ptr"][pp], h["panel_step_ptr"][pp + 1])
+                    if not (int(h["step_meta"][st]) >> 30) & 1]
+        assert chunks(p) == chunks(p ^ 1)
+    assert n_tiles_seen == h["n_tiles"]
     np.testing.assert_array_equal(seen, mask.astype(int))
     np.testing.assert_array_equal(dense, m.to_dense_codes())
     if density == 1.0 and not swiglu:
         # a full panel fuses each of its columns into a single N=256 run
-        assert int(((h["runs"][:, 3] >> 17) & 0x3F).max()) == 32
+        rec0 = data[:int(h["step_off"][1]) * 16]
+        assert int((rec0[16:32].view(np.uint32)[3] >> 17) & 0x3F) == 32
