@@ -198,6 +198,28 @@ int mortar_mlp_decode(const mortar_stream *gate_up, const mortar_stream *down,
                       int32_t n_planes, int32_t flags,
                       void *workspace, int64_t workspace_bytes, void *stream);
 
+/* mortar_mlp_decode without a caller workspace.  This entry point has no counterpart in the
+ * reference.  It exists for callers that cannot hand over device memory of their own: code
+ * that binds this ABI from a runtime without a CUDA allocator, a serving loop that must not
+ * call cudaMalloc on its hot path (the call synchronises the device), or a caller already
+ * inside a region where allocation is not allowed.  The activation planes live in an 8 MiB
+ * array built into the library (mortar_mlp_static_scratch_bytes()); each GPU that loads the
+ * library holds it until the process exits.  Calls whose planes do not fit
+ * (mortar_mlp_workspace_bytes(rows, d_model, d_ff, n_planes) > 8 MiB, e.g. more than 182
+ * rows of the 2048/5632 shape at 3 planes) return MORTAR_ERR_CAPACITY.
+ * The call allocates nothing.  The first call on a device looks up the array's device
+ * address (cudaGetSymbolAddress) with that device current; make that first call outside any
+ * stream capture.  All calls on a device share the one array: it keeps the previous call's
+ * contents (nothing in it needs clearing, every element read is written first), and two
+ * calls that overlap on the GPU (different streams) race on it -- serialise them. */
+int64_t mortar_mlp_static_scratch_bytes(void);
+int mortar_mlp_decode_static(const mortar_stream *gate_up, const mortar_stream *down,
+                             const void *x, int x_dtype, int64_t ldx, int64_t rows,
+                             const float *rms_weight, float eps,
+                             const float *gates, int64_t ld_gates, int32_t n_clusters,
+                             void *y, int y_dtype, int64_t ldy,
+                             int32_t n_planes, int32_t flags, void *stream);
+
 /* ---- prefill: tcgen05 / tensor-memory path --------------------------------------------
  * Execution layout for blocks of 128 activation rows ("panel schedule"), built once on the
  * host from the canonical format.  A panel is 16 tile rows that share tensor memory (for a

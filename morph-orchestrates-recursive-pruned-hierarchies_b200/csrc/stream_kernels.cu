@@ -11,6 +11,7 @@
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <cstdint>
+#include <mutex>
 #include "common.h"
 
 namespace {
@@ -507,4 +508,51 @@ extern "C" int mortar_mlp_decode(const mortar_stream *gate_up, const mortar_stre
     return mortar_linear(down, hp, h_planes, rows * (int64_t)d_ff, d_ff, rows, y,
                          y_dtype == MORTAR_F32 ? MORTAR_OUT_F32 : MORTAR_OUT_BF16, 0, 0, ldy,
                          rb | (flags & MORTAR_FLAG_ACCUMULATE) | (gates ? MORTAR_FLAG_GATES_ON_INPUT : 0), gates, ld_gates, cs, nullptr, 0, nullptr, 0, stream);
+}
+
+// ---- MLP application on built-in scratch ---------------------------------------------------
+// Scratch for mortar_mlp_decode_static: activation planes of the input and of the hidden
+// layer.  It lives in the library image, so every GPU that loads the library holds these
+// bytes until the process exits.
+#define MORTAR_STATIC_SCRATCH_BYTES (8u << 20)
+static __device__ __align__(256) unsigned char g_mlp_static_scratch[MORTAR_STATIC_SCRATCH_BYTES];
+
+namespace {
+std::mutex g_static_scratch_mutex;
+void *g_static_scratch_ptr[64] = {nullptr};   // device address of the array, per device ordinal
+}  // namespace
+
+extern "C" int64_t mortar_mlp_static_scratch_bytes(void) { return (int64_t)MORTAR_STATIC_SCRATCH_BYTES; }
+
+extern "C" int mortar_mlp_decode_static(const mortar_stream *gate_up, const mortar_stream *down,
+                                        const void *x, int x_dtype, int64_t ldx, int64_t rows,
+                                        const float *rms_weight, float eps, const float *gates,
+                                        int64_t ld_gates, int32_t n_clusters, void *y, int y_dtype,
+                                        int64_t ldy, int32_t n_planes, int32_t flags, void *stream) {
+    if (!gate_up || !down) return MORTAR_ERR_NULL;
+    if (n_planes < 1 || n_planes > 3 || rows < 0) return MORTAR_ERR_DTYPE;
+    const int64_t need = mortar_mlp_workspace_bytes(rows, gate_up->tile_cols * 16, gate_up->tile_rows * 8,
+                                                    n_planes);
+    if (need < 0) return (int)need;
+    if (need > (int64_t)MORTAR_STATIC_SCRATCH_BYTES) return MORTAR_ERR_CAPACITY;   // rows too large for the built-in scratch
+    int dev = 0;
+    MORTAR_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return MORTAR_ERR_CAPACITY;
+    void *scratch = nullptr;
+    {
+        // First call on this device: resolve the device address of the array.  The array's
+        // name is only a host-side handle; kernels must be given the address from here.
+        std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+        if (g_static_scratch_ptr[dev] == nullptr) {
+            void *ptr = nullptr;
+            MORTAR_CUDA_CHECK(cudaGetSymbolAddress(&ptr, g_mlp_static_scratch));
+            g_static_scratch_ptr[dev] = ptr;
+        }
+        scratch = g_static_scratch_ptr[dev];
+    }
+    // Every plane element the two stages read is written earlier in the same call, so nothing
+    // in the scratch has to start at zero and stale contents of a previous call are harmless.
+    return mortar_mlp_decode(gate_up, down, x, x_dtype, ldx, rows, rms_weight, eps, gates, ld_gates,
+                             n_clusters, y, y_dtype, ldy, n_planes, flags, scratch,
+                             (int64_t)MORTAR_STATIC_SCRATCH_BYTES, stream);
 }

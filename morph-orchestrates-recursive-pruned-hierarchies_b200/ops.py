@@ -212,6 +212,40 @@ def mlp_decode(x: torch.Tensor, gate_up: StreamMatrix, down: StreamMatrix, *,
     return out.reshape(*lead, d_model)
 
 
+def mlp_decode_static(x: torch.Tensor, gate_up: StreamMatrix, down: StreamMatrix, out: torch.Tensor, *,
+                      rms_weight: Optional[torch.Tensor] = None, eps: float = 1e-6,
+                      gates: Optional[torch.Tensor] = None, n_clusters: int = 0,
+                      n_planes: int = 3, round_bf16: bool = False, accumulate: bool = False) -> torch.Tensor:
+    """``mlp_decode`` for callers that must not allocate: the activation planes go to an 8 MiB
+    array built into the library instead of a workspace tensor, and the result is written to
+    the caller's ``out``.  Every argument must already be a contiguous CUDA tensor of its final
+    dtype (fp32 gates / rms_weight): this wrapper converts and allocates nothing.  Raises
+    ``ValueError`` when the batch needs more than the built-in scratch.  Calls share the
+    scratch, so run them one after another on a stream, not concurrently."""
+    global _launches
+    _require_cuda(x, "x")
+    d_model, d_ff = gate_up.in_features, gate_up.out_features // 2
+    if x.dim() != 2 or x.shape[1] != d_model or x.stride(1) != 1:
+        raise ValueError("x must be [rows, d_model] with unit inner stride")
+    if out.shape != x.shape or out.stride(1) != 1 or not out.is_cuda:
+        raise ValueError("out must be a CUDA tensor shaped like x")
+    for name, t in (("rms_weight", rms_weight), ("gates", gates)):
+        if t is not None and (t.dtype != torch.float32 or not t.is_cuda or not t.is_contiguous()):
+            raise ValueError(f"{name} must be a contiguous float32 CUDA tensor")
+    rows = x.shape[0]
+    if rows == 0:
+        return out
+    gu, dn = gate_up.c_struct(), down.c_struct()
+    _lib.check(_lib.lib().mortar_mlp_decode_static(
+        C.byref(gu), C.byref(dn), _ptr(x), _dtype_code(x), x.stride(0), rows, _ptr(rms_weight), float(eps),
+        _ptr(gates), gates.stride(0) if gates is not None else 0, int(n_clusters), _ptr(out),
+        _dtype_code(out), out.stride(0), int(n_planes),
+        (_lib.FLAG_ROUND_BF16 if round_bf16 else 0) | (_lib.FLAG_ACCUMULATE if accumulate else 0),
+        _stream_ptr()), "mortar_mlp_decode_static")
+    _launches += 3
+    return out
+
+
 def mlp_prefill(x: torch.Tensor, gate_up: StreamMatrix, down: StreamMatrix, *,
                 gates: Optional[torch.Tensor] = None, n_clusters: int = 0,
                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
