@@ -344,8 +344,20 @@ int launch_wpr(const LinearParams &p, int wpr, unsigned grid_y, cudaStream_t st)
 
 template <int P, bool SWIGLU>
 int launch_nt(const LinearParams &p, int wpr, cudaStream_t st) {
-    if (p.rows <= 8) return launch_wpr<1, P, SWIGLU>(p, wpr, 1, st);
-    if (p.rows <= 16) return launch_wpr<2, P, SWIGLU>(p, wpr, 1, st);
+    // Small matrices and small batches are latency-bound: prefer many light CTAs (8 rows each,
+    // weights re-read from L2 per row block) until the grid covers the GPU a few times over.
+    const int upc = kWarpsPerCta / wpr;
+    const long long ctas_x = (p.units + upc - 1) / upc;
+    const long long blocks8 = (p.rows + 7) / 8;
+    if (p.rows <= 8 || ctas_x * blocks8 <= 148 * 16) {
+        if (blocks8 > 65535) return MORTAR_ERR_CAPACITY;
+        return launch_wpr<1, P, SWIGLU>(p, wpr, (unsigned)blocks8, st);
+    }
+    const long long blocks16 = (p.rows + 15) / 16;
+    if (p.rows <= 16 || ctas_x * blocks16 <= 148 * 16) {
+        if (blocks16 > 65535) return MORTAR_ERR_CAPACITY;
+        return launch_wpr<2, P, SWIGLU>(p, wpr, (unsigned)blocks16, st);
+    }
     const long long blocks = (p.rows + 31) / 32;
     if (blocks > 65535) return MORTAR_ERR_CAPACITY;
     return launch_wpr<4, P, SWIGLU>(p, wpr, (unsigned)blocks, st);
