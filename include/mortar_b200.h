@@ -220,6 +220,39 @@ int mortar_mlp_decode_static(const mortar_stream *gate_up, const mortar_stream *
                              void *y, int y_dtype, int64_t ldy,
                              int32_t n_planes, int32_t flags, void *stream);
 
+/* ---- persistent decode of a stack of MLP applications ---------------------------------
+ * One launch runs x <- x + MLP_i(rmsnorm_i(x)) for a whole list of MLP applications (the MLP
+ * sites of one decode step in StaticDecodeEngine's site order,
+ * morph/inference/engine.py:207-213, with the residual add of
+ * morph/model/hyper_connections.py:182-229), fp32 semantics as mortar_mlp_decode.
+ * Each block of 8 activation rows is owned by one thread-block cluster that walks the whole
+ * list by itself: the residual rows, their normalised planes and the hidden slice stay in
+ * shared memory, CTAs exchange partial sums through distributed shared memory and meet at
+ * cluster barriers (hardware, bounded by construction), and the weights of application i+1
+ * stream into shared memory while application i computes.
+ *
+ * Weights come as per-(layer, cluster rank) blobs built on the host (16-byte aligned):
+ *   int32 hdr[16] = { n_gate_up_groups, n_down_groups, byte offsets of gate_up grp_ptr,
+ *                     grp_cols, grp_codes, down grp_ptr, grp_cols, grp_codes,
+ *                     gate_up scale bits, down scale bits, blob bytes, 0... }
+ * where rank c's gate_up part is the stream layout of gate tile rows [cU,(c+1)U) followed by
+ * the matching up tile rows (U = d_ff/16/cluster_size) and its down part is the stream layout
+ * of all output tile rows restricted to hidden tile columns [cU,(c+1)U) (column indices local).
+ *   blobs        device bytes
+ *   blob_table   device int32 [n_layers][cluster_size][2] = {offset in 16-byte units, bytes}
+ *   app_layer    device int32 [n_apps] layer of every application
+ *   rms_weights  device fp32 [n_layers][d_model], or NULL for no normalisation
+ *   x            fp32 [rows][ldx] residual carrier, updated in place
+ *   status       device int32, set non-zero if a bounded wait inside the kernel expires
+ * Limits: cluster_size 8 (or 16 where the device accepts it), d_ff/16 and d_model divisible
+ * by cluster_size, everything of one application's rank share must fit shared memory
+ * (MORTAR_ERR_CAPACITY otherwise: use mortar_mlp_decode per application). */
+int mortar_stack_decode(const void *blobs, const int32_t *blob_table, const int32_t *app_layer,
+                        const float *rms_weights, int32_t n_apps, int32_t n_layers,
+                        int32_t d_model, int32_t d_ff, int32_t max_blob_bytes, int32_t cluster_size,
+                        float *x, int64_t ldx, int64_t rows, float eps, int32_t n_planes,
+                        int32_t *status, void *stream);
+
 /* ---- prefill: tcgen05 / tensor-memory path --------------------------------------------
  * Execution layout for blocks of 128 activation rows ("panel schedule"), built once on the
  * host from the canonical format.  A panel is 16 tile rows that share tensor memory (for a

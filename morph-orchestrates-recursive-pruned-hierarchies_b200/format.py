@@ -201,6 +201,29 @@ class MortarMatrix:
         m[rows, self.col_idx.astype(np.int64)] = True
         return m
 
+    def slice_tile_rows(self, tile_rows) -> "MortarMatrix":
+        """Sub-matrix made of the listed tile rows, in the listed order (same columns, same scale)."""
+        tile_rows = np.asarray(tile_rows, dtype=np.int64)
+        counts = (self.row_ptr[tile_rows + 1] - self.row_ptr[tile_rows]).astype(np.int64)
+        idx = np.concatenate([np.arange(self.row_ptr[r], self.row_ptr[r + 1]) for r in tile_rows]) \
+            if len(tile_rows) else np.zeros(0, dtype=np.int64)
+        row_ptr = np.zeros(len(tile_rows) + 1, dtype=np.int32)
+        np.cumsum(counts, out=row_ptr[1:])
+        return MortarMatrix(len(tile_rows) * TILE, self.in_features, row_ptr,
+                            np.ascontiguousarray(self.col_idx[idx]), np.ascontiguousarray(self.codes[idx]),
+                            self.scale)
+
+    def slice_tile_cols(self, c0: int, c1: int) -> "MortarMatrix":
+        """Sub-matrix of tile columns [c0, c1) (all rows; column indices become local)."""
+        keep = (self.col_idx >= c0) & (self.col_idx < c1)
+        rows = np.repeat(np.arange(self.tile_rows), np.diff(self.row_ptr))
+        counts = np.bincount(rows[keep], minlength=self.tile_rows)
+        row_ptr = np.zeros(self.tile_rows + 1, dtype=np.int32)
+        np.cumsum(counts, out=row_ptr[1:])
+        return MortarMatrix(self.out_features, (c1 - c0) * TILE, row_ptr,
+                            np.ascontiguousarray((self.col_idx[keep] - c0).astype(np.uint16)),
+                            np.ascontiguousarray(self.codes[keep]), self.scale)
+
     def algorithmic_bytes(self) -> int:
         """Bytes a kernel must read to use this matrix once: 64 per tile of codes, 2 per tile of
         column index, 4 per row pointer, 4 of scale."""

@@ -246,6 +246,106 @@ def mlp_decode_static(x: torch.Tensor, gate_up: StreamMatrix, down: StreamMatrix
     return out
 
 
+class _StackBlobs:
+    """Per-(layer, cluster rank) weight blobs of a stack for one cluster size."""
+
+    def __init__(self, layers, d_model, d_ff, cs, device):
+        import numpy as np
+        F_ = d_ff // TILE
+        U = F_ // cs
+        blobs, table, off = [], np.zeros((len(layers), cs, 2), dtype=np.int32), 0
+        for li, (gu, dn, w) in enumerate(layers):
+            wb = b"" if w is None else w.detach().float().cpu().numpy().astype(np.float32).tobytes()
+            for c in range(cs):
+                rows = list(range(c * U, (c + 1) * U)) + list(range(F_ + c * U, F_ + (c + 1) * U))
+                parts = []
+                for sub in (gu.slice_tile_rows(rows), dn.slice_tile_cols(c * U, (c + 1) * U)):
+                    gp, gc, gcd, G = sub.build_stream_host()
+                    parts.append((G, gp.tobytes(), gc[:max(G, 1) * 8].tobytes(), gcd[:max(G, 1) * 512].tobytes()))
+                hdr = np.zeros(16, dtype=np.int32)
+                body, pos = [], 64
+                for k, raw in enumerate([parts[0][1], parts[0][2], parts[0][3], parts[1][1], parts[1][2],
+                                         parts[1][3], wb]):
+                    if k == 6:
+                        hdr[11] = pos if raw else 0
+                    else:
+                        hdr[2 + k] = pos
+                    pad = (-len(raw)) % 16
+                    body.append(raw + b"\0" * pad)
+                    pos += len(raw) + pad
+                hdr[0], hdr[1] = parts[0][0], parts[1][0]
+                hdr[8] = np.float32(gu.scale).view(np.int32)
+                hdr[9] = np.float32(dn.scale).view(np.int32)
+                hdr[10] = pos
+                blob = hdr.tobytes() + b"".join(body)
+                table[li, c] = (off // 16, len(blob))
+                blobs.append(blob)
+                off += len(blob)
+        self.cs = cs
+        self.max_blob = (int(table[:, :, 1].max()) + 127) // 128 * 128
+        self.blobs = torch.from_numpy(np.frombuffer(b"".join(blobs), dtype=np.uint8).copy()).to(device)
+        self.table = torch.from_numpy(table.reshape(-1)).to(device)
+
+
+class DecodeStack:
+    """A list of MLP applications (the MLP sites of one decode step, in execution order) that
+    one persistent launch walks: x <- x + MLP_i(rmsnorm_i(x)).  `layers` are (gate_up, down,
+    rms_weight) triples of canonical ``MortarMatrix`` / fp32 tensor (or None); `order` indexes
+    into them.  Every thread-block cluster rank gets its share of each layer as one blob: the
+    gate/up tile rows of its hidden slice and the matching K-slice of the down projection.
+    Blobs are built for clusters of 8 and, where the shapes divide, of 16 (used for small
+    batches, where only a few clusters run and 16 SMs per row block halve the latency)."""
+
+    def __init__(self, layers, order, device="cuda", cluster_sizes=(8, 16)):
+        self.order = list(order)
+        gu0, dn0, _ = layers[0]
+        self.d_model, self.d_ff = gu0.in_features, gu0.out_features // 2
+        for gu, dn, w in layers:
+            if (gu.in_features, gu.out_features // 2) != (self.d_model, self.d_ff) or \
+                    (dn.in_features, dn.out_features) != (self.d_ff, self.d_model):
+                raise ValueError("every application of a stack must have the same d_model and d_ff")
+        self.variants = {}
+        for cs in cluster_sizes:
+            if (self.d_ff // TILE) % cs == 0 and self.d_model % (4 * cs) == 0:
+                self.variants[cs] = _StackBlobs(layers, self.d_model, self.d_ff, cs, device)
+        if not self.variants:
+            raise ValueError("d_ff/16 and d_model/4 must be divisible by the cluster size (8 or 16)")
+        self.app_layer = torch.tensor(self.order, dtype=torch.int32, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.n_apps, self.n_layers = len(self.order), len(layers)
+
+    def pick(self, rows: int) -> "_StackBlobs":
+        # at most 4 clusters of 16 CTAs are co-resident on the 8 GPCs: use them for <= 32 rows
+        if 16 in self.variants and (rows <= 32 or 8 not in self.variants):
+            return self.variants[16]
+        return self.variants[8] if 8 in self.variants else next(iter(self.variants.values()))
+
+    def error(self, reset: bool = True) -> int:
+        """Non-zero if a bounded wait inside the kernel expired (synchronises)."""
+        v = int(self.status.item())
+        if reset and v:
+            self.status.zero_()
+        return v
+
+
+def stack_decode(x: torch.Tensor, stack: DecodeStack, *, eps: float = 1e-6, n_planes: int = 3,
+                 cluster_size: Optional[int] = None) -> torch.Tensor:
+    """In-place decode step of a whole MLP stack on the fp32 residual carrier x [rows, d_model]:
+    one launch, every block of 8 rows walks all applications inside one thread-block cluster."""
+    global _launches
+    _require_cuda(x, "x")
+    if x.dtype != torch.float32 or x.dim() != 2 or x.shape[1] != stack.d_model or x.stride(1) != 1:
+        raise ValueError("x must be float32 [rows, d_model] with unit inner stride")
+    rows = x.shape[0]
+    v = stack.variants[cluster_size] if cluster_size else stack.pick(rows)
+    _lib.check(_lib.lib().mortar_stack_decode(
+        _ptr(v.blobs), _ptr(v.table), _ptr(stack.app_layer), None, stack.n_apps, stack.n_layers,
+        stack.d_model, stack.d_ff, v.max_blob, v.cs, _ptr(x), x.stride(0), rows,
+        float(eps), int(n_planes), _ptr(stack.status), _stream_ptr()), "mortar_stack_decode")
+    _launches += 1
+    return x
+
+
 def mlp_prefill(x: torch.Tensor, gate_up: StreamMatrix, down: StreamMatrix, *,
                 gates: Optional[torch.Tensor] = None, n_clusters: int = 0,
                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
