@@ -428,9 +428,9 @@ def run_ours(args, rank, world, local_rank):
     print(json.dumps(line), flush=True)
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of bcsr_stream_kernel, from the ncu
-# capture summarised in profiles/ (cold caches under ncu; null until a capture exists)
-TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one stack_decode_kernel launch at batch 64, from
+# the ncu capture summarised in profiles/stack_decode_kernel_decode_stack_b64.md
+TRAFFIC_BYTES_PER_LAUNCH = 6170368
 
 
 def run_prefill(mb, device, pk, flush, tokens: int = PREFILL_TOKENS, reps: int = 3):
