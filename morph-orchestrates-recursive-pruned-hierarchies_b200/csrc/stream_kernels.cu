@@ -44,6 +44,8 @@ struct LinearParams {
     const int *col_act;
     long long ld_col_act;
     int units;                         // output tile rows (LINEAR) or hidden tile rows (SWIGLU)
+    int fold;                          // >0: the planes are folded into the 8 MMA columns (see below)
+    long long real_rows;               // activation rows when fold > 0 (rows = fold * real_rows)
 };
 
 __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
@@ -104,7 +106,8 @@ bcsr_stream_kernel(const LinearParams p) {
     const int unit_local = warp / WPR, sub = warp % WPR;
     const int unit = blockIdx.x * UPC + unit_local;
     const long long row0 = (long long)blockIdx.y * (8 * NT);
-    const int nrows = (int)min((long long)(8 * NT), p.rows - row0);
+    // with folded planes the MMA columns are virtual rows; gates and flags are per real row
+    const int nrows = p.fold > 0 ? (int)p.real_rows : (int)min((long long)(8 * NT), p.rows - row0);
 
     __shared__ float red[(WPR > 1) ? UPC * (WPR - 1) * NACC * NT * 4 * 32 : 1];
     __shared__ unsigned char col_active[kMaxFlagCols];
@@ -252,35 +255,59 @@ bcsr_stream_kernel(const LinearParams p) {
 
     // Epilogue.  acc[.][n][0..3] = (neuron g, row 2t), (g, 2t+1), (g+8, 2t), (g+8, 2t+1).
     const float scale = p.round_bf16 ? round_bf16(p.scale) : p.scale;
+    auto emit = [&](long long row, int neuron_local, float sum_a, float sum_b) {
+        const int neuron = unit * 16 + neuron_local;
+        float v;
+        if (SWIGLU) {
+            float gv = scale * sum_a;
+            float uv = scale * sum_b;
+            float gate = 1.f;
+            if (p.gates != nullptr) gate = p.gates[row * p.ld_gates + neuron / p.cluster_size];
+            if (p.round_bf16) {
+                gv = round_bf16(gv);
+                uv = round_bf16(uv);
+                const float sg = round_bf16(gv / (1.f + expf(-gv)));
+                v = round_bf16(sg * uv);
+                if (p.gates != nullptr) v = round_bf16(v * round_bf16(gate));
+            } else {
+                v = gv * (1.f / (1.f + expf(-gv))) * uv;
+                if (p.gates != nullptr) v *= gate;
+            }
+            if (!active || (p.gates != nullptr && !(gate > 0.f))) v = 0.f;
+        } else {
+            v = scale * sum_a;
+            if (!active) v = 0.f;
+        }
+        store_value(p, row, neuron, v);
+    };
+    if (NT == 1 && P == 1 && p.fold > 0) {
+        // Folded planes: MMA column pl*real_rows + b holds plane pl of activation row b, so the
+        // value of row b is the sum of `fold` columns.  Stage the 16x8 tile and combine.
+        __shared__ float fold_s[UPC][NACC][16][9];
+#pragma unroll
+        for (int a = 0; a < NACC; ++a)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) fold_s[unit_local][a][g + 8 * (i >> 1)][2 * t + (i & 1)] = acc[a][0][i];
+        __syncwarp();
+        const int rr = (int)p.real_rows;
+        for (int idx = lane; idx < 16 * rr; idx += 32) {
+            const int neuron_local = idx & 15, b = idx >> 4;
+            float sa = 0.f, sb = 0.f;
+            for (int pl = 0; pl < p.fold; ++pl) {
+                sa += fold_s[unit_local][0][neuron_local][pl * rr + b];
+                sb += fold_s[unit_local][NACC - 1][neuron_local][pl * rr + b];
+            }
+            emit(b, neuron_local, sa, sb);
+        }
+        return;
+    }
 #pragma unroll
     for (int n = 0; n < NT; ++n) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const long long row = row0 + n * 8 + 2 * t + (i & 1);
             if (row >= p.rows) continue;
-            const int neuron = unit * 16 + g + 8 * (i >> 1);
-            float v;
-            if (SWIGLU) {
-                float gv = scale * acc[0][n][i];
-                float uv = scale * acc[NACC - 1][n][i];
-                float gate = 1.f;
-                if (p.gates != nullptr) gate = p.gates[row * p.ld_gates + neuron / p.cluster_size];
-                if (p.round_bf16) {
-                    gv = round_bf16(gv);
-                    uv = round_bf16(uv);
-                    const float sg = round_bf16(gv / (1.f + expf(-gv)));
-                    v = round_bf16(sg * uv);
-                    if (p.gates != nullptr) v = round_bf16(v * round_bf16(gate));
-                } else {
-                    v = gv * (1.f / (1.f + expf(-gv))) * uv;
-                    if (p.gates != nullptr) v *= gate;
-                }
-                if (!active || (p.gates != nullptr && !(gate > 0.f))) v = 0.f;
-            } else {
-                v = scale * acc[0][n][i];
-                if (!active) v = 0.f;
-            }
-            store_value(p, row, neuron, v);
+            emit(row, g + 8 * (i >> 1), acc[0][n][i], acc[NACC - 1][n][i]);
         }
     }
 }
@@ -444,6 +471,15 @@ extern "C" int mortar_linear(const mortar_stream *w, const void *planes, int32_t
     if (!swiglu && !gates_on_input) p.gates = nullptr;
     if (!swiglu && gates_on_input && !p.gates_on_input) p.gates = nullptr;
     p.units = units;
+    p.fold = 0;
+    p.real_rows = rows;
+    // Small batches: fold the P exact planes into the 8 columns of one MMA (one MMA and one pair
+    // of activation loads per tile instead of P of each).  Needs the planes back to back.
+    if (n_planes > 1 && rows * n_planes <= 8 && plane_stride == rows * ld_planes) {
+        p.fold = n_planes;
+        p.rows = rows * n_planes;
+        p.n_planes = 1;
+    }
 
     const double avg = (double)w->n_groups / (double)units;   // groups per unit
     const int wpr = avg >= 3.0 ? 4 : (avg >= 1.5 ? 2 : 1);

@@ -184,6 +184,33 @@ class MortarMatrix:
             cms.mortar_offsets.detach().cpu().numpy(), cms.mortar_column_indices.detach().cpu().numpy(),
             packed, scale, blk, cms.out_features, cms.in_features, drop_zero_tiles)
 
+    @staticmethod
+    def from_state_dict(state: dict, prefix: str, out_features: int, in_features: int,
+                        blocking: int = 128, drop_zero_tiles: bool = False) -> "MortarMatrix":
+        """A carved layer straight from a checkpoint ``state_dict``: the keys the reference
+        persists (``{prefix}mortar_offsets``, ``mortar_column_indices`` and either the packed pair
+        ``mortar_packed`` / ``mortar_scale`` of deploy_quant.py:361-365 or the unpacked
+        ``mortar_data`` of block_sparse.py:783-799, which is ternarised with the deploy rule)."""
+        def get(name):
+            v = state[prefix + name]
+            return v.detach().cpu() if isinstance(v, torch.Tensor) else torch.as_tensor(v)
+        for k in ("mortar_offsets", "mortar_column_indices"):
+            if prefix + k not in state:
+                raise KeyError(f"{prefix}{k} missing: the layer was not carved when it was saved")
+        if prefix + "mortar_packed" in state:
+            packed = get("mortar_packed").numpy()
+            scale = float(get("mortar_scale"))
+        elif prefix + "mortar_data" in state:
+            data = get("mortar_data")
+            blocking = int(data.shape[1])
+            q, scale = ternary_quantize(data)
+            packed = pack_codes_2bit(q.numpy().reshape(-1, 4)).reshape(-1)
+        else:
+            raise KeyError(f"neither {prefix}mortar_packed nor {prefix}mortar_data in the state dict")
+        return MortarMatrix.from_reference_bcsr(get("mortar_offsets").numpy(),
+                                                get("mortar_column_indices").numpy(), packed, scale,
+                                                blocking, out_features, in_features, drop_zero_tiles)
+
     # ---- views ----------------------------------------------------------------------
     def to_dense_codes(self) -> np.ndarray:
         """int8 [out, in] with zeros in pruned tiles."""

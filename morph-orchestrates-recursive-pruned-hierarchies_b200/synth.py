@@ -121,6 +121,35 @@ def make_layer(d_model: int, d_ff: int, density: float = 0.25, seed: int = 0,
     return SynthLayer(d_model, d_ff, mats[0], mats[1])
 
 
+def make_block_matrix(out_features: int, in_features: int, density: float = 0.25, blocking: int = 128,
+                      ragged: bool = True, seed: int = 0, scale: float = 0.02) -> MortarMatrix:
+    """Block-aligned ragged topology in the shape of the reference's large-model decode bench
+    (tile-prover/proofs/decode/gemv_bw_30b.py:124-165): every block row keeps
+    round(density*C*(0.5+u)) random block columns, u ~ U(0,1); codes are uniform over {-1,0,+1}.
+    Returned in the canonical tile-16 format (each kept block = (blocking/16)^2 tiles)."""
+    rng = np.random.default_rng(seed)
+    Rb, Cb = out_features // blocking, in_features // blocking
+    tpb = blocking // TILE
+    rows_cols = []
+    for _ in range(Rb):
+        k = int(round(density * Cb * (0.5 + rng.random()))) if ragged else int(round(density * Cb))
+        k = max(1, min(Cb, k))
+        rows_cols.append(np.sort(rng.permutation(Cb)[:k]))
+    row_ptr = [0]
+    col_idx = []
+    for cols in rows_cols:
+        tile_cols = (cols[:, None] * tpb + np.arange(tpb)[None, :]).reshape(-1)
+        for _ in range(tpb):
+            col_idx.append(tile_cols)
+            row_ptr.append(row_ptr[-1] + tile_cols.size)
+    col_idx = np.concatenate(col_idx).astype(np.uint16)
+    nnz = int(row_ptr[-1])
+    stored = rng.integers(0, 3, size=(nnz, 64, 4), dtype=np.uint8)
+    codes = (stored[..., 0] | (stored[..., 1] << 2) | (stored[..., 2] << 4) | (stored[..., 3] << 6))
+    return MortarMatrix(out_features, in_features, np.asarray(row_ptr, dtype=np.int32), col_idx,
+                        np.ascontiguousarray(codes.astype(np.uint8)), float(scale))
+
+
 def make_activations(rows: int, d_model: int, seed: int, dtype=torch.bfloat16) -> torch.Tensor:
     """x ~ N(0,1), RMS-normalised (eps 1e-6, unit weight), cast to `dtype`."""
     gen = torch.Generator().manual_seed(seed)

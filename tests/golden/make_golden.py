@@ -144,6 +144,9 @@ def build_case(name, d_model, d_ff, blocking, n_clusters, ratio, x_shape, seed, 
     if "logits" in cap and cap["logits"].shape[-1] == n_clusters:
         out["router_logits"] = cap["logits"].numpy().copy()
         out["router_gates"] = g2.numpy().copy()
+        # the router's own parameters, so a mirror can be loaded and run on the same input
+        for k, v in r2.state_dict().items():
+            out["router_sd__" + k.replace(".", "__")] = v.detach().numpy().copy()
 
     path = os.path.join(HERE, f"{name}.npz")
     np.savez_compressed(path, **out)

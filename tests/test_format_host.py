@@ -277,3 +277,53 @@ def test_prefill_schedule_covers_every_tile_once(swiglu, density):
         # a full panel fuses each of its columns into a single N=256 run
         rec0 = data[:int(h["step_off"][1]) * 16]
         assert int((rec0[16:32].view(np.uint32)[3] >> 17) & 0x3F) == 32
+
+
+@pytest.mark.parametrize("case", GOLDEN_CASES)
+def test_state_dict_ingestion(case):
+    """mortar_* checkpoint keys (packed and unpacked flavours) -> canonical matrix."""
+    from conftest import bf16_from_bits
+    g = load_golden(case)
+    d_model, d_ff, blk, ncls = (int(v) for v in g["meta"])
+    for tag, (O, I) in (("gu", (2 * d_ff, d_model)), ("dn", (d_model, d_ff))):
+        direct = mb.MortarMatrix.from_reference_bcsr(g[f"{tag}_offsets"], g[f"{tag}_column_indices"],
+                                                     g[f"{tag}_packed"], float(g[f"{tag}_scale"]), blk, O, I)
+        sd = {"mlp.x._cms.mortar_offsets": torch.from_numpy(g[f"{tag}_offsets"]),
+              "mlp.x._cms.mortar_column_indices": torch.from_numpy(g[f"{tag}_column_indices"]),
+              "mlp.x._cms.mortar_packed": torch.from_numpy(g[f"{tag}_packed"]),
+              "mlp.x._cms.mortar_scale": torch.tensor(float(g[f"{tag}_scale"]))}
+        m = mb.MortarMatrix.from_state_dict(sd, "mlp.x._cms.", O, I, blocking=blk)
+        np.testing.assert_array_equal(m.codes, direct.codes)
+        assert m.scale == direct.scale
+        nnz = g[f"{tag}_codes"].shape[0]
+        sd2 = {"p.mortar_offsets": sd["mlp.x._cms.mortar_offsets"],
+               "p.mortar_column_indices": sd["mlp.x._cms.mortar_column_indices"],
+               "p.mortar_data": bf16_from_bits(g[f"{tag}_data_bf16"]).reshape(nnz, blk, blk)}
+        m2 = mb.MortarMatrix.from_state_dict(sd2, "p.", O, I)
+        np.testing.assert_array_equal(m2.codes, direct.codes)
+        assert np.float32(m2.scale) == np.float32(direct.scale)
+    with pytest.raises(KeyError):
+        mb.MortarMatrix.from_state_dict({}, "p.", 64, 64)
+
+
+def test_router_mirror_matches_reference_gates():
+    """TileRouter mirror loaded with the reference router's own parameters reproduces the
+    reference's logits and gates on the same input."""
+    from importlib import import_module
+    from conftest import bf16_from_bits
+    router = import_module(mb.__name__ + ".router")
+    g = load_golden("mlp_tile16_d128_cs16")
+    r = router.TileRouter(16, 128, activation_ratio=0.25)
+    assert r.activation_k == int(g["k"]) and r.n_sub_keys == 4
+    sd = {k[len("router_sd__"):].replace("__", "."): torch.from_numpy(v)
+          for k, v in g.items() if k.startswith("router_sd__")}
+    assert set(sd) == set(r.state_dict())
+    r.load_state_dict(sd)
+    r.eval()
+    x = bf16_from_bits(g["x_bf16"]).float().reshape(-1, 128)
+    with torch.no_grad():
+        logits = r.group_logits(x)
+        gates, aux = r(x)
+    np.testing.assert_allclose(logits.numpy(), g["router_logits"], rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(gates.numpy(), g["router_gates"], rtol=1e-4, atol=1e-6)
+    assert aux.ndim == 0 and float(aux) >= 0
