@@ -180,16 +180,25 @@ __device__ __forceinline__ void expand_row(uint32_t w, uint4 &lo, uint4 &hi) {
     hi = make_uint4(out[4], out[5], out[6], out[7]);
 }
 
-// One output value of the epilogue with the reference's rounding points.
-__device__ __forceinline__ float finish(const PrefillParams &p, float acc_a, float acc_b, bool live_a,
-                                        bool live_b, float gate, bool gated) {
-    float g = live_a ? rbf(p.scale * acc_a) : 0.f;
-    if (!p.swiglu) return g;
-    const float u = live_b ? rbf(p.scale * acc_b) : 0.f;
-    const float sg = rbf(__fdividef(g, 1.f + __expf(-g)));
-    float hv = rbf(sg * u);
-    if (gated) hv = gate > 0.f ? rbf(hv * rbf(gate)) : 0.f;
-    return hv;
+// Two adjacent outputs of the epilogue with the reference's rounding points, in packed bf16:
+// the reference's ops ARE bf16 ops (each rounds to nearest even), so after the fp32 scale and
+// the fp32 silu the products are single bf16x2 multiplies.
+__device__ __forceinline__ uint32_t finish2(float scale, bool swiglu, float a0, float a1, float b0, float b1,
+                                            bool live_a, bool live_b, bool gated, float gate0, float gate1) {
+    __nv_bfloat162 g2 = __floats2bfloat162_rn(live_a ? scale * a0 : 0.f, live_a ? scale * a1 : 0.f);
+    if (!swiglu) return *reinterpret_cast<uint32_t *>(&g2);
+    const __nv_bfloat162 u2 = __floats2bfloat162_rn(live_b ? scale * b0 : 0.f, live_b ? scale * b1 : 0.f);
+    const float gx = __low2float(g2), gy = __high2float(g2);
+    const __nv_bfloat162 s2 = __floats2bfloat162_rn(__fdividef(gx, 1.f + __expf(-gx)),
+                                                    __fdividef(gy, 1.f + __expf(-gy)));
+    __nv_bfloat162 h2 = __hmul2(s2, u2);
+    if (gated) {
+        h2 = __hmul2(h2, __floats2bfloat162_rn(gate0, gate1));
+        // a gate of zero (inactive group) yields an exact zero
+        if (!(gate0 > 0.f)) h2.x = __float2bfloat16_rn(0.f);
+        if (!(gate1 > 0.f)) h2.y = __float2bfloat16_rn(0.f);
+    }
+    return *reinterpret_cast<uint32_t *>(&h2);
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -257,19 +266,18 @@ prefill_panel_kernel(const __grid_constant__ CUtensorMap tmap_x, const PrefillPa
                 uint32_t packed[16];
 #pragma unroll
                 for (int e = 0; e < 32; e += 2) {
-                    float v[2];
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        const int jj = j + ((e + h) >> 4);
-                        const bool live_a = (mask >> jj) & 1u;
-                        const bool live_b = p.swiglu ? ((mask >> (units + jj)) & 1u) : true;
-                        float gate = 1.f;
-                        if (gated) gate = p.gates[row * p.ld_gates + (col0 + e + h) / p.cluster_size];
-                        v[h] = finish(p, __uint_as_float(a[e + h]), p.swiglu ? __uint_as_float(b[e + h]) : 0.f,
-                                      live_a, live_b, gate, gated);
+                    const int jj = j + (e >> 4);
+                    const bool live_a = (mask >> jj) & 1u;
+                    const bool live_b = p.swiglu ? ((mask >> (units + jj)) & 1u) : true;
+                    float gate0 = 1.f, gate1 = 1.f;
+                    if (gated) {
+                        gate0 = p.gates[row * p.ld_gates + (col0 + e) / p.cluster_size];
+                        gate1 = p.gates[row * p.ld_gates + (col0 + e + 1) / p.cluster_size];
                     }
-                    __nv_bfloat162 pr = __floats2bfloat162_rn(v[0], v[1]);
-                    packed[e >> 1] = *reinterpret_cast<uint32_t *>(&pr);
+                    packed[e >> 1] = finish2(p.scale, p.swiglu != 0, __uint_as_float(a[e]), __uint_as_float(a[e + 1]),
+                                             p.swiglu ? __uint_as_float(b[e]) : 0.f,
+                                             p.swiglu ? __uint_as_float(b[e + 1]) : 0.f, live_a, live_b,
+                                             gated, gate0, gate1);
                 }
                 if (in_range) {
                     uint4 *dst = reinterpret_cast<uint4 *>(p.out + row * p.ld_out + col0);
