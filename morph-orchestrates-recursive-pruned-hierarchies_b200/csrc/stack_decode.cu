@@ -18,6 +18,7 @@
 #include <cooperative_groups.h>
 #include <cstdint>
 #include "common.h"
+#include "decode.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -57,15 +58,6 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4],
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// Two 2-bit stored values (bits 2q and 16+2q of `word`) -> packed bf16 pair of codes.
-__device__ __forceinline__ uint32_t decode_pair(uint32_t word, int q) {
-    uint32_t v = ((word >> (2 * q)) & 0x00030003u) | 0x43004300u;
-    const uint32_t k129 = 0x43014301u;
-    __nv_bfloat162 r = __hsub2(*reinterpret_cast<__nv_bfloat162 *>(&v),
-                               *reinterpret_cast<const __nv_bfloat162 *>(&k129));
-    return *reinterpret_cast<uint32_t *>(&r);
-}
-
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
@@ -96,7 +88,7 @@ __device__ __forceinline__ void tile_row(uint32_t grp_ptr, uint32_t cols, uint32
             if (col != 0xffffu) {                               // padding slots end a row
                 uint32_t af[4];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) af[i] = decode_pair(cws[s >> 1], (s & 1) * 4 + i);
+                for (int i = 0; i < 4; ++i) af[i] = mortar_decode_pair(cws[s >> 1], (s & 1) * 4 + i);
                 uint32_t b0[P], b1[P];
 #pragma unroll
                 for (int pl = 0; pl < P; ++pl) lds_bfrag(act[pl] + col * 32u, b0[pl], b1[pl]);

@@ -11,8 +11,10 @@
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <cstdint>
+#include <cstdlib>
 #include <mutex>
 #include "common.h"
+#include "decode.cuh"
 
 namespace {
 
@@ -57,15 +59,6 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4],
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// Two 2-bit stored values (bits 2q and 16+2q of `word`) -> packed bf16 pair of codes.
-// 0x4300|s is the bf16 number 128+s; subtracting 129 leaves s-1 in {-1,0,+1} exactly.
-__device__ __forceinline__ uint32_t decode_pair(uint32_t word, int q) {
-    uint32_t v = ((word >> (2 * q)) & 0x00030003u) | 0x43004300u;
-    const uint32_t k129 = 0x43014301u;
-    __nv_bfloat162 r = __hsub2(*reinterpret_cast<__nv_bfloat162 *>(&v),
-                               *reinterpret_cast<const __nv_bfloat162 *>(&k129));
-    return *reinterpret_cast<uint32_t *>(&r);
-}
 
 __device__ __forceinline__ float round_bf16(float v) {
     return __bfloat162float(__float2bfloat16_rn(v));
@@ -86,6 +79,59 @@ __device__ __forceinline__ void store_value(const LinearParams &p, long long row
             __nv_bfloat16 h = __float2bfloat16_rn(r);
             o[pl * p.out_plane_stride] = h;
             r -= __bfloat162float(h);
+        }
+    }
+}
+
+// One 8-tile group against NT blocks of 8 activation rows and P planes.  Activation fragments
+// of SB slots are fetched together before any of them is consumed, so the loads overlap
+// instead of each waiting behind the previous MMA.  CHECK = false is the all-slots-live case.
+template <int NT, int P, int SB, bool CHECK>
+__device__ __forceinline__ void group_mma(float (&acc)[NT][4], const uint4 cw, const uint4 cl,
+                                          const uint32_t *const (&xb)[NT], long long plane_stride_w,
+                                          const unsigned char *col_active) {
+    const uint32_t cws[4] = {cw.x, cw.y, cw.z, cw.w};
+    const uint32_t cls[4] = {cl.x, cl.y, cl.z, cl.w};
+#pragma unroll
+    for (int s0 = 0; s0 < 8; s0 += SB) {
+        uint32_t bf[SB][NT][P][2];
+        bool live[SB];
+#pragma unroll
+        for (int ss = 0; ss < SB; ++ss) {
+            const int s = s0 + ss;
+            const uint32_t col = (s & 1) ? (cls[s >> 1] >> 16) : (cls[s >> 1] & 0xffffu);
+            live[ss] = true;
+            if (CHECK) {
+                live[ss] = (col != 0xffffu);                 // padding slots end a row
+                if (col_active != nullptr && live[ss]) live[ss] = col_active[col] != 0;
+            }
+            if (live[ss]) {
+#pragma unroll
+                for (int n = 0; n < NT; ++n) {
+                    const uint32_t *px = xb[n] + (long long)col * 8;
+#pragma unroll
+                    for (int pl = 0; pl < P; ++pl) {
+                        bf[ss][n][pl][0] = __ldg(px);
+                        bf[ss][n][pl][1] = __ldg(px + 4);
+                        px += plane_stride_w;
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int ss = 0; ss < SB; ++ss) {
+            const int s = s0 + ss;
+            if (live[ss]) {
+                const uint32_t word = cws[s >> 1];
+                uint32_t af[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) af[i] = mortar_decode_pair(word, (s & 1) * 4 + i);
+#pragma unroll
+                for (int n = 0; n < NT; ++n)
+#pragma unroll
+                    for (int pl = 0; pl < P; ++pl)
+                        mma_16816(acc[n], af, bf[ss][n][pl][0], bf[ss][n][pl][1]);
+            }
         }
     }
 }
@@ -179,47 +225,12 @@ bcsr_stream_kernel(const LinearParams p) {
                     ncw = __ldg(p.grp_codes + (long long)ngrp * 32 + lane);
                     ncl = __ldg(p.grp_cols + ngrp);
                 }
-                const uint32_t cws[4] = {cw.x, cw.y, cw.z, cw.w};
-                const uint32_t cls[4] = {cl.x, cl.y, cl.z, cl.w};
-#pragma unroll
-                for (int s0 = 0; s0 < 8; s0 += SB) {
-                    uint32_t bf[SB][NT][P][2];
-                    bool live[SB];
-#pragma unroll
-                    for (int ss = 0; ss < SB; ++ss) {
-                        const int s = s0 + ss;
-                        const uint32_t col = (cls[s >> 1] >> (16 * (s & 1))) & 0xffffu;
-                        live[ss] = (col != 0xffffu);                 // padding slots end a row
-                        if (use_cact && live[ss]) live[ss] = col_active[col] != 0;
-                        if (live[ss]) {
-#pragma unroll
-                            for (int n = 0; n < NT; ++n) {
-                                const uint32_t *px = xb[n] + (long long)col * 8;
-#pragma unroll
-                                for (int pl = 0; pl < P; ++pl) {
-                                    bf[ss][n][pl][0] = __ldg(px);
-                                    bf[ss][n][pl][1] = __ldg(px + 4);
-                                    px += p.plane_stride_w;
-                                }
-                            }
-                        }
-                    }
-#pragma unroll
-                    for (int ss = 0; ss < SB; ++ss) {
-                        const int s = s0 + ss;
-                        if (live[ss]) {
-                            const uint32_t word = cws[s >> 1];
-                            uint32_t af[4];
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) af[i] = decode_pair(word, (s & 1) * 4 + i);
-#pragma unroll
-                            for (int n = 0; n < NT; ++n)
-#pragma unroll
-                                for (int pl = 0; pl < P; ++pl)
-                                    mma_16816(acc[a][n], af, bf[ss][n][pl][0], bf[ss][n][pl][1]);
-                        }
-                    }
-                }
+                // a group whose last slot is a real tile has no padding: skip the per-slot tests
+                if (!use_cact && (cl.w >> 16) != 0xffffu)
+                    group_mma<NT, P, SB, false>(acc[a], cw, cl, xb, p.plane_stride_w, col_active);
+                else
+                    group_mma<NT, P, SB, true>(acc[a], cw, cl, xb, p.plane_stride_w,
+                                               use_cact ? col_active : nullptr);
                 cw = ncw; cl = ncl; grp = ngrp;
             }
             done += gend - gbeg;
@@ -482,7 +493,8 @@ extern "C" int mortar_linear(const mortar_stream *w, const void *planes, int32_t
     }
 
     const double avg = (double)w->n_groups / (double)units;   // groups per unit
-    const int wpr = avg >= 3.0 ? 4 : (avg >= 1.5 ? 2 : 1);
+    int wpr = avg >= 3.0 ? 4 : (avg >= 1.5 ? 2 : 1);
+    if (getenv("MORTAR_WPR")) wpr = atoi(getenv("MORTAR_WPR"));
     cudaStream_t st = (cudaStream_t)stream;
     return swiglu ? launch_planes<true>(p, wpr, st) : launch_planes<false>(p, wpr, st);
 }
