@@ -20,8 +20,10 @@ __device__ __forceinline__ uint32_t mortar_decode_pair(uint32_t word, int q) {
     const uint32_t mask = 0x00030003u << (2 * j);
     const uint32_t base = j == 0 ? 0x43004300u : j == 1 ? 0x42004200u : j == 2 ? 0x41004100u : 0x40004000u;
     const uint32_t bias = j == 0 ? 0x43014301u : j == 1 ? 0x42044204u : j == 2 ? 0x41104110u : 0x40404040u;
-    uint32_t v = (w & mask) | base;
-    __nv_bfloat162 r = __hsub2(*reinterpret_cast<__nv_bfloat162 *>(&v),
-                               *reinterpret_cast<const __nv_bfloat162 *>(&bias));
-    return *reinterpret_cast<uint32_t *>(&r);
+    // (w & mask) | base as ONE three-input logic op (left to the compiler it becomes two), then
+    // the packed bf16 subtraction
+    uint32_t v, r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(v) : "r"(w), "r"(mask), "r"(base));
+    asm("sub.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(v), "r"(bias));
+    return r;
 }

@@ -20,6 +20,12 @@ namespace {
 
 constexpr int kWarpsPerCta = 4;
 constexpr int kMaxFlagCols = 4096;     // tile columns coverable by the column-activity bitmap
+constexpr int kBulkStages = 2;         // shared-memory stages of the bulk-copy pipeline
+constexpr int kBulkChunkGroups = 16;   // groups per stage: 8 KB of codes + 256 B of column indices
+constexpr uint32_t kBulkWaitLimit = 1u << 20;   // polls of one mbarrier before the kernel gives up
+
+// Set when a bounded mbarrier wait of the bulk-copy pipeline ran out (never in a healthy run).
+__device__ int g_linear_error = 0;
 
 struct LinearParams {
     const uint4 *grp_codes;
@@ -60,6 +66,23 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4],
 }
 
 
+__device__ __forceinline__ uint32_t smem_u32(const void *ptr) {
+    return (uint32_t)__cvta_generic_to_shared(ptr);
+}
+
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kBulkWaitLimit; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n.reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.b32 %0, 1, 0, p;\n}\n"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
 __device__ __forceinline__ float round_bf16(float v) {
     return __bfloat162float(__float2bfloat16_rn(v));
 }
@@ -83,13 +106,46 @@ __device__ __forceinline__ void store_value(const LinearParams &p, long long row
     }
 }
 
+// Finished sums of one output element -> scale, SwiGLU and cluster gate (with the reference's
+// bf16 rounding points when asked for), then the store.  sum_a is the gate (or only) tile row's
+// sum, sum_b the up tile row's.
+template <bool SWIGLU>
+__device__ __forceinline__ void emit_value(const LinearParams &p, float scale, int unit, bool active,
+                                           long long row, int neuron_local, float sum_a, float sum_b) {
+    const int neuron = unit * 16 + neuron_local;
+    float v;
+    if (SWIGLU) {
+        float gv = scale * sum_a;
+        float uv = scale * sum_b;
+        float gate = 1.f;
+        if (p.gates != nullptr) gate = p.gates[row * p.ld_gates + neuron / p.cluster_size];
+        if (p.round_bf16) {
+            gv = round_bf16(gv);
+            uv = round_bf16(uv);
+            const float sg = round_bf16(gv / (1.f + expf(-gv)));
+            v = round_bf16(sg * uv);
+            if (p.gates != nullptr) v = round_bf16(v * round_bf16(gate));
+        } else {
+            v = gv * (1.f / (1.f + expf(-gv))) * uv;
+            if (p.gates != nullptr) v *= gate;
+        }
+        if (!active || (p.gates != nullptr && !(gate > 0.f))) v = 0.f;
+    } else {
+        v = scale * sum_a;
+        if (!active) v = 0.f;
+    }
+    store_value(p, row, neuron, v);
+}
+
 // One 8-tile group against NT blocks of 8 activation rows and P planes.  Activation fragments
 // of SB slots are fetched together before any of them is consumed, so the loads overlap
 // instead of each waiting behind the previous MMA.  CHECK = false is the all-slots-live case.
-template <int NT, int P, int SB, bool CHECK>
+// SCOLS: the eight column indices are read one by one from shared memory (address `cols_s`,
+// load/store pipe) instead of being extracted from the register quad `cl` (integer pipe).
+template <int NT, int P, int SB, bool CHECK, bool SCOLS = false>
 __device__ __forceinline__ void group_mma(float (&acc)[NT][4], const uint4 cw, const uint4 cl,
                                           const uint32_t *const (&xb)[NT], long long plane_stride_w,
-                                          const unsigned char *col_active) {
+                                          const uint32_t *col_active, uint32_t cols_s = 0) {
     const uint32_t cws[4] = {cw.x, cw.y, cw.z, cw.w};
     const uint32_t cls[4] = {cl.x, cl.y, cl.z, cl.w};
 #pragma unroll
@@ -99,11 +155,13 @@ __device__ __forceinline__ void group_mma(float (&acc)[NT][4], const uint4 cw, c
 #pragma unroll
         for (int ss = 0; ss < SB; ++ss) {
             const int s = s0 + ss;
-            const uint32_t col = (s & 1) ? (cls[s >> 1] >> 16) : (cls[s >> 1] & 0xffffu);
+            uint32_t col;
+            if (SCOLS) asm volatile("ld.shared.u16 %0, [%1];" : "=r"(col) : "r"(cols_s + 2u * s));
+            else col = (s & 1) ? (cls[s >> 1] >> 16) : (cls[s >> 1] & 0xffffu);
             live[ss] = true;
             if (CHECK) {
                 live[ss] = (col != 0xffffu);                 // padding slots end a row
-                if (col_active != nullptr && live[ss]) live[ss] = col_active[col] != 0;
+                if (col_active != nullptr && live[ss]) live[ss] = ((col_active[col >> 5] >> (col & 31u)) & 1u) != 0;
             }
             if (live[ss]) {
 #pragma unroll
@@ -139,9 +197,17 @@ __device__ __forceinline__ void group_mma(float (&acc)[NT][4], const uint4 cw, c
 // One CTA = 4 warps; WPR warps cooperate on one unit (a tile row, or for SWIGLU a hidden
 // tile row = gate row u and up row u+units), 4/WPR units per CTA.  blockIdx.y selects a
 // block of 8*NT activation rows.
-template <int NT, int P, bool SWIGLU, int WPR>
-__global__ void __launch_bounds__(kWarpsPerCta * 32)
+//
+// BULK (needs WPR = 4, one unit per CTA): the unit's groups are not read with per-lane loads but
+// staged into shared memory by bulk asynchronous copies (one elected thread, mbarrier
+// completion), kBulkStages chunks of kBulkChunkGroups groups in flight per CTA from the first
+// instruction on.  That is what keeps enough bytes in flight to stream a matrix much larger
+// than L2; the group-to-warp assignment and the summation order are those of the plain path,
+// so both give bit-identical results.
+template <int NT, int P, bool SWIGLU, int WPR, bool BULK>
+__global__ void __launch_bounds__(kWarpsPerCta * 32, (BULK && NT == 1) ? (P == 1 ? 8 : 6) : 1)
 bcsr_stream_kernel(const LinearParams p) {
+    static_assert(!BULK || WPR == kWarpsPerCta, "the bulk pipeline serves one unit per CTA");
     constexpr int UPC = kWarpsPerCta / WPR;
     // tile slots whose activation fragments are fetched together before any of them is
     // consumed, so the loads overlap instead of each waiting behind the previous MMA
@@ -155,23 +221,44 @@ bcsr_stream_kernel(const LinearParams p) {
     // with folded planes the MMA columns are virtual rows; gates and flags are per real row
     const int nrows = p.fold > 0 ? (int)p.real_rows : (int)min((long long)(8 * NT), p.rows - row0);
 
-    __shared__ float red[(WPR > 1) ? UPC * (WPR - 1) * NACC * NT * 4 * 32 : 1];
-    __shared__ unsigned char col_active[kMaxFlagCols];
+    constexpr int kRedFloats = (WPR > 1) ? UPC * (WPR - 1) * NACC * NT * 4 * 32 : 1;
+    constexpr int kStageBytes = BULK ? kBulkStages * kBulkChunkGroups * 512 : 0;
+    // the cross-warp sum reuses the stage memory once every chunk has been consumed
+    constexpr int kPoolBytes = kStageBytes > kRedFloats * 4 ? kStageBytes : kRedFloats * 4;
+    __shared__ __align__(128) unsigned char pool[kPoolBytes];
+    __shared__ __align__(16) uint4 cols_s[BULK ? kBulkStages * kBulkChunkGroups : 1];
+    __shared__ __align__(8) unsigned long long bars[BULK ? 2 * kBulkStages : 1];   // full[], empty[]
+    float *red = reinterpret_cast<float *>(pool);
+    __shared__ uint32_t col_active[kMaxFlagCols / 32];       // one bit per tile column
+    if (BULK && threadIdx.x == 0) {
+        for (int i = 0; i < kBulkStages; ++i) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_u32(&bars[i])));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(&bars[kBulkStages + i])),
+                         "r"(kWarpsPerCta));
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (BULK) __syncthreads();
 
     // Column-activity bitmap for this block of rows (only built for small batches).
     const bool use_cact = (p.col_act != nullptr) || (p.gates_on_input != 0);
     if (use_cact) {
-        for (int c = threadIdx.x; c < p.C; c += blockDim.x) {
-            int any = 0;
-            if (p.col_act != nullptr) {
-                for (int b = 0; b < nrows; ++b) any |= p.col_act[(row0 + b) * p.ld_col_act + c];
-            } else {
-                const int lo = (c * 16) / p.cluster_size, hi = (c * 16 + 15) / p.cluster_size;
-                for (int b = 0; b < nrows; ++b)
-                    for (int k = lo; k <= hi; ++k)
-                        any |= (p.gates[(row0 + b) * p.ld_gates + k] > 0.f);
+        for (int wd = threadIdx.x; wd < (p.C + 31) / 32; wd += blockDim.x) {
+            uint32_t bits = 0;
+            for (int j = 0; j < 32 && wd * 32 + j < p.C; ++j) {
+                const int c = wd * 32 + j;
+                int any = 0;
+                if (p.col_act != nullptr) {
+                    for (int b = 0; b < nrows; ++b) any |= p.col_act[(row0 + b) * p.ld_col_act + c];
+                } else {
+                    const int lo = (c * 16) / p.cluster_size, hi = (c * 16 + 15) / p.cluster_size;
+                    for (int b = 0; b < nrows; ++b)
+                        for (int k = lo; k <= hi; ++k)
+                            any |= (p.gates[(row0 + b) * p.ld_gates + k] > 0.f);
+                }
+                bits |= (uint32_t)(any != 0) << j;
             }
-            col_active[c] = (unsigned char)(any != 0);
+            col_active[wd] = bits;
         }
         __syncthreads();
     }
@@ -207,6 +294,79 @@ bcsr_stream_kernel(const LinearParams p) {
             if (tok > p.rows - 1) tok = p.rows - 1;      // clamped rows compute discarded values
             xb[n] = p.planes + tok * p.ld_w + t;
         }
+        if constexpr (BULK) {
+            constexpr int S = kBulkStages, CG = kBulkChunkGroups;
+            const uint4 *codes_s = reinterpret_cast<const uint4 *>(pool);
+            int gb[NACC], nch[NACC], len[NACC], total = 0;
+#pragma unroll
+            for (int a = 0; a < NACC; ++a) {
+                const int trow = unit + a * p.units;
+                gb[a] = p.grp_ptr[trow];
+                len[a] = p.grp_ptr[trow + 1] - gb[a];
+                nch[a] = (len[a] + CG - 1) / CG;
+                total += nch[a];
+            }
+            // chunk c of the unit -> its first group and group count
+            auto chunk_of = [&](int c, int &g0, int &ng) {
+                int a = 0;
+                if (NACC > 1 && c >= nch[0]) { a = NACC - 1; c -= nch[0]; }
+                g0 = gb[a] + c * CG;
+                ng = min(CG, len[a] - c * CG);
+            };
+            auto issue = [&](int c) {
+                int g0, ng;
+                chunk_of(c, g0, ng);
+                const int st = c % S;
+                const uint32_t bar = smem_u32(&bars[st]);
+                const uint32_t cbytes = (uint32_t)ng * 512u, lbytes = (uint32_t)ng * 16u;
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar),
+                             "r"(cbytes + lbytes) : "memory");
+                asm volatile(
+                    "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                    ::"r"(smem_u32(pool + st * (CG * 512))), "l"(p.grp_codes + (long long)g0 * 32), "r"(cbytes),
+                    "r"(bar) : "memory");
+                asm volatile(
+                    "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                    ::"r"(smem_u32(cols_s + st * CG)), "l"(p.grp_cols + g0), "r"(lbytes), "r"(bar) : "memory");
+            };
+            if (threadIdx.x == 0)
+                for (int c = 0; c < total && c < S; ++c) issue(c);
+            int c = 0, done = 0;
+            bool ok = true;
+#pragma unroll
+            for (int a = 0; a < NACC; ++a) {
+                for (int cc = 0; cc < nch[a] && ok; ++cc, ++c) {
+                    const int st = c % S;
+                    const uint32_t ph = (uint32_t)(c / S) & 1u;
+                    const int ng = min(CG, len[a] - cc * CG);
+                    ok = mbar_wait_bounded(smem_u32(&bars[st]), ph);
+                    if (!ok) { g_linear_error = 1; break; }
+                    for (int gi = ((sub - done) % WPR + WPR) % WPR; gi < ng; gi += WPR) {
+                        const uint4 cw = codes_s[(st * CG + gi) * 32 + lane];
+                        const uint4 cl = make_uint4(0, 0, 0, 0);
+                        const uint32_t cols_a = smem_u32(cols_s + st * CG + gi);
+                        // only the last group of a tile row can hold padding slots
+                        if (!use_cact && cc * CG + gi != len[a] - 1)
+                            group_mma<NT, P, SB, false, true>(acc[a], cw, cl, xb, p.plane_stride_w, nullptr, cols_a);
+                        else
+                            group_mma<NT, P, SB, true, true>(acc[a], cw, cl, xb, p.plane_stride_w,
+                                                             use_cact ? col_active : nullptr, cols_a);
+                    }
+                    if (c + S < total) {
+                        // hand the stage back; the elected thread refills it once all four warps have
+                        __syncwarp();
+                        if (lane == 0)
+                            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&bars[S + st])) : "memory");
+                        if (threadIdx.x == 0) {
+                            if (mbar_wait_bounded(smem_u32(&bars[S + st]), ph)) issue(c + S);
+                            else g_linear_error = 1;
+                        }
+                        __syncwarp();
+                    }
+                }
+                done += len[a];
+            }
+        } else {
         int done = 0;   // groups of earlier tile rows of this unit, keeps the round-robin going
 #pragma unroll
         for (int a = 0; a < NACC; ++a) {
@@ -235,11 +395,13 @@ bcsr_stream_kernel(const LinearParams p) {
             }
             done += gend - gbeg;
         }
+        }
     }
 
     if (WPR > 1) {
         // fixed-order cross-warp sum: warps sub=1..WPR-1 publish, warp sub=0 adds in order
         float *mine = red + ((unit_local * (WPR - 1) + (sub > 0 ? sub - 1 : 0)) * NACC * NT * 4) * 32;
+        if (BULK) __syncthreads();      // every warp is done reading the stages that `red` reuses
         if (sub > 0) {
 #pragma unroll
             for (int a = 0; a < NACC; ++a)
@@ -267,29 +429,7 @@ bcsr_stream_kernel(const LinearParams p) {
     // Epilogue.  acc[.][n][0..3] = (neuron g, row 2t), (g, 2t+1), (g+8, 2t), (g+8, 2t+1).
     const float scale = p.round_bf16 ? round_bf16(p.scale) : p.scale;
     auto emit = [&](long long row, int neuron_local, float sum_a, float sum_b) {
-        const int neuron = unit * 16 + neuron_local;
-        float v;
-        if (SWIGLU) {
-            float gv = scale * sum_a;
-            float uv = scale * sum_b;
-            float gate = 1.f;
-            if (p.gates != nullptr) gate = p.gates[row * p.ld_gates + neuron / p.cluster_size];
-            if (p.round_bf16) {
-                gv = round_bf16(gv);
-                uv = round_bf16(uv);
-                const float sg = round_bf16(gv / (1.f + expf(-gv)));
-                v = round_bf16(sg * uv);
-                if (p.gates != nullptr) v = round_bf16(v * round_bf16(gate));
-            } else {
-                v = gv * (1.f / (1.f + expf(-gv))) * uv;
-                if (p.gates != nullptr) v *= gate;
-            }
-            if (!active || (p.gates != nullptr && !(gate > 0.f))) v = 0.f;
-        } else {
-            v = scale * sum_a;
-            if (!active) v = 0.f;
-        }
-        store_value(p, row, neuron, v);
+        emit_value<SWIGLU>(p, scale, unit, active, row, neuron_local, sum_a, sum_b);
     };
     if (NT == 1 && P == 1 && p.fold > 0) {
         // Folded planes: MMA column pl*real_rows + b holds plane pl of activation row b, so the
@@ -322,6 +462,8 @@ bcsr_stream_kernel(const LinearParams p) {
         }
     }
 }
+
+#include "gemv_persistent.cuh"
 
 // x[rows, cols] -> bf16 planes, optional RMSNorm prologue.  One CTA per row.
 template <typename T>
@@ -370,18 +512,19 @@ __global__ void route_flags_kernel(const float *gates, long long ld_gates, const
 }
 
 template <int NT, int P, bool SWIGLU>
-int launch_wpr(const LinearParams &p, int wpr, unsigned grid_y, cudaStream_t st) {
+int launch_wpr(const LinearParams &p, int wpr, bool bulk, unsigned grid_y, cudaStream_t st) {
     const int upc = kWarpsPerCta / wpr;
     dim3 grid((p.units + upc - 1) / upc, grid_y);
-    if (wpr == 4) bcsr_stream_kernel<NT, P, SWIGLU, 4><<<grid, kWarpsPerCta * 32, 0, st>>>(p);
-    else if (wpr == 2) bcsr_stream_kernel<NT, P, SWIGLU, 2><<<grid, kWarpsPerCta * 32, 0, st>>>(p);
-    else bcsr_stream_kernel<NT, P, SWIGLU, 1><<<grid, kWarpsPerCta * 32, 0, st>>>(p);
+    if (wpr == 4 && bulk) bcsr_stream_kernel<NT, P, SWIGLU, 4, true><<<grid, kWarpsPerCta * 32, 0, st>>>(p);
+    else if (wpr == 4) bcsr_stream_kernel<NT, P, SWIGLU, 4, false><<<grid, kWarpsPerCta * 32, 0, st>>>(p);
+    else if (wpr == 2) bcsr_stream_kernel<NT, P, SWIGLU, 2, false><<<grid, kWarpsPerCta * 32, 0, st>>>(p);
+    else bcsr_stream_kernel<NT, P, SWIGLU, 1, false><<<grid, kWarpsPerCta * 32, 0, st>>>(p);
     MORTAR_CUDA_CHECK(cudaGetLastError());
     return MORTAR_OK;
 }
 
 template <int P, bool SWIGLU>
-int launch_nt(const LinearParams &p, int wpr, cudaStream_t st) {
+int launch_nt(const LinearParams &p, int wpr, bool bulk, cudaStream_t st) {
     // Small matrices and small batches are latency-bound: prefer many light CTAs (8 rows each,
     // weights re-read from L2 per row block) until the grid covers the GPU a few times over.
     const int upc = kWarpsPerCta / wpr;
@@ -389,23 +532,37 @@ int launch_nt(const LinearParams &p, int wpr, cudaStream_t st) {
     const long long blocks8 = (p.rows + 7) / 8;
     if (p.rows <= 8 || ctas_x * blocks8 <= 148 * 16) {
         if (blocks8 > 65535) return MORTAR_ERR_CAPACITY;
-        return launch_wpr<1, P, SWIGLU>(p, wpr, (unsigned)blocks8, st);
+        return launch_wpr<1, P, SWIGLU>(p, wpr, bulk, (unsigned)blocks8, st);
     }
     const long long blocks16 = (p.rows + 15) / 16;
     if (p.rows <= 16 || ctas_x * blocks16 <= 148 * 16) {
         if (blocks16 > 65535) return MORTAR_ERR_CAPACITY;
-        return launch_wpr<2, P, SWIGLU>(p, wpr, (unsigned)blocks16, st);
+        return launch_wpr<2, P, SWIGLU>(p, wpr, bulk, (unsigned)blocks16, st);
     }
     const long long blocks = (p.rows + 31) / 32;
     if (blocks > 65535) return MORTAR_ERR_CAPACITY;
-    return launch_wpr<4, P, SWIGLU>(p, wpr, (unsigned)blocks, st);
+    return launch_wpr<4, P, SWIGLU>(p, wpr, bulk, (unsigned)blocks, st);
 }
 
 template <bool SWIGLU>
-int launch_planes(const LinearParams &p, int wpr, cudaStream_t st) {
-    if (p.n_planes == 1) return launch_nt<1, SWIGLU>(p, wpr, st);
-    if (p.n_planes == 2) return launch_nt<2, SWIGLU>(p, wpr, st);
-    return launch_nt<3, SWIGLU>(p, wpr, st);
+int launch_planes(const LinearParams &p, int wpr, bool bulk, cudaStream_t st) {
+    if (p.n_planes == 1) return launch_nt<1, SWIGLU>(p, wpr, bulk, st);
+    if (p.n_planes == 2) return launch_nt<2, SWIGLU>(p, wpr, bulk, st);
+    return launch_nt<3, SWIGLU>(p, wpr, bulk, st);
+}
+
+template <bool SWIGLU>
+int launch_persistent(const LinearParams &p, cudaStream_t st) {
+    const PsLayout L = ps_layout(p.C, (int)p.rows, SWIGLU);
+    int dev = 0, sms = 0;
+    MORTAR_CUDA_CHECK(cudaGetDevice(&dev));
+    MORTAR_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    MORTAR_CUDA_CHECK(cudaFuncSetAttribute(gemv_persistent_kernel<SWIGLU>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, L.total));
+    const int grid = p.units < sms ? p.units : sms;
+    gemv_persistent_kernel<SWIGLU><<<grid, kPsWarps * 32, L.total, st>>>(p);
+    MORTAR_CUDA_CHECK(cudaGetLastError());
+    return MORTAR_OK;
 }
 
 inline bool aligned(const void *ptr, size_t a) { return (reinterpret_cast<uintptr_t>(ptr) % a) == 0; }
@@ -496,7 +653,18 @@ extern "C" int mortar_linear(const mortar_stream *w, const void *planes, int32_t
     int wpr = avg >= 3.0 ? 4 : (avg >= 1.5 ? 2 : 1);
     if (getenv("MORTAR_WPR")) wpr = atoi(getenv("MORTAR_WPR"));
     cudaStream_t st = (cudaStream_t)stream;
-    return swiglu ? launch_planes<true>(p, wpr, st) : launch_planes<false>(p, wpr, st);
+    // At most 8 MMA columns against a matrix that does not stay in L2: the persistent kernel
+    // (activations in shared memory, weight rings fed by bulk copies).  It has no routing inputs.
+    bool persistent = false;
+    if (getenv("MORTAR_PERSISTENT"))
+        persistent = atoi(getenv("MORTAR_PERSISTENT")) != 0 && p.n_planes == 1 && p.rows <= 8 && !p.gates &&
+                     !p.row_act && !p.col_act && !p.gates_on_input &&
+                     ps_layout(p.C, (int)p.rows, swiglu).total <= kPsMaxSmem;
+    if (persistent) return swiglu ? launch_persistent<true>(p, st) : launch_persistent<false>(p, st);
+    // matrices that do not stay in L2 are staged by bulk copies (many more bytes in flight)
+    bool bulk = wpr == 4 && (int64_t)w->n_groups * 528 >= (int64_t)(8 << 20);
+    if (getenv("MORTAR_BULK")) bulk = wpr == 4 && atoi(getenv("MORTAR_BULK")) != 0;
+    return swiglu ? launch_planes<true>(p, wpr, bulk, st) : launch_planes<false>(p, wpr, bulk, st);
 }
 
 extern "C" int mortar_route_flags(const float *gates, int64_t rows, int64_t ld_gates,
