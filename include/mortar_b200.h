@@ -138,10 +138,22 @@ enum {
     MORTAR_FLAG_GATES_ON_INPUT = 4, /* non-SWIGLU call: `gates` describe the INPUT neurons
                                     (the down projection); tile columns whose spanned
                                     clusters are all gated to 0 are skipped (rows <= 8) */
-    MORTAR_FLAG_ACCUMULATE = 8   /* out += result (MORTAR_OUT_F32 / MORTAR_OUT_BF16): the caller's
+    MORTAR_FLAG_ACCUMULATE = 8,  /* out += result (MORTAR_OUT_F32 / MORTAR_OUT_BF16): the caller's
                                     residual carrier receives the MLP output directly, the
                                     add the reference performs after the MLP
                                     (morph/model/hyper_connections.py:182-229) */
+    /* Kernel choice (bits 4-5); no counterpart in the reference.  PLAIN: per-lane loads with a
+       register prefetch.  STAGED: the unit's groups are brought into shared memory by bulk
+       copies (needs rows of at least 3 groups on average).  PERSISTENT: one CTA per SM with
+       producer warps, for at most 8 MMA columns of activations (8 bf16 rows, or 2 fp32 rows as
+       folded planes) that fit shared memory, no routing inputs.  AUTO runs the plain path (the
+       fastest one measured at every shape tried so far); a pinned path that cannot serve the
+       call falls back to the plain one. */
+    MORTAR_FLAG_PATH_AUTO = 0,
+    MORTAR_FLAG_PATH_PLAIN = 16,
+    MORTAR_FLAG_PATH_STAGED = 32,
+    MORTAR_FLAG_PATH_PERSISTENT = 48,
+    MORTAR_FLAG_PATH_MASK = 48
 };
 
 /* y = act @ W^T for a stream-format matrix; replaces mortar_gemv
@@ -314,6 +326,12 @@ int mortar_mlp_prefill(const mortar_sched *gate_up, const mortar_sched *down, co
                        int64_t ldx, int64_t rows, const float *gates, int64_t ld_gates,
                        int32_t n_clusters, void *y, int64_t ldy, void *workspace,
                        int64_t workspace_bytes, void *stream);
+
+/* Reads (and optionally clears) the error word the staged and persistent paths of
+ * mortar_linear set when one of their bounded barrier waits expires: 0 = none, 1 = staged
+ * path, 2 = a consumer of the persistent kernel, 3 = one of its producers.  Synchronises.
+ * No counterpart in the reference. */
+int mortar_linear_error(int32_t *code, int32_t reset);
 
 /* Reads (and optionally clears) the error word the prefill kernel sets when one of its
  * bounded barrier waits expires: 0 = none, 1..4 = the waiting role.  Synchronises. */

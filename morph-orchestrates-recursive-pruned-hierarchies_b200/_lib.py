@@ -15,6 +15,7 @@ OK = 0
 F32, BF16 = 0, 1
 OUT_F32, OUT_BF16, OUT_PLANES = 0, 1, 2
 FLAG_SWIGLU, FLAG_ROUND_BF16, FLAG_GATES_ON_INPUT, FLAG_ACCUMULATE = 1, 2, 4, 8
+PATH_FLAGS = {"auto": 0, "plain": 16, "staged": 32, "persistent": 48}
 
 _SHAPE_ERRORS = {-2, -3, -4, -5, -6, -7, -8}
 
@@ -75,6 +76,7 @@ _SIGNATURES = {
     "mortar_mlp_prefill": (C.c_int, [C.POINTER(Sched), C.POINTER(Sched), _vp, _i64, _i64, _vp, _i64,
                                      _i32, _vp, _i64, _vp, _i64, _vp]),
     "mortar_prefill_error": (C.c_int, [_vp, _i32]),
+    "mortar_linear_error": (C.c_int, [_vp, _i32]),
 }
 
 # entry points added by later translation units; bound when present in the header list

@@ -77,6 +77,13 @@ __device__ __forceinline__ void tile_row(uint32_t grp_ptr, uint32_t cols, uint32
     asm volatile("ld.shared.u32 %0, [%2];\n\tld.shared.u32 %1, [%2+4];\n" : "=r"(gbeg), "=r"(gend) : "r"(grp_ptr + 4u * trow));
     uint32_t caddr = codes + (uint32_t)(gbeg * 32 + lane) * 16u;
     uint32_t laddr = cols + (uint32_t)gbeg * 16u;
+    // one accumulator chain per plane: the P MMAs of a tile are independent of each other, so
+    // a warp has P of them in flight instead of waiting for each one's result
+    float part[P][4];
+#pragma unroll
+    for (int pl = 0; pl < P; ++pl)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) part[pl][i] = 0.f;
     for (int grp = gbeg; grp < gend; ++grp, caddr += 512u, laddr += 16u) {
         const uint4 cw = lds128(caddr);
         const uint4 cl = lds128(laddr);
@@ -93,9 +100,16 @@ __device__ __forceinline__ void tile_row(uint32_t grp_ptr, uint32_t cols, uint32
 #pragma unroll
                 for (int pl = 0; pl < P; ++pl) lds_bfrag(act[pl] + col * 32u, b0[pl], b1[pl]);
 #pragma unroll
-                for (int pl = 0; pl < P; ++pl) mma_16816(acc, af, b0[pl], b1[pl]);
+                for (int pl = 0; pl < P; ++pl) mma_16816(part[pl], af, b0[pl], b1[pl]);
             }
         }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float v = part[0][i];
+#pragma unroll
+        for (int pl = 1; pl < P; ++pl) v += part[pl][i];
+        acc[i] += v;
     }
 }
 

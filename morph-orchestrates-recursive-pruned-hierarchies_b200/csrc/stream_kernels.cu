@@ -11,7 +11,6 @@
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <cstdint>
-#include <cstdlib>
 #include <mutex>
 #include "common.h"
 #include "decode.cuh"
@@ -650,21 +649,30 @@ extern "C" int mortar_linear(const mortar_stream *w, const void *planes, int32_t
     }
 
     const double avg = (double)w->n_groups / (double)units;   // groups per unit
-    int wpr = avg >= 3.0 ? 4 : (avg >= 1.5 ? 2 : 1);
-    if (getenv("MORTAR_WPR")) wpr = atoi(getenv("MORTAR_WPR"));
+    const int wpr = avg >= 3.0 ? 4 : (avg >= 1.5 ? 2 : 1);
     cudaStream_t st = (cudaStream_t)stream;
-    // At most 8 MMA columns against a matrix that does not stay in L2: the persistent kernel
-    // (activations in shared memory, weight rings fed by bulk copies).  It has no routing inputs.
-    bool persistent = false;
-    if (getenv("MORTAR_PERSISTENT"))
-        persistent = atoi(getenv("MORTAR_PERSISTENT")) != 0 && p.n_planes == 1 && p.rows <= 8 && !p.gates &&
-                     !p.row_act && !p.col_act && !p.gates_on_input &&
-                     ps_layout(p.C, (int)p.rows, swiglu).total <= kPsMaxSmem;
-    if (persistent) return swiglu ? launch_persistent<true>(p, st) : launch_persistent<false>(p, st);
-    // matrices that do not stay in L2 are staged by bulk copies (many more bytes in flight)
-    bool bulk = wpr == 4 && (int64_t)w->n_groups * 528 >= (int64_t)(8 << 20);
-    if (getenv("MORTAR_BULK")) bulk = wpr == 4 && atoi(getenv("MORTAR_BULK")) != 0;
+    // Kernel path.  Measured on B200 at the 30B-model shapes (8192 x 43648 / 21824 x 8192, 25%
+    // tiles, batch 1..8) the plain path is the fastest of the three or within noise of it, so
+    // it is what MORTAR_FLAG_PATH_AUTO runs; the staged and persistent paths run when pinned.
+    const int path = flags & MORTAR_FLAG_PATH_MASK;
+    const bool persistent_ok = p.n_planes == 1 && p.rows <= 8 && !p.gates && !p.row_act && !p.col_act &&
+                               !p.gates_on_input && ps_layout(p.C, (int)p.rows, swiglu).total <= kPsMaxSmem;
+    if (persistent_ok && path == MORTAR_FLAG_PATH_PERSISTENT)
+        return swiglu ? launch_persistent<true>(p, st) : launch_persistent<false>(p, st);
+    const bool bulk = wpr == 4 && path == MORTAR_FLAG_PATH_STAGED;
     return swiglu ? launch_planes<true>(p, wpr, bulk, st) : launch_planes<false>(p, wpr, bulk, st);
+}
+
+extern "C" int mortar_linear_error(int32_t *code, int32_t reset) {
+    if (!code) return MORTAR_ERR_NULL;
+    int v = 0;
+    MORTAR_CUDA_CHECK(cudaMemcpyFromSymbol(&v, g_linear_error, sizeof(int)));
+    *code = v;
+    if (reset && v != 0) {
+        const int zero = 0;
+        MORTAR_CUDA_CHECK(cudaMemcpyToSymbol(g_linear_error, &zero, sizeof(int)));
+    }
+    return MORTAR_OK;
 }
 
 extern "C" int mortar_route_flags(const float *gates, int64_t rows, int64_t ld_gates,
@@ -729,13 +737,15 @@ extern "C" int mortar_mlp_decode(const mortar_stream *gate_up, const mortar_stre
     const int cs = gates ? d_ff / n_clusters : 0;
     const int rb = flags & MORTAR_FLAG_ROUND_BF16;
     const int h_planes = rb ? 1 : n_planes;
+    const int path = flags & MORTAR_FLAG_PATH_MASK;
     int rc = mortar_linear(gate_up, xin, xin_planes, xin_stride, xin_ld, rows, hp, MORTAR_OUT_PLANES,
-                           h_planes, rows * (int64_t)d_ff, d_ff, MORTAR_FLAG_SWIGLU | rb, gates,
+                           h_planes, rows * (int64_t)d_ff, d_ff, MORTAR_FLAG_SWIGLU | rb | path, gates,
                            ld_gates, cs, nullptr, 0, nullptr, 0, stream);
     if (rc != MORTAR_OK) return rc;
     return mortar_linear(down, hp, h_planes, rows * (int64_t)d_ff, d_ff, rows, y,
                          y_dtype == MORTAR_F32 ? MORTAR_OUT_F32 : MORTAR_OUT_BF16, 0, 0, ldy,
-                         rb | (flags & MORTAR_FLAG_ACCUMULATE) | (gates ? MORTAR_FLAG_GATES_ON_INPUT : 0), gates, ld_gates, cs, nullptr, 0, nullptr, 0, stream);
+                         rb | path | (flags & MORTAR_FLAG_ACCUMULATE) | (gates ? MORTAR_FLAG_GATES_ON_INPUT : 0),
+                         gates, ld_gates, cs, nullptr, 0, nullptr, 0, stream);
 }
 
 // ---- MLP application on built-in scratch ---------------------------------------------------

@@ -76,10 +76,12 @@ def linear_planes(w: StreamMatrix, planes: torch.Tensor, *, swiglu: bool = False
                   out_dtype: torch.dtype = torch.float32, out_planes: int = 0,
                   round_bf16: bool = False, gates: Optional[torch.Tensor] = None,
                   cluster_size: int = 0, gates_on_input: bool = False,
-                  row_act: Optional[torch.Tensor] = None, col_act: Optional[torch.Tensor] = None):
+                  row_act: Optional[torch.Tensor] = None, col_act: Optional[torch.Tensor] = None,
+                  path: str = "auto"):
     """Block-sparse ternary linear on activation planes [P, rows, in]: returns [rows, out]
     (or [rows, out/2] = silu(gate)*up with ``swiglu``), as float32/bfloat16 or, with
-    ``out_planes`` > 0, as planes [out_planes, rows, n]."""
+    ``out_planes`` > 0, as planes [out_planes, rows, n].  ``path`` pins one of the kernel's
+    paths ("plain", "staged", "persistent"); "auto" picks by matrix size and batch."""
     global _launches
     _require_cuda(planes, "planes")
     if planes.dim() != 3 or planes.dtype != torch.bfloat16 or not planes.is_contiguous():
@@ -103,7 +105,7 @@ def linear_planes(w: StreamMatrix, planes: torch.Tensor, *, swiglu: bool = False
     if rows == 0:
         return out
     flags = (_lib.FLAG_SWIGLU if swiglu else 0) | (_lib.FLAG_ROUND_BF16 if round_bf16 else 0) \
-        | (_lib.FLAG_GATES_ON_INPUT if gates_on_input else 0)
+        | (_lib.FLAG_GATES_ON_INPUT if gates_on_input else 0) | _lib.PATH_FLAGS[path]
     if gates is not None:
         gates = gates.to(device=dev, dtype=torch.float32).reshape(rows, -1).contiguous()
     for name, a in (("row_act", row_act), ("col_act", col_act)):
@@ -162,7 +164,7 @@ def mlp_decode(x: torch.Tensor, gate_up: StreamMatrix, down: StreamMatrix, *,
                n_planes: int = 3, round_bf16: bool = False,
                out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None,
                accumulate: bool = False,
-               workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+               workspace: Optional[torch.Tensor] = None, path: str = "auto") -> torch.Tensor:
     """One SwiGLU MLP application for a block of rows: [rmsnorm] -> gate_up -> silu(g)*u
     [*gates] -> down.  Mirrors StaticDecodeEngine._mlp_fn (morph/inference/engine.py:936-986)
     with ``n_planes=3`` (fp32 semantics) and ``_SwiGLUMortar.forward`` under autocast
@@ -204,7 +206,8 @@ def mlp_decode(x: torch.Tensor, gate_up: StreamMatrix, down: StreamMatrix, *,
         C.byref(gu), C.byref(dn), _ptr(x2), _dtype_code(x2), x2.stride(0), rows, _ptr(w), float(eps),
         _ptr(g), g.stride(0) if g is not None else 0, int(n_clusters), _ptr(out2), _dtype_code(out2),
         out2.stride(0), int(n_planes),
-        (_lib.FLAG_ROUND_BF16 if round_bf16 else 0) | (_lib.FLAG_ACCUMULATE if accumulate else 0),
+        (_lib.FLAG_ROUND_BF16 if round_bf16 else 0) | (_lib.FLAG_ACCUMULATE if accumulate else 0)
+        | _lib.PATH_FLAGS[path],
         _ptr(workspace), workspace.numel(), _stream_ptr()), "mortar_mlp_decode")
     direct = x2.dtype == torch.bfloat16 and rms_weight is None and x2.stride(0) % 2 == 0 \
         and x2.data_ptr() % 4 == 0
@@ -423,6 +426,13 @@ def mlp_prefill_tc(x: torch.Tensor, gate_up: SchedMatrix, down: SchedMatrix, *,
         _ptr(workspace), workspace.numel(), _stream_ptr()), "mortar_mlp_prefill")
     _launches += 2
     return out.reshape(*lead, d_model)
+
+
+def linear_error(reset: bool = True) -> int:
+    """Error word of the staged / persistent paths of ``mortar_linear`` (0 = none; synchronises)."""
+    code = C.c_int32(0)
+    _lib.check(_lib.lib().mortar_linear_error(C.byref(code), int(reset)), "mortar_linear_error")
+    return code.value
 
 
 def prefill_error(reset: bool = True) -> int:

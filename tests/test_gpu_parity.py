@@ -215,6 +215,64 @@ def test_linear_edge_topologies():
         mb.ops.linear(torch.zeros(2, C * 16 + 16, device=DEV), s)
 
 
+@pytest.mark.parametrize("path", ["plain", "staged", "persistent"])
+@pytest.mark.parametrize("B", [1, 2, 5, 8, 24, 64])
+@pytest.mark.parametrize("in_dtype", [torch.bfloat16, torch.float32])
+def test_mlp_decode_every_kernel_path(local_layer, path, B, in_dtype):
+    """The three paths of the linear kernel (per-lane loads, bulk-copy staging, persistent with
+    producer warps) pinned one by one; a path that cannot serve a call (the persistent one past
+    8 MMA columns) falls back, so every combination must still match the oracle."""
+    L, gu, dn = local_layer
+    x = mb.synth.make_activations(B, 768, seed=40 + B).to(in_dtype)
+    y = mb.ops.mlp_decode(x.to(DEV), gu, dn, n_planes=3, out_dtype=torch.float32, path=path)
+    ref = _decode_oracle(x, L)
+    assert float((y.cpu() - ref).abs().max()) <= F32_TOL * float(ref.abs().max())
+    assert mb.ops.linear_error() == 0
+
+
+@pytest.mark.parametrize("path", ["staged", "persistent"])
+def test_routed_decode_on_pinned_paths(local_layer, path):
+    """Routing inputs: the staged path honours gates and gather flags, the persistent one has none
+    and must hand such calls to a path that does."""
+    L, gu, dn = local_layer
+    B, ncls, k = 4, 16, 8
+    gen = torch.Generator().manual_seed(123)
+    x = torch.randn(B, 768, generator=gen) * 2.0
+    rms_w = 1.0 + 0.1 * torch.randn(768, generator=gen)
+    gates = mb.synth.make_gates(B, L, ncls, k, seed=31)
+    y = mb.ops.mlp_decode(x.to(DEV), gu, dn, rms_weight=rms_w.to(DEV), gates=gates.to(DEV),
+                          n_clusters=ncls, n_planes=3, path=path)
+    ref = _decode_oracle(x, L, gates, ncls, rms_w)
+    assert float((y.cpu() - ref).abs().max()) <= F32_TOL * float(ref.abs().max())
+    assert mb.ops.linear_error() == 0
+
+
+@pytest.mark.parametrize("path", ["plain", "staged", "persistent"])
+def test_linear_edge_topologies_on_pinned_paths(path):
+    """empty rows, one tile, a full row, rows longer than one stage (more than 16 groups), ragged
+    tails; exact integer arithmetic, so every path must agree bit for bit."""
+    rng = np.random.default_rng(13)
+    R, C = 23, 300
+    mask = rng.random((R, C)) < 0.25
+    mask[0] = False
+    mask[1] = True                                  # 300 tiles = 38 groups: three stages and a tail
+    mask[2] = False; mask[2, C - 1] = True
+    mask[3] = False; mask[3, :8] = True             # exactly one full group
+    mask[4] = False; mask[4, :129] = True           # 16 groups and one padded group
+    codes = rng.integers(-1, 2, size=(R * 16, C * 16)).astype(np.int8)
+    m = mb.MortarMatrix.from_codes(codes, mask, 0.5)
+    s = m.to_stream(DEV)
+    W = torch.from_numpy(m.to_dense_codes()).float().to(DEV)
+    for rows in (1, 2, 3, 8, 9, 40):
+        xi = torch.randint(-4, 5, (rows, C * 16), generator=torch.Generator().manual_seed(rows)).float()
+        for planes in ((xi.to(torch.bfloat16).unsqueeze(0)),
+                       torch.stack([xi.to(torch.bfloat16), torch.zeros_like(xi, dtype=torch.bfloat16),
+                                    torch.zeros_like(xi, dtype=torch.bfloat16)])):
+            y = mb.ops.linear_planes(s, planes.contiguous().to(DEV), out_dtype=torch.float32, path=path)
+            assert torch.equal(y, (xi.to(DEV) @ W.T) * np.float32(0.5))
+    assert mb.ops.linear_error() == 0
+
+
 def test_linear_is_linear_and_exact_on_integers():
     """size-independent properties: integer-valued activations make every partial sum exact,
     so the kernel must agree with integer arithmetic bit for bit."""
