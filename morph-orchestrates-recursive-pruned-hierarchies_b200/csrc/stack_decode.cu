@@ -77,13 +77,6 @@ __device__ __forceinline__ void tile_row(uint32_t grp_ptr, uint32_t cols, uint32
     asm volatile("ld.shared.u32 %0, [%2];\n\tld.shared.u32 %1, [%2+4];\n" : "=r"(gbeg), "=r"(gend) : "r"(grp_ptr + 4u * trow));
     uint32_t caddr = codes + (uint32_t)(gbeg * 32 + lane) * 16u;
     uint32_t laddr = cols + (uint32_t)gbeg * 16u;
-    // one accumulator chain per plane: the P MMAs of a tile are independent of each other, so
-    // a warp has P of them in flight instead of waiting for each one's result
-    float part[P][4];
-#pragma unroll
-    for (int pl = 0; pl < P; ++pl)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) part[pl][i] = 0.f;
     for (int grp = gbeg; grp < gend; ++grp, caddr += 512u, laddr += 16u) {
         const uint4 cw = lds128(caddr);
         const uint4 cl = lds128(laddr);
@@ -100,16 +93,9 @@ __device__ __forceinline__ void tile_row(uint32_t grp_ptr, uint32_t cols, uint32
 #pragma unroll
                 for (int pl = 0; pl < P; ++pl) lds_bfrag(act[pl] + col * 32u, b0[pl], b1[pl]);
 #pragma unroll
-                for (int pl = 0; pl < P; ++pl) mma_16816(part[pl], af, b0[pl], b1[pl]);
+                for (int pl = 0; pl < P; ++pl) mma_16816(acc, af, b0[pl], b1[pl]);
             }
         }
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        float v = part[0][i];
-#pragma unroll
-        for (int pl = 1; pl < P; ++pl) v += part[pl][i];
-        acc[i] += v;
     }
 }
 
@@ -273,8 +259,8 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
             __syncthreads();
             // silu(gate) * up -> exact bf16 planes of the hidden slice
             const int HW = U * 16;
-            for (int e = threadIdx.x; e < 8 * HW; e += kThreads) {
-                const int r = e / HW, c = e % HW;
+            const int r = warp >> 1;                             // two warps per activation row
+            for (int c = (warp & 1) * 32 + lane; c < HW; c += 64) {
                 const float gv = gu_out[r * W + c], uv = gu_out[r * W + HW + c];
                 float hv = gv * (1.f / (1.f + expf(-gv))) * uv;
                 __nv_bfloat16 *o = hp + r * p.h_pitch + c;
@@ -305,23 +291,37 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
         cluster.sync();      // all partial sums of the cluster are in place
 
         // ---- combine: this rank owns output columns [rank*OC, (rank+1)*OC) ----
+        // All remote loads of an element are issued before the first add; the adds stay in
+        // rank order.
         {
             float *mine = xnew + (size_t)buf * 8 * OC;
-            for (int e = threadIdx.x; e < 8 * OC; e += kThreads) {
-                const int r = e / OC, c = rank * OC + e % OC;
+            const int r = warp >> 1;                             // two warps per activation row
+            for (int cl = (warp & 1) * 32 + lane; cl < OC; cl += 64) {
+                const int c = rank * OC + cl;
+                float part[16];
+#pragma unroll
+                for (int q = 0; q < 16; ++q)
+                    if (q < 8 || cs == 16) part[q] = cluster.map_shared_rank(ypart, q)[r * D + c];
                 float v = xs[r * D + c];
-                for (int q = 0; q < cs; ++q) v += cluster.map_shared_rank(ypart, q)[r * D + c];   // rank order
-                mine[e] = v;
+#pragma unroll
+                for (int q = 0; q < 16; ++q)
+                    if (q < 8 || cs == 16) v += part[q];                 // rank order
+                mine[r * OC + cl] = v;
             }
         }
         cluster.sync();      // new residual slices published; partial sums no longer needed
 
         // ---- gather the new residual rows from all ranks ----
-        for (int i = threadIdx.x; i < 8 * D / 4; i += kThreads) {
-            const int r = i / (D / 4), c = (i % (D / 4)) * 4;
-            const int q = c / OC;
-            const float *src = cluster.map_shared_rank(xnew, q) + (size_t)buf * 8 * OC + r * OC + (c - q * OC);
-            *reinterpret_cast<float4 *>(xs + r * D + c) = *reinterpret_cast<const float4 *>(src);
+        {
+            const int r = warp >> 1;                             // two warps per activation row
+            const float inv_oc = 1.f / (float)OC;
+#pragma unroll 3
+            for (int c4 = (warp & 1) * 32 + lane; c4 < D / 4; c4 += 64) {
+                const int c = c4 * 4;
+                const int q = (int)(((float)c + 0.5f) * inv_oc);          // c / OC for these small integers
+                const float *src = cluster.map_shared_rank(xnew, q) + (size_t)buf * 8 * OC + r * OC + (c - q * OC);
+                *reinterpret_cast<float4 *>(xs + r * D + c) = *reinterpret_cast<const float4 *>(src);
+            }
         }
         __syncthreads();
     }
