@@ -249,26 +249,48 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
             for (int pl = 0; pl < P; ++pl)
                 act[pl] = smem_u32(xp) + (uint32_t)(pl * xplane_w + g * (p.x_pitch / 2) + t) * 4u;
             const int W = 2 * U * 16;                            // gate columns then up columns
-            for (int trow = warp; trow < 2 * U; trow += kWarps) {
-                float acc[4] = {0.f, 0.f, 0.f, 0.f};
-                tile_row<P>(gu_ptr, gu_cols, gu_codes, trow, act, lane, acc);
-#pragma unroll
-                for (int i = 0; i < 4; ++i)                      // (neuron g + 8*(i>>1), row 2t + (i&1))
-                    gu_out[(2 * t + (i & 1)) * W + trow * 16 + g + 8 * (i >> 1)] = scale_gu * acc[i];
-            }
-            __syncthreads();
-            // silu(gate) * up -> exact bf16 planes of the hidden slice
             const int HW = U * 16;
-            const int r = warp >> 1;                             // two warps per activation row
-            for (int c = (warp & 1) * 32 + lane; c < HW; c += 64) {
-                const float gv = gu_out[r * W + c], uv = gu_out[r * W + HW + c];
-                float hv = gv * (1.f / (1.f + expf(-gv))) * uv;
-                __nv_bfloat16 *o = hp + r * p.h_pitch + c;
+            if (U >= kWarps) {
+                // enough hidden tile rows for every warp: one warp computes the gate and the up
+                // tile row of a hidden tile row and applies SwiGLU in registers
+                for (int hrow = warp; hrow < U; hrow += kWarps) {
+                    float ag[4] = {0.f, 0.f, 0.f, 0.f}, au[4] = {0.f, 0.f, 0.f, 0.f};
+                    tile_row<P>(gu_ptr, gu_cols, gu_codes, hrow, act, lane, ag);
+                    tile_row<P>(gu_ptr, gu_cols, gu_codes, U + hrow, act, lane, au);
 #pragma unroll
-                for (int pl = 0; pl < P; ++pl) {
-                    const __nv_bfloat16 hb = __float2bfloat16_rn(hv);
-                    o[(size_t)pl * 8 * p.h_pitch] = hb;
-                    hv -= __bfloat162float(hb);
+                    for (int i = 0; i < 4; ++i) {                // (neuron g + 8*(i>>1), row 2t + (i&1))
+                        const float gv = scale_gu * ag[i], uv = scale_gu * au[i];
+                        float hv = gv * (1.f / (1.f + expf(-gv))) * uv;
+                        __nv_bfloat16 *o = hp + (2 * t + (i & 1)) * p.h_pitch + hrow * 16 + g + 8 * (i >> 1);
+#pragma unroll
+                        for (int pl = 0; pl < P; ++pl) {
+                            const __nv_bfloat16 hb = __float2bfloat16_rn(hv);
+                            o[(size_t)pl * 8 * p.h_pitch] = hb;
+                            hv -= __bfloat162float(hb);
+                        }
+                    }
+                }
+            } else {
+                for (int trow = warp; trow < 2 * U; trow += kWarps) {
+                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                    tile_row<P>(gu_ptr, gu_cols, gu_codes, trow, act, lane, acc);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)                  // (neuron g + 8*(i>>1), row 2t + (i&1))
+                        gu_out[(2 * t + (i & 1)) * W + trow * 16 + g + 8 * (i >> 1)] = scale_gu * acc[i];
+                }
+                __syncthreads();
+                // silu(gate) * up -> exact bf16 planes of the hidden slice
+                const int r = warp >> 1;                         // two warps per activation row
+                for (int c = (warp & 1) * 32 + lane; c < HW; c += 64) {
+                    const float gv = gu_out[r * W + c], uv = gu_out[r * W + HW + c];
+                    float hv = gv * (1.f / (1.f + expf(-gv))) * uv;
+                    __nv_bfloat16 *o = hp + r * p.h_pitch + c;
+#pragma unroll
+                    for (int pl = 0; pl < P; ++pl) {
+                        const __nv_bfloat16 hb = __float2bfloat16_rn(hv);
+                        o[(size_t)pl * 8 * p.h_pitch] = hb;
+                        hv -= __bfloat162float(hb);
+                    }
                 }
             }
         }
