@@ -327,6 +327,25 @@ int mortar_mlp_prefill(const mortar_sched *gate_up, const mortar_sched *down, co
                        int32_t n_clusters, void *y, int64_t ldy, void *workspace,
                        int64_t workspace_bytes, void *stream);
 
+/* ReMoE router: gates[rows, n_groups] from activations x[rows, d_model] (fp32), the producer of
+ * the `gates` input of the MLP entry points.  Replaces TileRouter.forward
+ * (morph/model/routing.py:159-284) and the decode engine's two-launch fused_router
+ * (morph/kernels/triton/fused_router.py:101-139):
+ *   q = LayerNorm(x wq^T + iter_vec)        wq [d, d] row-major, iter_vec [d] or NULL
+ *   sa = q[:d/2] sub_keys_a^T, sb = q[d/2:] sub_keys_b^T      sub keys [n_sub_keys, d/2]
+ *   logits: sums sa[a] + sb[b] (a-major) + group_bias -- mapped 1:1 when n_sub_keys^2 ==
+ *           n_groups, the n_groups largest in descending order when there are more, repeated
+ *           cyclically when there are fewer (routing.py:185-204)
+ *   gates = relu(logits - k-th largest) * k / max(sum, 1e-6)   (k >= n_groups: no threshold)
+ * qv_scratch: device, rows*d_model floats (the projected query between the two launches).
+ * Two launches on `stream`; no allocation, no synchronisation. */
+int mortar_router_gates(const float *x, int64_t ldx, int64_t rows, int32_t d_model,
+                        const float *wq, const float *iter_vec, const float *ln_weight,
+                        const float *ln_bias, float ln_eps, const float *sub_keys_a,
+                        const float *sub_keys_b, int32_t n_sub_keys, const float *group_bias,
+                        int32_t n_groups, int32_t k, float *qv_scratch, float *gates,
+                        int64_t ld_gates, void *stream);
+
 /* Reads (and optionally clears) the error word the staged and persistent paths of
  * mortar_linear set when one of their bounded barrier waits expires: 0 = none, 1 = staged
  * path, 2 = a consumer of the persistent kernel, 3 = one of its producers.  Synchronises.

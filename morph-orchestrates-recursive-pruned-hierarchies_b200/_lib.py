@@ -77,6 +77,8 @@ _SIGNATURES = {
                                      _i32, _vp, _i64, _vp, _i64, _vp]),
     "mortar_prefill_error": (C.c_int, [_vp, _i32]),
     "mortar_linear_error": (C.c_int, [_vp, _i32]),
+    "mortar_router_gates": (C.c_int, [_vp, _i64, _i64, _i32, _vp, _vp, _vp, _vp, _f32, _vp, _vp, _i32, _vp,
+                                      _i32, _i32, _vp, _vp, _i64, _vp]),
 }
 
 # entry points added by later translation units; bound when present in the header list

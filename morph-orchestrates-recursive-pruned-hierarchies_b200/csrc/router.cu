@@ -1,0 +1,165 @@
+// ReMoE tile router in two launches: the query projection (a dense fp32 product, many CTAs) and
+// everything after it (one CTA per row).  Same arithmetic as TileRouter.forward
+// (morph/model/routing.py:159-284): q = LayerNorm(x Wq^T + iter_embed); product-key scores
+// sa = q[:d/2] Ka^T, sb = q[d/2:] Kb^T; group logits from the nsk x nsk sums sa[a] + sb[b];
+// gate = relu(logit - k-th largest) * k / max(sum, 1e-6).  The decode engine of the reference
+// does the same in two Triton launches for ONE row and the 1:1 product map only
+// (morph/kernels/triton/fused_router.py:101-139); here any number of rows and all three maps.
+#include <cuda_runtime.h>
+#include <cstdint>
+#include "common.h"
+
+namespace {
+
+constexpr int kProjRows = 8;        // activation rows a warp accumulates for one output at a time
+constexpr int kTailThreads = 256;
+
+// qv[b, o] = sum_i x[b, i] * wq[o, i] + iter_vec[o].  One warp per output feature, kProjRows rows
+// of x per pass (blockIdx.y), so a weight row is read once per 8 rows.
+__global__ void __launch_bounds__(256)
+router_project_kernel(const float *x, long long ldx, long long rows, int d, const float *wq,
+                      const float *iter_vec, float *qv) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int o = blockIdx.x * 8 + warp;
+    if (o >= d) return;
+    const long long b0 = (long long)blockIdx.y * kProjRows;
+    float acc[kProjRows];
+#pragma unroll
+    for (int r = 0; r < kProjRows; ++r) acc[r] = 0.f;
+    const float *w = wq + (long long)o * d;
+    for (int i = lane; i < d; i += 32) {
+        const float wv = __ldg(w + i);
+#pragma unroll
+        for (int r = 0; r < kProjRows; ++r) {
+            const long long b = b0 + r < rows ? b0 + r : rows - 1;       // clamped rows are discarded
+            acc[r] = fmaf(__ldg(x + b * ldx + i), wv, acc[r]);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < kProjRows; ++r)
+        for (int off = 16; off > 0; off >>= 1) acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], off);
+    if (lane == 0) {
+        const float bias = iter_vec ? iter_vec[o] : 0.f;
+#pragma unroll
+        for (int r = 0; r < kProjRows; ++r)
+            if (b0 + r < rows) qv[(b0 + r) * d + o] = acc[r] + bias;
+    }
+}
+
+__device__ __forceinline__ float block_sum(float v, float *scratch) {
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();                                   // scratch may still be read from the last call
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float t = 0.f;
+    for (int w = 0; w < kTailThreads / 32; ++w) t += scratch[w];
+    return t;
+}
+
+// One CTA per row.  Dynamic shared memory: q[d] | prod[nsk*nsk] | logits[G] | sa[nsk] | sb[nsk].
+__global__ void __launch_bounds__(kTailThreads)
+router_tail_kernel(const float *qv, int d, const float *ln_w, const float *ln_b, float ln_eps,
+                   const float *ska, const float *skb, int nsk, const float *gbias, int G, int k,
+                   float *gates, long long ld_gates) {
+    extern __shared__ float sm[];
+    __shared__ float scratch[kTailThreads / 32];
+    __shared__ float kth_s;
+    float *q = sm, *prod = q + d, *logits = prod + nsk * nsk, *sa = logits + G, *sb = sa + nsk;
+    const long long row = blockIdx.x;
+    const float *qr = qv + row * d;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int d2 = d / 2, np = nsk * nsk;
+
+    // LayerNorm over d (biased variance, as torch.nn.LayerNorm)
+    float s = 0.f;
+    for (int i = tid; i < d; i += kTailThreads) { const float v = qr[i]; q[i] = v; s += v; }
+    const float mean = block_sum(s, scratch) / (float)d;
+    float s2 = 0.f;
+    for (int i = tid; i < d; i += kTailThreads) { const float c = q[i] - mean; s2 += c * c; }
+    const float rstd = 1.f / sqrtf(block_sum(s2, scratch) / (float)d + ln_eps);
+    for (int i = tid; i < d; i += kTailThreads) q[i] = (q[i] - mean) * rstd * ln_w[i] + ln_b[i];
+    __syncthreads();
+
+    // sub-key scores: 2*nsk dot products of length d/2, one warp each
+    for (int j = warp; j < 2 * nsk; j += kTailThreads / 32) {
+        const bool second = j >= nsk;
+        const float *key = (second ? skb : ska) + (long long)(second ? j - nsk : j) * d2;
+        const float *qh = q + (second ? d2 : 0);
+        float a = 0.f;
+        for (int i = lane; i < d2; i += 32) a = fmaf(qh[i], __ldg(key + i), a);
+        for (int off = 16; off > 0; off >>= 1) a += __shfl_xor_sync(0xffffffffu, a, off);
+        if (lane == 0) (second ? sb : sa)[second ? j - nsk : j] = a;
+    }
+    __syncthreads();
+    for (int pidx = tid; pidx < np; pidx += kTailThreads) prod[pidx] = sa[pidx / nsk] + sb[pidx % nsk];
+    __syncthreads();
+
+    // group logits: 1:1 map, the G largest products in descending order, or products repeated
+    if (np == G) {
+        for (int g = tid; g < G; g += kTailThreads) logits[g] = prod[g] + gbias[g];
+    } else if (np > G) {
+        for (int pidx = tid; pidx < np; pidx += kTailThreads) {
+            const float v = prod[pidx];
+            int rank = 0;                                // position in a stable descending sort
+            for (int j = 0; j < np; ++j) rank += (prod[j] > v) || (prod[j] == v && j < pidx);
+            if (rank < G) logits[rank] = v + gbias[rank];
+        }
+    } else {
+        for (int g = tid; g < G; g += kTailThreads) logits[g] = prod[g % np] + gbias[g];
+    }
+    __syncthreads();
+
+    // k-th largest value by exact descending rank (ties by index, the order torch.topk yields)
+    if (tid == 0) kth_s = 0.f;
+    __syncthreads();
+    if (k < G) {
+        for (int g = tid; g < G; g += kTailThreads) {
+            const float v = logits[g];
+            int rank = 0;
+            for (int j = 0; j < G; ++j) rank += (logits[j] > v) || (logits[j] == v && j < g);
+            if (rank == k - 1) kth_s = v;
+        }
+        __syncthreads();
+    }
+    const float kth = k < G ? kth_s : 0.f;
+    float gs = 0.f;
+    for (int g = tid; g < G; g += kTailThreads) {
+        const float v = fmaxf(logits[g] - kth, 0.f);
+        logits[g] = v;
+        gs += v;
+    }
+    const float total = fmaxf(block_sum(gs, scratch), 1e-6f);
+    const float mul = (float)k / total;
+    for (int g = tid; g < G; g += kTailThreads) gates[row * ld_gates + g] = logits[g] * mul;
+}
+
+}  // namespace
+
+extern "C" int mortar_router_gates(const float *x, int64_t ldx, int64_t rows, int32_t d_model,
+                                   const float *wq, const float *iter_vec, const float *ln_weight,
+                                   const float *ln_bias, float ln_eps, const float *sub_keys_a,
+                                   const float *sub_keys_b, int32_t n_sub_keys, const float *group_bias,
+                                   int32_t n_groups, int32_t k, float *qv_scratch, float *gates,
+                                   int64_t ld_gates, void *stream) {
+    if (!x || !wq || !ln_weight || !ln_bias || !sub_keys_a || !sub_keys_b || !group_bias || !qv_scratch || !gates)
+        return MORTAR_ERR_NULL;
+    if (rows < 0 || d_model <= 0 || (d_model & 1) || ldx < d_model || n_sub_keys <= 0 || n_groups <= 0 ||
+        k <= 0 || ld_gates < n_groups)
+        return MORTAR_ERR_SHAPE;
+    if (rows == 0) return MORTAR_OK;
+    if (rows > 0x7fffffffLL || (rows + kProjRows - 1) / kProjRows > 65535) return MORTAR_ERR_CAPACITY;
+    const size_t smem = sizeof(float) * ((size_t)d_model + (size_t)n_sub_keys * n_sub_keys + n_groups + 2 * (size_t)n_sub_keys);
+    if (smem > 200 * 1024) return MORTAR_ERR_CAPACITY;
+    cudaStream_t st = (cudaStream_t)stream;
+    dim3 grid((d_model + 7) / 8, (unsigned)((rows + kProjRows - 1) / kProjRows));
+    router_project_kernel<<<grid, 256, 0, st>>>(x, ldx, rows, d_model, wq, iter_vec, qv_scratch);
+    MORTAR_CUDA_CHECK(cudaGetLastError());
+    if (smem > 48 * 1024)
+        MORTAR_CUDA_CHECK(cudaFuncSetAttribute(router_tail_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    router_tail_kernel<<<(unsigned)rows, kTailThreads, smem, st>>>(qv_scratch, d_model, ln_weight, ln_bias, ln_eps,
+                                                                    sub_keys_a, sub_keys_b, n_sub_keys, group_bias,
+                                                                    n_groups, k, gates, ld_gates);
+    MORTAR_CUDA_CHECK(cudaGetLastError());
+    return MORTAR_OK;
+}

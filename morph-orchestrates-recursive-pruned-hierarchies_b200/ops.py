@@ -457,6 +457,47 @@ def route_flags(gates: torch.Tensor, rlo: torch.Tensor, rhi: torch.Tensor, clo: 
     _launches += 1
 
 
+def router_gates(x: torch.Tensor, router, iter_idx: int = 0, out: Optional[torch.Tensor] = None,
+                 scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Gates [rows, n_groups] (fp32) of a ReMoE router for activations x[..., d_model]: the
+    projection, LayerNorm, product-key logits and the relu(logit - k-th) * k / sum rule of
+    ``TileRouter.forward`` (morph/model/routing.py:159-284) in two launches, the role of the
+    reference's ``fused_router`` (morph/kernels/triton/fused_router.py:101-139) for any number of
+    rows.  ``router`` is anything with the reference router's parameters (``query_proj.weight``,
+    ``iter_embed``, ``query_norm``, ``sub_keys_a/b``, ``group_bias``, ``activation_k``,
+    ``n_sub_keys``, ``n_tile_groups``) in fp32 on the device of x."""
+    global _launches
+    _require_cuda(x, "x")
+    d = router.d_model
+    x2 = _rows2d(x, d, "x")
+    if x2.dtype != torch.float32:
+        x2 = x2.float()
+    if x2.stride(1) != 1:
+        x2 = x2.contiguous()
+    rows = x2.shape[0]
+    G, nsk = int(router.n_tile_groups), int(router.n_sub_keys)
+    params = [router.query_proj.weight, router.iter_embed, router.query_norm.weight, router.query_norm.bias,
+              router.sub_keys_a, router.sub_keys_b, router.group_bias]
+    for t in params:
+        if t.dtype != torch.float32 or not t.is_cuda or not t.is_contiguous():
+            raise ValueError("router parameters must be contiguous float32 CUDA tensors")
+    it = max(0, min(int(iter_idx), router.iter_embed.shape[0] - 1))
+    if out is None:
+        out = torch.empty(rows, G, device=x.device, dtype=torch.float32)
+    if scratch is None:
+        scratch = torch.empty(max(rows, 1) * d, device=x.device, dtype=torch.float32)
+    if rows == 0:
+        return out
+    _lib.check(_lib.lib().mortar_router_gates(
+        _ptr(x2), x2.stride(0), rows, d, _ptr(router.query_proj.weight), _ptr(router.iter_embed[it]),
+        _ptr(router.query_norm.weight), _ptr(router.query_norm.bias), float(router.query_norm.eps),
+        _ptr(router.sub_keys_a), _ptr(router.sub_keys_b), nsk, _ptr(router.group_bias), G,
+        int(router.activation_k), _ptr(scratch), _ptr(out), out.stride(0), _stream_ptr()),
+        "mortar_router_gates")
+    _launches += 2
+    return out
+
+
 def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     """fp32 RMSNorm over the last dim (fused_decode_step.py:305-321), evaluated by the
     activation-prep kernel and re-assembled from its three exact planes."""

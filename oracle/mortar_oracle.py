@@ -293,6 +293,32 @@ def remoe_gates(logits: Tensor, k: int) -> Tensor:
     return g * (k / s)
 
 
+def router_logits(x: np.ndarray, wq: np.ndarray, iter_vec: np.ndarray, ln_w: np.ndarray, ln_b: np.ndarray,
+                  ln_eps: float, ska: np.ndarray, skb: np.ndarray, gbias: np.ndarray) -> np.ndarray:
+    """Group logits of the ReMoE router for rows x[N, d] (float64 accumulation, returned as
+    float32).  routing.py:166-204: q = LayerNorm(x Wq^T + iter_embed); product-key scores of the
+    two halves of q; the nsk^2 sums sa[a] + sb[b] (a-major) mapped onto G groups 1:1, as the G
+    largest in descending order, or repeated cyclically; + group_bias."""
+    x = np.asarray(x, dtype=np.float64)
+    qv = x @ np.asarray(wq, dtype=np.float64).T + np.asarray(iter_vec, dtype=np.float64)
+    mean = qv.mean(axis=1, keepdims=True)
+    var = ((qv - mean) ** 2).mean(axis=1, keepdims=True)          # biased, as torch LayerNorm
+    q = (qv - mean) / np.sqrt(var + ln_eps) * np.asarray(ln_w, dtype=np.float64) + np.asarray(ln_b, dtype=np.float64)
+    d2 = x.shape[1] // 2
+    sa = q[:, :d2] @ np.asarray(ska, dtype=np.float64).T
+    sb = q[:, d2:] @ np.asarray(skb, dtype=np.float64).T
+    nsk = sa.shape[1]
+    prod = (sa[:, :, None] + sb[:, None, :]).reshape(x.shape[0], nsk * nsk)
+    G = gbias.shape[0]
+    if nsk * nsk == G:
+        lg = prod
+    elif nsk * nsk > G:
+        lg = -np.sort(-prod, axis=1, kind="stable")[:, :G]
+    else:
+        lg = prod[:, np.arange(G) % (nsk * nsk)]
+    return (lg + np.asarray(gbias, dtype=np.float64)).astype(np.float32)
+
+
 def cluster_spans(d_ff: int, n_clusters: int, blk: int):
     """Cluster span (lo, hi) of every gate_up output block-row (gate half then up half,
     same neuron mapping) and every down input block-column.  engine.py:384-413."""

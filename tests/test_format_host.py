@@ -9,7 +9,7 @@ import pytest
 import torch
 
 import mortar_b200 as mb
-from conftest import GOLDEN_CASES, ROOT, load_golden
+from conftest import GOLDEN_CASES, ROOT, bf16_from_bits, load_golden
 from oracle import mortar_oracle as orc
 
 fmt = mb.format if hasattr(mb, "format") else None
@@ -327,3 +327,51 @@ def test_router_mirror_matches_reference_gates():
     np.testing.assert_allclose(logits.numpy(), g["router_logits"], rtol=1e-5, atol=1e-6)
     np.testing.assert_allclose(gates.numpy(), g["router_gates"], rtol=1e-4, atol=1e-6)
     assert aux.ndim == 0 and float(aux) >= 0
+
+
+def test_custom_ops_have_fake_kernels_and_no_cpu_path():
+    """The registered ops trace through fake tensors (shapes and dtypes only) and refuse CPU
+    tensors the way the reference's CUDA-only operator does."""
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    with FakeTensorMode():
+        x = torch.empty(3, 5, 64, device="cuda", dtype=torch.bfloat16)
+        gp = torch.empty(9, device="cuda", dtype=torch.int32)
+        gc = torch.empty(10, 8, device="cuda", dtype=torch.int16)
+        gk = torch.empty(10, 512, device="cuda", dtype=torch.uint8)
+        y = torch.ops.mortar_b200.linear(x, gp, gc, gk, 0.5, 128, 64, 10)
+        assert y.shape == (3, 5, 128) and y.dtype == torch.bfloat16 and y.device.type == "cuda"
+        y = torch.ops.mortar_b200.mlp_prefill(x, gp, gc, gk, 0.5, 256, 64, 10, gp, gc, gk, 0.5, 64, 128, 10, None, 0)
+        assert y.shape == (3, 5, 64) and y.dtype == torch.bfloat16
+        xf = torch.empty(7, 64, device="cuda", dtype=torch.float32)
+        y = torch.ops.mortar_b200.mlp_decode(xf, None, 1e-6, gp, gc, gk, 0.5, 256, 64, 10, gp, gc, gk, 0.5, 64, 128,
+                                             10, None, 0)
+        assert y.shape == (7, 64) and y.dtype == torch.float32
+    with pytest.raises(NotImplementedError):
+        torch.ops.mortar_b200.linear(torch.zeros(2, 64), torch.zeros(9, dtype=torch.int32),
+                                     torch.zeros(1, 8, dtype=torch.int16), torch.zeros(1, 512, dtype=torch.uint8),
+                                     0.5, 128, 64, 1)
+    with pytest.raises(NotImplementedError):
+        z = torch.zeros(1)
+        mb.torch_ops.stk_dds(torch.zeros(2, 64), z, z, z, z, z, z, z, 64, 128, True)
+
+
+@pytest.mark.parametrize("case", GOLDEN_CASES)
+def test_dds_shim_conversion_of_effective_weights(case):
+    """[nnz, blk, blk] effective weights (code * bf16 scale, what a ternarised layer feeds the
+    reference operator) + the reference's row pointers / column ids -> the same tiles as the
+    packed-storage converter; anything that is not ternary is refused."""
+    g = load_golden(case)
+    d_model, d_ff, blk, ncls = (int(v) for v in g["meta"])
+    for tag, (O, I) in (("gu", (2 * d_ff, d_model)), ("dn", (d_model, d_ff))):
+        sc = torch.tensor(float(g[f"{tag}_scale"])).to(torch.bfloat16)
+        data = (torch.from_numpy(g[f"{tag}_codes"]).float() * sc.float()).to(torch.bfloat16)
+        m = mb.torch_ops._ternary_matrix_from_data(data, torch.from_numpy(g[f"{tag}_offsets"]),
+                                                   torch.from_numpy(g[f"{tag}_column_indices"]), O, I)
+        ref = mb.MortarMatrix.from_reference_bcsr(g[f"{tag}_offsets"], g[f"{tag}_column_indices"],
+                                                  g[f"{tag}_packed"], float(g[f"{tag}_scale"]), blk, O, I)
+        np.testing.assert_array_equal(m.to_dense_codes(), ref.to_dense_codes())
+        assert m.scale == float(sc)
+        raw = bf16_from_bits(g[f"{tag}_data_bf16"])          # the un-ternarised carved weights
+        with pytest.raises(ValueError):
+            mb.torch_ops._ternary_matrix_from_data(raw, torch.from_numpy(g[f"{tag}_offsets"]),
+                                                   torch.from_numpy(g[f"{tag}_column_indices"]), O, I)

@@ -316,3 +316,47 @@ def test_module_mirror_matches_ops(local_layer):
     assert lin.is_compact and lin.bias is None and abs(lin.get_density() - 0.25) < 1e-6
     with pytest.raises(AssertionError):
         lin.carve()
+
+
+@pytest.mark.parametrize("case", GOLDEN_CASES)
+def test_registered_ops_and_dds_shim_against_reference_outputs(case):
+    """The MLP assembled from the reference operator's own call (stk_dds twice, the elementwise
+    steps in torch as transformer.py:402-431 has them) and through the registered
+    mortar_b200:: ops, against the bf16 outputs the reference produced."""
+    g = load_golden(case)
+    d_model, d_ff, blk, ncls = (int(v) for v in g["meta"])
+    x = bf16_from_bits(g["x_bf16"]).to(DEV)
+    x2 = x.reshape(-1, d_model)
+    z = torch.zeros(1, dtype=torch.int16, device=DEV)
+    datas, mats = {}, {}
+    for tag, (O, I) in (("gu", (2 * d_ff, d_model)), ("dn", (d_model, d_ff))):
+        sc = torch.tensor(float(g[f"{tag}_scale"])).to(torch.bfloat16)
+        datas[tag] = ((torch.from_numpy(g[f"{tag}_codes"]).float() * sc.float()).to(torch.bfloat16).to(DEV),
+                      torch.from_numpy(g[f"{tag}_offsets"]).to(DEV),
+                      torch.from_numpy(g[f"{tag}_column_indices"]).to(DEV), I, O)
+        mats[tag] = mb.MortarMatrix.from_reference_bcsr(
+            g[f"{tag}_offsets"], g[f"{tag}_column_indices"], g[f"{tag}_packed"],
+            float(g[f"{tag}_scale"]), blk, O, I).to_stream(DEV)
+
+    def dds(inp, tag):
+        data, off, ci, I, O = datas[tag]
+        return mb.torch_ops.stk_dds(inp, data, off, z, ci, z, z, z, I, O, True)
+
+    gu = dds(x2, "gu")
+    assert gu.dtype == torch.bfloat16 and gu.shape == (x2.shape[0], 2 * d_ff)
+    gate, up = gu.chunk(2, dim=-1)
+    h = torch.nn.functional.silu(gate) * up
+    y = dds(h.contiguous(), "dn").reshape(*x.shape[:-1], d_model)
+    _assert_bf16_close(y, bf16_from_bits(g["y_bf16"]))
+    # the registered ops, unrouted and routed
+    args = (*mb.torch_ops.stream_args(mats["gu"]), *mb.torch_ops.stream_args(mats["dn"]))
+    y = torch.ops.mortar_b200.mlp_prefill(x, *args, None, 0)
+    _assert_bf16_close(y, bf16_from_bits(g["y_bf16"]))
+    gates = torch.from_numpy(g["gates_autocast"]).to(DEV)
+    y = torch.ops.mortar_b200.mlp_prefill(x, *args, gates, ncls)
+    _assert_bf16_close(y, bf16_from_bits(g["y_routed_bf16"]))
+    y32 = torch.ops.mortar_b200.mlp_decode(x.float(), None, 1e-6, *args, None, 0).cpu()
+    ref = torch.from_numpy(g["y_fp32"])
+    assert float((y32 - ref).abs().max()) <= 1.5e-2 * float(ref.abs().max())
+    y1 = torch.ops.mortar_b200.linear(x, *mb.torch_ops.stream_args(mats["gu"]))
+    assert torch.equal(y1.reshape(-1, 2 * d_ff), gu)

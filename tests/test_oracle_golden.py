@@ -149,3 +149,18 @@ def test_decode_algebra_matches_dense_path(case):
         assert np.abs(y - yo.numpy()).max() <= 1e-5 * scale
         ref = (g["y_routed_fp32"] if routed else g["y_fp32"]).reshape(-1, d_model)[:3]
         assert np.abs(y - ref).max() <= 2e-2 * np.abs(ref).max()
+
+
+def test_router_logits_and_gates_match_reference_router():
+    """The router restatement on the reference router's own parameters and input reproduces the
+    logits its forward fed to topk and the gates it returned (tests/golden/make_golden.py)."""
+    g = load_golden("mlp_tile16_d128_cs16")
+    sd = {k[len("router_sd__"):]: v for k, v in g.items() if k.startswith("router_sd__")}
+    x = bf16_from_bits(g["x_bf16"]).float().reshape(-1, 128).numpy()
+    lg = orc.router_logits(x, sd["query_proj__weight"], sd["iter_embed"][0], sd["query_norm__weight"],
+                           sd["query_norm__bias"], 1e-5, sd["sub_keys_a"], sd["sub_keys_b"], sd["group_bias"])
+    np.testing.assert_allclose(lg, g["router_logits"], rtol=1e-5, atol=2e-6)
+    k = max(1, round(0.25 * 16))
+    gates = orc.remoe_gates(torch.from_numpy(g["router_logits"]), k).numpy()
+    np.testing.assert_allclose(gates, g["router_gates"], rtol=1e-5, atol=1e-6)
+    assert ((gates > 0).sum(axis=1) == k - 1).all()
