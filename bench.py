@@ -534,6 +534,48 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def run_probe(name: str):
+    """A few untimed launches of one kernel on a small case of its workload: the command the
+    profiler captures (`ncu ... python bench.py --probe <name>`).  Prints nothing but "done"."""
+    import mortar_b200 as mb
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    if name == "stack":              # stack_decode_kernel, the headline launch (batch 64)
+        stack = Stack(LOCAL, mb, device)
+        x = mb.synth.make_activations(DECODE_BATCH, LOCAL["d_model"], seed=1, dtype=torch.float32).to(device)
+        x0 = x.clone()
+        for _ in range(4):
+            x.copy_(x0)
+            mb.ops.stack_decode(x, stack.decode_stack)
+    elif name == "decode":           # bcsr_stream_kernel, one MLP application at batch 64 (3 launches)
+        L = mb.synth.make_layer(LOCAL["d_model"], LOCAL["d_ff"], DENSITY, seed=100)
+        gu, dn = L.gate_up.to_stream(device), L.down.to_stream(device)
+        x = mb.synth.make_activations(DECODE_BATCH, LOCAL["d_model"], seed=1, dtype=torch.float32).to(device)
+        out = torch.empty_like(x)
+        for _ in range(4):
+            mb.ops.mlp_decode(x, gu, dn, n_planes=3, out_dtype=torch.float32, out=out)
+    elif name == "gemv":             # bcsr_stream_kernel, 30B-model gate_up at batch 1, cold L2
+        gu = mb.synth.make_block_matrix(2 * 21824, 8192, DENSITY, seed=1).to_stream(device)
+        xp = mb.ops.act_prep(mb.synth.make_activations(1, 8192, seed=3, dtype=torch.float32).to(device), 3)
+        flush = torch.empty(L2_FLUSH_BYTES, device=device, dtype=torch.uint8)
+        for i in range(3):
+            flush.fill_(i)
+            mb.ops.linear_planes(gu, xp, swiglu=True, out_planes=3)
+    elif name == "prefill":          # prefill_panel_kernel, one cloud-shape MLP on 4096 tokens
+        L = mb.synth.make_layer(CLOUD["d_model"], CLOUD["d_ff"], DENSITY, seed=200)
+        gu, dn = L.gate_up.to_sched(True, device), L.down.to_sched(False, device)
+        x = mb.synth.make_activations(4096, CLOUD["d_model"], seed=2).to(device)
+        h = torch.empty(4096, CLOUD["d_ff"], device=device, dtype=torch.bfloat16)
+        y = torch.empty(4096, CLOUD["d_model"], device=device, dtype=torch.bfloat16)
+        for _ in range(3):
+            mb.ops.linear_tc(x, gu, out=h)
+            mb.ops.linear_tc(h, dn, out=y)
+    else:
+        raise SystemExit(f"unknown probe {name}")
+    torch.cuda.synchronize()
+    print("done", flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -541,7 +583,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--quick", action="store_true", help="headline measurement only")
+    ap.add_argument("--probe", default=None, choices=["stack", "decode", "gemv", "prefill"],
+                    help="run a few untimed launches of one kernel (small case) for a profiler capture")
     args = ap.parse_args()
+    if args.probe:
+        run_probe(args.probe)
+        return
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
