@@ -360,3 +360,34 @@ def test_registered_ops_and_dds_shim_against_reference_outputs(case):
     assert float((y32 - ref).abs().max()) <= 1.5e-2 * float(ref.abs().max())
     y1 = torch.ops.mortar_b200.linear(x, *mb.torch_ops.stream_args(mats["gu"]))
     assert torch.equal(y1.reshape(-1, 2 * d_ff), gu)
+
+
+def test_remoe_cloud_configuration():
+    """The routed configuration at its own sizes: d_model 2048, d_ff 5632, 352 groups of 16 hidden
+    neurons, k = 88 (87 active per token).  A 64-token decode batch against the oracle; the
+    4096-token prefill through properties that do not need a CPU pass of that size: a token
+    whose gates are all zero yields exact zeros, and the routed output of a token equals the
+    one it gets inside a smaller batch (tokens are independent)."""
+    L = mb.synth.make_layer(2048, 5632, 0.25, seed=200)
+    gu, dn = L.gate_up.to_stream(DEV), L.down.to_stream(DEV)
+    ncls, k = 352, 88
+    x = mb.synth.make_activations(64, 2048, seed=5, dtype=torch.float32)
+    gates = mb.synth.make_gates(64, L, ncls, k, seed=6)
+    assert int((gates > 0).sum(dim=1).max()) == k - 1
+    y = mb.ops.mlp_decode(x.to(DEV), gu, dn, gates=gates.to(DEV), n_clusters=ncls, n_planes=3)
+    ref = _decode_oracle(x, L, gates, ncls)
+    assert float((y.cpu() - ref).abs().max()) <= F32_TOL * float(ref.abs().max())
+    # prefill at 4096 tokens on the tensor-core path
+    gs, ds = L.gate_up.to_sched(True, DEV), L.down.to_sched(False, DEV)
+    xb = mb.synth.make_activations(4096, 2048, seed=7).to(DEV)
+    g4 = mb.synth.make_gates(4096, L, ncls, k, seed=8).to(DEV)
+    g4[17] = 0.0
+    y4 = mb.ops.mlp_prefill_tc(xb, gs, ds, gates=g4, n_clusters=ncls)
+    assert mb.ops.prefill_error() == 0
+    assert float(y4[17].float().abs().max()) == 0.0
+    sub = slice(1000, 1128)
+    ysub = mb.ops.mlp_prefill_tc(xb[sub].contiguous(), gs, ds, gates=g4[sub].contiguous(), n_clusters=ncls)
+    assert torch.equal(ysub, y4[sub])
+    ref = orc.swiglu_mlp(xb[sub].cpu().float(), _dense(L.gate_up), _dense(L.down), g4[sub].cpu(), ncls,
+                         dtype=torch.bfloat16)
+    _assert_bf16_close(ysub, ref)
