@@ -395,6 +395,7 @@ def run_ours(args, rank, world, local_rank):
                 "bcsr_stream_kernel_us_per_launch": round(us_launch, 3),
                 "checksum": r["checksum"]}
             extra["prefill_cloud"] = run_prefill(mb, device, pk, flush)
+            extra["prefill_cloud_blocks128"] = run_prefill_blocks128(mb, device, pk, flush)
             extra["gemv_large_b1"] = run_gemv_large(mb, device, pk, flush)
         if world == 1:
             c = cpu_reference_decode(DECODE_BATCH, budget_s=12.0)
@@ -467,6 +468,28 @@ def run_prefill(mb, device, pk, flush, tokens: int = PREFILL_TOKENS, reps: int =
                          "frac": round(tf / pk["bf16_tflops_sustained"], 5),
                          "peak_source": pk["source"] + " (bf16 sustained)"},
             "device_error_word": err}
+
+
+def run_prefill_blocks128(mb, device, pk, flush, tokens: int = PREFILL_TOKENS, reps: int = 5):
+    """One cloud-shape MLP whose 25% topology is made of ragged 128x128 blocks, the granularity the
+    reference carves at in production (carve(blocking=128), block_sparse.py:810-907; 64 tiles per
+    block after the split).  Vertically adjacent tiles fuse into N = 128 tensor-core runs, so this
+    is the same kernel at the rate the tensor pipe gives wide MMAs; configs[2] with single-tile
+    topology is the `prefill_cloud` entry."""
+    d, f = CLOUD["d_model"], CLOUD["d_ff"]
+    gu_m = mb.synth.make_block_matrix(2 * f, d, DENSITY, seed=11)
+    dn_m = mb.synth.make_block_matrix(d, f, DENSITY, seed=12)
+    gu, dn = gu_m.to_sched(True, device), dn_m.to_sched(False, device)
+    x = mb.synth.make_activations(tokens, d, seed=7).to(device)
+    y = torch.empty_like(x)
+    ws = torch.empty(tokens * f * 2 + 256, device=device, dtype=torch.uint8)
+    t = time_steps(lambda: mb.ops.mlp_prefill_tc(x, gu, dn, out=y, workspace=ws), reps, 2, flush)
+    ms = statistics.median(t)
+    flops = 2 * 256 * (gu_m.nnz + dn_m.nnz) * tokens
+    tf = flops / (ms * 1e-3) / 1e12
+    return {"ms_per_application": round(ms, 3), "tokens": tokens, "useful_tflops": round(tf, 2),
+            "frac_of_measured_bf16_sustained": round(tf / pk["bf16_tflops_sustained"], 5),
+            "device_error_word": mb.ops.prefill_error()}
 
 
 def run_gemv_large(mb, device, pk, flush, reps: int = 20, copies: int = 8):

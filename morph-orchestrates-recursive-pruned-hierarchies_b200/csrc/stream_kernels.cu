@@ -204,7 +204,7 @@ __device__ __forceinline__ void group_mma(float (&acc)[NT][4], const uint4 cw, c
 // than L2; the group-to-warp assignment and the summation order are those of the plain path,
 // so both give bit-identical results.
 template <int NT, int P, bool SWIGLU, int WPR, bool BULK>
-__global__ void __launch_bounds__(kWarpsPerCta * 32, (BULK && NT == 1) ? (P == 1 ? 8 : 6) : 1)
+__global__ void __launch_bounds__(kWarpsPerCta * 32, 1)
 bcsr_stream_kernel(const LinearParams p) {
     static_assert(!BULK || WPR == kWarpsPerCta, "the bulk pipeline serves one unit per CTA");
     constexpr int UPC = kWarpsPerCta / WPR;
