@@ -24,9 +24,10 @@ constexpr int kPsConsumers = kPsSlots * kPsSlotWarps * 32;
 constexpr int kPsStages = 3;            // ring depth per slot
 constexpr int kPsChunk = 16;            // groups per stage (8 KB of codes + 256 B of column indices)
 constexpr int kPsMaxSmem = 227 * 1024;
+constexpr int kPsTabUnits = 64;         // units of a CTA whose row pointers are cached in shared memory
 
 struct PsLayout {
-    int stages, cols, bars, red, fold, misc, x, total;      // byte offsets into dynamic shared memory
+    int stages, cols, bars, red, fold, misc, tab, x, total; // byte offsets into dynamic shared memory
     int x_pitch;                                            // bytes between activation rows
 };
 
@@ -36,9 +37,10 @@ __host__ __device__ inline PsLayout ps_layout(int C, int vrows, bool swiglu) {
     L.stages = off; off += kPsSlots * kPsStages * kPsChunk * 512;
     L.cols = off;   off += kPsSlots * kPsStages * kPsChunk * 16;
     L.bars = off;   off += kPsSlots * 2 * kPsStages * 8;
-    L.red = off;    off += kPsSlots * kPsSlotWarps * (swiglu ? 2 : 1) * 4 * 32 * 4;
+    L.red = off;    off += 2 * kPsSlots * kPsSlotWarps * (swiglu ? 2 : 1) * 4 * 32 * 4;   // two buffers, by unit parity
     L.fold = off;   off += kPsSlots * 2 * 16 * 9 * 4;
     L.misc = off;   off += 16;
+    L.tab = off;    off += kPsTabUnits * 2 * 2 * 4;          // (first group, group count) of both tile rows
     off = (off + 127) / 128 * 128;
     // rows 32 bytes apart modulo 128, so the 16 lanes of a half-warp (4 rows x 4 lane pairs of
     // 8 bytes) cover all 32 banks once
@@ -168,6 +170,30 @@ gemv_persistent_kernel(const LinearParams p) {
     }
     __syncthreads();
     const int u_lo = misc[0], u_hi = misc[1];
+    // row pointers of this CTA's first kPsTabUnits units -> shared memory (a tile row starts every
+    // few hundred cycles per slot; a dependent global load there would be on the critical path)
+    int *tab = reinterpret_cast<int *>(ps_smem + L.tab);
+    for (int e = tid; e < kPsTabUnits * NACC; e += kPsWarps * 32) {
+        const int ul = e / NACC, a = e % NACC;
+        if (u_lo + ul < u_hi) {
+            const int trow = u_lo + ul + a * p.units;
+            const int gbeg = __ldg(p.grp_ptr + trow);
+            tab[(ul * 2 + a) * 2] = gbeg;
+            tab[(ul * 2 + a) * 2 + 1] = __ldg(p.grp_ptr + trow + 1) - gbeg;
+        }
+    }
+    __syncthreads();
+    auto row_info = [&](int u, int a, int &gbeg, int &len) {
+        const int ul = u - u_lo;
+        if (ul < kPsTabUnits) {
+            gbeg = tab[(ul * 2 + a) * 2];
+            len = tab[(ul * 2 + a) * 2 + 1];
+        } else {
+            const int trow = u + a * p.units;
+            gbeg = __ldg(p.grp_ptr + trow);
+            len = __ldg(p.grp_ptr + trow + 1) - gbeg;
+        }
+    };
 
     // A wait that runs out records it and turns every later wait of the CTA into a no-op, so a
     // broken pipeline ends quickly (with wrong numbers and the error word set) instead of hanging.
@@ -227,18 +253,20 @@ gemv_persistent_kernel(const LinearParams p) {
         asm volatile("bar.sync %0, %1;" ::"r"(kPsSlots + 1), "r"(kPsConsumers) : "memory");
     }
     const uint32_t xs_lane = smem_u32(ps_smem + L.x) + (uint32_t)min(g, vrows - 1) * (uint32_t)L.x_pitch + t * 8u;
-    float *red = reinterpret_cast<float *>(ps_smem + L.red) + slot * kPsSlotWarps * NACC * 4 * 32;
+    float *red0 = reinterpret_cast<float *>(ps_smem + L.red) + slot * 2 * kPsSlotWarps * NACC * 4 * 32;
     float(*fold_s)[16][9] = reinterpret_cast<float(*)[16][9]>(ps_smem + L.fold) + slot * 2;
     const float scale = p.round_bf16 ? round_bf16(p.scale) : p.scale;
 
     int c = 0;                                                  // chunks consumed by this slot so far
     int turn = 0;                                               // which warp of the slot finishes this unit
-    for (int u = u_lo + slot; u < u_hi; u += kPsSlots, turn = (turn + 1 == kPsSlotWarps) ? 0 : turn + 1) {
+    int parity = 0;                                             // which `red` buffer this unit uses
+    for (int u = u_lo + slot; u < u_hi; u += kPsSlots, turn = (turn + 1 == kPsSlotWarps) ? 0 : turn + 1, parity ^= 1) {
         float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc_gate[4] = {0.f, 0.f, 0.f, 0.f};
         int rot = sw;                                           // group r of a tile row is this warp's when (r + rot') % 7 == 0
         for (int a = 0; a < NACC; ++a) {
-            const int trow = u + a * p.units;
-            const int gbeg = __ldg(p.grp_ptr + trow), len = __ldg(p.grp_ptr + trow + 1) - gbeg;
+            int gbeg, len;
+            row_info(u, a, gbeg, len);
+            (void)gbeg;
             int first = rot;                                    // this warp's first group index in the tile row
             for (int cc = 0; cc * CG < len; ++cc, ++c) {
                 const int st = c % S;
@@ -262,7 +290,10 @@ gemv_persistent_kernel(const LinearParams p) {
                 for (int i = 0; i < 4; ++i) { acc_gate[i] = acc[i]; acc[i] = 0.f; }
             }
         }
-        // ---- partial sums meet in shared memory; the warp whose turn it is adds them in warp order ----
+        // ---- partial sums meet in shared memory; the warp whose turn it is adds them in warp order.
+        // One barrier per unit: the other warps go on to the next unit, whose partial sums use
+        // the other buffer; a buffer is written again only after a barrier its reader has joined.
+        float *red = red0 + parity * kPsSlotWarps * NACC * 4 * 32;
         {
             float *mine = red + sw * NACC * 4 * 32;
 #pragma unroll
@@ -284,7 +315,6 @@ gemv_persistent_kernel(const LinearParams p) {
                 }
             }
         }
-        ps_slot_sync(slot);                                      // `red` may be written again
         if (sw == turn) {
             // acc[0..3] = (neuron g, column 2t), (g, 2t+1), (g+8, 2t), (g+8, 2t+1)
             if (p.fold > 0) {
