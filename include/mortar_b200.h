@@ -201,7 +201,8 @@ int64_t mortar_mlp_workspace_bytes(int64_t rows, int32_t d_model, int32_t d_ff, 
  * With MORTAR_FLAG_ROUND_BF16 in `flags` and n_planes == 1 the call reproduces the bf16
  * rounding points of _SwiGLUMortar.forward under autocast (transformer.py:402-431).
  * With MORTAR_FLAG_ACCUMULATE, y += MLP(x) (x and y may be the same buffer: x is fully
- * consumed by the first stage before y is written). */
+ * consumed by the first stage before y is written).  MORTAR_FLAG_PATH_* bits are handed on to
+ * both mortar_linear launches. */
 int mortar_mlp_decode(const mortar_stream *gate_up, const mortar_stream *down,
                       const void *x, int x_dtype, int64_t ldx, int64_t rows,
                       const float *rms_weight, float eps,
