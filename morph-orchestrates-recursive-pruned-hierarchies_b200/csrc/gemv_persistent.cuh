@@ -3,23 +3,24 @@
 // For at most 8 MMA columns of activations (up to 8 bf16 rows, or 2 fp32 rows as 3 exact planes
 // folded into the columns) against a matrix far larger than L2, the work per weight byte is so
 // small that everything besides the weight stream has to be taken off the critical path:
-//   * one CTA of 32 warps per SM, resident for the whole launch; the CTA's share of the matrix
+//   * one CTA of 24 warps per SM (85 registers per thread: measured faster than 32 warps at 64
+//     or 16 at 128), resident for the whole launch; the CTA's share of the matrix
 //     is a contiguous range of units balanced by group count (found by a parallel search of the
 //     row-pointer prefix sums, no atomics, no scratch memory);
 //   * the activations are staged ONCE per CTA into shared memory, laid out so that a lane's
 //     whole B fragment is one conflict-free 64-bit load;
-//   * four slots of 7 consumer warps each walk the CTA's units; every slot owns a ring of stages
-//     that its own producer warp (warps 28..31) fills with bulk asynchronous copies (mbarrier
+//   * four slots of 5 consumer warps each walk the CTA's units; every slot owns a ring of stages
+//     that its own producer warp (warps 20..23) fills with bulk asynchronous copies (mbarrier
 //     completion), so the weight bytes of the next chunks are in flight while the current one
 //     is decoded and multiplied, and nothing a consumer does can delay a refill;
-//   * partial sums of the 7 warps of a slot meet in shared memory and are added in warp order
+//   * partial sums of the 5 warps of a slot meet in shared memory and are added in warp order
 //     by one of them (taking turns, unit by unit), which also runs the epilogue.
 // The epilogue is the one of the row-block kernel, so results follow the same rounding rules.
 #pragma once
 
-constexpr int kPsWarps = 32;            // warps per CTA
+constexpr int kPsWarps = 24;            // warps per CTA
 constexpr int kPsSlots = 4;             // units in flight per CTA
-constexpr int kPsSlotWarps = 7;         // consumer warps per slot; warp 28 + slot is the slot's producer
+constexpr int kPsSlotWarps = 5;         // consumer warps per slot; warp 20 + slot is the slot's producer
 constexpr int kPsConsumers = kPsSlots * kPsSlotWarps * 32;
 constexpr int kPsStages = 3;            // ring depth per slot
 constexpr int kPsChunk = 16;            // groups per stage (8 KB of codes + 256 B of column indices)
@@ -262,7 +263,7 @@ gemv_persistent_kernel(const LinearParams p) {
     int parity = 0;                                             // which `red` buffer this unit uses
     for (int u = u_lo + slot; u < u_hi; u += kPsSlots, turn = (turn + 1 == kPsSlotWarps) ? 0 : turn + 1, parity ^= 1) {
         float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc_gate[4] = {0.f, 0.f, 0.f, 0.f};
-        int rot = sw;                                           // group r of a tile row is this warp's when (r + rot') % 7 == 0
+        int rot = sw;                                           // this warp's first group in the tile row (round robin over the slot's warps)
         for (int a = 0; a < NACC; ++a) {
             int gbeg, len;
             row_info(u, a, gbeg, len);
