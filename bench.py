@@ -397,6 +397,7 @@ def run_ours(args, rank, world, local_rank):
             extra["prefill_cloud"] = run_prefill(mb, device, pk, flush)
             extra["prefill_cloud_blocks128"] = run_prefill_blocks128(mb, device, pk, flush)
             extra["gemv_large_b1"] = run_gemv_large(mb, device, pk, flush)
+            extra["router"] = run_router(mb, device)
         if world == 1:
             c = cpu_reference_decode(DECODE_BATCH, budget_s=12.0)
             cpu = {"value": round(c["tokens_per_s"], 1), "unit": "tokens/s", "cores": c["cores"],
@@ -490,6 +491,26 @@ def run_prefill_blocks128(mb, device, pk, flush, tokens: int = PREFILL_TOKENS, r
     return {"ms_per_application": round(ms, 3), "tokens": tokens, "useful_tflops": round(tf, 2),
             "frac_of_measured_bf16_sustained": round(tf / pk["bf16_tflops_sustained"], 5),
             "device_error_word": mb.ops.prefill_error()}
+
+
+def run_router(mb, device, reps: int = 20, calls: int = 16):
+    """The two-launch ReMoE router (query projection + tail) at the decode shapes: d_model 768,
+    16 groups, k = 8, fp32, batch 1 and 64; one CUDA graph of `calls` router calls, weights warm
+    in L2 (2.4 MB of projection weights).  The reference's engine runs the same function as two
+    Triton launches for one row (morph/kernels/triton/fused_router.py:101-139)."""
+    from importlib import import_module
+    router = import_module(mb.__name__ + ".router").TileRouter(16, LOCAL["d_model"], activation_ratio=0.5)
+    router = router.to(device).eval()
+    out = {}
+    for b in (1, DECODE_BATCH):
+        x = mb.synth.make_activations(b, LOCAL["d_model"], seed=9, dtype=torch.float32).to(device)
+        gates = torch.empty(b, 16, device=device, dtype=torch.float32)
+        scratch = torch.empty(b * LOCAL["d_model"], device=device, dtype=torch.float32)
+        g = capture(lambda: [mb.ops.router_gates(x, router, out=gates, scratch=scratch) for _ in range(calls)])
+        t = time_steps(g.replay, reps, 3, None)
+        out[f"b{b}_us_per_call"] = round(statistics.median(t) * 1e3 / calls, 2)
+    out["launches_per_call"] = 2
+    return out
 
 
 def run_gemv_large(mb, device, pk, flush, reps: int = 20, copies: int = 8):
