@@ -15,7 +15,9 @@ constexpr int kProjRows = 8;        // activation rows a warp accumulates for on
 constexpr int kTailThreads = 256;
 
 // qv[b, o] = sum_i x[b, i] * wq[o, i] + iter_vec[o].  One warp per output feature, kProjRows rows
-// of x per pass (blockIdx.y), so a weight row is read once per 8 rows.
+// of x per pass (blockIdx.y), so a weight row is read once per 8 rows.  VEC: 128-bit loads (d a
+// multiple of 4, rows and weights 16-byte aligned).
+template <bool VEC>
 __global__ void __launch_bounds__(256)
 router_project_kernel(const float *x, long long ldx, long long rows, int d, const float *wq,
                       const float *iter_vec, float *qv) {
@@ -27,12 +29,25 @@ router_project_kernel(const float *x, long long ldx, long long rows, int d, cons
 #pragma unroll
     for (int r = 0; r < kProjRows; ++r) acc[r] = 0.f;
     const float *w = wq + (long long)o * d;
-    for (int i = lane; i < d; i += 32) {
-        const float wv = __ldg(w + i);
+    const float *xr[kProjRows];
 #pragma unroll
-        for (int r = 0; r < kProjRows; ++r) {
-            const long long b = b0 + r < rows ? b0 + r : rows - 1;       // clamped rows are discarded
-            acc[r] = fmaf(__ldg(x + b * ldx + i), wv, acc[r]);
+    for (int r = 0; r < kProjRows; ++r)
+        xr[r] = x + (b0 + r < rows ? b0 + r : rows - 1) * ldx;       // clamped rows are discarded
+    if (VEC) {
+        for (int i = lane * 4; i < d; i += 128) {
+            const float4 wv = __ldg(reinterpret_cast<const float4 *>(w + i));
+#pragma unroll
+            for (int r = 0; r < kProjRows; ++r) {
+                const float4 xv = __ldg(reinterpret_cast<const float4 *>(xr[r] + i));
+                acc[r] = fmaf(xv.x, wv.x, acc[r]); acc[r] = fmaf(xv.y, wv.y, acc[r]);
+                acc[r] = fmaf(xv.z, wv.z, acc[r]); acc[r] = fmaf(xv.w, wv.w, acc[r]);
+            }
+        }
+    } else {
+        for (int i = lane; i < d; i += 32) {
+            const float wv = __ldg(w + i);
+#pragma unroll
+            for (int r = 0; r < kProjRows; ++r) acc[r] = fmaf(__ldg(xr[r] + i), wv, acc[r]);
         }
     }
 #pragma unroll
@@ -153,7 +168,10 @@ extern "C" int mortar_router_gates(const float *x, int64_t ldx, int64_t rows, in
     if (smem > 200 * 1024) return MORTAR_ERR_CAPACITY;
     cudaStream_t st = (cudaStream_t)stream;
     dim3 grid((d_model + 7) / 8, (unsigned)((rows + kProjRows - 1) / kProjRows));
-    router_project_kernel<<<grid, 256, 0, st>>>(x, ldx, rows, d_model, wq, iter_vec, qv_scratch);
+    const bool vec = (d_model % 4) == 0 && (ldx % 4) == 0 && (reinterpret_cast<uintptr_t>(x) % 16) == 0 &&
+                     (reinterpret_cast<uintptr_t>(wq) % 16) == 0;
+    if (vec) router_project_kernel<true><<<grid, 256, 0, st>>>(x, ldx, rows, d_model, wq, iter_vec, qv_scratch);
+    else router_project_kernel<false><<<grid, 256, 0, st>>>(x, ldx, rows, d_model, wq, iter_vec, qv_scratch);
     MORTAR_CUDA_CHECK(cudaGetLastError());
     if (smem > 48 * 1024)
         MORTAR_CUDA_CHECK(cudaFuncSetAttribute(router_tail_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
