@@ -273,7 +273,11 @@ gemv_persistent_kernel(const LinearParams p) {
                 const int st = c % S;
                 wait_or_flag(full0 + st * 8, (uint32_t)(c / S) & 1u, 2);   // on failure keeps going: every barrier is still met
                 const int hi = min(len, (cc + 1) * CG);
+                // once a wait has given up the stage contents are not to be trusted (column indices
+                // become addresses): skip the arithmetic, keep the barrier protocol
+                const bool dead = *reinterpret_cast<volatile int *>(&misc[2]) != 0;
                 for (; first < hi; first += kPsSlotWarps) {
+                    if (dead) continue;
                     const int gi = first - cc * CG;
                     const uint32_t codes_a = stage_base + (uint32_t)((st * CG + gi) * 512 + lane * 16);
                     const uint32_t cols_a = cols_base + (uint32_t)((st * CG + gi) * 16);

@@ -170,7 +170,14 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
             : "memory");
     };
 
+    // Both weight buffers start as zeros: a blob of zeros describes tile rows without groups, so if
+    // a copy should ever fail to arrive (the bounded wait below reports it) the walk over the
+    // buffer stays inside it instead of following uninitialised offsets.
+    for (int i = threadIdx.x; i < 2 * p.max_blob / 16; i += kThreads)
+        reinterpret_cast<uint4 *>(wbuf)[i] = make_uint4(0u, 0u, 0u, 0u);
+    __syncthreads();
     if (threadIdx.x == 0) {
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // zeros before the bulk copy's writes
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_u32(&bars[0])));
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_u32(&bars[1])));
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
