@@ -247,18 +247,21 @@ int mortar_mlp_decode_static(const mortar_stream *gate_up, const mortar_stream *
  * Weights come as per-(layer, cluster rank) blobs built on the host (16-byte aligned):
  *   int32 hdr[16] = { n_gate_up_groups, n_down_groups, byte offsets of gate_up grp_ptr,
  *                     grp_cols, grp_codes, down grp_ptr, grp_cols, grp_codes,
- *                     gate_up scale bits, down scale bits, blob bytes, 0... }
+ *                     gate_up scale bits, down scale bits, blob bytes,
+ *                     byte offset of an fp32[d_model] rmsnorm weight inside the blob or 0, 0... }
  * where rank c's gate_up part is the stream layout of gate tile rows [cU,(c+1)U) followed by
  * the matching up tile rows (U = d_ff/16/cluster_size) and its down part is the stream layout
  * of all output tile rows restricted to hidden tile columns [cU,(c+1)U) (column indices local).
  *   blobs        device bytes
  *   blob_table   device int32 [n_layers][cluster_size][2] = {offset in 16-byte units, bytes}
  *   app_layer    device int32 [n_apps] layer of every application
- *   rms_weights  device fp32 [n_layers][d_model], or NULL for no normalisation
+ *   rms_weights  device fp32 [n_layers][d_model] (16-byte aligned), or NULL.  A layer whose blobs
+ *                carry their own copy of the weight (hdr[11] != 0) uses that copy; otherwise row
+ *                `layer` of this array; with neither the application runs without normalisation
  *   x            fp32 [rows][ldx] residual carrier, updated in place
  *   status       device int32, set non-zero if a bounded wait inside the kernel expires
- * Limits: cluster_size 8 (or 16 where the device accepts it), d_ff/16 and d_model divisible
- * by cluster_size, everything of one application's rank share must fit shared memory
+ * Limits: cluster_size 8 (or 16 where the device accepts it), d_ff/16 divisible by cluster_size
+ * and d_model by 4*cluster_size, everything of one application's rank share must fit shared memory
  * (MORTAR_ERR_CAPACITY otherwise: use mortar_mlp_decode per application). */
 int mortar_stack_decode(const void *blobs, const int32_t *blob_table, const int32_t *app_layer,
                         const float *rms_weights, int32_t n_apps, int32_t n_layers,
@@ -270,13 +273,22 @@ int mortar_stack_decode(const void *blobs, const int32_t *blob_table, const int3
  * Execution layout for blocks of 128 activation rows ("panel schedule"), built once on the
  * host from the canonical format.  A panel is 16 tile rows that share tensor memory (for a
  * gate_up matrix: 8 gate rows and the 8 matching up rows); a chunk is 4 tile columns (64
- * features).  The kept tiles of a (panel, chunk) cell are ordered by column then row;
- * vertically adjacent tiles of one column form a run that a single MMA of N = 16*len covers.
- * A step is the part of a cell that fits one stage of the kernel (at most 32 tiles); empty
- * cells produce no step.  Each step is one contiguous record, staged by one bulk copy:
- *   [ n_tiles, n_runs, meta, 0 ][ n_runs x {A offset, B offset, accumulator column |
- *     accumulate<<31, instruction descriptor} ][ n_tiles x 64 bytes of canonical tile codes ]
- *   meta = chunk index | reuses-previous-chunk<<30 | last-on-chunk<<31
+ * features).  Inside a (panel, chunk) cell the kept tiles of one tile column are covered by
+ * runs: a run is an interval of the panel's 16 local rows that a single MMA of N = 16*len
+ * covers; rows of the interval without a kept tile are filled with zero tiles (two kept tiles a
+ * few rows apart cost less as one wide MMA than as two narrow ones -- the builder minimises the
+ * summed tensor-pipe time max(45, 8*len) cycles per run).  The first run of a panel covers all
+ * 16 rows and overwrites the accumulators; every other run accumulates.
+ * A step is the part of a cell that fits one stage of the kernel (at most 48 tile slots); empty
+ * cells produce no step.  Each step is one contiguous record the kernel's decode warps read
+ * straight from global memory:
+ *   [ n_tiles, n_runs, meta, init ][ n_runs x uint16, padded to 8 ][ n_tiles x 16 row words ]
+ *   run  = first local row | first tile slot << 4 | column in chunk << 10 | (len - 1) << 12
+ *   row word = the 16 stored 2-bit values of one tile row, columns 0,2,..,14 in bits 0..15 and
+ *          columns 1,3,..,15 in bits 16..31 (2 bits each)
+ *   meta = chunk index | n_tiles << 14 | n_runs << 20 | init << 29 |
+ *          reuses-previous-chunk << 30 | last-on-chunk << 31;  init = the step starts with its
+ *          panel's overwriting run
  *   step_data       uint8[16*data_units]  the records
  *   step_off        uint32[n_steps+1]     record offsets in 16-byte units
  *   step_meta       uint32[n_steps]       copy of every record's meta word

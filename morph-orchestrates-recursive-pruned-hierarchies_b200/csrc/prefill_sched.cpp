@@ -4,6 +4,7 @@
 // columns = 64 input features = one 128-byte swizzle row of the activation block.  Inside a
 // (panel, chunk) cell tiles are ordered by column then row, and vertically adjacent tiles
 // of one column are fused into a "run" that one MMA of N = 16*len covers.
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 #include "common.h"
@@ -20,19 +21,63 @@ inline int panel_of(int trow, int R, int swiglu, int *local) {
     return u / half;
 }
 
-inline uint32_t idesc_for(int n) {
-    // kind::f16, D fp32 (bit 4), A bf16 (bit 7), B bf16 (bit 10), both K-major, N>>3 at 17, M>>4 at 24
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((128u >> 4) << 24);
+
+// One tcgen05.mma of M = 128, K = 16 occupies the tensor pipe for max(kMmaFloorClk, N/2) cycles
+// (measured: about 45 cycles up to N = 80, then N/2), and the issuing thread and the barrier
+// hand-shakes add a per-instruction cost on top, so two kept tiles a few rows apart are cheaper as
+// ONE wider MMA over the rows between them (zero tiles in the gaps) than as two narrow ones.
+// cover_column picks, for the kept rows s[l] >= 0 of one tile column of a panel, the set of row
+// intervals [lo, hi) with the smallest summed cost max(kMmaFloorClk, 8 * len); ties go to fewer
+// zero tiles.  Returns the number of intervals.
+#ifdef MORTAR_SCHED_TUNING
+static int kMmaFloorClk = 45;   // tuning builds: overridable through MORTAR_SCHED_FLOOR
+#else
+constexpr int kMmaFloorClk = 45;
+#endif
+
+inline int cover_column(const int32_t *s, int *lo, int *hi) {
+    // best[i]: cheapest cover of the kept rows among rows [0, i); from[i]: start of the last interval
+    // (or -1 when row i-1 is dead and simply skipped)
+    long best[P + 1];
+    int from[P + 1];
+    best[0] = 0; from[0] = -1;
+    for (int i = 1; i <= P; ++i) {
+        best[i] = -1; from[i] = -1;
+        if (s[i - 1] < 0) { best[i] = best[i - 1]; from[i] = -1; continue; }
+        for (int j = 0; j < i; ++j) {
+            if (s[j] < 0) continue;                       // an interval starts on a kept row
+            const int len = i - j;
+            int gaps = 0;
+            for (int k = j; k < i; ++k) gaps += s[k] < 0;
+            const long c = best[j] + (long)(8 * len > kMmaFloorClk ? 8 * len : kMmaFloorClk) * 64 + gaps;
+            if (best[i] < 0 || c < best[i]) { best[i] = c; from[i] = j; }
+        }
+    }
+    int n = 0, i = P;
+    int rlo[P], rhi[P];
+    while (i > 0) {
+        if (from[i] < 0) { --i; continue; }
+        rlo[n] = from[i]; rhi[n] = i; ++n;
+        i = from[i];
+    }
+    for (int k = 0; k < n; ++k) { lo[k] = rlo[n - 1 - k]; hi[k] = rhi[n - 1 - k]; }
+    return n;
 }
 }  // namespace
 
 // Emits the schedule as a list of steps per panel.  A step is the part of a (panel, chunk)
-// cell that fits one B stage of the kernel (at most MORTAR_STEP_TILES tiles, split at run
-// boundaries); empty cells produce no step.  Every step is one contiguous record in
-// step_data so a single bulk copy stages it:
-//   [ header: n_tiles, n_runs, meta, 0 ][ n_runs run records of 16 bytes ][ n_tiles x 64 bytes ]
-// meta = chunk index, bit 30 set when the step reuses the activation chunk of the previous
-// step, bit 31 set when it is the last step on that chunk.  step_off is in 16-byte units.
+// cell that fits one B stage of the kernel (at most MORTAR_STEP_TILES tile slots, split at run
+// boundaries); empty cells produce no step.  Every step is one contiguous record in step_data:
+//   [ header: n_tiles, n_runs, meta, init ][ n_runs x uint16, padded to 8 ][ n_tiles x 64 bytes ]
+// A run (one MMA) is 16 bits: first local row | first tile slot << 4 | column in chunk << 10 |
+// (length - 1) << 12.  init = 1 when the step's first run is the panel's initialising MMA (all 16
+// rows, overwrites the accumulators); every other MMA accumulates.  A tile slot holds 16 row
+// words; row word = the row's 16 stored 2-bit values with the even columns in bits 0..15 and the
+// odd columns in bits 16..31 (column 2q in bits 2q.., column 2q+1 in bits 16+2q..), the order the
+// kernel's shift-free expansion reads; slots of rows without a kept tile hold zero codes.
+// meta = chunk index | n_tiles << 14 | n_runs << 20, bit 29 = init, bit 30 set when the step reuses
+// the activation chunk of the previous step, bit 31 set when it is the last step on that chunk;
+// step_meta repeats it per step.  step_off is in 16-byte units.
 // Panels 2s and 2s+1 are executed side by side on one stream of activation chunks, so both
 // list exactly the same chunks: a panel without tiles on a chunk its partner uses gets an
 // empty step (header only) there.
@@ -51,6 +96,9 @@ static int build(const int32_t *row_ptr, const uint16_t *col_idx, const uint8_t 
     const int NP = ((units + per_panel - 1) / per_panel + 1) & ~1;
     const int NC = (C + CC - 1) / CC;
     const bool fill = step_data != nullptr;
+#ifdef MORTAR_SCHED_TUNING
+    if (const char *e = getenv("MORTAR_SCHED_FLOOR")) kMmaFloorClk = atoi(e);
+#endif
     if (fill && (!step_off || !step_meta || !panel_step_ptr || !panel_mask || !col_idx || !codes))
         return MORTAR_ERR_NULL;
     // bucket tiles by cell: slot[cell][col_local][row_local] = tile index or -1
@@ -66,31 +114,45 @@ static int build(const int32_t *row_ptr, const uint16_t *col_idx, const uint8_t 
             slot[(((size_t)panel * NC + c / CC) * CC + c % CC) * P + local] = (int32_t)j;
         }
     }
-    struct Run { uint32_t a, d, idesc; int first, len; };
-    int64_t nt = 0, nr = 0, ns = 0, units16 = 0;
+    struct Run { int cl, lo, first, len; };
+    int64_t nt = 0, nr = 0, ns = 0, units16 = 0, n_gap = 0;
     std::vector<Run> step_runs;
     std::vector<int32_t> step_tiles;
+    bool step_init = false;            // the step under construction starts with the initialising MMA
     auto flush = [&](int ch, bool reuse, bool last) {
         const int ntile = (int)step_tiles.size(), nrun = (int)step_runs.size();
+        const int run_units = (nrun + 7) / 8;
         if (fill) {
             step_off[ns] = (uint32_t)units16;
-            const uint32_t meta = (uint32_t)ch | (reuse ? 0x40000000u : 0u) | (last ? 0x80000000u : 0u);
+            const uint32_t meta = (uint32_t)ch | ((uint32_t)ntile << 14) | ((uint32_t)nrun << 20) |
+                                  (step_init ? 0x20000000u : 0u) | (reuse ? 0x40000000u : 0u) |
+                                  (last ? 0x80000000u : 0u);
             step_meta[ns] = meta;
             uint32_t *hdr = reinterpret_cast<uint32_t *>(step_data + units16 * 16);
-            hdr[0] = (uint32_t)ntile; hdr[1] = (uint32_t)nrun; hdr[2] = meta; hdr[3] = 0;
-            uint32_t *rr = hdr + 4;
-            for (int i = 0; i < nrun; ++i) {
-                rr[4 * i + 0] = step_runs[i].a;
-                rr[4 * i + 1] = (uint32_t)(step_runs[i].first * 32);   // B start offset, 16-byte units
-                rr[4 * i + 2] = step_runs[i].d;
-                rr[4 * i + 3] = step_runs[i].idesc;
+            hdr[0] = (uint32_t)ntile; hdr[1] = (uint32_t)nrun; hdr[2] = meta; hdr[3] = step_init ? 1u : 0u;
+            uint16_t *rr = reinterpret_cast<uint16_t *>(hdr + 4);
+            for (int i = 0; i < run_units * 8; ++i) rr[i] = 0;
+            for (int i = 0; i < nrun; ++i)
+                rr[i] = (uint16_t)(step_runs[i].lo | (step_runs[i].first << 4) | (step_runs[i].cl << 10) |
+                                   ((step_runs[i].len - 1) << 12));
+            uint32_t *td = reinterpret_cast<uint32_t *>(step_data + (units16 + 1 + run_units) * 16);
+            for (int i = 0; i < ntile; ++i) {
+                for (int row = 0; row < 16; ++row) {
+                    uint32_t canon = 0x55555555u;                        // stored value 1 = code 0
+                    if (step_tiles[i] >= 0) memcpy(&canon, codes + (int64_t)step_tiles[i] * 64 + row * 4, 4);
+                    uint32_t w = 0;
+                    for (int q = 0; q < 8; ++q) {
+                        w |= ((canon >> (4 * q)) & 3u) << (2 * q);
+                        w |= ((canon >> (4 * q + 2)) & 3u) << (16 + 2 * q);
+                    }
+                    td[i * 16 + row] = w;
+                }
             }
-            uint8_t *td = reinterpret_cast<uint8_t *>(rr + 4 * nrun);
-            for (int i = 0; i < ntile; ++i) memcpy(td + 64 * i, codes + (int64_t)step_tiles[i] * 64, 64);
         }
-        units16 += 1 + nrun + 4 * (int64_t)ntile;
+        units16 += 1 + run_units + 4 * (int64_t)ntile;
         nt += ntile; nr += nrun; ++ns;
         step_runs.clear(); step_tiles.clear();
+        step_init = false;
     };
     // which cells hold at least one tile
     std::vector<uint8_t> cell_used((size_t)cells, 0);
@@ -98,6 +160,7 @@ static int build(const int32_t *row_ptr, const uint16_t *col_idx, const uint8_t 
         if (slot[i] >= 0) cell_used[i / ((size_t)CC * P)] = 1;
     for (int p = 0; p < NP; ++p) {
         uint32_t touched = 0;
+        bool initialised = false;       // the panel's accumulators hold defined values
         if (fill) panel_step_ptr[p] = (int32_t)ns;
         const int partner = p ^ 1;      // the kernel runs panels 2s and 2s+1 side by side on shared chunks
         for (int ch = 0; ch < NC; ++ch) {
@@ -110,28 +173,36 @@ static int build(const int32_t *row_ptr, const uint16_t *col_idx, const uint8_t 
             bool first_of_chunk = true;
             for (int cl = 0; cl < CC; ++cl) {
                 const int32_t *s = &slot[(cell * CC + cl) * P];
-                int l = 0;
-                while (l < P) {
-                    if (s[l] < 0) { ++l; continue; }
-                    // a run must not mix rows already holding a partial sum with fresh rows:
-                    // the first MMA into a row overwrites, later ones accumulate
-                    const bool acc = (touched >> l) & 1u;
-                    int e = l;
-                    while (e < P && s[e] >= 0 && (((touched >> e) & 1u) != 0) == acc) ++e;
-                    const int len = e - l;
+                int n_live = 0;
+                for (int l = 0; l < P; ++l) n_live += s[l] >= 0;
+                if (n_live == 0) continue;
+                // intervals [lo, hi) of local rows that one MMA each will cover
+                int lo[P], hi[P], n_iv = 0;
+                if (!initialised) {
+                    // the panel's first MMA overwrites all 256 accumulator columns (dead rows get
+                    // zero tiles), so every later MMA of the item accumulates
+                    lo[0] = 0; hi[0] = P; n_iv = 1;
+                } else {
+                    n_iv = cover_column(s, lo, hi);
+                }
+                for (int v = 0; v < n_iv; ++v) {
+                    const int len = hi[v] - lo[v];
                     if ((int)step_tiles.size() + len > MORTAR_STEP_TILES) {
                         flush(ch, !first_of_chunk, false);
                         first_of_chunk = false;
                     }
                     Run run;
-                    run.a = (uint32_t)(cl * 2);                          // A start offset, 16-byte units
-                    run.d = (uint32_t)(l * 16) | (acc ? 0x80000000u : 0u);
-                    run.idesc = idesc_for(16 * len);
+                    run.cl = cl; run.lo = lo[v];
                     run.first = (int)step_tiles.size();
                     run.len = len;
+                    if (!initialised) step_init = true;      // always the first run of a fresh step (see below)
                     step_runs.push_back(run);
-                    for (int k = l; k < e; ++k) { step_tiles.push_back(s[k]); touched |= 1u << k; }
-                    l = e;
+                    for (int k = lo[v]; k < hi[v]; ++k) {
+                        step_tiles.push_back(s[k]);                      // -1 = zero tile (gap)
+                        if (s[k] >= 0) touched |= 1u << k;
+                        else ++n_gap;
+                    }
+                    initialised = true;
                 }
             }
             if (!step_tiles.empty()) flush(ch, !first_of_chunk, true);

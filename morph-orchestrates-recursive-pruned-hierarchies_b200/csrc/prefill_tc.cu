@@ -5,58 +5,71 @@
 // of panels (2 x 16 weight tile rows); each panel has its own pipeline ("pipe") and its own
 // 256 fp32 accumulator columns in tensor memory, and both pipes consume the same stream of
 // activation chunks, so an activation chunk is fetched once for 32 tile rows.
-// Warp roles (19 warps):
-//   warps 0..7    epilogue (4 per pipe): tcgen05.ld, per-matrix scale, the reference's bf16
-//                 rounding points, SwiGLU, cluster gates, bf16 stores
-//   warps 8, 9    MMA issue, one per pipe: one tcgen05.mma per run (M=128, N=16*len, K=16),
-//                 tcgen05.commit to hand stages back (two issuers: a single thread issues
-//                 an MMA with fresh descriptors every ~120 clk, the tensor pipe accepts one
-//                 every ~45 clk)
-//   warp 10       TMA producer: per activation chunk one tiled [128 x 64] bf16 load (128-byte
-//                 swizzle) into a 4-stage ring; per schedule step of either pipe one bulk copy
-//                 of the step record (run records + packed 2-bit codes) into a 6-stage ring
-//   warps 11..18  decode (4 per pipe): expand the staged 2-bit codes into bf16 B tiles
-//                 (K-major, no swizzle) in a 3-stage ring
+// Warp roles (20 warps; a warp's scheduler is its index modulo 4, so the three single-lane
+// issuing roles sit together on scheduler 3, away from the arithmetic of the decode warps):
+//   warps 0..7    epilogue (4 per pipe, one per tensor-memory lane quadrant): tcgen05.ld,
+//                 per-matrix scale, the reference's bf16 rounding points, SwiGLU, cluster gates,
+//                 bf16 stores; idle while the MMAs of an item run
+//   warps 11, 15  MMA issue, one per pipe: one tcgen05.mma per run (M=128, N=16*len, K=16) from
+//                 16-bit run records, tcgen05.commit to hand stages back
+//   warp 19       TMA producer: per activation chunk one tiled [128 x 64] bf16 load (128-byte
+//                 swizzle) into a 4-stage ring
+//   warps 8, 9, 10, 12 (pipe 0) and 13, 14, 16, 17 (pipe 1)   decode: read the step records
+//                 (run list + packed 2-bit codes) straight from global memory one step ahead
+//                 and expand the codes into bf16 B tiles (K-major, no swizzle) in a 3-stage ring
+//   warp 18       unused
 // Every mbarrier wait is bounded; on expiry the CTA records an error code, every role unwinds
 // and tensor memory is released.
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <cstdint>
+#include <mutex>
 #include "common.h"
+#include "decode.cuh"
 
 namespace {
 
 constexpr int kPanelRows = MORTAR_PANEL_ROWS;
 constexpr int kChunkCols = MORTAR_CHUNK_COLS;
-constexpr int kStepTiles = MORTAR_STEP_TILES;                // 32 tiles per step
+constexpr int kStepTiles = MORTAR_STEP_TILES;                // 48 tile slots per step
 constexpr int kPipes = 2;                                    // panels executed side by side per item
 constexpr int kAStages = 4;                                  // activation-chunk ring (shared)
 constexpr int kBStages = 3;                                  // expanded-tile ring, per pipe
-constexpr int kRawStages = 6;                                // step-record ring, per pipe
 constexpr int kRows = 128;                                   // activation rows per item (MMA M)
 constexpr int kAStage = kRows * 128;                         // 16 KB
-constexpr int kBTiles = kStepTiles * 512;                    // 16 KB of expanded tiles
-constexpr int kBStage = kBTiles + (kStepTiles + 1) * 16;     // + the step's run records and header
-constexpr int kRawStage = 16 + kStepTiles * 16 + kStepTiles * 64;   // 2576 B: header, runs, codes
-constexpr int kRawStride = 2688;                             // stage pitch (multiple of 128)
+constexpr int kBTiles = kStepTiles * 512;                    // 24 KB of expanded tiles
+constexpr int kRunBytes = 128;                               // the step's 16-bit run records (up to 48)
+constexpr int kBStage = kBTiles + kRunBytes + 128;           // + the step header; pitch stays a multiple of 128
 constexpr int kAccCols = kPanelRows * 16;                    // 256 accumulator columns per pipe
 constexpr int kTmemCols = kPipes * kAccCols;                 // 512
 constexpr int kDecodeThreads = 128;                          // per pipe
 constexpr int kEpilogueWarps = 4 * kPipes;
 constexpr int kEpilogueThreads = 32 * kEpilogueWarps;
-constexpr int kMmaWarp0 = kEpilogueWarps;                    // warps 8, 9
-constexpr int kTmaWarp = kMmaWarp0 + kPipes;                 // warp 10
-constexpr int kDecodeWarp0 = kTmaWarp + 1;                   // warps 11..18
-constexpr int kThreads = 32 * (kDecodeWarp0 + 4 * kPipes);   // 608
-constexpr int kWordsPerThread = kStepTiles * 16 / kDecodeThreads;   // 4 code words per decoder per step
-constexpr int kNumBars = 2 * kAStages + kPipes * (2 * kBStages + 2 * kRawStages) + 2;
-constexpr int kSmemBytes = kAStages * kAStage + kPipes * (kBStages * kBStage + kRawStages * kRawStride) +
-                           kNumBars * 8 + 1024 /*align*/;
+constexpr int kMmaWarp0 = 11, kMmaWarp1 = 15, kTmaWarp = 19, kIdleWarp = 18;
+constexpr int kThreads = 32 * 20;                            // 640
+constexpr int kWordsPerThread = kStepTiles * 16 / kDecodeThreads;   // 6 row words per decoder per step
+constexpr int kNumBars = 2 * kAStages + kPipes * 2 * kBStages + 2;
+constexpr int kSmemBytes = kAStages * kAStage + kPipes * kBStages * kBStage + kNumBars * 8 + 1024 /*align*/;
 constexpr uint32_t kWaitLimit = 1u << 22;
-static_assert(kRawStage <= kRawStride, "raw stage pitch too small");
+static_assert(kStepTiles * 2 <= kRunBytes, "run records do not fit their area");
+static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 
 __device__ int g_prefill_error;   // first error recorded by any CTA (0 = none)
+
+// Per-role cycle accounting for profiling builds (-DMORTAR_PREFILL_TIMING): every role of pipe 0
+// sums the cycles it spends in each of its phases; CTA 0 adds them to g_prefill_ticks.
+#ifdef MORTAR_PREFILL_TIMING
+__device__ unsigned long long g_prefill_ticks[40];
+#define PF_DECL long long tk[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long tprev = clock64()
+#define PF_ACC(i) do { const long long tn_ = clock64(); tk[i] += tn_ - tprev; tprev = tn_; } while (0)
+#define PF_PUT(base, cond) do { if ((cond) && blockIdx.x == 0) for (int i_ = 0; i_ < 8; ++i_) \
+        atomicAdd(&g_prefill_ticks[(base) + i_], (unsigned long long)tk[i_]); } while (0)
+#else
+#define PF_DECL
+#define PF_ACC(i)
+#define PF_PUT(base, cond)
+#endif
 
 struct PrefillParams {
     const uint8_t *step_data;     // step records
@@ -165,34 +178,20 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 
 __device__ __forceinline__ float rbf(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
-// 16 stored 2-bit values (one tile row) -> 16 bf16 codes as two 16-byte vectors.
-__device__ __forceinline__ void expand_row(uint32_t w, uint4 &lo, uint4 &hi) {
-    const uint32_t k129 = 0x43014301u;
-    uint32_t out[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        uint32_t v = ((w >> (4 * i)) & 3u) | (((w >> (4 * i + 2)) & 3u) << 16) | 0x43004300u;
-        __nv_bfloat162 r = __hsub2(*reinterpret_cast<__nv_bfloat162 *>(&v),
-                                   *reinterpret_cast<const __nv_bfloat162 *>(&k129));
-        out[i] = *reinterpret_cast<uint32_t *>(&r);
-    }
-    lo = make_uint4(out[0], out[1], out[2], out[3]);
-    hi = make_uint4(out[4], out[5], out[6], out[7]);
-}
-
 // Two adjacent outputs of the epilogue with the reference's rounding points, in packed bf16:
 // the reference's ops ARE bf16 ops (each rounds to nearest even), so after the fp32 scale and
 // the fp32 silu the products are single bf16x2 multiplies.
-__device__ __forceinline__ uint32_t finish2(float scale, bool swiglu, float a0, float a1, float b0, float b1,
-                                            bool live_a, bool live_b, bool gated, float gate0, float gate1) {
+template <bool SWIGLU, bool GATED>
+__device__ __forceinline__ uint32_t finish2(float scale, float a0, float a1, float b0, float b1,
+                                            bool live_a, bool live_b, float gate0, float gate1) {
     __nv_bfloat162 g2 = __floats2bfloat162_rn(live_a ? scale * a0 : 0.f, live_a ? scale * a1 : 0.f);
-    if (!swiglu) return *reinterpret_cast<uint32_t *>(&g2);
+    if (!SWIGLU) return *reinterpret_cast<uint32_t *>(&g2);
     const __nv_bfloat162 u2 = __floats2bfloat162_rn(live_b ? scale * b0 : 0.f, live_b ? scale * b1 : 0.f);
     const float gx = __low2float(g2), gy = __high2float(g2);
     const __nv_bfloat162 s2 = __floats2bfloat162_rn(__fdividef(gx, 1.f + __expf(-gx)),
                                                     __fdividef(gy, 1.f + __expf(-gy)));
     __nv_bfloat162 h2 = __hmul2(s2, u2);
-    if (gated) {
+    if (GATED) {
         h2 = __hmul2(h2, __floats2bfloat162_rn(gate0, gate1));
         // a gate of zero (inactive group) yields an exact zero
         if (!(gate0 > 0.f)) h2.x = __float2bfloat16_rn(0.f);
@@ -201,20 +200,89 @@ __device__ __forceinline__ uint32_t finish2(float scale, bool swiglu, float a0, 
     return *reinterpret_cast<uint32_t *>(&h2);
 }
 
+// Flattened walk over the schedule steps of one pipe for every item of this CTA.
+struct StepCursor {
+    int item, s, s_end;
+    __device__ __forceinline__ bool valid(const PrefillParams &p) const { return item < p.n_items; }
+    __device__ __forceinline__ void enter(const PrefillParams &p, int n_super, int pipe) {
+        // moves forward to the next item that has steps
+        while (item < p.n_items) {
+            const int panel = (item % n_super) * kPipes + pipe;
+            s = __ldg(p.panel_step_ptr + panel);
+            s_end = __ldg(p.panel_step_ptr + panel + 1);
+            if (s < s_end) return;
+            item += gridDim.x;
+        }
+    }
+    __device__ __forceinline__ void start(const PrefillParams &p, int n_super, int pipe) {
+        item = blockIdx.x; s = s_end = 0;
+        enter(p, n_super, pipe);
+    }
+    __device__ __forceinline__ void next(const PrefillParams &p, int n_super, int pipe) {
+        if (++s < s_end) return;
+        item += gridDim.x;
+        enter(p, n_super, pipe);
+    }
+};
+
+// Drains one item's accumulators of one pipe: the epilogue of warp (pipe, quadrant q).
+template <bool SWIGLU, bool GATED>
+__device__ __forceinline__ void epilogue_item(const PrefillParams &p, uint32_t taddr, int panel, long long row,
+                                              bool in_range, uint32_t mask) {
+    constexpr int units = SWIGLU ? kPanelRows / 2 : kPanelRows;
+    const bool tile_gates = GATED && (p.cluster_size % 16 == 0);     // one gate per 16-column tile
+#pragma unroll 1
+    for (int j = 0; j < units; j += 2) {                              // two output tile columns at a time
+        uint32_t a[32], b[32];
+        tc_ld32(taddr + j * 16, a);
+        if (SWIGLU) tc_ld32(taddr + (units + j) * 16, b);
+        const long long col0 = ((long long)panel * units + j) * 16;
+        float tg[2] = {1.f, 1.f};
+        if (GATED && tile_gates && in_range) {
+            tg[0] = __ldg(p.gates + row * p.ld_gates + col0 / p.cluster_size);
+            tg[1] = __ldg(p.gates + row * p.ld_gates + (col0 + 16) / p.cluster_size);
+        }
+        uint32_t packed[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+            const int jj = j + (e >> 4);
+            const bool live_a = (mask >> jj) & 1u;
+            const bool live_b = SWIGLU ? ((mask >> (units + jj)) & 1u) : true;
+            float gate0 = tg[e >> 4], gate1 = tg[e >> 4];
+            if (GATED && !tile_gates && in_range) {
+                gate0 = __ldg(p.gates + row * p.ld_gates + (col0 + e) / p.cluster_size);
+                gate1 = __ldg(p.gates + row * p.ld_gates + (col0 + e + 1) / p.cluster_size);
+            }
+            packed[e >> 1] = finish2<SWIGLU, GATED>(p.scale, __uint_as_float(a[e]), __uint_as_float(a[e + 1]),
+                                                    SWIGLU ? __uint_as_float(b[e]) : 0.f,
+                                                    SWIGLU ? __uint_as_float(b[e + 1]) : 0.f, live_a, live_b,
+                                                    gate0, gate1);
+        }
+        if (in_range) {
+            uint4 *dst = reinterpret_cast<uint4 *>(p.out + row * p.ld_out + col0);
+            if (panel * units + j < p.total_units) {
+                dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+            }
+            if (panel * units + j + 1 < p.total_units) {
+                dst[2] = make_uint4(packed[8], packed[9], packed[10], packed[11]);
+                dst[3] = make_uint4(packed[12], packed[13], packed[14], packed[15]);
+            }
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_panel_kernel(const __grid_constant__ CUtensorMap tmap_x, const PrefillParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *sA = smem;                                          // kAStages x 16 KB, 1024-byte aligned
-    uint8_t *sB = sA + kAStages * kAStage;                       // kPipes x kBStages x 16 KB
-    uint8_t *sRaw = sB + kPipes * kBStages * kBStage;            // kPipes x kRawStages x kRawStride
-    uint64_t *bars = reinterpret_cast<uint64_t *>(sRaw + kPipes * kRawStages * kRawStride);
+    uint8_t *sB = sA + kAStages * kAStage;                       // kPipes x kBStages x kBStage
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sB + kPipes * kBStages * kBStage);
     uint64_t *a_full = bars, *a_empty = a_full + kAStages;
     uint64_t *b_full = a_empty + kAStages;                       // [pipe][stage]
     uint64_t *b_empty = b_full + kPipes * kBStages;
-    uint64_t *raw_full = b_empty + kPipes * kBStages;
-    uint64_t *raw_empty = raw_full + kPipes * kRawStages;
-    uint64_t *acc_full = raw_empty + kPipes * kRawStages, *acc_empty = acc_full + 1;
+    uint64_t *acc_full = b_empty + kPipes * kBStages, *acc_empty = acc_full + 1;
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
 
@@ -225,7 +293,6 @@ prefill_panel_kernel(const __grid_constant__ CUtensorMap tmap_x, const PrefillPa
         abort_s = 0;
         for (int s = 0; s < kAStages; ++s) { mbar_init(smem_u32(&a_full[s]), 1); mbar_init(smem_u32(&a_empty[s]), kPipes); }
         for (int s = 0; s < kPipes * kBStages; ++s) { mbar_init(smem_u32(&b_full[s]), kDecodeThreads); mbar_init(smem_u32(&b_empty[s]), 1); }
-        for (int s = 0; s < kPipes * kRawStages; ++s) { mbar_init(smem_u32(&raw_full[s]), 1); mbar_init(smem_u32(&raw_empty[s]), kDecodeThreads); }
         mbar_init(smem_u32(acc_full), kPipes);
         mbar_init(smem_u32(acc_empty), kEpilogueThreads);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -248,78 +315,61 @@ prefill_panel_kernel(const __grid_constant__ CUtensorMap tmap_x, const PrefillPa
         int it = 0;
         bool ok = true;
         const int units = p.swiglu ? kPanelRows / 2 : kPanelRows;
+        (void)units;
+        PF_DECL;
         for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++it) {
             const int panel = (item % n_super) * kPipes + pipe;
             const long long row = (long long)(item / n_super) * kRows + q * 32 + lane;
             const bool in_range = row < p.rows;
             const uint32_t mask = p.panel_mask[panel];
+            PF_ACC(0);
             ok = mbar_wait_relaxed(smem_u32(acc_full), it & 1, abort_flag, 8);
             if (!ok) break;
+            PF_ACC(1);
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const uint32_t taddr = tmem + pipe * kAccCols + ((uint32_t)(q * 32) << 16);
-            const bool gated = p.swiglu && p.gates != nullptr && in_range;
-            for (int j = 0; j < units; j += 2) {                      // two output tile columns at a time
-                uint32_t a[32], b[32];
-                tc_ld32(taddr + j * 16, a);
-                if (p.swiglu) tc_ld32(taddr + (units + j) * 16, b);
-                const long long col0 = ((long long)panel * units + j) * 16;
-                uint32_t packed[16];
-#pragma unroll
-                for (int e = 0; e < 32; e += 2) {
-                    const int jj = j + (e >> 4);
-                    const bool live_a = (mask >> jj) & 1u;
-                    const bool live_b = p.swiglu ? ((mask >> (units + jj)) & 1u) : true;
-                    float gate0 = 1.f, gate1 = 1.f;
-                    if (gated) {
-                        gate0 = p.gates[row * p.ld_gates + (col0 + e) / p.cluster_size];
-                        gate1 = p.gates[row * p.ld_gates + (col0 + e + 1) / p.cluster_size];
-                    }
-                    packed[e >> 1] = finish2(p.scale, p.swiglu != 0, __uint_as_float(a[e]), __uint_as_float(a[e + 1]),
-                                             p.swiglu ? __uint_as_float(b[e]) : 0.f,
-                                             p.swiglu ? __uint_as_float(b[e + 1]) : 0.f, live_a, live_b,
-                                             gated, gate0, gate1);
-                }
-                if (in_range) {
-                    uint4 *dst = reinterpret_cast<uint4 *>(p.out + row * p.ld_out + col0);
-                    if (panel * units + j < p.total_units) {
-                        dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                        dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-                    }
-                    if (panel * units + j + 1 < p.total_units) {
-                        dst[2] = make_uint4(packed[8], packed[9], packed[10], packed[11]);
-                        dst[3] = make_uint4(packed[12], packed[13], packed[14], packed[15]);
-                    }
-                }
-            }
+            if (!p.swiglu) epilogue_item<false, false>(p, taddr, panel, row, in_range, mask);
+            else if (p.gates == nullptr) epilogue_item<true, false>(p, taddr, panel, row, in_range, mask);
+            else epilogue_item<true, true>(p, taddr, panel, row, in_range, mask);
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             mbar_arrive(smem_u32(acc_empty));                         // accumulators drained
+            PF_ACC(2);
         }
-    } else if (warp == kMmaWarp0 || warp == kMmaWarp0 + 1) {
+        PF_PUT(0, warp == 0 && lane == 0);
+    } else if (warp == kMmaWarp0 || warp == kMmaWarp1) {
         // ---------------- MMA issue, one warp per pipe ----------------
-        const int pipe = warp - kMmaWarp0;
+        const int pipe = warp == kMmaWarp0 ? 0 : 1;
         uint64_t *bf = b_full + pipe * kBStages, *be = b_empty + pipe * kBStages;
         const uint8_t *bbase = sB + pipe * kBStages * kBStage;
         const uint32_t acc = tmem + pipe * kAccCols;
+        // instruction descriptor of an N = 16 MMA: kind::f16, D fp32 (bit 4), A bf16 (bit 7), B bf16
+        // (bit 10), both K-major, N>>3 at bit 17, M>>4 at bit 24; a run of len tiles adds (len-1)<<18
+        constexpr uint32_t kIdesc16 = (1u << 4) | (1u << 7) | (1u << 10) | (2u << 17) | ((128u >> 4) << 24);
         int g = 0, ga = -1, it = 0;
         bool ok = true;
+        PF_DECL;
         for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++it) {
             const int panel = (item % n_super) * kPipes + pipe;
             const int n_steps = p.panel_step_ptr[panel + 1] - p.panel_step_ptr[panel];
+            PF_ACC(0);
             ok = mbar_wait_relaxed(smem_u32(acc_empty), (it & 1) ^ 1u, abort_flag, 9);
             if (!ok) break;
+            PF_ACC(1);
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             for (int i = 0; i < n_steps; ++i, ++g) {
                 const int bs = g % kBStages;
-                // the decoders publish the step (tiles, header, run records) in the B stage
+                // the decoders publish the step (tiles, run records, header) in the B stage
                 ok = mbar_wait(smem_u32(&bf[bs]), (g / kBStages) & 1, abort_flag, 3);
                 if (!ok) break;
+                PF_ACC(2);
                 const uint8_t *rec = bbase + bs * kBStage + kBTiles;
-                const uint4 hdr = *reinterpret_cast<const uint4 *>(rec + kStepTiles * 16);
+                const uint4 hdr = *reinterpret_cast<const uint4 *>(rec + kRunBytes);
                 if (!(hdr.z & 0x40000000u)) {              // this step starts a new activation chunk
                     ++ga;
                     ok = mbar_wait(smem_u32(&a_full[ga % kAStages]), (ga / kAStages) & 1, abort_flag, 2);
                     if (!ok) break;
                 }
+                PF_ACC(3);
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 if (lane == 0) {
                     const int as = ga % kAStages;
@@ -329,19 +379,23 @@ prefill_panel_kernel(const __grid_constant__ CUtensorMap tmap_x, const PrefillPa
                     const uint32_t b_lo = (uint32_t)b0, b_hi = (uint32_t)(b0 >> 32);
                     const uint4 *rr = reinterpret_cast<const uint4 *>(rec);
                     const int nrun = (int)hdr.y;
-                    for (int r = 0; r < nrun; r += 4) {
-                        // fetch four run records, then issue: the loads do not wait behind the MMAs
-                        uint4 qv[4];
+                    const uint32_t keep0 = hdr.w ? 0u : 1u;   // the panel's first MMA overwrites the accumulators
+                    for (int r = 0; r < nrun; r += 8) {
+                        const uint4 qv = rr[r >> 3];
+                        const uint32_t ws[4] = {qv.x, qv.y, qv.z, qv.w};
 #pragma unroll
-                        for (int k = 0; k < 4; ++k) qv[k] = rr[min(r + k, nrun - 1)];
-#pragma unroll
-                        for (int k = 0; k < 4; ++k)
+                        for (int k = 0; k < 8; ++k) {
+                            const uint32_t w = (k & 1) ? (ws[k >> 1] >> 16) : (ws[k >> 1] & 0xffffu);
                             if (r + k < nrun)
-                                tc_mma(acc + (qv[k].z & 0xffffu), a_lo + qv[k].x, a_hi, b_lo + qv[k].y, b_hi,
-                                       qv[k].w, qv[k].z >> 31);
+                                tc_mma(acc + (w & 15u) * 16u, a_lo + ((w >> 10) & 3u) * 2u, a_hi,
+                                       b_lo + ((w >> 4) & 63u) * 32u, b_hi, kIdesc16 + ((w >> 12) << 18),
+                                       (r + k) ? 1u : keep0);
+                        }
                     }
+                    PF_ACC(4);
                     tc_commit(smem_u32(&be[bs]));          // B stage reusable once these MMAs retire
                     if (hdr.z & 0x80000000u) tc_commit(smem_u32(&a_empty[as]));   // last step on this chunk
+                    PF_ACC(5);
                 }
                 __syncwarp();
             }
@@ -352,134 +406,133 @@ prefill_panel_kernel(const __grid_constant__ CUtensorMap tmap_x, const PrefillPa
             }
             __syncwarp();
         }
+        PF_PUT(8, pipe == 0 && lane == 0);
     } else if (warp == kTmaWarp) {
-        // ---------------- TMA producer: activation chunks + both pipes' step records ----------------
-        int g[kPipes] = {0, 0};
+        // ---------------- TMA producer: the activation chunks pipe 0's steps name ----------------
+        // (both panels of a pair list the same chunks)
         int ga = 0;
         bool ok = true;
-        for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
-            const int panel0 = (item % n_super) * kPipes;
-            const int row0 = (item / n_super) * kRows;
-            int cur[kPipes], end[kPipes], base[kPipes];
-            uint32_t o0[kPipes], o1[kPipes], mt[kPipes];
-#pragma unroll
-            for (int k = 0; k < kPipes; ++k) {
-                cur[k] = p.panel_step_ptr[panel0 + k];
-                end[k] = p.panel_step_ptr[panel0 + k + 1];
-                base[k] = -64;
-                o0[k] = o1[k] = mt[k] = 0;
+        PF_DECL;
+        StepCursor c;
+        for (c.start(p, n_super, 0); c.valid(p) && ok; c.next(p, n_super, 0)) {
+            const uint32_t meta = __ldg(p.step_meta + c.s);
+            if (meta & 0x40000000u) continue;                        // reuses the chunk already requested
+            const int row0 = (c.item / n_super) * kRows;
+            const int as = ga % kAStages;
+            PF_ACC(0);
+            ok = mbar_wait_relaxed(smem_u32(&a_empty[as]), ((ga / kAStages) & 1) ^ 1u, abort_flag, 5);
+            if (!ok) break;
+            PF_ACC(1);
+            if (lane == 0) {
+                const uint32_t bar = smem_u32(&a_full[as]);
+                mbar_arrive_expect_tx(bar, kAStage);
+                asm volatile(
+                    "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+                    "[%0], [%1, {%2, %3}], [%4];\n"
+                    ::"r"(smem_u32(sA + as * kAStage)), "l"(&tmap_x),
+                      "r"((int)(meta & 0x3fffu) * kChunkCols * 16), "r"(row0), "r"(bar) : "memory");
             }
-            // both panels list the same chunks; walk them chunk by chunk
-            while (cur[0] < end[0] && ok) {
-                bool first = true;
-#pragma unroll
-                for (int k = 0; k < kPipes; ++k) {
-                    bool last = false;
-                    while (!last && cur[k] < end[k] && ok) {
-                        if (cur[k] >= base[k] + 32) {            // refill this pipe's metadata batch
-                            base[k] = cur[k];
-                            const int i = base[k] + lane;
-                            o0[k] = o1[k] = mt[k] = 0;
-                            if (i < end[k]) {
-                                o0[k] = __ldg(p.step_off + i);
-                                o1[k] = __ldg(p.step_off + i + 1);
-                                mt[k] = __ldg(p.step_meta + i);
-                            }
-                        }
-                        const int sl = cur[k] - base[k];
-                        const uint32_t so0 = __shfl_sync(0xffffffffu, o0[k], sl);
-                        const uint32_t so1 = __shfl_sync(0xffffffffu, o1[k], sl);
-                        const uint32_t sm = __shfl_sync(0xffffffffu, mt[k], sl);
-                        if (k == 0 && first) {                   // new activation chunk
-                            const int as = ga % kAStages;
-                            ok = mbar_wait_relaxed(smem_u32(&a_empty[as]), ((ga / kAStages) & 1) ^ 1u, abort_flag, 5);
-                            if (!ok) break;
-                            if (lane == 0) {
-                                const uint32_t bar = smem_u32(&a_full[as]);
-                                mbar_arrive_expect_tx(bar, kAStage);
-                                asm volatile(
-                                    "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
-                                    "[%0], [%1, {%2, %3}], [%4];\n"
-                                    ::"r"(smem_u32(sA + as * kAStage)), "l"(&tmap_x),
-                                      "r"((int)(sm & 0xffffffu) * kChunkCols * 16), "r"(row0), "r"(bar) : "memory");
-                            }
-                            ++ga;
-                            first = false;
-                        }
-                        const int rs = g[k] % kRawStages;
-                        ok = mbar_wait_relaxed(smem_u32(&raw_empty[k * kRawStages + rs]),
-                                               ((g[k] / kRawStages) & 1) ^ 1u, abort_flag, 4);
-                        if (!ok) break;
-                        if (lane == 0) {
-                            const uint32_t bar = smem_u32(&raw_full[k * kRawStages + rs]);
-                            const uint32_t bytes = (so1 - so0) * 16u;
-                            mbar_arrive_expect_tx(bar, bytes);
-                            asm volatile(
-                                "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
-                                ::"r"(smem_u32(sRaw + (k * kRawStages + rs) * kRawStride)),
-                                  "l"(p.step_data + (size_t)so0 * 16), "r"(bytes), "r"(bar) : "memory");
-                        }
-                        __syncwarp();
-                        last = (sm & 0x80000000u) != 0;
-                        ++g[k];
-                        ++cur[k];
-                    }
-                }
-            }
+            __syncwarp();
+            ++ga;
         }
-    } else {
-        // ---------------- tile decode: warps 11..14 pipe 0, 15..18 pipe 1 ----------------
-        const int pipe = (warp - kDecodeWarp0) >> 2;
-        const int td = threadIdx.x - (kDecodeWarp0 + 4 * pipe) * 32;
+        PF_ACC(0);
+        PF_PUT(16, lane == 0);
+    } else if (warp != kIdleWarp) {
+        // ---------------- tile decode: warps 8, 9, 10, 12 pipe 0; 13, 14, 16, 17 pipe 1 ----------------
+        const int di = warp - 8 - (warp > kMmaWarp0 ? 1 : 0) - (warp > kMmaWarp1 ? 1 : 0);
+        const int pipe = di >> 2;
+        const int td = (di & 3) * 32 + lane;
         uint64_t *bf = b_full + pipe * kBStages, *be = b_empty + pipe * kBStages;
-        uint64_t *rf = raw_full + pipe * kRawStages, *re = raw_empty + pipe * kRawStages;
-        const uint8_t *raw = sRaw + pipe * kRawStages * kRawStride;
         uint8_t *bbase = sB + pipe * kBStages * kBStage;
         int g = 0;
         bool ok = true;
-        for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
-            const int panel = (item % n_super) * kPipes + pipe;
-            const int n_steps = p.panel_step_ptr[panel + 1] - p.panel_step_ptr[panel];
-            for (int i = 0; i < n_steps; ++i, ++g) {
-                const int rs = g % kRawStages, bs = g % kBStages;
-                ok = mbar_wait_relaxed(smem_u32(&rf[rs]), (g / kRawStages) & 1, abort_flag, 6);
-                if (!ok) break;
-                const uint8_t *rec = raw + rs * kRawStride;
-                const uint4 hdr = *reinterpret_cast<const uint4 *>(rec);
-                const uint32_t *words = reinterpret_cast<const uint32_t *>(rec + 16 + hdr.y * 16);
-                const int items = (int)hdr.x * 16;                    // (tile, row) pairs
-                uint32_t w[kWordsPerThread];
+        PF_DECL;
+        // a step's record, fetched one step ahead of its expansion: meta word and offset two ahead
+        auto fetch_info = [&](const StepCursor &c, uint32_t &meta, uint32_t &off) {
+            meta = 0; off = 0;
+            if (c.valid(p)) { meta = __ldg(p.step_meta + c.s); off = __ldg(p.step_off + c.s); }
+        };
+        auto fetch_words = [&](uint32_t meta, uint32_t off, uint32_t (&w)[kWordsPerThread], uint4 &run) {
+            const int ntile = (meta >> 14) & 63, nrun = (meta >> 20) & 63;
+            const int run_units = (nrun + 7) >> 3;
+            const uint8_t *rec = p.step_data + (size_t)off * 16;
+            run = make_uint4(0, 0, 0, 0);
+            if (td < run_units) run = __ldg(reinterpret_cast<const uint4 *>(rec + 16) + td);
+            const uint32_t *words = reinterpret_cast<const uint32_t *>(rec + 16 + run_units * 16);
 #pragma unroll
-                for (int k = 0; k < kWordsPerThread; ++k) {
-                    const int idx = td + k * kDecodeThreads;
-                    w[k] = idx < items ? words[idx] : 0u;
-                }
-                // the MMA warp reads the header and run records from the B stage, so the raw
-                // stage is free as soon as the decoders hold its contents in registers
-                uint4 run = make_uint4(0, 0, 0, 0);
-                if (td < (int)hdr.y) run = *reinterpret_cast<const uint4 *>(rec + 16 + td * 16);
-                mbar_arrive(smem_u32(&re[rs]));                       // codes and runs are in registers
-                ok = mbar_wait_relaxed(smem_u32(&be[bs]), ((g / kBStages) & 1) ^ 1u, abort_flag, 7);
-                if (!ok) break;
-                uint8_t *bdst = bbase + bs * kBStage;
-                if (td < (int)hdr.y) *reinterpret_cast<uint4 *>(bdst + kBTiles + td * 16) = run;
-                if (td == kDecodeThreads - 1) *reinterpret_cast<uint4 *>(bdst + kBTiles + kStepTiles * 16) = hdr;
-#pragma unroll
-                for (int k = 0; k < kWordsPerThread; ++k) {
-                    const int idx = td + k * kDecodeThreads;
-                    if (idx < items) {
-                        const int tile = idx >> 4, row = idx & 15;
-                        uint4 lo, hi;
-                        expand_row(w[k], lo, hi);
-                        uint8_t *d = bdst + tile * 512 + (row >> 3) * 256 + (row & 7) * 16;
-                        *reinterpret_cast<uint4 *>(d) = lo;           // features 0..7 of the tile column
-                        *reinterpret_cast<uint4 *>(d + 128) = hi;     // features 8..15
-                    }
-                }
-                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-                mbar_arrive(smem_u32(&bf[bs]));
+            for (int k = 0; k < kWordsPerThread; ++k) {
+                const int idx = td + k * kDecodeThreads;
+                w[k] = idx < ntile * 16 ? __ldg(words + idx) : 0u;
             }
+        };
+        // Expands the step (cur, mc) held in (w, run) into its B stage; before that it requests the
+        // following step's record (mn, on) into (wn, runn), so those loads are in flight while this
+        // step waits for its stage and is expanded.  The two register sets swap roles from call to
+        // call (no copy, so nothing waits for the loads before they are used).
+        auto do_step = [&](uint32_t mc, const uint32_t (&w)[kWordsPerThread], const uint4 &run,
+                           bool have_next, uint32_t mn, uint32_t on, uint32_t (&wn)[kWordsPerThread],
+                           uint4 &runn) -> bool {
+            const int bs = g % kBStages;
+            if (have_next) fetch_words(mn, on, wn, runn);
+            PF_ACC(0);
+            if (!mbar_wait_relaxed(smem_u32(&be[bs]), ((g / kBStages) & 1) ^ 1u, abort_flag, 7)) return false;
+            PF_ACC(3);
+            uint8_t *bdst = bbase + bs * kBStage;
+            const int ntile = (mc >> 14) & 63, nrun = (mc >> 20) & 63;
+            if (td < ((nrun + 7) >> 3)) *reinterpret_cast<uint4 *>(bdst + kBTiles + td * 16) = run;
+            if (td == kDecodeThreads - 1) {
+                // header for the MMA warp: n_tiles, n_runs, meta, 1 if the step's first run is the
+                // panel's initialising MMA (it overwrites the accumulators)
+                *reinterpret_cast<uint4 *>(bdst + kBTiles + kRunBytes) = make_uint4(ntile, nrun, mc, (mc >> 29) & 1u);
+            }
+#pragma unroll
+            for (int k = 0; k < kWordsPerThread; ++k) {
+                const int idx = td + k * kDecodeThreads;
+                if (idx < ntile * 16) {
+                    const int tile = idx >> 4, row = idx & 15;
+                    uint32_t o[8];
+#pragma unroll
+                    for (int qq = 0; qq < 8; ++qq) o[qq] = mortar_decode_pair(w[k], qq);
+                    uint8_t *d = bdst + tile * 512 + (row >> 3) * 256 + (row & 7) * 16;
+                    *reinterpret_cast<uint4 *>(d) = make_uint4(o[0], o[1], o[2], o[3]);         // features 0..7
+                    *reinterpret_cast<uint4 *>(d + 128) = make_uint4(o[4], o[5], o[6], o[7]);   // features 8..15
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            mbar_arrive(smem_u32(&bf[bs]));
+            PF_ACC(4);
+            ++g;
+            return true;
+        };
+        // cursors and (meta, offset) of the current step and the three after it
+        StepCursor c[4];
+        uint32_t m[4], o[4];
+        c[0].start(p, n_super, pipe);
+        fetch_info(c[0], m[0], o[0]);
+        for (int k = 1; k < 4; ++k) {
+            c[k] = c[k - 1];
+            if (c[k].valid(p)) c[k].next(p, n_super, pipe);
+            fetch_info(c[k], m[k], o[k]);
         }
+        uint32_t wa[kWordsPerThread], wb[kWordsPerThread];
+        uint4 runa, runb;
+        if (c[0].valid(p)) fetch_words(m[0], o[0], wa, runa);
+        auto advance = [&]() {
+#pragma unroll
+            for (int k = 0; k < 3; ++k) { c[k] = c[k + 1]; m[k] = m[k + 1]; o[k] = o[k + 1]; }
+            if (c[3].valid(p)) c[3].next(p, n_super, pipe);
+            fetch_info(c[3], m[3], o[3]);
+        };
+        while (c[0].valid(p) && ok) {
+            ok = do_step(m[0], wa, runa, c[1].valid(p), m[1], o[1], wb, runb);
+            if (!ok) break;
+            advance();
+            if (!c[0].valid(p)) break;
+            ok = do_step(m[0], wb, runb, c[1].valid(p), m[1], o[1], wa, runa);
+            if (!ok) break;
+            advance();
+        }
+        PF_PUT(24, pipe == 0 && td == 0);
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -494,8 +547,11 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
                                   CUtensorMapFloatOOBfill);
 
+std::mutex g_prefill_init_mutex;   // guards the first-use initialisation below
+
 int get_encode_fn(EncodeTiledFn *out) {
     static EncodeTiledFn cached = nullptr;
+    std::lock_guard<std::mutex> lock(g_prefill_init_mutex);
     if (!cached) {
         void *fn = nullptr;
         cudaDriverEntryPointQueryResult qres;
@@ -551,13 +607,18 @@ extern "C" int mortar_linear_tc(const mortar_sched *w, const void *x, int64_t ld
     int dev = 0;
     MORTAR_CUDA_CHECK(cudaGetDevice(&dev));
     static int sm_count[64] = {0};
-    static bool attr_set[64] = {false};
     if (dev < 0 || dev >= 64) return MORTAR_ERR_CAPACITY;
-    if (!attr_set[dev]) {
-        MORTAR_CUDA_CHECK(cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev));
-        MORTAR_CUDA_CHECK(cudaFuncSetAttribute(prefill_panel_kernel,
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-        attr_set[dev] = true;
+    int sms = 0;
+    {
+        std::lock_guard<std::mutex> lock(g_prefill_init_mutex);
+        if (sm_count[dev] == 0) {
+            int v = 0;
+            MORTAR_CUDA_CHECK(cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev));
+            MORTAR_CUDA_CHECK(cudaFuncSetAttribute(prefill_panel_kernel,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+            sm_count[dev] = v;
+        }
+        sms = sm_count[dev];
     }
     PrefillParams p;
     p.step_data = reinterpret_cast<const uint8_t *>(w->step_data);
@@ -576,7 +637,7 @@ extern "C" int mortar_linear_tc(const mortar_sched *w, const void *x, int64_t ld
     p.gates = gates;
     p.ld_gates = ld_gates;
     p.cluster_size = cluster_size > 0 ? cluster_size : 1;
-    const unsigned grid = (unsigned)(n_items < sm_count[dev] ? n_items : sm_count[dev]);
+    const unsigned grid = (unsigned)(n_items < sms ? n_items : sms);
     prefill_panel_kernel<<<grid, kThreads, kSmemBytes, (cudaStream_t)stream>>>(tmap, p);
     MORTAR_CUDA_CHECK(cudaGetLastError());
     return MORTAR_OK;
@@ -598,6 +659,17 @@ extern "C" int mortar_mlp_prefill(const mortar_sched *gate_up, const mortar_sche
     if (rc != MORTAR_OK) return rc;
     return mortar_linear_tc(down, workspace, d_ff, rows, y, ldy, nullptr, 0, 0, stream);
 }
+
+#ifdef MORTAR_PREFILL_TIMING
+// Profiling builds only: copies (and clears) the 40 cycle counters.  Synchronises.
+extern "C" int mortar_prefill_ticks(unsigned long long *out) {
+    if (!out) return MORTAR_ERR_NULL;
+    MORTAR_CUDA_CHECK(cudaMemcpyFromSymbol(out, g_prefill_ticks, sizeof(unsigned long long) * 40));
+    static const unsigned long long zeros[40] = {0};
+    MORTAR_CUDA_CHECK(cudaMemcpyToSymbol(g_prefill_ticks, zeros, sizeof(zeros)));
+    return MORTAR_OK;
+}
+#endif
 
 extern "C" int mortar_prefill_error(int32_t *code, int32_t reset) {
     if (!code) return MORTAR_ERR_NULL;

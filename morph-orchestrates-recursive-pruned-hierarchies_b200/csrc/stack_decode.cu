@@ -17,6 +17,7 @@
 #include <cuda_bf16.h>
 #include <cooperative_groups.h>
 #include <cstdint>
+#include <mutex>
 #include "common.h"
 #include "decode.cuh"
 
@@ -211,7 +212,10 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
         const uint32_t gu_ptr = blob_s + hdr[2], gu_cols = blob_s + hdr[3], gu_codes = blob_s + hdr[4];
         const uint32_t dn_ptr = blob_s + hdr[5], dn_cols = blob_s + hdr[6], dn_codes = blob_s + hdr[7];
         const float scale_gu = __int_as_float(hdr[8]), scale_dn = __int_as_float(hdr[9]);
-        const float *rms_w = hdr[11] ? reinterpret_cast<const float *>(blob + hdr[11]) : nullptr;
+        // rmsnorm weight of this application: the copy inside the blob when the packer put one
+        // there (hdr[11]), else the caller's [n_layers][d_model] array, else no normalisation
+        const float *rms_w = hdr[11] ? reinterpret_cast<const float *>(blob + hdr[11])
+                                     : (p.rms != nullptr ? p.rms + (size_t)p.app_layer[a] * D : nullptr);
 
         // ---- n = rmsnorm(x) as exact bf16 planes (warp i stages row i) ----
         {
@@ -378,8 +382,9 @@ extern "C" int mortar_stack_decode(const void *blobs, const int32_t *blob_table,
                                    int32_t d_model, int32_t d_ff, int32_t max_blob_bytes,
                                    int32_t cluster_size, float *x, int64_t ldx, int64_t rows, float eps,
                                    int32_t n_planes, int32_t *status, void *stream) {
-    (void)rms_weights; (void)n_layers;
     if (!blobs || !blob_table || !app_layer || !x || !status) return MORTAR_ERR_NULL;
+    if (n_layers <= 0) return MORTAR_ERR_SHAPE;
+    if (rms_weights && (reinterpret_cast<uintptr_t>(rms_weights) % 16)) return MORTAR_ERR_ALIGN;
     if (n_apps < 0 || d_model <= 0 || d_ff <= 0 || d_model % 16 || d_ff % 16 || rows < 0 || ldx < d_model)
         return MORTAR_ERR_SHAPE;
     if (cluster_size != 8 && cluster_size != 16) return MORTAR_ERR_SHAPE;
@@ -395,6 +400,10 @@ extern "C" int mortar_stack_decode(const void *blobs, const int32_t *blob_table,
     MORTAR_CUDA_CHECK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return MORTAR_ERR_CAPACITY;
     static int smem_optin[64] = {0};
+    static std::mutex init_mutex;
+    int smem_limit = 0;
+    {
+    std::lock_guard<std::mutex> lock(init_mutex);
     if (smem_optin[dev] == 0) {
         int v = 0;
         MORTAR_CUDA_CHECK(cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
@@ -406,6 +415,8 @@ extern "C" int mortar_stack_decode(const void *blobs, const int32_t *blob_table,
         }
         smem_optin[dev] = v;
     }
+    smem_limit = smem_optin[dev];
+    }
     StackParams p;
     p.blobs = reinterpret_cast<const uint8_t *>(blobs);
     p.blob_table = blob_table; p.app_layer = app_layer; p.rms = rms_weights;
@@ -415,7 +426,7 @@ extern "C" int mortar_stack_decode(const void *blobs, const int32_t *blob_table,
     p.h_pitch = pitch_for(d_ff / cluster_size);
     p.max_blob = max_blob_bytes;
     const SmemLayout L = smem_layout(d_model, d_ff, cluster_size, n_planes, p.x_pitch, p.h_pitch, max_blob_bytes);
-    if (L.total > smem_optin[dev]) return MORTAR_ERR_CAPACITY;   // a rank's share does not fit shared memory
+    if (L.total > smem_limit) return MORTAR_ERR_CAPACITY;   // a rank's share does not fit shared memory
 
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(((rows + 7) / 8) * cluster_size));

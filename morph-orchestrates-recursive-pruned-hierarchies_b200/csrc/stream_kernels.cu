@@ -555,9 +555,21 @@ int launch_persistent(const LinearParams &p, cudaStream_t st) {
     const PsLayout L = ps_layout(p.C, (int)p.rows, SWIGLU);
     int dev = 0, sms = 0;
     MORTAR_CUDA_CHECK(cudaGetDevice(&dev));
-    MORTAR_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    MORTAR_CUDA_CHECK(cudaFuncSetAttribute(gemv_persistent_kernel<SWIGLU>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, L.total));
+    if (dev < 0 || dev >= 64) return MORTAR_ERR_CAPACITY;
+    {
+        // once per device: SM count and the opt-in to the full shared-memory carve-out
+        static std::mutex mu;
+        static int sm_count[64] = {0};
+        std::lock_guard<std::mutex> lock(mu);
+        if (sm_count[dev] == 0) {
+            int v = 0;
+            MORTAR_CUDA_CHECK(cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev));
+            MORTAR_CUDA_CHECK(cudaFuncSetAttribute(gemv_persistent_kernel<SWIGLU>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, kPsMaxSmem));
+            sm_count[dev] = v;
+        }
+        sms = sm_count[dev];
+    }
     const int grid = p.units < sms ? p.units : sms;
     gemv_persistent_kernel<SWIGLU><<<grid, kPsWarps * 32, L.total, st>>>(p);
     MORTAR_CUDA_CHECK(cudaGetLastError());
@@ -768,7 +780,8 @@ extern "C" int mortar_mlp_decode_static(const mortar_stream *gate_up, const mort
                                         int64_t ld_gates, int32_t n_clusters, void *y, int y_dtype,
                                         int64_t ldy, int32_t n_planes, int32_t flags, void *stream) {
     if (!gate_up || !down) return MORTAR_ERR_NULL;
-    if (n_planes < 1 || n_planes > 3 || rows < 0) return MORTAR_ERR_DTYPE;
+    if (rows < 0) return MORTAR_ERR_SHAPE;
+    if (n_planes < 1 || n_planes > 3) return MORTAR_ERR_DTYPE;
     const int64_t need = mortar_mlp_workspace_bytes(rows, gate_up->tile_cols * 16, gate_up->tile_rows * 8,
                                                     n_planes);
     if (need < 0) return (int)need;

@@ -286,7 +286,7 @@ class MortarMatrix:
                             self.algorithmic_bytes())
 
 
-PANEL_ROWS, CHUNK_COLS, STEP_TILES = 16, 4, 32
+PANEL_ROWS, CHUNK_COLS, STEP_TILES = 16, 4, 48
 
 
 def build_sched_host(m: "MortarMatrix", swiglu: bool):

@@ -200,13 +200,25 @@ def test_synth_generators_shapes_and_densities():
     np.testing.assert_array_equal(mb.synth.remoe_gates(lg, 4).numpy(), orc.remoe_gates(lg, 4).numpy())
 
 
+def _unpack_row_words(words):
+    """schedule row words (even columns in bits 0..15, odd columns in bits 16..31, 2 bits each)
+    -> int8 codes [..., 16]"""
+    w = np.asarray(words, dtype=np.uint32)
+    out = np.zeros(w.shape + (16,), dtype=np.int8)
+    for q in range(8):
+        out[..., 2 * q] = ((w >> (2 * q)) & 3).astype(np.int8) - 1
+        out[..., 2 * q + 1] = ((w >> (16 + 2 * q)) & 3).astype(np.int8) - 1
+    return out
+
+
 @pytest.mark.parametrize("swiglu", [False, True])
 @pytest.mark.parametrize("density", [0.35, 1.0])
 def test_prefill_schedule_covers_every_tile_once(swiglu, density):
-    """Rebuild the dense code matrix from the panel schedule: every kept tile appears exactly
-    once, at the accumulator column and activation offset its run record names; the first
-    MMA into an accumulator row overwrites, later ones accumulate; runs are vertical; steps
-    hold at most 48 tiles and only the first step on a chunk fetches it."""
+    """Replay the panel schedule on the host: summing every run's tile slots into the accumulator
+    rows it names rebuilds the dense code matrix exactly -- every kept tile appears once, slots
+    of rows without a kept tile hold zero codes; a panel's first run covers all 16 rows and
+    overwrites, every other run accumulates; steps hold at most 48 slots and only the first
+    step on a chunk fetches it."""
     rng = np.random.default_rng(3)
     R, C = (40, 23) if not swiglu else (48, 23)
     mask = rng.random((R, C)) < density
@@ -220,63 +232,71 @@ def test_prefill_schedule_covers_every_tile_once(swiglu, density):
     units = R // 2 if swiglu else R
     per_panel = P // 2 if swiglu else P
     assert h["n_panels"] == (-(-units // per_panel) + 1) // 2 * 2     # padded to panel pairs
-    assert h["n_tiles"] == m.nnz
-    dense = np.zeros_like(codes)
+    assert h["n_tiles"] >= m.nnz                                      # kept tiles + zero-fill slots
+    dense = np.zeros_like(codes, dtype=np.int32)
     seen = np.zeros((R, C), dtype=int)
     data = h["step_data"]
-    n_tiles_seen = 0
+    n_slots_seen = n_live_seen = 0
     for p in range(h["n_panels"]):
         touched = 0
+        started = False
         prev_chunk, prev_last = -1, True
         for st in range(h["panel_step_ptr"][p], h["panel_step_ptr"][p + 1]):
             rec = data[int(h["step_off"][st]) * 16:int(h["step_off"][st + 1]) * 16]
             hdr = rec[:16].view(np.uint32)
-            n_in_step, n_runs, ck = int(hdr[0]), int(hdr[1]), int(hdr[2])
-            assert ck == int(h["step_meta"][st]) and hdr[3] == 0
-            assert len(rec) == 16 + 16 * n_runs + 64 * n_in_step
-            ch, reuse, last = ck & 0xFFFFFF, (ck >> 30) & 1, (ck >> 31) & 1
+            n_in_step, n_runs, ck, init = (int(v) for v in hdr)
+            assert ck == int(h["step_meta"][st])
+            run_units = (n_runs + 7) // 8
+            assert len(rec) == 16 + 16 * run_units + 64 * n_in_step
+            ch, reuse, last = ck & 0x3FFF, (ck >> 30) & 1, (ck >> 31) & 1
+            assert (ck >> 14) & 63 == n_in_step and (ck >> 20) & 63 == n_runs and (ck >> 29) & 1 == init
             assert reuse == (0 if prev_last else 1)
             assert ch == prev_chunk if reuse else ch > prev_chunk
             prev_chunk, prev_last = ch, bool(last)
-            assert 0 <= n_in_step <= fmt.STEP_TILES
+            assert 0 <= n_in_step <= fmt.STEP_TILES == 48
             assert n_in_step > 0 or (n_runs == 0 and last and not reuse)      # mirror step of the partner
-            n_tiles_seen += n_in_step
-            runs = rec[16:16 + 16 * n_runs].view(np.uint32).reshape(n_runs, 4)
-            tiles = fmt.unpack_codes_2bit(rec[16 + 16 * n_runs:].reshape(n_in_step, 64)).reshape(-1, 16, 16)
+            n_slots_seen += n_in_step
+            runs = rec[16:16 + 2 * n_runs].view(np.uint16).astype(int)
+            tiles = _unpack_row_words(rec[16 + 16 * run_units:].view(np.uint32).reshape(n_in_step, 16))
+            assert init == (1 if (n_runs and not started) else 0)
             for r in range(n_runs):
-                a_off, b_off, d, idesc = (int(v) for v in runs[r])
-                n = ((idesc >> 17) & 0x3F) << 3
-                assert (idesc >> 24) & 0x1F == 8 and n % 16 == 0 and 16 <= n <= 256
-                cl, first, l0, acc = a_off // 2, b_off // 32, (d & 0xFFFF) // 16, d >> 31
-                assert first + n // 16 <= n_in_step
-                for k in range(n // 16):
+                w = int(runs[r])
+                l0, first, cl, n = w & 15, (w >> 4) & 63, (w >> 10) & 3, ((w >> 12) & 15) + 1
+                assert first + n <= n_in_step and l0 + n <= P
+                if not started:
+                    assert (l0, n) == (0, P)          # the panel's first MMA overwrites all 16 rows
+                    started = True
+                col = ch * CC + cl
+                for k in range(n):
                     l = l0 + k
-                    assert ((touched >> l) & 1) == acc
                     if swiglu:
                         half = P // 2
                         trow = p * half + l if l < half else R // 2 + p * half + (l - half)
                     else:
                         trow = p * P + l
-                    col = ch * CC + cl
-                    dense[trow * 16:(trow + 1) * 16, col * 16:(col + 1) * 16] = tiles[first + k]
+                    t = tiles[first + k].astype(np.int32)
+                    if trow >= R or not mask[trow, col]:
+                        assert not t.any()           # zero-fill slot
+                        continue
+                    dense[trow * 16:(trow + 1) * 16, col * 16:(col + 1) * 16] += t
                     seen[trow, col] += 1
-                for k in range(n // 16):
-                    touched |= 1 << (l0 + k)
+                    n_live_seen += 1
+                    touched |= 1 << l
         assert prev_last
         assert touched == int(h["panel_mask"][p])
         # both panels of a pair list the same chunks
         def chunks(pp):
-            return [int(h["step_meta"][st]) & 0xFFFFFF
+            return [int(h["step_meta"][st]) & 0x3FFF
                     for st in range(h["panel_step_ptr"][pp], h["panel_step_ptr"][pp + 1])
                     if not (int(h["step_meta"][st]) >> 30) & 1]
         assert chunks(p) == chunks(p ^ 1)
-    assert n_tiles_seen == h["n_tiles"]
+    assert n_slots_seen == h["n_tiles"] and n_live_seen == m.nnz
     np.testing.assert_array_equal(seen, mask.astype(int))
     np.testing.assert_array_equal(dense, m.to_dense_codes())
     if density == 1.0 and not swiglu:
-        # a full panel fuses each of its columns into a single N=256 run
+        # a full panel fuses each of its columns into a single N=256 run (16 rows)
         rec0 = data[:int(h["step_off"][1]) * 16]
-        assert int((rec0[16:32].view(np.uint32)[3] >> 17) & 0x3F) == 32
+        assert all(((int(w) >> 12) & 15) + 1 == 16 for w in rec0[16:16 + 2 * int(rec0[4:8].view(np.uint32)[0])].view(np.uint16))
 
 
 @pytest.mark.parametrize("case", GOLDEN_CASES)
@@ -307,8 +327,9 @@ def test_state_dict_ingestion(case):
 
 
 def test_router_mirror_matches_reference_gates():
-    """TileRouter mirror loaded with the reference router's own parameters reproduces the
-    reference's logits and gates on the same input."""
+    """The TileRouter mirror takes the reference router's own ``state_dict`` (same names and
+    shapes); on those parameters the router restatement reproduces the reference's logits and
+    gates, and the mirror itself has no CPU evaluation."""
     from importlib import import_module
     from conftest import bf16_from_bits
     router = import_module(mb.__name__ + ".router")
@@ -321,12 +342,15 @@ def test_router_mirror_matches_reference_gates():
     r.load_state_dict(sd)
     r.eval()
     x = bf16_from_bits(g["x_bf16"]).float().reshape(-1, 128)
-    with torch.no_grad():
-        logits = r.group_logits(x)
-        gates, aux = r(x)
-    np.testing.assert_allclose(logits.numpy(), g["router_logits"], rtol=1e-5, atol=1e-6)
+    p = {k: v.numpy() for k, v in sd.items()}
+    logits = orc.router_logits(x.numpy(), p["query_proj.weight"], p["iter_embed"][0], p["query_norm.weight"],
+                               p["query_norm.bias"], r.query_norm.eps, p["sub_keys_a"], p["sub_keys_b"],
+                               p["group_bias"])
+    gates = orc.remoe_gates(torch.from_numpy(logits), r.activation_k)
+    np.testing.assert_allclose(logits, g["router_logits"], rtol=1e-5, atol=1e-6)
     np.testing.assert_allclose(gates.numpy(), g["router_gates"], rtol=1e-4, atol=1e-6)
-    assert aux.ndim == 0 and float(aux) >= 0
+    with pytest.raises(NotImplementedError):
+        r(x)
 
 
 def test_custom_ops_have_fake_kernels_and_no_cpu_path():
