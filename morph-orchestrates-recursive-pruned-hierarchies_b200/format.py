@@ -166,10 +166,16 @@ class MortarMatrix:
         return m
 
     @staticmethod
-    def from_reference_cms(cms, drop_zero_tiles: bool = False) -> "MortarMatrix":
+    def from_reference_cms(cms, drop_zero_tiles: bool = False,
+                           threshold: Optional[float] = None) -> "MortarMatrix":
         """A carved reference ``CMSBlockLinear`` (``MortarLinear._cms``): packed
         (``mortar_packed``/``mortar_scale``, deploy_quant.py:361-365) or still holding
-        ``mortar_data`` (block_sparse.py:783-799), which is ternarised with the deploy rule."""
+        ``mortar_data`` (block_sparse.py:783-799).  Unpacked values are ternarised the way the
+        layer itself would: with its own ``_values_threshold`` when its values-ternary STE is on
+        (block_sparse.py:909-919), else with the deploy packer's rule and default threshold 0.5
+        (``pack_mortar_ternary``, deploy_quant.py:344-358) -- i.e. the conversion of a layer
+        that is not in ternary mode is the deploy-time snap, not its training forward.
+        ``threshold`` overrides both."""
         if not getattr(cms, "_mortar", False):
             raise ValueError("layer is not carved: call carve() first, or use from_weight with "
                              "its _prune_mask")
@@ -178,7 +184,9 @@ class MortarMatrix:
             packed = cms.mortar_packed.detach().cpu().numpy()
             scale = float(cms.mortar_scale)
         else:
-            q, scale = ternary_quantize(cms.mortar_data.data)
+            if threshold is None:
+                threshold = float(cms._values_threshold) if getattr(cms, "_values_ternary_mode", False) else 0.5
+            q, scale = ternary_quantize(cms.mortar_data.data, threshold)
             packed = pack_codes_2bit(q.cpu().numpy().reshape(-1, 4)).reshape(-1)
         return MortarMatrix.from_reference_bcsr(
             cms.mortar_offsets.detach().cpu().numpy(), cms.mortar_column_indices.detach().cpu().numpy(),
@@ -203,7 +211,12 @@ class MortarMatrix:
         elif prefix + "mortar_data" in state:
             data = get("mortar_data")
             blocking = int(data.shape[1])
-            q, scale = ternary_quantize(data)
+            threshold = 0.5
+            if prefix + "mortar_ternary" in state:             # [flag, threshold] (block_sparse.py:796)
+                mt = get("mortar_ternary")
+                if float(mt[0]) > 0:
+                    threshold = float(mt[1])
+            q, scale = ternary_quantize(data, threshold)
             packed = pack_codes_2bit(q.numpy().reshape(-1, 4)).reshape(-1)
         else:
             raise KeyError(f"neither {prefix}mortar_packed nor {prefix}mortar_data in the state dict")
@@ -330,6 +343,21 @@ class SchedMatrix:
         self.panel_mask = t(h["panel_mask"].view(np.int32))
         self._c = None
 
+    @classmethod
+    def from_tensors(cls, step_data, step_off, step_meta, panel_step_ptr, panel_mask, n_tiles, n_runs,
+                     n_steps, data_units, n_panels, out_features, in_features, swiglu, scale) -> "SchedMatrix":
+        """A schedule whose arrays already live on the device (the registered ops pass them as
+        tensors); borrows the tensors."""
+        self = cls.__new__(cls)
+        self.out_features, self.in_features = int(out_features), int(in_features)
+        self.swiglu, self.scale, self.nnz = bool(swiglu), float(scale), 0
+        self.n_tiles, self.n_runs, self.n_steps = int(n_tiles), int(n_runs), int(n_steps)
+        self.n_panels, self.data_units = int(n_panels), int(data_units)
+        self.step_data, self.step_off, self.step_meta = step_data, step_off, step_meta
+        self.panel_step_ptr, self.panel_mask = panel_step_ptr, panel_mask
+        self._c = None
+        return self
+
     @property
     def n_out(self) -> int:
         return self.out_features // 2 if self.swiglu else self.out_features
@@ -356,6 +384,23 @@ def unpack_stream_host(grp_ptr, grp_cols, grp_codes, row_ptr, tile_rows):
                                                tile_rows, _ptr(col_idx), _ptr(codes)),
                "mortar_unpack_stream")
     return col_idx, codes
+
+
+def matrix_from_stream(w: "StreamMatrix") -> MortarMatrix:
+    """Canonical matrix recovered from a device-resident stream layout (padding slots carry the
+    column sentinel 0xFFFF and are dropped)."""
+    grp_ptr = w.grp_ptr.detach().cpu().numpy().astype(np.int32)
+    grp_cols = w.grp_cols.detach().cpu().numpy().view(np.uint16).reshape(-1)
+    grp_codes = w.grp_codes.detach().cpu().numpy().reshape(-1)
+    R = w.out_features // TILE
+    G = int(grp_ptr[-1])
+    live = (grp_cols[:G * 8] != 0xFFFF).reshape(G, 8).sum(axis=1)
+    per_group = np.concatenate([[0], np.cumsum(live)]).astype(np.int64)
+    row_ptr = per_group[grp_ptr.astype(np.int64)].astype(np.int32)
+    col_idx, codes = unpack_stream_host(grp_ptr, grp_cols, grp_codes, row_ptr, R)
+    m = MortarMatrix(w.out_features, w.in_features, row_ptr, col_idx, codes, w.scale)
+    m.validate()
+    return m
 
 
 class StreamMatrix:

@@ -14,10 +14,24 @@ from . import _lib
 from .format import TILE, MortarMatrix, SchedMatrix, StreamMatrix
 
 _launches = 0      # kernels launched by this module (bench.py reports it)
+_kernel_counts: dict = {}   # the same, per kernel family
 
 
 def launch_count() -> int:
     return _launches
+
+
+def kernel_counts() -> dict:
+    """Launches so far per kernel family: "act_prep", "bcsr_stream" (the streaming linear / SwiGLU
+    kernel), "prefill_panel" (tcgen05 / tensor memory), "stack_decode", "route_flags", "router".
+    Tests use the deltas to tell which kernel an operator or module forward ran."""
+    return dict(_kernel_counts)
+
+
+def _count(name: str, n: int = 1) -> None:
+    global _launches
+    _launches += n
+    _kernel_counts[name] = _kernel_counts.get(name, 0) + n
 
 
 def _stream_ptr() -> C.c_void_p:
@@ -55,7 +69,6 @@ def act_prep(x: torch.Tensor, n_planes: int = 3, rms_weight: Optional[torch.Tens
              eps: float = 1e-6) -> torch.Tensor:
     """x[rows, cols] -> bf16 planes [n_planes, rows, cols] whose sum is x (after the optional
     RMSNorm (x*rsqrt(mean x^2+eps))*w, fused_decode_step.py:293-321)."""
-    global _launches
     _require_cuda(x, "x")
     x2 = _rows2d(x, x.shape[-1], "x")
     rows, cols = x2.shape
@@ -68,7 +81,7 @@ def act_prep(x: torch.Tensor, n_planes: int = 3, rms_weight: Optional[torch.Tens
     _lib.check(_lib.lib().mortar_act_prep(_ptr(x2), _dtype_code(x2), rows, cols, x2.stride(0), _ptr(w),
                                           float(eps), _ptr(planes), n_planes, rows * cols, cols,
                                           _stream_ptr()), "mortar_act_prep")
-    _launches += 1
+    _count("act_prep")
     return planes
 
 
@@ -82,7 +95,6 @@ def linear_planes(w: StreamMatrix, planes: torch.Tensor, *, swiglu: bool = False
     (or [rows, out/2] = silu(gate)*up with ``swiglu``), as float32/bfloat16 or, with
     ``out_planes`` > 0, as planes [out_planes, rows, n].  ``path`` pins one of the kernel's
     paths ("plain", "staged", "persistent"); "auto" picks by matrix size and batch."""
-    global _launches
     _require_cuda(planes, "planes")
     if planes.dim() != 3 or planes.dtype != torch.bfloat16 or not planes.is_contiguous():
         raise ValueError("planes must be a contiguous bfloat16 tensor [P, rows, in_features]")
@@ -119,7 +131,7 @@ def linear_planes(w: StreamMatrix, planes: torch.Tensor, *, swiglu: bool = False
         int(cluster_size), _ptr(row_act), row_act.stride(0) if row_act is not None else 0,
         _ptr(col_act), col_act.stride(0) if col_act is not None else 0, _stream_ptr()),
         "mortar_linear")
-    _launches += 1
+    _count("bcsr_stream")
     return out
 
 
@@ -150,7 +162,10 @@ _workspaces: dict = {}
 
 
 def _workspace(device, nbytes: int) -> torch.Tensor:
-    key = (device.type, device.index)
+    """Scratch for the hidden activations of one MLP call when the caller passes none: one buffer
+    per (device, stream), so calls on different streams never share it; it grows by
+    reallocation, so code that captures CUDA graphs should pass its own ``workspace``."""
+    key = (device.type, device.index, torch.cuda.current_stream(device).cuda_stream)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
         ws = torch.empty(max(nbytes, 1 << 20), device=device, dtype=torch.uint8)
@@ -170,7 +185,6 @@ def mlp_decode(x: torch.Tensor, gate_up: StreamMatrix, down: StreamMatrix, *,
     with ``n_planes=3`` (fp32 semantics) and ``_SwiGLUMortar.forward`` under autocast
     (morph/model/transformer.py:402-431) with ``n_planes=1, round_bf16=True``.  With
     ``accumulate`` the result is added into ``out`` (the residual carrier)."""
-    global _launches
     _require_cuda(x, "x")
     d_model, d_ff = gate_up.in_features, gate_up.out_features // 2
     lead = x.shape[:-1]
@@ -211,7 +225,9 @@ def mlp_decode(x: torch.Tensor, gate_up: StreamMatrix, down: StreamMatrix, *,
         _ptr(workspace), workspace.numel(), _stream_ptr()), "mortar_mlp_decode")
     direct = x2.dtype == torch.bfloat16 and rms_weight is None and x2.stride(0) % 2 == 0 \
         and x2.data_ptr() % 4 == 0
-    _launches += 2 if direct else 3
+    if not direct:
+        _count("act_prep")
+    _count("bcsr_stream", 2)
     return out.reshape(*lead, d_model)
 
 
@@ -225,7 +241,6 @@ def mlp_decode_static(x: torch.Tensor, gate_up: StreamMatrix, down: StreamMatrix
     dtype (fp32 gates / rms_weight): this wrapper converts and allocates nothing.  Raises
     ``ValueError`` when the batch needs more than the built-in scratch.  Calls share the
     scratch, so run them one after another on a stream, not concurrently."""
-    global _launches
     _require_cuda(x, "x")
     d_model, d_ff = gate_up.in_features, gate_up.out_features // 2
     if x.dim() != 2 or x.shape[1] != d_model or x.stride(1) != 1:
@@ -235,6 +250,8 @@ def mlp_decode_static(x: torch.Tensor, gate_up: StreamMatrix, down: StreamMatrix
     for name, t in (("rms_weight", rms_weight), ("gates", gates)):
         if t is not None and (t.dtype != torch.float32 or not t.is_cuda or not t.is_contiguous()):
             raise ValueError(f"{name} must be a contiguous float32 CUDA tensor")
+    if x.device.index != torch.cuda.current_device() or out.device != x.device:
+        raise ValueError("x and out must live on the current CUDA device (its scratch array and stream are used)")
     rows = x.shape[0]
     if rows == 0:
         return out
@@ -245,7 +262,10 @@ def mlp_decode_static(x: torch.Tensor, gate_up: StreamMatrix, down: StreamMatrix
         _dtype_code(out), out.stride(0), int(n_planes),
         (_lib.FLAG_ROUND_BF16 if round_bf16 else 0) | (_lib.FLAG_ACCUMULATE if accumulate else 0),
         _stream_ptr()), "mortar_mlp_decode_static")
-    _launches += 3
+    direct = x.dtype == torch.bfloat16 and rms_weight is None and x.stride(0) % 2 == 0 and x.data_ptr() % 4 == 0
+    if not direct:
+        _count("act_prep")
+    _count("bcsr_stream", 2)
     return out
 
 
@@ -335,7 +355,6 @@ def stack_decode(x: torch.Tensor, stack: DecodeStack, *, eps: float = 1e-6, n_pl
                  cluster_size: Optional[int] = None) -> torch.Tensor:
     """In-place decode step of a whole MLP stack on the fp32 residual carrier x [rows, d_model]:
     one launch, every block of 8 rows walks all applications inside one thread-block cluster."""
-    global _launches
     _require_cuda(x, "x")
     if x.dtype != torch.float32 or x.dim() != 2 or x.shape[1] != stack.d_model or x.stride(1) != 1:
         raise ValueError("x must be float32 [rows, d_model] with unit inner stride")
@@ -345,7 +364,28 @@ def stack_decode(x: torch.Tensor, stack: DecodeStack, *, eps: float = 1e-6, n_pl
         _ptr(v.blobs), _ptr(v.table), _ptr(stack.app_layer), None, stack.n_apps, stack.n_layers,
         stack.d_model, stack.d_ff, v.max_blob, v.cs, _ptr(x), x.stride(0), rows,
         float(eps), int(n_planes), _ptr(stack.status), _stream_ptr()), "mortar_stack_decode")
-    _launches += 1
+    _count("stack_decode")
+    return x
+
+
+def stack_decode_raw(x: torch.Tensor, blobs: torch.Tensor, blob_table: torch.Tensor, app_layer: torch.Tensor,
+                     rms_weights: Optional[torch.Tensor], status: torch.Tensor, n_layers: int, d_model: int,
+                     d_ff: int, max_blob_bytes: int, cluster_size: int, eps: float = 1e-6,
+                     n_planes: int = 3) -> torch.Tensor:
+    """``mortar_stack_decode`` on raw tensors (what ``DecodeStack`` holds): in place on x
+    [rows, d_model] fp32.  ``rms_weights`` [n_layers, d_model] fp32 serves layers whose blobs do
+    not carry their own norm weight."""
+    _require_cuda(x, "x")
+    if x.dtype != torch.float32 or x.dim() != 2 or x.shape[1] != d_model or x.stride(1) != 1:
+        raise ValueError("x must be float32 [rows, d_model] with unit inner stride")
+    if rms_weights is not None and (rms_weights.dtype != torch.float32 or not rms_weights.is_contiguous()
+                                    or tuple(rms_weights.shape) != (n_layers, d_model)):
+        raise ValueError("rms_weights must be contiguous float32 [n_layers, d_model]")
+    _lib.check(_lib.lib().mortar_stack_decode(
+        _ptr(blobs), _ptr(blob_table), _ptr(app_layer), _ptr(rms_weights), int(app_layer.numel()),
+        int(n_layers), int(d_model), int(d_ff), int(max_blob_bytes), int(cluster_size), _ptr(x), x.stride(0),
+        x.shape[0], float(eps), int(n_planes), _ptr(status), _stream_ptr()), "mortar_stack_decode")
+    _count("stack_decode")
     return x
 
 
@@ -365,7 +405,6 @@ def linear_tc(x: torch.Tensor, w: SchedMatrix, *, gates: Optional[torch.Tensor] 
     """Tensor-memory (tcgen05) block-sparse linear for token blocks: bf16 x[rows, in] ->
     bf16 [rows, out] (or [rows, out/2] = silu(gate)*up for a swiglu schedule), with the
     reference's prefill rounding (stk dds, triton_kernels.py:203-226)."""
-    global _launches
     _require_cuda(x, "x")
     if x.dtype != torch.bfloat16:
         raise ValueError("linear_tc takes bfloat16 activations")
@@ -387,7 +426,7 @@ def linear_tc(x: torch.Tensor, w: SchedMatrix, *, gates: Optional[torch.Tensor] 
     _lib.check(_lib.lib().mortar_linear_tc(C.byref(st), _ptr(x2), x2.stride(0), rows, _ptr(out2),
                                            out2.stride(0), _ptr(g), g.stride(0) if g is not None else 0,
                                            int(cluster_size), _stream_ptr()), "mortar_linear_tc")
-    _launches += 1
+    _count("prefill_panel")
     return out.reshape(*lead, n_out)
 
 
@@ -397,7 +436,6 @@ def mlp_prefill_tc(x: torch.Tensor, gate_up: SchedMatrix, down: SchedMatrix, *,
                    workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``_SwiGLUMortar.forward`` on a token block through the tcgen05 kernels: bf16 in, bf16
     out, the reference's autocast rounding points (transformer.py:402-431)."""
-    global _launches
     _require_cuda(x, "x")
     xb = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
     d_model, d_ff = gate_up.in_features, gate_up.out_features // 2
@@ -424,7 +462,7 @@ def mlp_prefill_tc(x: torch.Tensor, gate_up: SchedMatrix, down: SchedMatrix, *,
         C.byref(gu), C.byref(dn), _ptr(x2), x2.stride(0), rows, _ptr(g),
         g.stride(0) if g is not None else 0, int(n_clusters), _ptr(out2), out2.stride(0),
         _ptr(workspace), workspace.numel(), _stream_ptr()), "mortar_mlp_prefill")
-    _launches += 2
+    _count("prefill_panel", 2)
     return out.reshape(*lead, d_model)
 
 
@@ -447,14 +485,13 @@ def route_flags(gates: torch.Tensor, rlo: torch.Tensor, rhi: torch.Tensor, clo: 
     """Same contract as the reference ``route_flags`` (fused_decode_step.py:1913-1927): gates
     [B, n_clusters] fp32; rlo/rhi [NR], clo/chi [NC] int32 cluster spans; ract [B, NR] /
     cact [B, NC] int32 outputs (may be sliced views of a wider scratch)."""
-    global _launches
     _require_cuda(gates, "gates")
     B = gates.shape[0]
     _lib.check(_lib.lib().mortar_route_flags(
         _ptr(gates), B, gates.stride(0), _ptr(rlo), _ptr(rhi), rlo.numel(), _ptr(clo), _ptr(chi),
         clo.numel(), _ptr(ract), ract.stride(0), _ptr(cact), cact.stride(0), _stream_ptr()),
         "mortar_route_flags")
-    _launches += 1
+    _count("route_flags")
 
 
 def router_gates(x: torch.Tensor, router, iter_idx: int = 0, out: Optional[torch.Tensor] = None,
@@ -466,7 +503,6 @@ def router_gates(x: torch.Tensor, router, iter_idx: int = 0, out: Optional[torch
     rows.  ``router`` is anything with the reference router's parameters (``query_proj.weight``,
     ``iter_embed``, ``query_norm``, ``sub_keys_a/b``, ``group_bias``, ``activation_k``,
     ``n_sub_keys``, ``n_tile_groups``) in fp32 on the device of x."""
-    global _launches
     _require_cuda(x, "x")
     d = router.d_model
     x2 = _rows2d(x, d, "x")
@@ -494,7 +530,7 @@ def router_gates(x: torch.Tensor, router, iter_idx: int = 0, out: Optional[torch
         _ptr(router.sub_keys_a), _ptr(router.sub_keys_b), nsk, _ptr(router.group_bias), G,
         int(router.activation_k), _ptr(scratch), _ptr(out), out.stride(0), _stream_ptr()),
         "mortar_router_gates")
-    _launches += 2
+    _count("router", 2)
     return out
 
 

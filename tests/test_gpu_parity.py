@@ -17,15 +17,18 @@ F32_TOL = 1e-5
 BF16_RTOL, BF16_ATOL = 1e-2, 1e-3
 
 
-def _assert_bf16_close(y: torch.Tensor, ref: torch.Tensor):
+def _assert_bf16_close(y: torch.Tensor, ref: torch.Tensor, near_zero: float = 4e-3):
     """... and the internal gate: an output may differ from the oracle only where an fp32 sum
     landed on a bf16 rounding boundary -- by at most two bf16 steps of its own magnitude, or
     (for outputs that cancel to nearly zero) by 4e-3 of the output RMS, the size of one-step
-    flips of a few hidden activations -- and only a small fraction of outputs may differ."""
+    flips of a few hidden activations -- and only a small fraction of outputs may differ.
+    `near_zero` is that allowance in units of the output RMS.  The flips add up like a random walk
+    over the terms of an output, so tests over 10^7 outputs (further out on the tail) and
+    row-clustered topologies (outputs with several times the average number of terms) pass 1e-2."""
     y, ref = y.cpu().reshape(-1).float(), ref.cpu().reshape(-1).float()
     torch.testing.assert_close(y, ref, rtol=BF16_RTOL, atol=BF16_ATOL)
     rms = float(ref.pow(2).mean().sqrt())
-    bound = torch.maximum(ref.abs() * 2.0 ** -7, torch.full_like(ref, 4e-3 * rms))
+    bound = torch.maximum(ref.abs() * 2.0 ** -7, torch.full_like(ref, near_zero * rms))
     excess = ((y - ref).abs() - bound).max()
     assert float(excess) <= 0, f"error exceeds two bf16 steps by {float(excess):.3e} (rms {rms:.3e})"
     frac = float((y != ref).float().mean())
@@ -305,7 +308,7 @@ def test_topology_sweep_cloud_shape(mask, density):
 
 def test_module_mirror_matches_ops(local_layer):
     L, gu, dn = local_layer
-    mlp = mb.SwiGLUMortar(L.gate_up, L.down, device=DEV)
+    mlp = mb.SwiGLUMortar.from_matrices(L.gate_up, L.down, device=DEV)
     x = mb.synth.make_activations(4 * 9, 768, seed=8).reshape(4, 9, 768).to(DEV)
     y = mlp(x)
     assert y.shape == (4, 9, 768) and y.dtype == torch.bfloat16

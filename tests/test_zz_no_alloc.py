@@ -43,6 +43,31 @@ def test_static_scratch_matches_workspace_entry_point_twice():
         assert err <= TOL, f"call {call}: relative error {err}"
 
 
+def test_static_scratch_against_the_oracle_bf16_input_and_accumulate():
+    """The same entry point against the CPU oracle (not only against its sibling), on the path
+    that skips the plane kernel (bf16 input, no norm: two launches) and with the residual add."""
+    from test_gpu_parity import _decode_oracle
+    L, gu, dn = _layer()
+    xb = mb.synth.make_activations(24, 768, seed=11)                       # bf16
+    ref = _decode_oracle(xb, L)
+    out = torch.full((24, 768), float("nan"), device=DEV)
+    before = mb.ops.kernel_counts()
+    mb.ops.mlp_decode_static(xb.to(DEV), gu, dn, out, n_planes=3)
+    after = mb.ops.kernel_counts()
+    assert after.get("act_prep", 0) == before.get("act_prep", 0)           # bf16 rows are used as a plane directly
+    assert float((out.cpu() - ref).abs().max()) <= TOL * float(ref.abs().max())
+    carrier = torch.randn(24, 768, generator=torch.Generator().manual_seed(3))
+    acc = carrier.clone().to(DEV)
+    mb.ops.mlp_decode_static(xb.to(DEV), gu, dn, acc, n_planes=3, accumulate=True)
+    want = carrier + ref
+    assert float((acc.cpu() - want).abs().max()) <= TOL * float(want.abs().max())
+    import ctypes as C
+    gus, dns = gu.c_struct(), dn.c_struct()
+    rc = mb._lib.lib().mortar_mlp_decode_static(C.byref(gus), C.byref(dns), None, 0, 768, -1, None, 1e-6, None, 0, 0,
+                                               None, 0, 768, 3, 0, None)
+    assert rc == -2                                                        # MORTAR_ERR_SHAPE for a negative row count
+
+
 def test_static_scratch_rejects_oversized_batches():
     L, gu, dn = _layer()
     limit = mb._lib.lib().mortar_mlp_static_scratch_bytes()
