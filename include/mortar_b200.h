@@ -187,6 +187,30 @@ int mortar_route_flags(const float *gates, int64_t rows, int64_t ld_gates,
                        int32_t *row_act, int64_t ld_row_act, int32_t *col_act, int64_t ld_col_act,
                        void *stream);
 
+/* ReMoE per-token tile gather (batches of more than 8 rows).  The reference's decode kernel skips
+ * work per stream: every batch item returns early on its own row flag and masks its own column
+ * flags (fused_decode_step.py:1371-1390, flags from :1883-1927, engine call engine.py:976-986).
+ * mortar_route_gather turns the gates into that schedule for a whole batch: for every hidden tile
+ * row u (16 hidden neurons; `units` = d_ff/16 of them) the ascending list of rows whose gate over
+ * any cluster the tile row spans is positive -- cnt[u] entries at list[u*ld_list ...].
+ *   gates  device fp32 [rows][ld_gates]; cluster = neuron / cluster_size
+ *   cnt    device int32 [units];  list  device int32 [units][ld_list], ld_list >= rows */
+int mortar_route_gather(const float *gates, int64_t rows, int64_t ld_gates, int32_t cluster_size,
+                        int32_t units, int32_t *cnt, int32_t *list, int64_t ld_list, void *stream);
+
+/* The gate/up + SwiGLU + gate-multiply stage of mortar_linear (MORTAR_FLAG_SWIGLU semantics,
+ * MORTAR_FLAG_ROUND_BF16 honoured) over the listed rows only: the gate and up tile rows of unit u
+ * are multiplied against blocks of 8 listed rows, so the tile MMAs of a (row, unit) pair whose
+ * gate is zero are never issued.  Outputs of pairs that are not listed are NOT written: the
+ * caller clears `out` first (a zero gate gives an exact zero, transformer.py:419-427).
+ * Arguments as mortar_linear; cnt / list from mortar_route_gather. */
+int mortar_linear_gathered(const mortar_stream *w, const void *planes, int32_t n_planes,
+                           int64_t plane_stride, int64_t ld_planes, int64_t rows, void *out,
+                           int32_t out_mode, int32_t n_out_planes, int64_t out_plane_stride,
+                           int64_t ld_out, int32_t flags, const float *gates, int64_t ld_gates,
+                           int32_t cluster_size, const int32_t *cnt, const int32_t *list,
+                           int64_t ld_list, void *stream);
+
 /* Bytes of caller-provided workspace mortar_mlp_decode / mortar_mlp_prefill need. */
 int64_t mortar_mlp_workspace_bytes(int64_t rows, int32_t d_model, int32_t d_ff, int32_t n_planes);
 
@@ -196,7 +220,10 @@ int64_t mortar_mlp_workspace_bytes(int64_t rows, int32_t d_model, int32_t d_ff, 
  * bf16 [rows][ldy].  n_planes selects the activation precision (3 = exact fp32 decode
  * semantics, 1 = bf16).  gates optional fp32 [rows][ld_gates] with n_clusters equal
  * contiguous clusters over d_ff; when given, hidden tile rows / down tile columns whose
- * gates are all zero are skipped.  workspace: device, 256-byte aligned,
+ * gates are all zero are skipped: for up to 8 rows by a joint test over the rows, for larger
+ * batches per row through mortar_route_gather / mortar_linear_gathered (the hidden layer is
+ * cleared first; the down projection then reads zeros for inactive groups).  workspace: device,
+ * 256-byte aligned,
  * mortar_mlp_workspace_bytes() bytes; contents are scratch.
  * With MORTAR_FLAG_ROUND_BF16 in `flags` and n_planes == 1 the call reproduces the bf16
  * rounding points of _SwiGLUMortar.forward under autocast (transformer.py:402-431).
@@ -218,7 +245,7 @@ int mortar_mlp_decode(const mortar_stream *gate_up, const mortar_stream *down,
  * inside a region where allocation is not allowed.  The activation planes live in an 8 MiB
  * array built into the library (mortar_mlp_static_scratch_bytes()); each GPU that loads the
  * library holds it until the process exits.  Calls whose planes do not fit
- * (mortar_mlp_workspace_bytes(rows, d_model, d_ff, n_planes) > 8 MiB, e.g. more than 182
+ * (mortar_mlp_workspace_bytes(rows, d_model, d_ff, n_planes) > 8 MiB, e.g. more than 176
  * rows of the 2048/5632 shape at 3 planes) return MORTAR_ERR_CAPACITY.
  * The call allocates nothing.  The first call on a device looks up the array's device
  * address (cudaGetSymbolAddress) with that device current; make that first call outside any

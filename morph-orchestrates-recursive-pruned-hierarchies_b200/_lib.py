@@ -60,6 +60,9 @@ _SIGNATURES = {
                                 _i64, _i32, _vp, _i64, _i32, _vp, _i64, _vp, _i64, _vp]),
     "mortar_route_flags": (C.c_int, [_vp, _i64, _i64, _vp, _vp, _i32, _vp, _vp, _i32, _vp, _i64, _vp,
                                      _i64, _vp]),
+    "mortar_route_gather": (C.c_int, [_vp, _i64, _i64, _i32, _i32, _vp, _vp, _i64, _vp]),
+    "mortar_linear_gathered": (C.c_int, [C.POINTER(Stream), _vp, _i32, _i64, _i64, _i64, _vp, _i32, _i32, _i64,
+                                         _i64, _i32, _vp, _i64, _i32, _vp, _vp, _i64, _vp]),
     "mortar_mlp_workspace_bytes": (_i64, [_i64, _i32, _i32, _i32]),
     "mortar_mlp_decode": (C.c_int, [C.POINTER(Stream), C.POINTER(Stream), _vp, C.c_int, _i64, _i64, _vp,
                                     _f32, _vp, _i64, _i32, _vp, C.c_int, _i64, _i32, _i32, _vp, _i64,

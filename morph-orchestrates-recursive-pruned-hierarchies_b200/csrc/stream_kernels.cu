@@ -462,6 +462,144 @@ bcsr_stream_kernel(const LinearParams p) {
     }
 }
 
+
+// ---- ReMoE per-token tile gather -----------------------------------------------------------
+// For batches of more than 8 rows the any-row-active test of the kernel above almost never
+// skips a hidden tile row (each row activates its own quarter of the groups).  Here the rows are
+// regrouped per hidden tile row instead: route_gather_kernel lists, for every hidden tile row,
+// the rows whose gate over it is positive (ascending), and bcsr_gather_kernel runs the gate and
+// up tile rows of a unit over blocks of 8*NT LISTED rows only -- the per-stream skip of the
+// reference's decode kernel (fused_decode_step.py:1371-1390) with the weights still fetched once
+// per block of rows instead of once per row.  Rows that are not listed keep the zeros the caller
+// put into the output, which is what the multiply by a zero gate gives (transformer.py:419-427).
+
+// gates[rows, n_clusters] -> cnt[units], list[units][ld_list]: one warp per hidden tile row.
+__global__ void __launch_bounds__(128)
+route_gather_kernel(const float *gates, long long ld_gates, int rows, int cluster_size, int units,
+                    int *cnt, int *list, long long ld_list) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int u = blockIdx.x * 4 + warp;
+    if (u >= units) return;
+    const int lo = (u * 16) / cluster_size, hi = (u * 16 + 15) / cluster_size;
+    int base = 0;
+    for (int t0 = 0; t0 < rows; t0 += 32) {
+        const int t = t0 + lane;
+        bool act = false;
+        if (t < rows)
+            for (int k = lo; k <= hi; ++k) act |= gates[(long long)t * ld_gates + k] > 0.f;
+        const uint32_t m = __ballot_sync(0xffffffffu, act);
+        if (act) list[(long long)u * ld_list + base + __popc(m & ((1u << lane) - 1u))] = t;
+        base += __popc(m);
+    }
+    if (lane == 0) cnt[u] = base;
+}
+
+template <int NT, int P, int WPR>
+__global__ void __launch_bounds__(kWarpsPerCta * 32, 1)
+bcsr_gather_kernel(const LinearParams p, const int *__restrict__ cnt, const int *__restrict__ list,
+                   long long ld_list) {
+    constexpr int UPC = kWarpsPerCta / WPR;
+    constexpr int SB = (16 / (NT * P) >= 8) ? 8 : (16 / (NT * P) >= 4) ? 4 : (16 / (NT * P) >= 2) ? 2 : 1;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int unit_local = warp / WPR, sub = warp % WPR;
+    const int unit = blockIdx.x * UPC + unit_local;
+    const bool unit_valid = unit < p.units;
+    const int my_cnt = unit_valid ? cnt[unit] : 0;
+    const int *my_list = list + (long long)(unit_valid ? unit : 0) * ld_list;
+
+    constexpr int kRedFloats = (WPR > 1) ? UPC * (WPR - 1) * 2 * NT * 4 * 32 : 1;
+    __shared__ __align__(16) float red[kRedFloats];
+    __shared__ int cnt_s[UPC];
+    if (sub == 0 && lane == 0) cnt_s[unit_local] = my_cnt;
+    __syncthreads();
+    int max_cnt = 0;                        // the warps of a CTA iterate together (shared-memory sum)
+#pragma unroll
+    for (int k = 0; k < UPC; ++k) max_cnt = max(max_cnt, cnt_s[k]);
+    const float scale = p.round_bf16 ? round_bf16(p.scale) : p.scale;
+
+    for (int j = blockIdx.y; j * (8 * NT) < max_cnt; j += gridDim.y) {
+        const int base = j * (8 * NT);
+        const bool live = base < my_cnt;
+        float acc[2][NT][4];
+#pragma unroll
+        for (int a = 0; a < 2; ++a)
+#pragma unroll
+            for (int n = 0; n < NT; ++n)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[a][n][i] = 0.f;
+        if (live) {
+            const uint32_t *xb[NT];
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                const int idx = min(base + n * 8 + g, my_cnt - 1);      // past the end: discarded values
+                xb[n] = p.planes + (long long)__ldg(my_list + idx) * p.ld_w + t;
+            }
+            int done = 0;
+#pragma unroll
+            for (int a = 0; a < 2; ++a) {
+                const int trow = unit + a * p.units;
+                const int gbeg = p.grp_ptr[trow], gend = p.grp_ptr[trow + 1];
+                int grp = gbeg + ((sub - done) % WPR + WPR) % WPR;
+                uint4 cw = make_uint4(0, 0, 0, 0), cl = make_uint4(0, 0, 0, 0);
+                if (grp < gend) {
+                    cw = __ldg(p.grp_codes + (long long)grp * 32 + lane);
+                    cl = __ldg(p.grp_cols + grp);
+                }
+                while (grp < gend) {
+                    const int ngrp = grp + WPR;
+                    uint4 ncw = cw, ncl = cl;
+                    if (ngrp < gend) {
+                        ncw = __ldg(p.grp_codes + (long long)ngrp * 32 + lane);
+                        ncl = __ldg(p.grp_cols + ngrp);
+                    }
+                    if ((cl.w >> 16) != 0xffffu) group_mma<NT, P, SB, false>(acc[a], cw, cl, xb, p.plane_stride_w, nullptr);
+                    else group_mma<NT, P, SB, true>(acc[a], cw, cl, xb, p.plane_stride_w, nullptr);
+                    cw = ncw; cl = ncl; grp = ngrp;
+                }
+                done += gend - gbeg;
+            }
+        }
+        if (WPR > 1) {
+            float *mine = red + ((unit_local * (WPR - 1) + (sub > 0 ? sub - 1 : 0)) * 2 * NT * 4) * 32;
+            if (sub > 0) {
+#pragma unroll
+                for (int a = 0; a < 2; ++a)
+#pragma unroll
+                    for (int n = 0; n < NT; ++n)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) mine[((a * NT + n) * 4 + i) * 32 + lane] = acc[a][n][i];
+            }
+            __syncthreads();
+            if (sub == 0) {
+                for (int w = 0; w < WPR - 1; ++w) {
+                    const float *theirs = red + ((unit_local * (WPR - 1) + w) * 2 * NT * 4) * 32;
+#pragma unroll
+                    for (int a = 0; a < 2; ++a)
+#pragma unroll
+                        for (int n = 0; n < NT; ++n)
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) acc[a][n][i] += theirs[((a * NT + n) * 4 + i) * 32 + lane];
+                }
+            }
+            __syncthreads();                    // `red` is free again for the next block of rows
+        }
+        if (sub == 0 && live) {
+            // acc[.][n][0..3] = (neuron g, column 2t), (g, 2t+1), (g+8, 2t), (g+8, 2t+1) of block n
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int idx = base + n * 8 + 2 * t + (i & 1);
+                    if (idx >= my_cnt) continue;
+                    emit_value<true>(p, scale, unit, true, __ldg(my_list + idx), g + 8 * (i >> 1), acc[0][n][i],
+                                     acc[1][n][i]);
+                }
+            }
+        }
+    }
+}
+
 #include "gemv_persistent.cuh"
 
 // x[rows, cols] -> bf16 planes, optional RMSNorm prologue.  One CTA per row.
@@ -548,6 +686,34 @@ int launch_planes(const LinearParams &p, int wpr, bool bulk, cudaStream_t st) {
     if (p.n_planes == 1) return launch_nt<1, SWIGLU>(p, wpr, bulk, st);
     if (p.n_planes == 2) return launch_nt<2, SWIGLU>(p, wpr, bulk, st);
     return launch_nt<3, SWIGLU>(p, wpr, bulk, st);
+}
+
+
+template <int NT, int P>
+int launch_gather_wpr(const LinearParams &p, int wpr, const int *cnt, const int *list, long long ld_list,
+                      cudaStream_t st) {
+    const int upc = kWarpsPerCta / wpr;
+    const long long ctas_x = (p.units + upc - 1) / upc;
+    long long blocks = (p.rows + 8 * NT - 1) / (8 * NT);
+    // enough CTAs per unit to cover the GPU a few times; each CTA loops over its unit's blocks
+    const long long cap = (148 * 24 + ctas_x - 1) / ctas_x;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    dim3 grid((unsigned)ctas_x, (unsigned)blocks);
+    if (wpr == 4) bcsr_gather_kernel<NT, P, 4><<<grid, kWarpsPerCta * 32, 0, st>>>(p, cnt, list, ld_list);
+    else if (wpr == 2) bcsr_gather_kernel<NT, P, 2><<<grid, kWarpsPerCta * 32, 0, st>>>(p, cnt, list, ld_list);
+    else bcsr_gather_kernel<NT, P, 1><<<grid, kWarpsPerCta * 32, 0, st>>>(p, cnt, list, ld_list);
+    MORTAR_CUDA_CHECK(cudaGetLastError());
+    return MORTAR_OK;
+}
+
+template <int P>
+int launch_gather(const LinearParams &p, int wpr, const int *cnt, const int *list, long long ld_list,
+                  cudaStream_t st) {
+    // a unit sees about a quarter of the rows: pick the rows-per-CTA step for that count
+    if (p.rows <= 128) return launch_gather_wpr<1, P>(p, wpr, cnt, list, ld_list, st);
+    if (p.rows <= 512) return launch_gather_wpr<2, P>(p, wpr, cnt, list, ld_list, st);
+    return launch_gather_wpr<4, P>(p, wpr, cnt, list, ld_list, st);
 }
 
 template <bool SWIGLU>
@@ -675,6 +841,62 @@ extern "C" int mortar_linear(const mortar_stream *w, const void *planes, int32_t
     return swiglu ? launch_planes<true>(p, wpr, bulk, st) : launch_planes<false>(p, wpr, bulk, st);
 }
 
+extern "C" int mortar_route_gather(const float *gates, int64_t rows, int64_t ld_gates, int32_t cluster_size,
+                                   int32_t units, int32_t *cnt, int32_t *list, int64_t ld_list, void *stream) {
+    if (!gates || !cnt || !list) return MORTAR_ERR_NULL;
+    if (rows < 0 || units <= 0 || cluster_size <= 0 || ld_list < rows) return MORTAR_ERR_SHAPE;
+    if (rows > 0x7fffffffLL) return MORTAR_ERR_CAPACITY;
+    route_gather_kernel<<<(unsigned)((units + 3) / 4), 128, 0, (cudaStream_t)stream>>>(
+        gates, ld_gates, (int)rows, cluster_size, units, cnt, list, ld_list);
+    MORTAR_CUDA_CHECK(cudaGetLastError());
+    return MORTAR_OK;
+}
+
+extern "C" int mortar_linear_gathered(const mortar_stream *w, const void *planes, int32_t n_planes,
+                                      int64_t plane_stride, int64_t ld_planes, int64_t rows, void *out,
+                                      int32_t out_mode, int32_t n_out_planes, int64_t out_plane_stride,
+                                      int64_t ld_out, int32_t flags, const float *gates, int64_t ld_gates,
+                                      int32_t cluster_size, const int32_t *cnt, const int32_t *list,
+                                      int64_t ld_list, void *stream) {
+    if (!w || !planes || !out || !w->grp_ptr || !gates || !cnt || !list) return MORTAR_ERR_NULL;
+    if (w->n_groups > 0 && (!w->grp_codes || !w->grp_cols)) return MORTAR_ERR_NULL;
+    if (w->tile_rows <= 0 || (w->tile_rows % 2) || w->tile_cols <= 0 || w->tile_cols > 65534 || rows < 0 ||
+        cluster_size <= 0 || ld_list < rows)
+        return MORTAR_ERR_SHAPE;
+    if (n_planes < 1 || n_planes > 3) return MORTAR_ERR_DTYPE;
+    if (out_mode < MORTAR_OUT_F32 || out_mode > MORTAR_OUT_PLANES) return MORTAR_ERR_DTYPE;
+    if (out_mode == MORTAR_OUT_PLANES && (n_out_planes < 1 || n_out_planes > 3)) return MORTAR_ERR_DTYPE;
+    const int units = w->tile_rows / 2;
+    if (ld_planes < (int64_t)w->tile_cols * 16 || ld_out < (int64_t)units * 16) return MORTAR_ERR_SHAPE;
+    if (!aligned(planes, 4) || (ld_planes & 1) || (plane_stride & 1)) return MORTAR_ERR_ALIGN;
+    if (!aligned(w->grp_codes, 16) || !aligned(w->grp_cols, 16)) return MORTAR_ERR_ALIGN;
+    if (flags & MORTAR_FLAG_ACCUMULATE) return MORTAR_ERR_UNSUPPORTED;
+    if (rows == 0) return MORTAR_OK;
+    if (rows > 0x7fffffffLL) return MORTAR_ERR_CAPACITY;
+    LinearParams p;
+    p.grp_codes = reinterpret_cast<const uint4 *>(w->grp_codes);
+    p.grp_cols = reinterpret_cast<const uint4 *>(w->grp_cols);
+    p.grp_ptr = w->grp_ptr;
+    p.R = w->tile_rows; p.C = w->tile_cols; p.scale = w->scale;
+    p.planes = reinterpret_cast<const uint32_t *>(planes);
+    p.plane_stride_w = plane_stride / 2; p.ld_w = ld_planes / 2; p.n_planes = n_planes;
+    p.rows = rows;
+    p.out = out; p.out_mode = out_mode; p.n_out_planes = n_out_planes;
+    p.out_plane_stride = out_plane_stride; p.ld_out = ld_out;
+    p.round_bf16 = (flags & MORTAR_FLAG_ROUND_BF16) != 0;
+    p.accumulate = 0;
+    p.gates = gates; p.ld_gates = ld_gates; p.cluster_size = cluster_size;
+    p.gates_on_input = 0;
+    p.row_act = nullptr; p.ld_row_act = 0; p.col_act = nullptr; p.ld_col_act = 0;
+    p.units = units; p.fold = 0; p.real_rows = rows;
+    const double avg = (double)w->n_groups / (double)units;
+    const int wpr = avg >= 3.0 ? 4 : (avg >= 1.5 ? 2 : 1);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (n_planes == 1) return launch_gather<1>(p, wpr, cnt, list, ld_list, st);
+    if (n_planes == 2) return launch_gather<2>(p, wpr, cnt, list, ld_list, st);
+    return launch_gather<3>(p, wpr, cnt, list, ld_list, st);
+}
+
 extern "C" int mortar_linear_error(int32_t *code, int32_t reset) {
     if (!code) return MORTAR_ERR_NULL;
     int v = 0;
@@ -708,8 +930,11 @@ static inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * 
 extern "C" int64_t mortar_mlp_workspace_bytes(int64_t rows, int32_t d_model, int32_t d_ff,
                                               int32_t n_planes) {
     if (rows < 0 || d_model <= 0 || d_ff <= 0 || n_planes < 1 || n_planes > 3) return MORTAR_ERR_SHAPE;
+    // activation planes of the input and of the hidden layer, then the routing lists of a gated
+    // call (per hidden tile row: a count and up to `rows` row numbers)
     return align_up((int64_t)n_planes * rows * d_model * 2, 256) +
-           align_up((int64_t)n_planes * rows * d_ff * 2, 256);
+           align_up((int64_t)n_planes * rows * d_ff * 2, 256) + align_up((int64_t)(d_ff / 16) * 4, 256) +
+           align_up((int64_t)(d_ff / 16) * rows * 4, 256);
 }
 
 extern "C" int mortar_mlp_decode(const mortar_stream *gate_up, const mortar_stream *down,
@@ -750,9 +975,24 @@ extern "C" int mortar_mlp_decode(const mortar_stream *gate_up, const mortar_stre
     const int rb = flags & MORTAR_FLAG_ROUND_BF16;
     const int h_planes = rb ? 1 : n_planes;
     const int path = flags & MORTAR_FLAG_PATH_MASK;
-    int rc = mortar_linear(gate_up, xin, xin_planes, xin_stride, xin_ld, rows, hp, MORTAR_OUT_PLANES,
+    int rc;
+    if (gates && rows > 8) {
+        // routed batch: hidden tile rows run over the rows that activate them only; the rest of the
+        // hidden layer is the zero the gate multiply would produce
+        char *lp = reinterpret_cast<char *>(hp) + align_up((int64_t)n_planes * rows * d_ff * 2, 256);
+        int32_t *cnt = reinterpret_cast<int32_t *>(lp);
+        int32_t *list = reinterpret_cast<int32_t *>(lp + align_up((int64_t)(d_ff / 16) * 4, 256));
+        MORTAR_CUDA_CHECK(cudaMemsetAsync(hp, 0, (size_t)h_planes * rows * d_ff * 2, (cudaStream_t)stream));
+        rc = mortar_route_gather(gates, rows, ld_gates, cs, d_ff / 16, cnt, list, rows, stream);
+        if (rc != MORTAR_OK) return rc;
+        rc = mortar_linear_gathered(gate_up, xin, xin_planes, xin_stride, xin_ld, rows, hp, MORTAR_OUT_PLANES,
+                                    h_planes, rows * (int64_t)d_ff, d_ff, rb, gates, ld_gates, cs, cnt, list,
+                                    rows, stream);
+    } else {
+        rc = mortar_linear(gate_up, xin, xin_planes, xin_stride, xin_ld, rows, hp, MORTAR_OUT_PLANES,
                            h_planes, rows * (int64_t)d_ff, d_ff, MORTAR_FLAG_SWIGLU | rb | path, gates,
                            ld_gates, cs, nullptr, 0, nullptr, 0, stream);
+    }
     if (rc != MORTAR_OK) return rc;
     return mortar_linear(down, hp, h_planes, rows * (int64_t)d_ff, d_ff, rows, y,
                          y_dtype == MORTAR_F32 ? MORTAR_OUT_F32 : MORTAR_OUT_BF16, 0, 0, ldy,

@@ -227,7 +227,12 @@ def mlp_decode(x: torch.Tensor, gate_up: StreamMatrix, down: StreamMatrix, *,
         and x2.data_ptr() % 4 == 0
     if not direct:
         _count("act_prep")
-    _count("bcsr_stream", 2)
+    if g is not None and rows > 8:          # routed batch: per-row gather of the hidden tile rows
+        _count("route_gather")
+        _count("bcsr_gather")
+        _count("bcsr_stream")
+    else:
+        _count("bcsr_stream", 2)
     return out.reshape(*lead, d_model)
 
 
@@ -265,7 +270,12 @@ def mlp_decode_static(x: torch.Tensor, gate_up: StreamMatrix, down: StreamMatrix
     direct = x.dtype == torch.bfloat16 and rms_weight is None and x.stride(0) % 2 == 0 and x.data_ptr() % 4 == 0
     if not direct:
         _count("act_prep")
-    _count("bcsr_stream", 2)
+    if gates is not None and rows > 8:
+        _count("route_gather")
+        _count("bcsr_gather")
+        _count("bcsr_stream")
+    else:
+        _count("bcsr_stream", 2)
     return out
 
 
@@ -492,6 +502,24 @@ def route_flags(gates: torch.Tensor, rlo: torch.Tensor, rhi: torch.Tensor, clo: 
         clo.numel(), _ptr(ract), ract.stride(0), _ptr(cact), cact.stride(0), _stream_ptr()),
         "mortar_route_flags")
     _count("route_flags")
+
+
+def route_gather(gates: torch.Tensor, cluster_size: int, units: int):
+    """Per hidden tile row (16 neurons; ``units`` of them) the ascending list of rows whose gate over
+    the clusters it spans is positive: returns (cnt int32 [units], rows int32 [units, n_rows]); only
+    the first cnt[u] entries of rows[u] are defined.  The per-stream activity of the reference's
+    decode kernel (fused_decode_step.py:1371-1390) as a schedule for a whole batch."""
+    _require_cuda(gates, "gates")
+    g = gates.to(torch.float32).reshape(-1, gates.shape[-1])
+    if g.stride(1) != 1:
+        g = g.contiguous()
+    n = g.shape[0]
+    cnt = torch.empty(units, device=g.device, dtype=torch.int32)
+    lst = torch.empty(units, max(n, 1), device=g.device, dtype=torch.int32)
+    _lib.check(_lib.lib().mortar_route_gather(_ptr(g), n, g.stride(0), int(cluster_size), int(units), _ptr(cnt),
+                                              _ptr(lst), lst.stride(0), _stream_ptr()), "mortar_route_gather")
+    _count("route_gather")
+    return cnt, lst
 
 
 def router_gates(x: torch.Tensor, router, iter_idx: int = 0, out: Optional[torch.Tensor] = None,

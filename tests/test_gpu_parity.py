@@ -394,3 +394,41 @@ def test_remoe_cloud_configuration():
     ref = orc.swiglu_mlp(xb[sub].cpu().float(), _dense(L.gate_up), _dense(L.down), g4[sub].cpu(), ncls,
                          dtype=torch.bfloat16)
     _assert_bf16_close(ysub, ref)
+
+
+@pytest.mark.parametrize("ncls,k", [(352, 88), (16, 8), (704, 176)])
+@pytest.mark.parametrize("rows", [9, 64, 300])
+def test_per_token_tile_gather(ncls, k, rows):
+    """Routed batches of more than 8 rows: the gather schedule lists exactly the (row, hidden tile
+    row) pairs with a positive gate; the gathered gate/up stage runs only those and the MLP still
+    equals the multiply semantics of the oracle, in both arithmetic modes.  704 clusters = two
+    clusters inside one tile row (a listed row may still have gated-off neurons)."""
+    L = mb.synth.make_layer(2048, 5632, 0.25, seed=200)
+    gu, dn = L.gate_up.to_stream(DEV), L.down.to_stream(DEV)
+    gates = mb.synth.make_gates(rows, L, ncls, k, seed=rows + ncls)
+    cs = 5632 // ncls
+    cnt, lst = mb.ops.route_gather(gates.to(DEV), cs, 352)
+    act = gates.reshape(rows, ncls).numpy() > 0
+    for u in (0, 1, 17, 200, 351):
+        lo, hi = (u * 16) // cs, (u * 16 + 15) // cs
+        want = np.nonzero(act[:, lo:hi + 1].any(axis=1))[0]
+        assert int(cnt[u]) == len(want)
+        np.testing.assert_array_equal(lst[u, :len(want)].cpu().numpy(), want)
+    listed = int(cnt.sum())
+    assert listed < 0.6 * rows * 352                        # most (row, tile row) pairs are skipped
+    x = mb.synth.make_activations(rows, 2048, seed=rows, dtype=torch.float32)
+    before = mb.ops.kernel_counts()
+    y = mb.ops.mlp_decode(x.to(DEV), gu, dn, gates=gates.to(DEV), n_clusters=ncls, n_planes=3)
+    after = mb.ops.kernel_counts()
+    assert after.get("bcsr_gather", 0) == before.get("bcsr_gather", 0) + 1
+    ref = _decode_oracle(x, L, gates, ncls)
+    assert float((y.cpu() - ref).abs().max()) <= F32_TOL * float(ref.abs().max())
+    xb = x.to(torch.bfloat16)
+    yb = mb.ops.mlp_prefill(xb.to(DEV), gu, dn, gates=gates.to(DEV), n_clusters=ncls)
+    refb = orc.swiglu_mlp(xb.float(), _dense(L.gate_up), _dense(L.down), gates, ncls, dtype=torch.bfloat16)
+    _assert_bf16_close(yb, refb)
+    # a row whose gates are all zero yields exact zeros
+    g0 = gates.clone()
+    g0[rows // 2] = 0.0
+    y0 = mb.ops.mlp_decode(x.to(DEV), gu, dn, gates=g0.to(DEV), n_clusters=ncls, n_planes=3)
+    assert float(y0[rows // 2].abs().max()) == 0.0
