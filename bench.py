@@ -1,6 +1,6 @@
 """Benchmark of the MORTAR sparse-MLP hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--quick]
 
 Headline workload (N=1 and every N): the decode stack of the default 3+6xT+3 layout --
 12 independent ternary MLP layers (d_model 768, d_ff 2048, 25% tile density, seeds
@@ -8,13 +8,17 @@ Headline workload (N=1 and every N): the decode stack of the default 3+6xT+3 lay
 step = one decode step of the whole stack: x <- x + MLP_i(rmsnorm_i(x)) for the 42
 applications (the residual add makes the chain data-dependent; attention between the
 applications is not part of this path).  `value` = tokens/s with inputs resident in HBM,
-`e2e` = the same through pinned host buffers with the copies inside the timed region.
-Between timed steps a 256 MiB buffer is written to flush L2.  The JSON line also carries
-batch 1 / 8 decode and cloud-shape prefill measurements, each with its own roofline.
+`e2e` = the same through pinned host buffers with the copies inside the timed region;
+`parity_max_rel` = the launch's result against the CPU oracle on the same input.
+Between timed steps a 256 MiB buffer is written to flush L2.  The JSON line also carries, each
+with its own roofline and clock record: batch 1 / 8 decode, the single-layer configuration with
+its CPU path timed beside it, cloud-shape prefill (through the module forward, device-resident
+and end to end), the density / topology sweep, the ReMoE-routed configuration, the 30B-model
+GEMV shape, the router, and a measured dense fp8 tensor peak.
 
 Under torchrun (N>1) every rank runs the same stack on its own GPU with its own 64 tokens
 (weights replicated, no collective on the data path); the aggregate is all tokens over
-the slowest rank's device time.
+the slowest rank's device time.  The cloud prefill is run the same way (16384 tokens per rank).
 """
 from __future__ import annotations
 
@@ -169,14 +173,6 @@ def decode_step(mb, stack: Stack, x: torch.Tensor, ws: torch.Tensor) -> None:
                           n_planes=3, out=x, accumulate=True, workspace=ws)
 
 
-def prefill_pass(mb, stack: Stack, x: torch.Tensor, y: torch.Tensor, ws: torch.Tensor) -> None:
-    """x [N, d] bf16 token block through every application of the stack (bf16 semantics, the
-    reference's rounding points); every application reads the same normalised block."""
-    for i in stack.order:
-        mb.ops.mlp_decode(x, stack.gu[i], stack.dn[i], n_planes=1, round_bf16=True,
-                          out_dtype=torch.bfloat16, out=y, workspace=ws)
-
-
 def time_steps(fn, steps: int, warmup: int, flush: torch.Tensor | None, pre=None, post=None):
     """Runs `fn` warmup+steps times; returns per-step device milliseconds (CUDA events on the
     current stream).  `pre`/`post` run inside the timed window (the host copies of the
@@ -254,7 +250,10 @@ def run_decode(mb, stack: Stack, batch: int, steps: int, warmup: int, flush, dev
     reset()
     t_warm = time_steps(step, steps, warmup, None)
     err = stack.decode_stack.error() if mode == "stack" else 0
-    return dict(batch=batch, t_dev=t_dev, t_e2e=t_e2e, t_warm=t_warm,
+    reset()
+    step()
+    output = x.detach().cpu().clone()          # one step on the seeded input, for the parity check
+    return dict(batch=batch, t_dev=t_dev, t_e2e=t_e2e, t_warm=t_warm, output=output,
                 launches_per_step=launches_per_step, h2d=hx.numel() * 4, d2h=hy.numel() * 4,
                 checksum=float(hy.double().abs().sum()), device_error_word=err)
 
@@ -289,47 +288,79 @@ def kernel_only(mb, stack: Stack, batch: int, reps: int, device):
     return statistics.mean(t) / launches * 1e3     # microseconds per launch
 
 
-def cpu_reference_decode(batch: int, budget_s: float, cfg=LOCAL):
+def bench_config(world: int) -> dict:
+    """The `config` object of the JSON line; identical for both arms."""
+    return {"workload": "decode stack 3+6x6+3 (configs[1]): d_model 768, d_ff 2048, 12 ternary layers at "
+                        "25% 16x16-tile density, 42 applications/token",
+            "batch_per_gpu": DECODE_BATCH, "l2": "256 MiB flush between timed steps",
+            "parallelism": f"dp{world} (token shards, replicated weights, no collective)"}
+
+
+def cpu_reference_decode(batch: int, budget_s: float, cfg=LOCAL, seed: int = 1):
     """The reference's CPU path for this MLP (dense reconstruction of the effective weights
     + F.linear, fp32, all host threads; morph/inference/engine.py:74-84 and
-    morph/model/transformer.py:402-431) on the same stack, for a bounded number of steps."""
-    from oracle import mortar_oracle as orc
-    import mortar_b200 as mb
-    import numpy as np
+    morph/model/transformer.py:402-431) on the same stack, for a bounded number of steps.
+    Uses the oracle's own workload generator: the CUDA library is not loaded."""
+    from oracle import workloads as wl
     torch.set_num_threads(os.cpu_count() or 1)
     n_layers = cfg["prelude"] + cfg["core"] + cfg["coda"]
-    dense = []
-    for i in range(n_layers):
-        L = mb.synth.make_layer(cfg["d_model"], cfg["d_ff"], DENSITY, seed=cfg["seed0"] + i)
-        ws = []
-        for m in (L.gate_up, L.down):
-            rows = np.repeat(np.arange(m.tile_rows), np.diff(m.row_ptr))
-            codes = torch.from_numpy(np.ascontiguousarray(
-                orc.unpack_ternary(m.codes.reshape(-1), m.nnz * 256).reshape(m.nnz, 16, 16)))
-            ws.append(orc.mortar_dense(codes, torch.tensor(m.scale), torch.from_numpy(rows),
-                                       torch.from_numpy(m.col_idx.astype(np.int64)),
-                                       m.out_features, m.in_features, bf16_weights=False))
-        dense.append(ws)
-    gen = torch.Generator().manual_seed(cfg["seed0"] + 999)
-    rms = [(1.0 + 0.05 * torch.randn(cfg["d_model"], generator=gen)) for _ in range(n_layers)]
+    dense = [wl.dense_layer(cfg["d_model"], cfg["d_ff"], DENSITY, cfg["seed0"] + i)[:2] for i in range(n_layers)]
+    rms = wl.norm_weights(n_layers, cfg["d_model"], cfg["seed0"] + 999)
     order = site_order(cfg)
-    x0 = mb.synth.make_activations(batch, cfg["d_model"], seed=1, dtype=torch.float32)
-
-    def step():
-        x = x0.clone()
-        for i in order:
-            xn = orc.rmsnorm_rows(x, rms[i], 1e-6)
-            x = x + orc.swiglu_mlp(xn, dense[i][0], dense[i][1])
-        return x
-    step()
+    x0 = wl.activations(batch, cfg["d_model"], seed=seed, dtype=torch.float32)
+    out = wl.decode_stack_step(x0.clone(), dense, rms, order)
     times = []
     t_start = time.perf_counter()
     while len(times) < 3 or (time.perf_counter() - t_start < budget_s and len(times) < 200):
         t0 = time.perf_counter()
-        step()
+        wl.decode_stack_step(x0.clone(), dense, rms, order)
         times.append(time.perf_counter() - t0)
     return dict(ms_per_step=1e3 * min(times), steps=len(times), cores=torch.get_num_threads(),
-                tokens_per_s=batch / min(times))
+                tokens_per_s=batch / min(times), output=out)
+
+
+def cpu_single_layer(tokens: int, reps: int = 3):
+    """configs[0] on the host cores: one 768/2048 layer, 4 x 4096 tokens, the reference's dense
+    reconstruction path under bf16 autocast rounding (and in fp32), best of `reps`."""
+    from oracle import mortar_oracle as orc
+    from oracle import workloads as wl
+    torch.set_num_threads(os.cpu_count() or 1)
+    wg, wd, _ = wl.dense_layer(LOCAL["d_model"], LOCAL["d_ff"], DENSITY, 0, bf16_scale=True)
+    x = wl.activations(tokens, LOCAL["d_model"], seed=0).float()
+    out = {"cores": torch.get_num_threads(), "torch": torch.__version__}
+    for name, dt in (("bf16", torch.bfloat16), ("fp32", torch.float32)):
+        ts = []
+        for _ in range(reps + 1):
+            t0 = time.perf_counter()
+            orc.swiglu_mlp(x, wg, wd, dtype=dt)
+            ts.append(time.perf_counter() - t0)
+        out[f"{name}_ms"] = round(1e3 * min(ts[1:]), 2)
+        out[f"{name}_tokens_per_s"] = round(tokens / min(ts[1:]), 1)
+    return out
+
+
+def measured_fp8_peak(device, n: int = 8192, reps: int = 10):
+    """Dense fp8 (e4m3) tensor-core peak of this GPU through the library GEMM (torch._scaled_mm),
+    burst figure, for the north star's 8-bit denominator.  Bench-only: nothing on the product path
+    calls a library GEMM."""
+    try:
+        a = torch.randn(n, n, device=device).to(torch.float8_e4m3fn)
+        b = torch.randn(n, n, device=device).to(torch.float8_e4m3fn).t()     # column-major second operand
+        one = torch.ones((), device=device)
+        fn = lambda: torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+        t = time_steps(fn, reps, 3, None)
+        return {"fp8_e4m3_tflops_burst": round(2 * n ** 3 / (min(t) * 1e-3) / 1e12, 1),
+                "how": f"torch._scaled_mm {n}^3, best of {reps}"}
+    except Exception as e:      # noqa: BLE001  (an absent kernel is reported, not fatal)
+        return {"unavailable": f"{type(e).__name__}: {str(e)[:160]}"}
+
+
+def tensor_roofline(tf: float, pk: dict, fp8: dict | None = None) -> dict:
+    r = {"bound": "tensor", "achieved": round(tf, 2), "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
+         "frac": round(tf / pk["bf16_tflops_sustained"], 5), "peak_source": pk["source"] + " (bf16 sustained)"}
+    if fp8 and "fp8_e4m3_tflops_burst" in fp8:
+        r["frac_of_measured_fp8_burst"] = round(tf / fp8["fp8_e4m3_tflops_burst"], 5)
+    return r
 
 
 def run_ours(args, rank, world, local_rank):
@@ -349,6 +380,14 @@ def run_ours(args, rank, world, local_rank):
 
     sync_all()
     with ClockSampler(local_rank) as clk:
+        # a second and a half of the same launch first, so the clock record holds tens of samples taken
+        # under this load (the timed steps follow without a pause)
+        soak = mb.synth.make_activations(DECODE_BATCH, LOCAL["d_model"], seed=1, dtype=torch.float32).to(device)
+        t_end = time.perf_counter() + 1.5
+        while time.perf_counter() < t_end:
+            for _ in range(20):
+                mb.ops.stack_decode(soak, stack.decode_stack)
+            torch.cuda.synchronize()
         main = run_decode(mb, stack, DECODE_BATCH, steps, warmup, flush, device, seed=1 + rank)
     sync_all()
 
@@ -360,9 +399,24 @@ def run_ours(args, rank, world, local_rank):
     value = job_throughput(DECODE_BATCH * steps, world, tot_dev)
     e2e = job_throughput(DECODE_BATCH * steps, world, tot_e2e)
 
+    # cloud prefill on every rank (weak scaling: 16384 tokens each)
+    prefill = None
+    if not args.quick:
+        sync_all()
+        with ClockSampler(local_rank) as pclk:
+            prefill = run_prefill(mb, device, pk, flush, seed=7 + rank, reps=3 if world == 1 else 2)
+        sync_all()
+        slow = max_over_ranks(prefill["ms_per_pass"], device)
+        slow_e2e = max_over_ranks(prefill["e2e_ms_per_pass"], device)
+        prefill["clocks"] = pclk.summary()
+        prefill["n_gpus"] = world
+        prefill["tokens_per_s"] = round(job_throughput(prefill["tokens"], world, slow), 1)
+        prefill["e2e"]["value"] = round(job_throughput(prefill["tokens"], world, slow_e2e), 1)
+
     extra = {}
     roof = None
     cpu = None
+    parity = None
     if rank == 0:
         ms_step = statistics.mean(main["t_dev"])
         alg = stack.algorithmic_bytes_per_step(DECODE_BATCH)
@@ -372,20 +426,32 @@ def run_ours(args, rank, world, local_rank):
                 "frac": round(achieved / pk["hbm_gbs"], 5), "peak_source": pk["source"],
                 "us_per_launch": round(ms_step * 1e3, 2),
                 "algorithmic_bytes_per_launch": int(alg),
-                "traffic": TRAFFIC_BYTES_PER_LAUNCH,
+                "traffic": profile_traffic("stack_decode_kernel_decode_stack_b64.md"),
                 "note": "the 12 layers (3.6 MB packed) are L2-resident and every rank streams its "
                         "share into shared memory: this configuration is bound by on-SM instruction "
                         "issue and cluster synchronisation latency, not by HBM"}
+        # the oracle on the very input of the headline launch (also the CPU baseline's timing run)
+        c = cpu_reference_decode(DECODE_BATCH, budget_s=12.0 if world == 1 else 0.0, seed=1 + rank)
+        parity = float((main["output"] - c["output"]).abs().max() / c["output"].abs().max())
+        if world == 1:
+            cpu = {"value": round(c["tokens_per_s"], 1), "unit": "tokens/s", "cores": c["cores"],
+                   "kind": "port",
+                   "sample": f"{c['steps']} decode steps of the same 42-application stack at batch "
+                             f"{DECODE_BATCH}, fp32 dense reconstruction + F.linear, best step"}
         if world == 1 and not args.quick:
+            fp8 = measured_fp8_peak(device)
+            extra["measured_fp8_peak"] = fp8
             for b in (1, 8):
-                r = run_decode(mb, stack, b, steps, warmup, flush, device, seed=11 + b)
+                with ClockSampler(local_rank) as sc:
+                    r = run_decode(mb, stack, b, steps, warmup, flush, device, seed=11 + b)
                 extra[f"decode_b{b}"] = {
                     "tokens_per_s": round(b * steps / (sum(r["t_dev"]) * 1e-3), 1),
                     "e2e_tokens_per_s": round(b * steps / (sum(r["t_e2e"]) * 1e-3), 1),
                     "ms_per_step": round(statistics.mean(r["t_dev"]), 4),
                     "hbm_frac_algorithmic": round(stack.algorithmic_bytes_per_step(b)
                                                   / (statistics.mean(r["t_dev"]) * 1e-3) / 1e9
-                                                  / pk["hbm_gbs"], 5)}
+                                                  / pk["hbm_gbs"], 5),
+                    "clocks": sc.summary()}
             r = run_decode(mb, stack, DECODE_BATCH, steps, warmup, flush, device, seed=1,
                            mode="per_application")
             us_launch = kernel_only(mb, stack, DECODE_BATCH, max(steps, 10), device)
@@ -394,16 +460,17 @@ def run_ours(args, rank, world, local_rank):
                 "launches_per_step": r["launches_per_step"],
                 "bcsr_stream_kernel_us_per_launch": round(us_launch, 3),
                 "checksum": r["checksum"]}
-            extra["prefill_cloud"] = run_prefill(mb, device, pk, flush)
-            extra["prefill_cloud_blocks128"] = run_prefill_blocks128(mb, device, pk, flush)
-            extra["gemv_large_b1"] = run_gemv_large(mb, device, pk, flush)
+            prefill["roofline"] = tensor_roofline(prefill["useful_tflops"], pk, fp8)
+            extra["prefill_cloud"] = prefill
+            for name, fn in (("single_layer_c0", run_single_layer), ("prefill_cloud_blocks128", run_prefill_blocks128),
+                             ("sweep_c3", run_sweep), ("remoe_c4", run_remoe), ("gemv_large_b1", run_gemv_large)):
+                with ClockSampler(local_rank) as sc:
+                    extra[name] = fn(mb, device, pk, flush)
+                extra[name]["clocks"] = sc.summary()
             extra["router"] = run_router(mb, device)
-        if world == 1:
-            c = cpu_reference_decode(DECODE_BATCH, budget_s=12.0)
-            cpu = {"value": round(c["tokens_per_s"], 1), "unit": "tokens/s", "cores": c["cores"],
-                   "kind": "port",
-                   "sample": f"{c['steps']} decode steps of the same 42-application stack at batch "
-                             f"{DECODE_BATCH}, fp32 dense reconstruction + F.linear, best step"}
+        elif prefill is not None:
+            prefill["roofline"] = tensor_roofline(prefill["useful_tflops"], pk)
+            extra["prefill_cloud"] = prefill
     if rank != 0:
         return
     ms_per_step = tot_dev / steps
@@ -413,17 +480,16 @@ def run_ours(args, rank, world, local_rank):
         "warmup": warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16 planes x ternary, fp32 accumulate",
         "data": "synthetic",
-        "config": {"workload": "decode stack 3+6x6+3 (configs[1]): d_model 768, d_ff 2048, 12 "
-                               "ternary layers at 25% 16x16-tile density, 42 applications/token",
-                   "batch_per_gpu": DECODE_BATCH, "l2": "256 MiB flush between timed steps",
-                   "launch": "one persistent cluster launch per decode step", "parallelism": f"dp{world} (token shards, replicated weights, no collective)"},
+        "config": bench_config(world),
         "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": main["h2d"],
                 "d2h_bytes_per_step": main["d2h"]},
         "gpu_launches": main["launches_per_step"] * steps,
+        "launch": "one persistent cluster launch per decode step",
         "warm_l2_tokens_per_s": round(tokens / (tot_warm * 1e-3), 1),
         "clocks": clk.summary(),
         "roofline": roof,
         "cpu_baseline": cpu,
+        "parity_max_rel": parity,
         "checksum": main["checksum"],
         "device_error_word": main["device_error_word"],
     }
@@ -431,44 +497,81 @@ def run_ours(args, rank, world, local_rank):
     print(json.dumps(line), flush=True)
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one stack_decode_kernel launch at batch 64, from
-# the ncu capture summarised in profiles/stack_decode_kernel_decode_stack_b64.md
-TRAFFIC_BYTES_PER_LAUNCH = 6170368
+def profile_traffic(name: str):
+    """dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the line
+    `dram_bytes_per_launch: N` of the ncu summary committed under profiles/ (None if absent)."""
+    import re
+    try:
+        with open(os.path.join(ROOT, "profiles", name)) as f:
+            m = re.search(r"dram_bytes_per_launch:\s*(\d+)", f.read())
+        return int(m.group(1)) if m else None
+    except OSError:
+        return None
 
 
-def run_prefill(mb, device, pk, flush, tokens: int = PREFILL_TOKENS, reps: int = 3):
-    """Cloud-shape prefill (configs[2]): 16 layers, 72 applications, 16384 tokens per GPU,
-    bf16 with the reference's rounding points, through the tcgen05 / tensor-memory kernels.
-    Every application reads the same normalised token block (64 MB, plus a 176 MB hidden
-    block: larger than L2)."""
+def cloud_modules(mb, device, n_layers=None, mask="topk_l2", density=DENSITY):
     cfg = CLOUD
-    n_layers = cfg["prelude"] + cfg["core"] + cfg["coda"]
-    layers = [mb.synth.make_layer(cfg["d_model"], cfg["d_ff"], DENSITY, seed=cfg["seed0"] + i)
+    n_layers = n_layers or (cfg["prelude"] + cfg["core"] + cfg["coda"])
+    layers = [mb.synth.make_layer(cfg["d_model"], cfg["d_ff"], density, seed=cfg["seed0"] + i, mask=mask)
               for i in range(n_layers)]
-    gu = [L.gate_up.to_sched(True, device) for L in layers]
-    dn = [L.down.to_sched(False, device) for L in layers]
+    mods = [mb.SwiGLUMortar.from_matrices(L.gate_up, L.down, device=device) for L in layers]
+    return layers, mods
+
+
+def run_prefill(mb, device, pk, flush, tokens: int = PREFILL_TOKENS, reps: int = 3, seed: int = 7):
+    """Cloud-shape prefill (configs[2]): 16 layers, 72 applications, 16384 tokens per GPU, bf16 with
+    the reference's rounding points, through the MODULE forward (``SwiGLUMortar.__call__``, which
+    sends token blocks to the tcgen05 / tensor-memory kernels).  Every application reads the same
+    normalised token block (64 MB, plus a 176 MB hidden block: larger than L2).  `e2e`: the same
+    pass with the token block copied in from pinned host memory and the last application's output
+    copied back inside the timed window."""
+    cfg = CLOUD
+    layers, mods = cloud_modules(mb, device)
     order = site_order(cfg)
-    d, f = cfg["d_model"], cfg["d_ff"]
-    x = mb.synth.make_activations(tokens, d, seed=7).to(device)
-    y = torch.empty_like(x)
-    ws = torch.empty(tokens * f * 2 + 256, device=device, dtype=torch.uint8)
+    d = cfg["d_model"]
+    x0 = mb.synth.make_activations(tokens, d, seed=seed)
+    x = x0.to(device)
+    n0 = mb.ops.kernel_counts().get("prefill_panel", 0)
+    state = {}
 
     def fn():
         for i in order:
-            mb.ops.mlp_prefill_tc(x, gu[i], dn[i], out=y, workspace=ws)
-    t = time_steps(fn, reps, 1, flush)
-    ms = statistics.mean(t)
+            state["y"] = mods[i](x)
+    with torch.no_grad():
+        t = time_steps(fn, reps, 1, flush)
+        launches = (mb.ops.kernel_counts().get("prefill_panel", 0) - n0) // (reps + 1)
+        hx, hy = x0.clone().pin_memory(), torch.empty_like(x0).pin_memory()
+        te = time_steps(fn, max(reps - 1, 1), 0, flush, pre=lambda: x.copy_(hx, non_blocking=True),
+                        post=lambda: hy.copy_(state["y"], non_blocking=True))
+    ms, ms_e2e = statistics.mean(t), statistics.mean(te)
     err = mb.ops.prefill_error()
     flops = sum(2 * 256 * (layers[i].gate_up.nnz + layers[i].down.nnz) for i in order) * tokens
     tf = flops / (ms * 1e-3) / 1e12
     return {"tokens_per_s": round(tokens / (ms * 1e-3), 1), "ms_per_pass": round(ms, 3),
-            "applications": len(order), "tokens": tokens, "kernel": "prefill_panel_kernel (tcgen05)",
+            "e2e_ms_per_pass": round(ms_e2e, 3),
+            "e2e": {"value": round(tokens / (ms_e2e * 1e-3), 1), "unit": "tokens/s",
+                    "h2d_bytes_per_step": hx.numel() * 2, "d2h_bytes_per_step": hy.numel() * 2},
+            "applications": len(order), "tokens": tokens, "through": "SwiGLUMortar.forward",
+            "kernel": "prefill_panel_kernel (tcgen05)", "prefill_panel_launches_per_pass": launches,
             "useful_tflops": round(tf, 2), "dense_equivalent_tflops": round(tf / DENSITY, 2),
-            "roofline": {"bound": "tensor", "achieved": round(tf, 2),
-                         "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
-                         "frac": round(tf / pk["bf16_tflops_sustained"], 5),
-                         "peak_source": pk["source"] + " (bf16 sustained)"},
-            "device_error_word": err}
+            "checksum": float(hy.double().abs().sum()), "device_error_word": err}
+
+
+def run_single_layer(mb, device, pk, flush, reps: int = 5):
+    """configs[0]: one 768/2048 layer at 25%, 4 x 4096 bf16 tokens, through the module forward on
+    the GPU and through the reference's dense-reconstruction path on the host cores."""
+    d, f, tokens = LOCAL["d_model"], LOCAL["d_ff"], 4 * 4096
+    L = mb.synth.make_layer(d, f, DENSITY, seed=0)
+    mlp = mb.SwiGLUMortar.from_matrices(L.gate_up, L.down, device=device)
+    x = mb.synth.make_activations(tokens, d, seed=0).reshape(4, 4096, d).to(device)
+    with torch.no_grad():
+        t = time_steps(lambda: mlp(x), reps, 3, flush)
+    ms = statistics.median(t)
+    flops = 2 * 256 * (L.gate_up.nnz + L.down.nnz) * tokens
+    tf = flops / (ms * 1e-3) / 1e12
+    return {"tokens": tokens, "ms": round(ms, 4), "tokens_per_s": round(tokens / (ms * 1e-3), 1),
+            "useful_tflops": round(tf, 2), "roofline": tensor_roofline(tf, pk),
+            "cpu_reference_path": cpu_single_layer(tokens), "device_error_word": mb.ops.prefill_error()}
 
 
 def run_prefill_blocks128(mb, device, pk, flush, tokens: int = PREFILL_TOKENS, reps: int = 5):
@@ -480,17 +583,92 @@ def run_prefill_blocks128(mb, device, pk, flush, tokens: int = PREFILL_TOKENS, r
     d, f = CLOUD["d_model"], CLOUD["d_ff"]
     gu_m = mb.synth.make_block_matrix(2 * f, d, DENSITY, seed=11)
     dn_m = mb.synth.make_block_matrix(d, f, DENSITY, seed=12)
-    gu, dn = gu_m.to_sched(True, device), dn_m.to_sched(False, device)
+    mlp = mb.SwiGLUMortar.from_matrices(gu_m, dn_m, device=device)
     x = mb.synth.make_activations(tokens, d, seed=7).to(device)
-    y = torch.empty_like(x)
-    ws = torch.empty(tokens * f * 2 + 256, device=device, dtype=torch.uint8)
-    t = time_steps(lambda: mb.ops.mlp_prefill_tc(x, gu, dn, out=y, workspace=ws), reps, 2, flush)
+    with torch.no_grad():
+        t = time_steps(lambda: mlp(x), reps, 2, flush)
     ms = statistics.median(t)
     flops = 2 * 256 * (gu_m.nnz + dn_m.nnz) * tokens
     tf = flops / (ms * 1e-3) / 1e12
     return {"ms_per_application": round(ms, 3), "tokens": tokens, "useful_tflops": round(tf, 2),
-            "frac_of_measured_bf16_sustained": round(tf / pk["bf16_tflops_sustained"], 5),
-            "device_error_word": mb.ops.prefill_error()}
+            "roofline": tensor_roofline(tf, pk), "device_error_word": mb.ops.prefill_error()}
+
+
+def run_sweep(mb, device, pk, flush, tokens: int = 8192, reps: int = 3):
+    """configs[3]: one cloud-shape MLP, 8192 tokens, tile density 12.5 / 25 / 50 / 100% under the
+    uniform-random and the Zipf(1.2) row-clustered mask generators; load balance shows in max /
+    mean kept tiles per tile row."""
+    import numpy as np
+    d, f = CLOUD["d_model"], CLOUD["d_ff"]
+    x = mb.synth.make_activations(tokens, d, seed=3).to(device)
+    cells = {}
+    for mask in ("uniform", "zipf_rows"):
+        for rho in (0.125, 0.25, 0.5, 1.0):
+            L = mb.synth.make_layer(d, f, rho, seed=300, mask=mask)
+            mlp = mb.SwiGLUMortar.from_matrices(L.gate_up, L.down, device=device)
+            with torch.no_grad():
+                t = time_steps(lambda: mlp(x), reps, 1, flush)
+            ms = statistics.median(t)
+            tf = 2 * 256 * (L.gate_up.nnz + L.down.nnz) * tokens / (ms * 1e-3) / 1e12
+            cells[f"{mask}_{rho}"] = {"ms": round(ms, 3), "useful_tflops": round(tf, 1),
+                                      "frac_of_measured_bf16_sustained": round(tf / pk["bf16_tflops_sustained"], 4),
+                                      "dense_equivalent_tflops": round(tf / rho, 1),
+                                      "gate_up_tiles_per_row_max_mean": [int(np.diff(L.gate_up.row_ptr).max()),
+                                                                         round(float(np.diff(L.gate_up.row_ptr).mean()), 1)],
+                                      "down_tiles_per_row_max_mean": [int(np.diff(L.down.row_ptr).max()),
+                                                                      round(float(np.diff(L.down.row_ptr).mean()), 1)]}
+            del mlp
+    return {"tokens": tokens, "cells": cells, "device_error_word": mb.ops.prefill_error()}
+
+
+def run_remoe(mb, device, pk, flush, reps: int = 10):
+    """configs[4]: cloud shape at 25%, 352 groups of 16 hidden neurons, k = 88 (87 active per
+    token), 4096 tokens -- as 64-token decode batches (fp32 semantics; routed through the per-row
+    tile gather vs unrouted) and as one prefill (bf16; the tensor-memory kernel with the gate
+    multiply in its epilogue vs the gathered streaming kernel)."""
+    d, f, ncls, k, tokens = CLOUD["d_model"], CLOUD["d_ff"], 352, 88, 4096
+    L = mb.synth.make_layer(d, f, DENSITY, seed=200)
+    gu, dn = L.gate_up.to_stream(device), L.down.to_stream(device)
+    gs, ds = L.gate_up.to_sched(True, device), L.down.to_sched(False, device)
+    gates = mb.synth.make_gates(tokens, L, ncls, k, seed=6).to(device)
+    x32 = mb.synth.make_activations(tokens, d, seed=5, dtype=torch.float32).to(device)
+    xb = x32.to(torch.bfloat16)
+    out = {"tokens": tokens, "groups": ncls, "active_per_token": int((gates[0] > 0).sum())}
+    cnt, _ = mb.ops.route_gather(gates, f // ncls, f // 16)
+    listed = float(cnt.sum()) / (tokens * (f // 16))
+    # gate/up tile MMAs follow the lists; down runs every tile for every block of 8 rows
+    nnz_gu, nnz_dn = L.gate_up.nnz, L.down.nnz
+    out["pairs_listed_frac"] = round(listed, 4)
+    out["tile_mmas_skipped_frac_decode"] = round(1.0 - (nnz_gu * listed + nnz_dn) / (nnz_gu + nnz_dn), 4)
+    B = DECODE_BATCH
+    ws = torch.empty(mb._lib.lib().mortar_mlp_workspace_bytes(B, d, f, 3) + 256, device=device, dtype=torch.uint8)
+    y = torch.empty(B, d, device=device)
+    nb = tokens // B
+
+    def decode_all(routed):
+        for j in range(nb):
+            sl = slice(j * B, (j + 1) * B)
+            mb.ops.mlp_decode(x32[sl], gu, dn, gates=gates[sl] if routed else None, n_clusters=ncls if routed else 0,
+                              n_planes=3, out=y, workspace=ws)
+    for routed in (True, False):
+        g = capture(lambda: decode_all(routed))
+        t = time_steps(g.replay, reps, 3, flush)
+        ms = statistics.median(t)
+        out["decode_b64_routed" if routed else "decode_b64_unrouted"] = {
+            "ms_per_4096_tokens": round(ms, 3), "tokens_per_s": round(tokens / (ms * 1e-3), 1),
+            "us_per_batch": round(ms * 1e3 / nb, 2)}
+    h = torch.empty(tokens, d, device=device, dtype=torch.bfloat16)
+    wsp = torch.empty(max(tokens * f * 2, mb._lib.lib().mortar_mlp_workspace_bytes(tokens, d, f, 1)) + 256,
+                      device=device, dtype=torch.uint8)
+    for name, fn in (("prefill_tc_gate_multiply", lambda: mb.ops.mlp_prefill_tc(xb, gs, ds, gates=gates, n_clusters=ncls, out=h, workspace=wsp)),
+                     ("prefill_tc_unrouted", lambda: mb.ops.mlp_prefill_tc(xb, gs, ds, out=h, workspace=wsp)),
+                     ("prefill_stream_gathered", lambda: mb.ops.mlp_decode(xb, gu, dn, gates=gates, n_clusters=ncls, n_planes=1,
+                                                                        round_bf16=True, out=h, workspace=wsp))):
+        t = time_steps(fn, 3, 1, flush)
+        ms = statistics.median(t)
+        out[name] = {"ms": round(ms, 3), "tokens_per_s": round(tokens / (ms * 1e-3), 1)}
+    out["device_error_word"] = mb.ops.prefill_error()
+    return out
 
 
 def run_router(mb, device, reps: int = 20, calls: int = 16):
@@ -554,6 +732,9 @@ def run_gemv_large(mb, device, pk, flush, reps: int = 20, copies: int = 8):
 # ---------------------------------------------------------------------------------------
 
 def run_reference(args, rank, world):
+    """The reference's own CPU implementation of the path (its carved kernels are CUDA/Triton-only,
+    so its dense-reconstruction forward is its CPU path), restated by the oracle, on all host
+    cores; rank 0 only.  Does not import the product package or load its library."""
     if rank != 0:
         return
     steps, warmup = args.steps, max(args.warmup, 1)
@@ -564,9 +745,7 @@ def run_reference(args, rank, world):
         "value": round(c["tokens_per_s"], 1), "unit": "tokens/s", "n_gpus": world, "steps": steps,
         "warmup": warmup, "ms_per_step": round(c["ms_per_step"], 3), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "decode stack 3+6x6+3 (configs[1]): d_model 768, d_ff 2048, 12 "
-                               "ternary layers at 25% 16x16-tile density, 42 applications/token",
-                   "batch_per_gpu": DECODE_BATCH},
+        "config": bench_config(world),
         "cpu_baseline": {"value": round(c["tokens_per_s"], 1), "unit": "tokens/s", "cores": c["cores"],
                          "kind": "port",
                          "sample": f"{c['steps']} decode steps at batch {DECODE_BATCH}, dense "

@@ -164,3 +164,18 @@ def test_router_logits_and_gates_match_reference_router():
     gates = orc.remoe_gates(torch.from_numpy(g["router_logits"]), k).numpy()
     np.testing.assert_allclose(gates, g["router_gates"], rtol=1e-5, atol=1e-6)
     assert ((gates > 0).sum(axis=1) == k - 1).all()
+
+
+def test_oracle_workloads_equal_the_product_generator():
+    """The benchmark layers restated for the CPU baseline (which must not load the CUDA
+    library) are the very matrices the product's generator makes."""
+    import mortar_b200 as mb
+    from oracle import workloads as wl
+    for (d, f, seed) in ((768, 2048, 100), (256, 512, 7)):
+        L = mb.synth.make_layer(d, f, 0.25, seed=seed)
+        wg, wd, nnz = wl.dense_layer(d, f, 0.25, seed)
+        assert nnz == L.gate_up.nnz + L.down.nnz
+        for dense, m in ((wg, L.gate_up), (wd, L.down)):
+            ref = torch.from_numpy(m.to_dense_codes()).float() * torch.tensor(m.scale)
+            assert torch.equal(dense, ref)
+    assert torch.equal(wl.activations(5, 64, 3), mb.synth.make_activations(5, 64, 3))
