@@ -267,9 +267,10 @@ int mortar_mlp_decode_static(const mortar_stream *gate_up, const mortar_stream *
  * morph/model/hyper_connections.py:182-229), fp32 semantics as mortar_mlp_decode.
  * Each block of 8 activation rows is owned by one thread-block cluster that walks the whole
  * list by itself: the residual rows, their normalised planes and the hidden slice stay in
- * shared memory, CTAs exchange partial sums through distributed shared memory and meet at
- * cluster barriers (hardware, bounded by construction), and the weights of application i+1
- * stream into shared memory while application i computes.
+ * shared memory, CTAs push partial sums and new residual slices into each other's shared
+ * memory with bulk copies counted on the receiver's mbarrier (every wait is bounded and reports
+ * through `status`), and the weights of application i+1 stream into shared memory while
+ * application i computes.
  *
  * Weights come as per-(layer, cluster rank) blobs built on the host (16-byte aligned):
  *   int32 hdr[16] = { n_gate_up_groups, n_down_groups, byte offsets of gate_up grp_ptr,
@@ -288,7 +289,7 @@ int mortar_mlp_decode_static(const mortar_stream *gate_up, const mortar_stream *
  *   x            fp32 [rows][ldx] residual carrier, updated in place
  *   status       device int32, set non-zero if a bounded wait inside the kernel expires
  * Limits: cluster_size 8 (or 16 where the device accepts it), d_ff/16 divisible by cluster_size
- * and d_model by 4*cluster_size, everything of one application's rank share must fit shared memory
+ * and d_model by 16*cluster_size, everything of one application's rank share must fit shared memory
  * (MORTAR_ERR_CAPACITY otherwise: use mortar_mlp_decode per application). */
 int mortar_stack_decode(const void *blobs, const int32_t *blob_table, const int32_t *app_layer,
                         const float *rms_weights, int32_t n_apps, int32_t n_layers,

@@ -3,16 +3,21 @@
 // A cluster of CS CTAs owns one block of 8 activation rows and walks the whole list
 //     x <- x + down_i(silu(gate_i(n)) * up_i(n)),  n = rmsnorm_i(x)
 // by itself, so blocks of rows never synchronise with each other and nothing but the final
-// x leaves the SMs.  Inside a cluster, rank c owns hidden tile rows [cU,(c+1)U): it computes
-// that slice of the hidden layer for the 8 rows (gate and up rows of its slice), multiplies
-// it straight into the matching K-slice of the down projection (a partial sum over its slice
-// for every output), and the ranks combine the partial sums through distributed shared
-// memory in rank order (deterministic).  Two cluster barriers per application.  The weights
-// of rank c for application i+1 (one contiguous blob) stream into shared memory with a bulk
-// copy while application i computes.  Arithmetic is the streaming kernel's: ternary tile as
-// the A operand of mma.m16n8k16 decoded from 2-bit codes in registers, 8 activation rows as
-// exact bf16 planes as the B operand, fp32 accumulation, scale after the sum
-// (morph/kernels/triton/fused_decode_step.py:1441-1459).
+// x leaves the SMs.  Inside a cluster, rank c owns hidden tile rows [cU,(c+1)U) and output
+// columns [c*OC,(c+1)*OC): it computes its slice of the hidden layer for the 8 rows (gate and up
+// rows of its slice), multiplies it straight into the matching K-slice of the down projection (a
+// partial sum over its slice for every output), and PUSHES the partial sums of every rank's
+// output columns into that rank's shared memory with one bulk copy per rank (shared memory to
+// distributed shared memory, completion counted on the receiver's mbarrier).  Each rank adds the
+// CS blocks it received in rank order (deterministic), adds the residual, and pushes its new
+// slice of x -- with the slice's sum of squares, so the next RMSNorm needs no reduction pass --
+// to every rank the same way.  An application therefore costs two waits on LOCAL mbarriers and no
+// cluster-wide barrier; a rank only ever waits for data it is about to read.  The weights of rank
+// c for application i+1 (one contiguous blob) stream into shared memory with a bulk copy while
+// application i computes.  Arithmetic is the streaming kernel's: ternary tile as the A operand of
+// mma.m16n8k16 decoded from 2-bit codes in registers, 8 activation rows as exact bf16 planes as
+// the B operand (one accumulator per plane, so the MMAs of a tile are independent), fp32
+// accumulation, scale after the sum (morph/kernels/triton/fused_decode_step.py:1441-1459).
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <cooperative_groups.h>
@@ -70,7 +75,30 @@ __device__ __forceinline__ void lds_bfrag(uint32_t addr, uint32_t &b0, uint32_t 
 
 // All groups of one tile row of a stream-format matrix held in shared memory, against the 8
 // staged activation rows.  Everything is addressed in the shared window (32-bit addresses):
-// act[pl] = address of plane pl, this lane's row (lane>>2), element 2*(lane&3).
+// act[pl] = address of plane pl, this lane's row (lane>>2), element 2*(lane&3).  Every plane has
+// its own accumulator (independent MMAs); a group whose last slot is a real tile has no padding
+// and runs without per-slot tests, so its loads and MMAs interleave freely.
+template <int P, bool CHECK>
+__device__ __forceinline__ void tile_group(const uint4 cw, const uint4 cl, const uint32_t (&act)[P],
+                                           float (&accp)[P][4]) {
+    const uint32_t cws[4] = {cw.x, cw.y, cw.z, cw.w};
+    const uint32_t cls[4] = {cl.x, cl.y, cl.z, cl.w};
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+        const uint32_t col = (s & 1) ? (cls[s >> 1] >> 16) : (cls[s >> 1] & 0xffffu);
+        if (!CHECK || col != 0xffffu) {                         // padding slots end a row
+            uint32_t af[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) af[i] = mortar_decode_pair(cws[s >> 1], (s & 1) * 4 + i);
+            uint32_t b0[P], b1[P];
+#pragma unroll
+            for (int pl = 0; pl < P; ++pl) lds_bfrag(act[pl] + col * 32u, b0[pl], b1[pl]);
+#pragma unroll
+            for (int pl = 0; pl < P; ++pl) mma_16816(accp[pl], af, b0[pl], b1[pl]);
+        }
+    }
+}
+
 template <int P>
 __device__ __forceinline__ void tile_row(uint32_t grp_ptr, uint32_t cols, uint32_t codes, int trow,
                                          const uint32_t (&act)[P], int lane, float (&acc)[4]) {
@@ -78,25 +106,23 @@ __device__ __forceinline__ void tile_row(uint32_t grp_ptr, uint32_t cols, uint32
     asm volatile("ld.shared.u32 %0, [%2];\n\tld.shared.u32 %1, [%2+4];\n" : "=r"(gbeg), "=r"(gend) : "r"(grp_ptr + 4u * trow));
     uint32_t caddr = codes + (uint32_t)(gbeg * 32 + lane) * 16u;
     uint32_t laddr = cols + (uint32_t)gbeg * 16u;
+    float accp[P][4];
+#pragma unroll
+    for (int pl = 0; pl < P; ++pl)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) accp[pl][i] = 0.f;
     for (int grp = gbeg; grp < gend; ++grp, caddr += 512u, laddr += 16u) {
         const uint4 cw = lds128(caddr);
         const uint4 cl = lds128(laddr);
-        const uint32_t cws[4] = {cw.x, cw.y, cw.z, cw.w};
-        const uint32_t cls[4] = {cl.x, cl.y, cl.z, cl.w};
+        if ((cl.w >> 16) != 0xffffu) tile_group<P, false>(cw, cl, act, accp);
+        else tile_group<P, true>(cw, cl, act, accp);
+    }
 #pragma unroll
-        for (int s = 0; s < 8; ++s) {
-            const uint32_t col = (s & 1) ? (cls[s >> 1] >> 16) : (cls[s >> 1] & 0xffffu);
-            if (col != 0xffffu) {                               // padding slots end a row
-                uint32_t af[4];
+    for (int i = 0; i < 4; ++i) {
+        float v = accp[0][i];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) af[i] = mortar_decode_pair(cws[s >> 1], (s & 1) * 4 + i);
-                uint32_t b0[P], b1[P];
-#pragma unroll
-                for (int pl = 0; pl < P; ++pl) lds_bfrag(act[pl] + col * 32u, b0[pl], b1[pl]);
-#pragma unroll
-                for (int pl = 0; pl < P; ++pl) mma_16816(acc, af, b0[pl], b1[pl]);
-            }
-        }
+        for (int pl = 1; pl < P; ++pl) v += accp[pl][i];
+        acc[i] += v;
     }
 }
 
@@ -111,27 +137,46 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 
 struct SmemLayout {
-    int xs, xp, hp, gu, xnew, wbuf, bars, total;   // byte offsets
+    int xs, xp, hp, gu, recv, xsend, wbuf, bars, total;   // byte offsets
 };
 
 __host__ __device__ inline int align_up_i(int v, int a) { return (v + a - 1) / a * a; }
+
+// xs holds the residual rows rank-major: block q = [8 rows][OC columns] of rank q's output columns
+// followed by the 8 sums of squares of those row slices -- the unit one rank pushes to its peers.
+__host__ __device__ inline int xs_block_floats(int d_model, int cs) { return 8 * (d_model / cs) + 8; }
 
 __host__ __device__ inline SmemLayout smem_layout(int d_model, int d_ff, int cs, int n_planes, int x_pitch,
                                                   int h_pitch, int max_blob) {
     SmemLayout L;
     int off = 0;
-    L.xs = off; off += 8 * d_model * 4;
-    L.xp = off;                                   // planes of the normalised rows; reused for the partial sums
-    const int xp_bytes = n_planes * 8 * x_pitch * 2, ypart_bytes = 8 * d_model * 4;
-    off += align_up_i(xp_bytes > ypart_bytes ? xp_bytes : ypart_bytes, 16);
+    L.xs = off; off += cs * xs_block_floats(d_model, cs) * 4;
+    L.xp = off;                                   // planes of the normalised rows; reused for the outgoing partial sums
+    const int xp_bytes = n_planes * 8 * x_pitch * 2, ysend_bytes = 8 * d_model * 4;
+    off += align_up_i(xp_bytes > ysend_bytes ? xp_bytes : ysend_bytes, 16);
     L.hp = off; off += align_up_i(n_planes * 8 * h_pitch * 2, 16);
-    L.gu = off; off += 8 * 2 * (d_ff / cs) * 4;       // gate and up sums of the hidden slice, fp32
-    L.xnew = off; off += 2 * 8 * (d_model / cs) * 4;
+    L.gu = off;                                   // gate and up sums of the hidden slice, fp32: only when a rank has
+    if (d_ff / 16 / cs < kWarps) off += 8 * 2 * (d_ff / cs) * 4;   // fewer hidden tile rows than warps
+    L.recv = off; off += 8 * d_model * 4;             // partial sums of this rank's columns, one block per source rank
+    L.xsend = off; off += xs_block_floats(d_model, cs) * 4;
     off = align_up_i(off, 128);
     L.wbuf = off; off += 2 * max_blob;
-    L.bars = off; off += 16;
+    L.bars = off; off += 32;
     L.total = off;
     return L;
+}
+
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t local_addr, int rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(local_addr), "r"(rank));
+    return r;
+}
+
+// shared memory of this CTA -> shared memory of a CTA of the cluster; the bytes are counted on
+// the RECEIVER's mbarrier (both destination addresses are cluster addresses of the same CTA)
+__device__ __forceinline__ void push_bulk(uint32_t dst_cluster, uint32_t src_local, uint32_t bytes, uint32_t bar_cluster) {
+    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                 ::"r"(dst_cluster), "r"(src_local), "r"(bytes), "r"(bar_cluster) : "memory");
 }
 
 template <int P>
@@ -143,20 +188,24 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
     const SmemLayout L = smem_layout(p.d_model, p.d_ff, cs, p.n_planes, p.x_pitch, p.h_pitch, p.max_blob);
     float *xs = reinterpret_cast<float *>(smem + L.xs);
     __nv_bfloat16 *xp = reinterpret_cast<__nv_bfloat16 *>(smem + L.xp);
-    float *ypart = reinterpret_cast<float *>(smem + L.xp);
+    float *ysend = reinterpret_cast<float *>(smem + L.xp);
     __nv_bfloat16 *hp = reinterpret_cast<__nv_bfloat16 *>(smem + L.hp);
     float *gu_out = reinterpret_cast<float *>(smem + L.gu);
-    float *xnew = reinterpret_cast<float *>(smem + L.xnew);
+    float *recv = reinterpret_cast<float *>(smem + L.recv);
+    float *xsend = reinterpret_cast<float *>(smem + L.xsend);
     uint8_t *wbuf = smem + L.wbuf;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + L.bars);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + L.bars);     // [0], [1]: weights; [2]: partial sums; [3]: x slices
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int row0 = (int)(blockIdx.x / cs) * 8;                 // this cluster's block of rows
     const int D = p.d_model, OC = D / cs;                         // output columns owned by a rank
     const int U = p.d_ff / 16 / cs;                               // hidden tile rows owned by a rank
-    const int RD = D / 16;
+    const int RD = D / 16, TR = OC / 16;                          // output tile rows: all, per rank
     const int xplane_w = 8 * p.x_pitch / 2, hplane_w = 8 * p.h_pitch / 2;
+    const int blk = xs_block_floats(D, cs);
+    const uint32_t part_bytes = (uint32_t)(8 * OC * 4), blk_bytes = (uint32_t)(blk * 4);
+    const uint32_t pbar = smem_u32(&bars[2]), xbar = smem_u32(&bars[3]);
 
     auto prefetch = [&](int app, int buf) {
         // one bulk copy of this rank's blob for application `app` into weight buffer `buf`
@@ -170,41 +219,52 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
             ::"r"(smem_u32(wbuf + (size_t)buf * p.max_blob)), "l"(p.blobs + (size_t)ent[0] * 16), "r"(bytes), "r"(bar)
             : "memory");
     };
+    auto expect = [&](uint32_t bar, uint32_t bytes) {
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+    };
+    // Bounded wait on a local mbarrier phase.  On expiry the status word is set and the walk goes
+    // on (with undefined numbers): every rank still sends what its peers wait for and reaches the
+    // final cluster barrier.
+    auto wait = [&](uint32_t bar, uint32_t parity) {
+        for (uint32_t i = 0; i < kWaitLimit; ++i)
+            if (mbar_try_wait(bar, parity)) return;
+        if (lane == 0) atomicExch(p.status, 1);
+    };
 
     // Both weight buffers start as zeros: a blob of zeros describes tile rows without groups, so if
-    // a copy should ever fail to arrive (the bounded wait below reports it) the walk over the
+    // a copy should ever fail to arrive (the bounded wait reports it) the walk over the
     // buffer stays inside it instead of following uninitialised offsets.
     for (int i = threadIdx.x; i < 2 * p.max_blob / 16; i += kThreads)
         reinterpret_cast<uint4 *>(wbuf)[i] = make_uint4(0u, 0u, 0u, 0u);
+    // this rank's slice of the residual rows (rows past the batch are zero) and its sums of squares
+    for (int e = threadIdx.x; e < 8 * OC; e += kThreads) {
+        const int r = e / OC, cl = e - r * OC;
+        xsend[e] = (row0 + r < p.rows) ? p.x[(long long)(row0 + r) * p.ldx + rank * OC + cl] : 0.f;
+    }
     __syncthreads();
+    if (warp < 8) {
+        float ss = 0.f;
+        for (int cl = lane; cl < OC; cl += 32) { const float v = xsend[warp * OC + cl]; ss += v * v; }
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) xsend[8 * OC + warp] = ss;
+    }
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic writes before the bulk copies read them
     if (threadIdx.x == 0) {
-        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // zeros before the bulk copy's writes
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_u32(&bars[0])));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_u32(&bars[1])));
+        for (int i = 0; i < 4; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_u32(&bars[i])));
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        expect(pbar, part_bytes * cs);                             // phase 0 of both exchange barriers
+        expect(xbar, blk_bytes * cs);
         if (p.n_apps > 0) prefetch(0, 0);
     }
-    // residual rows of this block -> shared memory (rows past the batch stay zero)
-    for (int i = threadIdx.x; i < 8 * D / 4; i += kThreads) {
-        const int r = i / (D / 4), c = (i % (D / 4)) * 4;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (row0 + r < p.rows) v = *reinterpret_cast<const float4 *>(p.x + (long long)(row0 + r) * p.ldx + c);
-        *reinterpret_cast<float4 *>(xs + r * D + c) = v;
-    }
     __syncthreads();
-    cluster.sync();          // every CTA of the cluster is resident before any remote access
+    cluster.sync();          // every CTA of the cluster is resident, its barriers armed, before any push
+    if (warp == 0 && lane < cs)
+        push_bulk(map_to_rank(smem_u32(xs + rank * blk), lane), smem_u32(xsend), blk_bytes, map_to_rank(xbar, lane));
 
     for (int a = 0; a < p.n_apps; ++a) {
         const int buf = a & 1;
         // ---- weights of this application (prefetched); start the next application's copy ----
-        {
-            const uint32_t bar = smem_u32(&bars[buf]);
-            const uint32_t parity = (a >> 1) & 1;
-            bool ok = false;
-            for (uint32_t i = 0; i < kWaitLimit; ++i)
-                if (mbar_try_wait(bar, parity)) { ok = true; break; }
-            if (!ok && threadIdx.x == 0) atomicExch(p.status, 1);     // keep going: no barrier may be skipped
-        }
+        wait(smem_u32(&bars[buf]), (a >> 1) & 1);
         if (threadIdx.x == 0 && a + 1 < p.n_apps) prefetch(a + 1, buf ^ 1);
         const uint8_t *blob = wbuf + (size_t)buf * p.max_blob;
         const int *hdr = reinterpret_cast<const int *>(blob);
@@ -217,25 +277,37 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
         const float *rms_w = hdr[11] ? reinterpret_cast<const float *>(blob + hdr[11])
                                      : (p.rms != nullptr ? p.rms + (size_t)p.app_layer[a] * D : nullptr);
 
-        // ---- n = rmsnorm(x) as exact bf16 planes (warp i stages row i) ----
+        // this thread's norm weights, requested before the wait so their latency hides behind it
+        // (they come from global memory unless the blob carries a copy)
+        constexpr int kWPre = 4;
+        float4 wpre[kWPre];
+        if (rms_w != nullptr) {
+#pragma unroll
+            for (int k = 0; k < kWPre; ++k) {
+                const int c = (warp & 1) * 128 + lane * 4 + k * 256;
+                if (c < D) wpre[k] = *reinterpret_cast<const float4 *>(rms_w + c);
+            }
+        }
+
+        // ---- the residual rows (every rank's slice) have arrived; arm the barrier's next phase ----
+        wait(xbar, a & 1);
+        if (threadIdx.x == 0) expect(xbar, blk_bytes * cs);
+
+        // ---- n = rmsnorm(x) as exact bf16 planes (two warps per row) ----
         {
-            const int row = warp >> 1, half = warp & 1;          // two warps per row
-            const float *xr = xs + row * D;
+            const int row = warp >> 1, half = warp & 1;
             float inv = 1.f;
             if (rms_w != nullptr) {
                 float ss = 0.f;
-                for (int c = lane * 4; c < D; c += 128) {
-                    const float4 v = *reinterpret_cast<const float4 *>(xr + c);
-                    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-                }
-                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                for (int q = 0; q < cs; ++q) ss += xs[q * blk + 8 * OC + row];      // rank order: same sum in every rank
                 inv = 1.f / sqrtf(ss / (float)D + p.eps);
             }
-            for (int c = half * 128 + lane * 4; c < D; c += 256) {
-                const float4 v = *reinterpret_cast<const float4 *>(xr + c);
+            const float inv_oc = 1.f / (float)OC;
+            auto plane_split = [&](int c, const float4 wv) {
+                const int q = (int)(((float)c + 0.5f) * inv_oc);                   // c / OC for these small integers
+                const float4 v = *reinterpret_cast<const float4 *>(xs + q * blk + row * OC + (c - q * OC));
                 float vv[4] = {v.x, v.y, v.z, v.w};
                 if (rms_w != nullptr) {
-                    const float4 wv = *reinterpret_cast<const float4 *>(rms_w + c);
                     vv[0] = (vv[0] * inv) * wv.x; vv[1] = (vv[1] * inv) * wv.y;
                     vv[2] = (vv[2] * inv) * wv.z; vv[3] = (vv[3] * inv) * wv.w;
                 }
@@ -249,7 +321,14 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
                     *reinterpret_cast<uint2 *>(xp + (size_t)pl * 8 * p.x_pitch + row * p.x_pitch + c) =
                         *reinterpret_cast<uint2 *>(h);
                 }
+            };
+#pragma unroll
+            for (int k = 0; k < kWPre; ++k) {
+                const int c = half * 128 + lane * 4 + k * 256;
+                if (c < D) plane_split(c, wpre[k]);
             }
+            for (int c = half * 128 + lane * 4 + kWPre * 256; c < D; c += 256)
+                plane_split(c, rms_w != nullptr ? *reinterpret_cast<const float4 *>(rms_w + c) : make_float4(1.f, 1.f, 1.f, 1.f));
         }
         __syncthreads();
 
@@ -307,7 +386,8 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
         }
         __syncthreads();
 
-        // ---- partial down projection over this rank's hidden slice, for every output ----
+        // ---- partial down projection over this rank's hidden slice, for every output; the sums of
+        //      output tile row trow go to the block of the rank that owns those columns ----
         {
             uint32_t act[P];
 #pragma unroll
@@ -316,55 +396,50 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
             for (int trow = warp; trow < RD; trow += kWarps) {
                 float acc[4] = {0.f, 0.f, 0.f, 0.f};
                 tile_row<P>(dn_ptr, dn_cols, dn_codes, trow, act, lane, acc);
+                const int q = trow / TR, cl0 = (trow - q * TR) * 16;
+                float *dst = ysend + (size_t)q * 8 * OC + cl0;
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
-                    ypart[(2 * t + (i & 1)) * D + trow * 16 + g + 8 * (i >> 1)] = scale_dn * acc[i];
+                    dst[(2 * t + (i & 1)) * OC + g + 8 * (i >> 1)] = scale_dn * acc[i];
             }
         }
-        cluster.sync();      // all partial sums of the cluster are in place
-
-        // ---- combine: this rank owns output columns [rank*OC, (rank+1)*OC) ----
-        // All remote loads of an element are issued before the first add; the adds stay in
-        // rank order.
-        {
-            float *mine = xnew + (size_t)buf * 8 * OC;
-            const int r = warp >> 1;                             // two warps per activation row
-            for (int cl = (warp & 1) * 32 + lane; cl < OC; cl += 64) {
-                const int c = rank * OC + cl;
-                float part[16];
-#pragma unroll
-                for (int q = 0; q < 16; ++q)
-                    if (q < 8 || cs == 16) part[q] = cluster.map_shared_rank(ypart, q)[r * D + c];
-                float v = xs[r * D + c];
-#pragma unroll
-                for (int q = 0; q < 16; ++q)
-                    if (q < 8 || cs == 16) v += part[q];                 // rank order
-                mine[r * OC + cl] = v;
-            }
-        }
-        cluster.sync();      // new residual slices published; partial sums no longer needed
-
-        // ---- gather the new residual rows from all ranks ----
-        {
-            const int r = warp >> 1;                             // two warps per activation row
-            const float inv_oc = 1.f / (float)OC;
-#pragma unroll 3
-            for (int c4 = (warp & 1) * 32 + lane; c4 < D / 4; c4 += 64) {
-                const int c = c4 * 4;
-                const int q = (int)(((float)c + 0.5f) * inv_oc);          // c / OC for these small integers
-                const float *src = cluster.map_shared_rank(xnew, q) + (size_t)buf * 8 * OC + r * OC + (c - q * OC);
-                *reinterpret_cast<float4 *>(xs + r * D + c) = *reinterpret_cast<const float4 *>(src);
-            }
-        }
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
         __syncthreads();
+        if (warp == 0 && lane < cs)
+            push_bulk(map_to_rank(smem_u32(recv + (size_t)rank * 8 * OC), lane), smem_u32(ysend + (size_t)lane * 8 * OC),
+                      part_bytes, map_to_rank(pbar, lane));
+
+        // ---- the partial sums of this rank's columns have arrived from every rank ----
+        wait(pbar, a & 1);
+        if (threadIdx.x == 0) expect(pbar, part_bytes * cs);
+        // new residual slice = old slice + partial sums in rank order; one warp per row
+        if (warp < 8) {
+            const int r = warp;
+            float ss = 0.f;
+            for (int cl = lane; cl < OC; cl += 32) {
+                float v = xs[rank * blk + r * OC + cl];
+                for (int q = 0; q < cs; ++q) v += recv[((size_t)q * 8 + r) * OC + cl];
+                xsend[r * OC + cl] = v;
+                ss += v * v;
+            }
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (lane == 0) xsend[8 * OC + r] = ss;
+        }
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        __syncthreads();
+        if (warp == 0 && lane < cs)
+            push_bulk(map_to_rank(smem_u32(xs + rank * blk), lane), smem_u32(xsend), blk_bytes, map_to_rank(xbar, lane));
     }
 
-    // this rank writes its column slice of the final rows
+    // this rank writes its column slice of the final rows (its own latest slice)
     for (int e = threadIdx.x; e < 8 * OC; e += kThreads) {
-        const int r = e / OC, c = rank * OC + e % OC;
-        if (row0 + r < p.rows) p.x[(long long)(row0 + r) * p.ldx + c] = xs[r * D + c];
+        const int r = e / OC, cl = e - r * OC;
+        if (row0 + r < p.rows) p.x[(long long)(row0 + r) * p.ldx + rank * OC + cl] = xsend[e];
     }
-    cluster.sync();          // no CTA leaves while a peer may still read its shared memory
+    // every slice pushed to this CTA has landed before it may exit; after the cluster barrier no
+    // peer still reads this CTA's shared memory either
+    wait(xbar, p.n_apps & 1);
+    cluster.sync();
 }
 
 inline int pitch_for(int features) {
@@ -388,7 +463,7 @@ extern "C" int mortar_stack_decode(const void *blobs, const int32_t *blob_table,
     if (n_apps < 0 || d_model <= 0 || d_ff <= 0 || d_model % 16 || d_ff % 16 || rows < 0 || ldx < d_model)
         return MORTAR_ERR_SHAPE;
     if (cluster_size != 8 && cluster_size != 16) return MORTAR_ERR_SHAPE;
-    if ((d_ff / 16) % cluster_size || d_model % (4 * cluster_size)) return MORTAR_ERR_SHAPE;
+    if ((d_ff / 16) % cluster_size || d_model % (16 * cluster_size)) return MORTAR_ERR_SHAPE;
     if (n_planes < 1 || n_planes > 3) return MORTAR_ERR_DTYPE;
     if ((reinterpret_cast<uintptr_t>(blobs) % 16) || (reinterpret_cast<uintptr_t>(x) % 16) || (ldx % 4) ||
         (max_blob_bytes % 128))
@@ -407,7 +482,7 @@ extern "C" int mortar_stack_decode(const void *blobs, const int32_t *blob_table,
     if (smem_optin[dev] == 0) {
         int v = 0;
         MORTAR_CUDA_CHECK(cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
-        v -= 1024;                                     // room for static shared variables
+        v -= 256;                                      // room for the kernel's few static shared bytes
         void (*kernels[3])(const StackParams) = {stack_decode_kernel<1>, stack_decode_kernel<2>, stack_decode_kernel<3>};
         for (auto k : kernels) {
             MORTAR_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, v));

@@ -282,13 +282,14 @@ def mlp_decode_static(x: torch.Tensor, gate_up: StreamMatrix, down: StreamMatrix
 class _StackBlobs:
     """Per-(layer, cluster rank) weight blobs of a stack for one cluster size."""
 
-    def __init__(self, layers, d_model, d_ff, cs, device):
+    def __init__(self, layers, d_model, d_ff, cs, device, embed_norm_weights):
         import numpy as np
         F_ = d_ff // TILE
         U = F_ // cs
         blobs, table, off = [], np.zeros((len(layers), cs, 2), dtype=np.int32), 0
         for li, (gu, dn, w) in enumerate(layers):
-            wb = b"" if w is None else w.detach().float().cpu().numpy().astype(np.float32).tobytes()
+            wb = b"" if (w is None or not embed_norm_weights) else \
+                w.detach().float().cpu().numpy().astype(np.float32).tobytes()
             for c in range(cs):
                 rows = list(range(c * U, (c + 1) * U)) + list(range(F_ + c * U, F_ + (c + 1) * U))
                 parts = []
@@ -337,12 +338,19 @@ class DecodeStack:
             if (gu.in_features, gu.out_features // 2) != (self.d_model, self.d_ff) or \
                     (dn.in_features, dn.out_features) != (self.d_ff, self.d_model):
                 raise ValueError("every application of a stack must have the same d_model and d_ff")
+        # norm weights: one [n_layers, d_model] array the kernel reads per application; only when
+        # some layers have a weight and others none do the blobs carry their own copies instead
+        have = [w is not None for _, _, w in layers]
+        self.rms_weights = None
+        if all(have):
+            self.rms_weights = torch.stack([w.detach().float().cpu() for _, _, w in layers]).contiguous().to(device)
+        embed = any(have) and not all(have)
         self.variants = {}
         for cs in cluster_sizes:
-            if (self.d_ff // TILE) % cs == 0 and self.d_model % (4 * cs) == 0:
-                self.variants[cs] = _StackBlobs(layers, self.d_model, self.d_ff, cs, device)
+            if (self.d_ff // TILE) % cs == 0 and self.d_model % (TILE * cs) == 0:
+                self.variants[cs] = _StackBlobs(layers, self.d_model, self.d_ff, cs, device, embed)
         if not self.variants:
-            raise ValueError("d_ff/16 and d_model/4 must be divisible by the cluster size (8 or 16)")
+            raise ValueError("d_ff/16 and d_model/16 must be divisible by the cluster size (8 or 16)")
         self.app_layer = torch.tensor(self.order, dtype=torch.int32, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.n_apps, self.n_layers = len(self.order), len(layers)
@@ -371,7 +379,7 @@ def stack_decode(x: torch.Tensor, stack: DecodeStack, *, eps: float = 1e-6, n_pl
     rows = x.shape[0]
     v = stack.variants[cluster_size] if cluster_size else stack.pick(rows)
     _lib.check(_lib.lib().mortar_stack_decode(
-        _ptr(v.blobs), _ptr(v.table), _ptr(stack.app_layer), None, stack.n_apps, stack.n_layers,
+        _ptr(v.blobs), _ptr(v.table), _ptr(stack.app_layer), _ptr(stack.rms_weights), stack.n_apps, stack.n_layers,
         stack.d_model, stack.d_ff, v.max_blob, v.cs, _ptr(x), x.stride(0), rows,
         float(eps), int(n_planes), _ptr(stack.status), _stream_ptr()), "mortar_stack_decode")
     _count("stack_decode")
