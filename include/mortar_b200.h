@@ -272,19 +272,20 @@ int mortar_mlp_decode_static(const mortar_stream *gate_up, const mortar_stream *
  * through `status`), and the weights of application i+1 stream into shared memory while
  * application i computes.
  *
- * Weights come as per-(layer, cluster rank) blobs built on the host (16-byte aligned):
- *   int32 hdr[16] = { n_gate_up_groups, n_down_groups, byte offsets of gate_up grp_ptr,
- *                     grp_cols, grp_codes, down grp_ptr, grp_cols, grp_codes,
- *                     gate_up scale bits, down scale bits, blob bytes,
- *                     byte offset of an fp32[d_model] rmsnorm weight inside the blob or 0, 0... }
- * where rank c's gate_up part is the stream layout of gate tile rows [cU,(c+1)U) followed by
- * the matching up tile rows (U = d_ff/16/cluster_size) and its down part is the stream layout
- * of all output tile rows restricted to hidden tile columns [cU,(c+1)U) (column indices local).
+ * Weights come per (layer, cluster rank) in two parts built on the host (16-byte aligned), each
+ *   int32 hdr[8] = { n_groups, byte offsets of grp_ptr, grp_cols, grp_codes, scale bits, part
+ *                    bytes, byte offset of an fp32[d_model] rmsnorm weight inside the part or 0, 0 }
+ * followed by the arrays: rank c's gate/up part is the stream layout of gate tile rows [cU,(c+1)U)
+ * followed by the matching up tile rows (U = d_ff/16/cluster_size); its down part is the stream
+ * layout of all output tile rows restricted to hidden tile columns [cU,(c+1)U) (column indices
+ * local).  A part's shared-memory buffer is refilled for the next application as soon as its
+ * stage is over.
  *   blobs        device bytes
- *   blob_table   device int32 [n_layers][cluster_size][2] = {offset in 16-byte units, bytes}
+ *   blob_table   device int32 [n_layers][cluster_size][4] = {gate/up part offset in 16-byte
+ *                units, bytes, down part offset in 16-byte units, bytes}
  *   app_layer    device int32 [n_apps] layer of every application
  *   rms_weights  device fp32 [n_layers][d_model] (16-byte aligned), or NULL.  A layer whose blobs
- *                carry their own copy of the weight (hdr[11] != 0) uses that copy; otherwise row
+ *                carry their own copy of the weight (hdr[6] != 0) uses that copy; otherwise row
  *                `layer` of this array; with neither the application runs without normalisation
  *   x            fp32 [rows][ldx] residual carrier, updated in place
  *   status       device int32, set non-zero if a bounded wait inside the kernel expires
@@ -293,7 +294,8 @@ int mortar_mlp_decode_static(const mortar_stream *gate_up, const mortar_stream *
  * (MORTAR_ERR_CAPACITY otherwise: use mortar_mlp_decode per application). */
 int mortar_stack_decode(const void *blobs, const int32_t *blob_table, const int32_t *app_layer,
                         const float *rms_weights, int32_t n_apps, int32_t n_layers,
-                        int32_t d_model, int32_t d_ff, int32_t max_blob_bytes, int32_t cluster_size,
+                        int32_t d_model, int32_t d_ff, int32_t max_gate_up_bytes,
+                        int32_t max_down_bytes, int32_t cluster_size,
                         float *x, int64_t ldx, int64_t rows, float eps, int32_t n_planes,
                         int32_t *status, void *stream);
 

@@ -71,7 +71,7 @@ _SIGNATURES = {
     "mortar_mlp_decode_static": (C.c_int, [C.POINTER(Stream), C.POINTER(Stream), _vp, C.c_int, _i64, _i64,
                                            _vp, _f32, _vp, _i64, _i32, _vp, C.c_int, _i64, _i32, _i32,
                                            _vp]),
-    "mortar_stack_decode": (C.c_int, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _i64, _i64,
+    "mortar_stack_decode": (C.c_int, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _i64, _i64,
                                       _f32, _i32, _vp, _vp]),
     "mortar_sched_sizes": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp]),
     "mortar_build_sched": (C.c_int, [_vp, _vp, _vp, _i32, _i32, _i64, _i32, _vp, _vp, _vp, _vp, _vp]),

@@ -31,12 +31,13 @@ namespace cg = cooperative_groups;
 namespace {
 
 constexpr int kWarps = 16;
+constexpr int kWarpsPerRow = kWarps / 8;      // warps that share one of the 8 activation rows in the elementwise passes
 constexpr int kThreads = kWarps * 32;
 constexpr uint32_t kWaitLimit = 1u << 22;
 
 struct StackParams {
     const uint8_t *blobs;
-    const int *blob_table;         // [n_layers][CS][2]
+    const int *blob_table;         // [n_layers][CS][4]: gate/up part offset (16-byte units), bytes; down part offset, bytes
     const int *app_layer;          // [n_apps]
     const float *rms;              // [n_layers][d_model] or nullptr
     int n_apps;
@@ -49,7 +50,7 @@ struct StackParams {
     int n_planes;
     int *status;
     int x_pitch, h_pitch;          // shared-memory row pitch of the plane buffers (bf16 elements)
-    int max_blob;                  // bytes reserved per weight buffer
+    int max_a, max_b;              // bytes reserved for the gate/up part and for the down part of a rank's weights
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -83,10 +84,29 @@ __device__ __forceinline__ void tile_group(const uint4 cw, const uint4 cl, const
                                            float (&accp)[P][4]) {
     const uint32_t cws[4] = {cw.x, cw.y, cw.z, cw.w};
     const uint32_t cls[4] = {cl.x, cl.y, cl.z, cl.w};
+    if (!CHECK) {
+        // all activation fragments of the group first (their latencies overlap), then the arithmetic
+        uint32_t b0[8][P], b1[8][P];
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            const uint32_t col = (s & 1) ? (cls[s >> 1] >> 16) : (cls[s >> 1] & 0xffffu);
+#pragma unroll
+            for (int pl = 0; pl < P; ++pl) lds_bfrag(act[pl] + col * 32u, b0[s][pl], b1[s][pl]);
+        }
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            uint32_t af[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) af[i] = mortar_decode_pair(cws[s >> 1], (s & 1) * 4 + i);
+#pragma unroll
+            for (int pl = 0; pl < P; ++pl) mma_16816(accp[pl], af, b0[s][pl], b1[s][pl]);
+        }
+        return;
+    }
 #pragma unroll
     for (int s = 0; s < 8; ++s) {
         const uint32_t col = (s & 1) ? (cls[s >> 1] >> 16) : (cls[s >> 1] & 0xffffu);
-        if (!CHECK || col != 0xffffu) {                         // padding slots end a row
+        if (col != 0xffffu) {                                   // padding slots end a row
             uint32_t af[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) af[i] = mortar_decode_pair(cws[s >> 1], (s & 1) * 4 + i);
@@ -136,6 +156,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// Per-phase cycle accounting for profiling builds (-DMORTAR_STACK_TIMING): thread 0 of CTA 0 sums the
+// cycles between the phase boundaries of every application into g_stack_ticks.
+#ifdef MORTAR_STACK_TIMING
+__device__ unsigned long long g_stack_ticks[16];
+#define ST_DECL long long st_prev = clock64()
+#define ST_ACC(i) do { if (blockIdx.x == 0 && threadIdx.x == 0) { const long long n_ = clock64(); \
+        atomicAdd(&g_stack_ticks[i], (unsigned long long)(n_ - st_prev)); st_prev = n_; } } while (0)
+#else
+#define ST_DECL
+#define ST_ACC(i)
+#endif
+
 struct SmemLayout {
     int xs, xp, hp, gu, recv, xsend, wbuf, bars, total;   // byte offsets
 };
@@ -147,20 +179,20 @@ __host__ __device__ inline int align_up_i(int v, int a) { return (v + a - 1) / a
 __host__ __device__ inline int xs_block_floats(int d_model, int cs) { return 8 * (d_model / cs) + 8; }
 
 __host__ __device__ inline SmemLayout smem_layout(int d_model, int d_ff, int cs, int n_planes, int x_pitch,
-                                                  int h_pitch, int max_blob) {
+                                                  int h_pitch, int max_a, int max_b) {
     SmemLayout L;
     int off = 0;
     L.xs = off; off += cs * xs_block_floats(d_model, cs) * 4;
     L.xp = off;                                   // planes of the normalised rows; reused for the outgoing partial sums
-    const int xp_bytes = n_planes * 8 * x_pitch * 2, ysend_bytes = 8 * d_model * 4;
+    const int xp_bytes = n_planes * 8 * x_pitch * 2, ysend_bytes = cs * 8 * (d_model / cs + 4) * 4;
     off += align_up_i(xp_bytes > ysend_bytes ? xp_bytes : ysend_bytes, 16);
     L.hp = off; off += align_up_i(n_planes * 8 * h_pitch * 2, 16);
     L.gu = off;                                   // gate and up sums of the hidden slice, fp32: only when a rank has
     if (d_ff / 16 / cs < kWarps) off += 8 * 2 * (d_ff / cs) * 4;   // fewer hidden tile rows than warps
-    L.recv = off; off += 8 * d_model * 4;             // partial sums of this rank's columns, one block per source rank
+    L.recv = off; off += cs * 8 * (d_model / cs + 4) * 4;   // partial sums of this rank's columns, one block per source rank
     L.xsend = off; off += xs_block_floats(d_model, cs) * 4;
     off = align_up_i(off, 128);
-    L.wbuf = off; off += 2 * max_blob;
+    L.wbuf = off; off += max_a + max_b;           // one buffer per part: a part is refilled as soon as its stage is over
     L.bars = off; off += 32;
     L.total = off;
     return L;
@@ -185,7 +217,7 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = (int)cluster.block_rank();
     const int cs = p.cs;
-    const SmemLayout L = smem_layout(p.d_model, p.d_ff, cs, p.n_planes, p.x_pitch, p.h_pitch, p.max_blob);
+    const SmemLayout L = smem_layout(p.d_model, p.d_ff, cs, p.n_planes, p.x_pitch, p.h_pitch, p.max_a, p.max_b);
     float *xs = reinterpret_cast<float *>(smem + L.xs);
     __nv_bfloat16 *xp = reinterpret_cast<__nv_bfloat16 *>(smem + L.xp);
     float *ysend = reinterpret_cast<float *>(smem + L.xp);
@@ -194,7 +226,7 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
     float *recv = reinterpret_cast<float *>(smem + L.recv);
     float *xsend = reinterpret_cast<float *>(smem + L.xsend);
     uint8_t *wbuf = smem + L.wbuf;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + L.bars);     // [0], [1]: weights; [2]: partial sums; [3]: x slices
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + L.bars);     // [0]: gate/up weights, [1]: down weights; [2]: partial sums; [3]: x slices
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -204,19 +236,22 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
     const int RD = D / 16, TR = OC / 16;                          // output tile rows: all, per rank
     const int xplane_w = 8 * p.x_pitch / 2, hplane_w = 8 * p.h_pitch / 2;
     const int blk = xs_block_floats(D, cs);
-    const uint32_t part_bytes = (uint32_t)(8 * OC * 4), blk_bytes = (uint32_t)(blk * 4);
+    // partial-sum blocks use a row pitch of OC + 4 floats: the four row pairs a warp stores at once
+    // then fall into different banks
+    const int OCP = OC + 4;
+    const uint32_t part_bytes = (uint32_t)(8 * OCP * 4), blk_bytes = (uint32_t)(blk * 4);
     const uint32_t pbar = smem_u32(&bars[2]), xbar = smem_u32(&bars[3]);
 
-    auto prefetch = [&](int app, int buf) {
-        // one bulk copy of this rank's blob for application `app` into weight buffer `buf`
+    auto prefetch = [&](int app, int part) {
+        // one bulk copy of part `part` (0 = gate/up, 1 = down) of this rank's weights for application `app`
         const int layer = p.app_layer[app];
-        const int *ent = p.blob_table + ((long long)layer * cs + rank) * 2;
+        const int *ent = p.blob_table + ((long long)layer * cs + rank) * 4 + part * 2;
         const uint32_t bytes = (uint32_t)ent[1];
-        const uint32_t bar = smem_u32(&bars[buf]);
+        const uint32_t bar = smem_u32(&bars[part]);
         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
         asm volatile(
             "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
-            ::"r"(smem_u32(wbuf + (size_t)buf * p.max_blob)), "l"(p.blobs + (size_t)ent[0] * 16), "r"(bytes), "r"(bar)
+            ::"r"(smem_u32(wbuf + (part ? p.max_a : 0))), "l"(p.blobs + (size_t)ent[0] * 16), "r"(bytes), "r"(bar)
             : "memory");
     };
     auto expect = [&](uint32_t bar, uint32_t bytes) {
@@ -234,7 +269,7 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
     // Both weight buffers start as zeros: a blob of zeros describes tile rows without groups, so if
     // a copy should ever fail to arrive (the bounded wait reports it) the walk over the
     // buffer stays inside it instead of following uninitialised offsets.
-    for (int i = threadIdx.x; i < 2 * p.max_blob / 16; i += kThreads)
+    for (int i = threadIdx.x; i < (p.max_a + p.max_b) / 16; i += kThreads)
         reinterpret_cast<uint4 *>(wbuf)[i] = make_uint4(0u, 0u, 0u, 0u);
     // this rank's slice of the residual rows (rows past the batch are zero) and its sums of squares
     for (int e = threadIdx.x; e < 8 * OC; e += kThreads) {
@@ -254,37 +289,40 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         expect(pbar, part_bytes * cs);                             // phase 0 of both exchange barriers
         expect(xbar, blk_bytes * cs);
-        if (p.n_apps > 0) prefetch(0, 0);
+        if (p.n_apps > 0) { prefetch(0, 0); prefetch(0, 1); }
     }
     __syncthreads();
     cluster.sync();          // every CTA of the cluster is resident, its barriers armed, before any push
     if (warp == 0 && lane < cs)
         push_bulk(map_to_rank(smem_u32(xs + rank * blk), lane), smem_u32(xsend), blk_bytes, map_to_rank(xbar, lane));
 
+    ST_DECL;
     for (int a = 0; a < p.n_apps; ++a) {
-        const int buf = a & 1;
-        // ---- weights of this application (prefetched); start the next application's copy ----
-        wait(smem_u32(&bars[buf]), (a >> 1) & 1);
-        if (threadIdx.x == 0 && a + 1 < p.n_apps) prefetch(a + 1, buf ^ 1);
-        const uint8_t *blob = wbuf + (size_t)buf * p.max_blob;
-        const int *hdr = reinterpret_cast<const int *>(blob);
-        const uint32_t blob_s = smem_u32(blob);
-        const uint32_t gu_ptr = blob_s + hdr[2], gu_cols = blob_s + hdr[3], gu_codes = blob_s + hdr[4];
-        const uint32_t dn_ptr = blob_s + hdr[5], dn_cols = blob_s + hdr[6], dn_codes = blob_s + hdr[7];
-        const float scale_gu = __int_as_float(hdr[8]), scale_dn = __int_as_float(hdr[9]);
-        // rmsnorm weight of this application: the copy inside the blob when the packer put one
-        // there (hdr[11]), else the caller's [n_layers][d_model] array, else no normalisation
-        const float *rms_w = hdr[11] ? reinterpret_cast<const float *>(blob + hdr[11])
-                                     : (p.rms != nullptr ? p.rms + (size_t)p.app_layer[a] * D : nullptr);
+        ST_ACC(0);
+        // ---- gate/up weights of this application (requested when the previous application's
+        //      gate/up stage ended) ----
+        wait(smem_u32(&bars[0]), a & 1);
+        ST_ACC(1);
+        // part header: int32 {n_groups, offsets of grp_ptr, grp_cols, grp_codes, scale bits, bytes,
+        // offset of an fp32[d_model] rmsnorm weight or 0, 0}
+        const uint8_t *part_a = wbuf, *part_b = wbuf + p.max_a;
+        const int *ha = reinterpret_cast<const int *>(part_a);
+        const uint32_t gu_ptr = smem_u32(part_a) + ha[1], gu_cols = smem_u32(part_a) + ha[2], gu_codes = smem_u32(part_a) + ha[3];
+        const float scale_gu = __int_as_float(ha[4]);
+        // rmsnorm weight of this application: the copy inside the weights when the packer put one
+        // there, else the caller's [n_layers][d_model] array, else no normalisation
+        const float *rms_w = ha[6] ? reinterpret_cast<const float *>(part_a + ha[6])
+                                   : (p.rms != nullptr ? p.rms + (size_t)p.app_layer[a] * D : nullptr);
 
         // this thread's norm weights, requested before the wait so their latency hides behind it
         // (they come from global memory unless the blob carries a copy)
-        constexpr int kWPre = 4;
+        constexpr int kWPre = 2;
+        constexpr int kRowStep = kWarpsPerRow * 128;             // columns one sweep of a row's warps covers
         float4 wpre[kWPre];
         if (rms_w != nullptr) {
 #pragma unroll
             for (int k = 0; k < kWPre; ++k) {
-                const int c = (warp & 1) * 128 + lane * 4 + k * 256;
+                const int c = (warp % kWarpsPerRow) * 128 + lane * 4 + k * kRowStep;
                 if (c < D) wpre[k] = *reinterpret_cast<const float4 *>(rms_w + c);
             }
         }
@@ -292,10 +330,11 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
         // ---- the residual rows (every rank's slice) have arrived; arm the barrier's next phase ----
         wait(xbar, a & 1);
         if (threadIdx.x == 0) expect(xbar, blk_bytes * cs);
+        ST_ACC(2);
 
-        // ---- n = rmsnorm(x) as exact bf16 planes (two warps per row) ----
+        // ---- n = rmsnorm(x) as exact bf16 planes (kWarpsPerRow warps per row) ----
         {
-            const int row = warp >> 1, half = warp & 1;
+            const int row = warp / kWarpsPerRow, half = warp % kWarpsPerRow;
             float inv = 1.f;
             if (rms_w != nullptr) {
                 float ss = 0.f;
@@ -312,25 +351,27 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
                     vv[2] = (vv[2] * inv) * wv.z; vv[3] = (vv[3] * inv) * wv.w;
                 }
                 for (int pl = 0; pl < P; ++pl) {
-                    __nv_bfloat16 h[4];
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        h[k] = __float2bfloat16_rn(vv[k]);
-                        vv[k] -= __bfloat162float(h[k]);
-                    }
-                    *reinterpret_cast<uint2 *>(xp + (size_t)pl * 8 * p.x_pitch + row * p.x_pitch + c) =
-                        *reinterpret_cast<uint2 *>(h);
+                    // packed conversions (two values per instruction, off the conversion unit)
+                    const __nv_bfloat162 h01 = __floats2bfloat162_rn(vv[0], vv[1]);
+                    const __nv_bfloat162 h23 = __floats2bfloat162_rn(vv[2], vv[3]);
+                    vv[0] -= __low2float(h01); vv[1] -= __high2float(h01);
+                    vv[2] -= __low2float(h23); vv[3] -= __high2float(h23);
+                    uint2 packed;
+                    packed.x = *reinterpret_cast<const uint32_t *>(&h01);
+                    packed.y = *reinterpret_cast<const uint32_t *>(&h23);
+                    *reinterpret_cast<uint2 *>(xp + (size_t)pl * 8 * p.x_pitch + row * p.x_pitch + c) = packed;
                 }
             };
 #pragma unroll
             for (int k = 0; k < kWPre; ++k) {
-                const int c = half * 128 + lane * 4 + k * 256;
+                const int c = half * 128 + lane * 4 + k * kRowStep;
                 if (c < D) plane_split(c, wpre[k]);
             }
-            for (int c = half * 128 + lane * 4 + kWPre * 256; c < D; c += 256)
+            for (int c = half * 128 + lane * 4 + kWPre * kRowStep; c < D; c += kRowStep)
                 plane_split(c, rms_w != nullptr ? *reinterpret_cast<const float4 *>(rms_w + c) : make_float4(1.f, 1.f, 1.f, 1.f));
         }
         __syncthreads();
+        ST_ACC(3);
 
         // ---- hidden slice: gate and up sums of this rank's 2U tile rows, one row per warp turn ----
         {
@@ -348,15 +389,20 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
                     tile_row<P>(gu_ptr, gu_cols, gu_codes, hrow, act, lane, ag);
                     tile_row<P>(gu_ptr, gu_cols, gu_codes, U + hrow, act, lane, au);
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {                // (neuron g + 8*(i>>1), row 2t + (i&1))
-                        const float gv = scale_gu * ag[i], uv = scale_gu * au[i];
-                        float hv = gv * (1.f / (1.f + expf(-gv))) * uv;
-                        __nv_bfloat16 *o = hp + (2 * t + (i & 1)) * p.h_pitch + hrow * 16 + g + 8 * (i >> 1);
+                    for (int i = 0; i < 4; i += 2) {             // (neuron g + 8*(i>>1), rows 2t and 2t+1)
+                        float hv[2];
+#pragma unroll
+                        for (int k = 0; k < 2; ++k) {
+                            const float gv = scale_gu * ag[i + k], uv = scale_gu * au[i + k];
+                            hv[k] = gv * __fdividef(1.f, 1.f + __expf(-gv)) * uv;
+                        }
+                        __nv_bfloat16 *o = hp + (2 * t) * p.h_pitch + hrow * 16 + g + 8 * (i >> 1);
 #pragma unroll
                         for (int pl = 0; pl < P; ++pl) {
-                            const __nv_bfloat16 hb = __float2bfloat16_rn(hv);
-                            o[(size_t)pl * 8 * p.h_pitch] = hb;
-                            hv -= __bfloat162float(hb);
+                            const __nv_bfloat162 hb = __floats2bfloat162_rn(hv[0], hv[1]);
+                            o[(size_t)pl * 8 * p.h_pitch] = __low2bfloat16(hb);
+                            o[(size_t)pl * 8 * p.h_pitch + p.h_pitch] = __high2bfloat16(hb);
+                            hv[0] -= __low2float(hb); hv[1] -= __high2float(hb);
                         }
                     }
                 }
@@ -370,10 +416,10 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
                 }
                 __syncthreads();
                 // silu(gate) * up -> exact bf16 planes of the hidden slice
-                const int r = warp >> 1;                         // two warps per activation row
-                for (int c = (warp & 1) * 32 + lane; c < HW; c += 64) {
+                const int r = warp / kWarpsPerRow;               // kWarpsPerRow warps per activation row
+                for (int c = (warp % kWarpsPerRow) * 32 + lane; c < HW; c += kWarpsPerRow * 32) {
                     const float gv = gu_out[r * W + c], uv = gu_out[r * W + HW + c];
-                    float hv = gv * (1.f / (1.f + expf(-gv))) * uv;
+                    float hv = gv * __fdividef(1.f, 1.f + __expf(-gv)) * uv;
                     __nv_bfloat16 *o = hp + r * p.h_pitch + c;
 #pragma unroll
                     for (int pl = 0; pl < P; ++pl) {
@@ -385,6 +431,12 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
             }
         }
         __syncthreads();
+        if (threadIdx.x == 0 && a + 1 < p.n_apps) prefetch(a + 1, 0);     // the gate/up buffer is free again
+        wait(smem_u32(&bars[1]), a & 1);                                    // down weights of this application
+        const int *hb = reinterpret_cast<const int *>(part_b);
+        const uint32_t dn_ptr = smem_u32(part_b) + hb[1], dn_cols = smem_u32(part_b) + hb[2], dn_codes = smem_u32(part_b) + hb[3];
+        const float scale_dn = __int_as_float(hb[4]);
+        ST_ACC(4);
 
         // ---- partial down projection over this rank's hidden slice, for every output; the sums of
         //      output tile row trow go to the block of the rank that owns those columns ----
@@ -397,20 +449,23 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
                 float acc[4] = {0.f, 0.f, 0.f, 0.f};
                 tile_row<P>(dn_ptr, dn_cols, dn_codes, trow, act, lane, acc);
                 const int q = trow / TR, cl0 = (trow - q * TR) * 16;
-                float *dst = ysend + (size_t)q * 8 * OC + cl0;
+                float *dst = ysend + (size_t)q * 8 * OCP + cl0;
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
-                    dst[(2 * t + (i & 1)) * OC + g + 8 * (i >> 1)] = scale_dn * acc[i];
+                    dst[(2 * t + (i & 1)) * OCP + g + 8 * (i >> 1)] = scale_dn * acc[i];
             }
         }
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
         __syncthreads();
         if (warp == 0 && lane < cs)
-            push_bulk(map_to_rank(smem_u32(recv + (size_t)rank * 8 * OC), lane), smem_u32(ysend + (size_t)lane * 8 * OC),
+            push_bulk(map_to_rank(smem_u32(recv + (size_t)rank * 8 * OCP), lane), smem_u32(ysend + (size_t)lane * 8 * OCP),
                       part_bytes, map_to_rank(pbar, lane));
+        if (threadIdx.x == 32 && a + 1 < p.n_apps) prefetch(a + 1, 1);    // the down buffer is free again
 
+        ST_ACC(5);
         // ---- the partial sums of this rank's columns have arrived from every rank ----
         wait(pbar, a & 1);
+        ST_ACC(6);
         if (threadIdx.x == 0) expect(pbar, part_bytes * cs);
         // new residual slice = old slice + partial sums in rank order; one warp per row
         if (warp < 8) {
@@ -418,7 +473,7 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
             float ss = 0.f;
             for (int cl = lane; cl < OC; cl += 32) {
                 float v = xs[rank * blk + r * OC + cl];
-                for (int q = 0; q < cs; ++q) v += recv[((size_t)q * 8 + r) * OC + cl];
+                for (int q = 0; q < cs; ++q) v += recv[((size_t)q * 8 + r) * OCP + cl];
                 xsend[r * OC + cl] = v;
                 ss += v * v;
             }
@@ -429,6 +484,7 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
         __syncthreads();
         if (warp == 0 && lane < cs)
             push_bulk(map_to_rank(smem_u32(xs + rank * blk), lane), smem_u32(xsend), blk_bytes, map_to_rank(xbar, lane));
+        ST_ACC(7);
     }
 
     // this rank writes its column slice of the final rows (its own latest slice)
@@ -452,9 +508,18 @@ inline int pitch_for(int features) {
 
 }  // namespace
 
+#ifdef MORTAR_STACK_TIMING
+extern "C" int mortar_stack_ticks(unsigned long long *out) {
+    MORTAR_CUDA_CHECK(cudaMemcpyFromSymbol(out, g_stack_ticks, sizeof(unsigned long long) * 16));
+    static const unsigned long long zeros[16] = {0};
+    MORTAR_CUDA_CHECK(cudaMemcpyToSymbol(g_stack_ticks, zeros, sizeof(zeros)));
+    return MORTAR_OK;
+}
+#endif
+
 extern "C" int mortar_stack_decode(const void *blobs, const int32_t *blob_table, const int32_t *app_layer,
                                    const float *rms_weights, int32_t n_apps, int32_t n_layers,
-                                   int32_t d_model, int32_t d_ff, int32_t max_blob_bytes,
+                                   int32_t d_model, int32_t d_ff, int32_t max_gate_up_bytes, int32_t max_down_bytes,
                                    int32_t cluster_size, float *x, int64_t ldx, int64_t rows, float eps,
                                    int32_t n_planes, int32_t *status, void *stream) {
     if (!blobs || !blob_table || !app_layer || !x || !status) return MORTAR_ERR_NULL;
@@ -466,7 +531,7 @@ extern "C" int mortar_stack_decode(const void *blobs, const int32_t *blob_table,
     if ((d_ff / 16) % cluster_size || d_model % (16 * cluster_size)) return MORTAR_ERR_SHAPE;
     if (n_planes < 1 || n_planes > 3) return MORTAR_ERR_DTYPE;
     if ((reinterpret_cast<uintptr_t>(blobs) % 16) || (reinterpret_cast<uintptr_t>(x) % 16) || (ldx % 4) ||
-        (max_blob_bytes % 128))
+        (max_gate_up_bytes % 128) || (max_down_bytes % 128) || max_gate_up_bytes < 128 || max_down_bytes < 128)
         return MORTAR_ERR_ALIGN;
     if (rows == 0 || n_apps == 0) return MORTAR_OK;
     if (rows > 8 * 65535LL / cluster_size) return MORTAR_ERR_CAPACITY;
@@ -499,8 +564,8 @@ extern "C" int mortar_stack_decode(const void *blobs, const int32_t *blob_table,
     p.x = x; p.ldx = ldx; p.rows = (int)rows; p.eps = eps; p.n_planes = n_planes; p.status = status;
     p.x_pitch = pitch_for(d_model);
     p.h_pitch = pitch_for(d_ff / cluster_size);
-    p.max_blob = max_blob_bytes;
-    const SmemLayout L = smem_layout(d_model, d_ff, cluster_size, n_planes, p.x_pitch, p.h_pitch, max_blob_bytes);
+    p.max_a = max_gate_up_bytes; p.max_b = max_down_bytes;
+    const SmemLayout L = smem_layout(d_model, d_ff, cluster_size, n_planes, p.x_pitch, p.h_pitch, max_gate_up_bytes, max_down_bytes);
     if (L.total > smem_limit) return MORTAR_ERR_CAPACITY;   // a rank's share does not fit shared memory
 
     cudaLaunchConfig_t cfg = {};

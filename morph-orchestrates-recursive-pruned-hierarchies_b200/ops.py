@@ -280,43 +280,49 @@ def mlp_decode_static(x: torch.Tensor, gate_up: StreamMatrix, down: StreamMatrix
 
 
 class _StackBlobs:
-    """Per-(layer, cluster rank) weight blobs of a stack for one cluster size."""
+    """Per-(layer, cluster rank) weights of a stack for one cluster size, in two parts per rank:
+    the stream layout of the rank's gate/up tile rows, and the stream layout of the matching
+    K-slice of the down projection.  Each part = int32[8] header {n_groups, byte offsets of
+    grp_ptr, grp_cols, grp_codes, scale bits, part bytes, byte offset of an fp32[d_model] norm
+    weight or 0, 0} followed by the arrays (16-byte aligned)."""
 
     def __init__(self, layers, d_model, d_ff, cs, device, embed_norm_weights):
         import numpy as np
         F_ = d_ff // TILE
         U = F_ // cs
-        blobs, table, off = [], np.zeros((len(layers), cs, 2), dtype=np.int32), 0
+        blobs, table, off = [], np.zeros((len(layers), cs, 4), dtype=np.int32), 0
         for li, (gu, dn, w) in enumerate(layers):
             wb = b"" if (w is None or not embed_norm_weights) else \
                 w.detach().float().cpu().numpy().astype(np.float32).tobytes()
             for c in range(cs):
                 rows = list(range(c * U, (c + 1) * U)) + list(range(F_ + c * U, F_ + (c + 1) * U))
-                parts = []
-                for sub in (gu.slice_tile_rows(rows), dn.slice_tile_cols(c * U, (c + 1) * U)):
+                subs = (gu.slice_tile_rows(rows), dn.slice_tile_cols(c * U, (c + 1) * U))
+                for part, sub in enumerate(subs):
                     gp, gc, gcd, G = sub.build_stream_host()
-                    parts.append((G, gp.tobytes(), gc[:max(G, 1) * 8].tobytes(), gcd[:max(G, 1) * 512].tobytes()))
-                hdr = np.zeros(16, dtype=np.int32)
-                body, pos = [], 64
-                for k, raw in enumerate([parts[0][1], parts[0][2], parts[0][3], parts[1][1], parts[1][2],
-                                         parts[1][3], wb]):
-                    if k == 6:
-                        hdr[11] = pos if raw else 0
-                    else:
-                        hdr[2 + k] = pos
-                    pad = (-len(raw)) % 16
-                    body.append(raw + b"\0" * pad)
-                    pos += len(raw) + pad
-                hdr[0], hdr[1] = parts[0][0], parts[1][0]
-                hdr[8] = np.float32(gu.scale).view(np.int32)
-                hdr[9] = np.float32(dn.scale).view(np.int32)
-                hdr[10] = pos
-                blob = hdr.tobytes() + b"".join(body)
-                table[li, c] = (off // 16, len(blob))
-                blobs.append(blob)
-                off += len(blob)
+                    arrays = [gp.tobytes(), gc[:max(G, 1) * 8].tobytes(), gcd[:max(G, 1) * 512].tobytes()]
+                    if part == 0:
+                        arrays.append(wb)
+                    hdr = np.zeros(8, dtype=np.int32)
+                    body, pos = [], 32
+                    for k, raw in enumerate(arrays):
+                        if k < 3:
+                            hdr[1 + k] = pos
+                        else:
+                            hdr[6] = pos if raw else 0
+                        pad = (-len(raw)) % 16
+                        body.append(raw + b"\0" * pad)
+                        pos += len(raw) + pad
+                    hdr[0] = G
+                    hdr[4] = np.float32(sub.scale).view(np.int32)
+                    hdr[5] = pos
+                    blob = hdr.tobytes() + b"".join(body)
+                    table[li, c, 2 * part] = off // 16
+                    table[li, c, 2 * part + 1] = len(blob)
+                    blobs.append(blob)
+                    off += len(blob)
         self.cs = cs
-        self.max_blob = (int(table[:, :, 1].max()) + 127) // 128 * 128
+        self.max_a = (int(table[:, :, 1].max()) + 127) // 128 * 128
+        self.max_b = (int(table[:, :, 3].max()) + 127) // 128 * 128
         self.blobs = torch.from_numpy(np.frombuffer(b"".join(blobs), dtype=np.uint8).copy()).to(device)
         self.table = torch.from_numpy(table.reshape(-1)).to(device)
 
@@ -380,7 +386,7 @@ def stack_decode(x: torch.Tensor, stack: DecodeStack, *, eps: float = 1e-6, n_pl
     v = stack.variants[cluster_size] if cluster_size else stack.pick(rows)
     _lib.check(_lib.lib().mortar_stack_decode(
         _ptr(v.blobs), _ptr(v.table), _ptr(stack.app_layer), _ptr(stack.rms_weights), stack.n_apps, stack.n_layers,
-        stack.d_model, stack.d_ff, v.max_blob, v.cs, _ptr(x), x.stride(0), rows,
+        stack.d_model, stack.d_ff, v.max_a, v.max_b, v.cs, _ptr(x), x.stride(0), rows,
         float(eps), int(n_planes), _ptr(stack.status), _stream_ptr()), "mortar_stack_decode")
     _count("stack_decode")
     return x
@@ -388,8 +394,8 @@ def stack_decode(x: torch.Tensor, stack: DecodeStack, *, eps: float = 1e-6, n_pl
 
 def stack_decode_raw(x: torch.Tensor, blobs: torch.Tensor, blob_table: torch.Tensor, app_layer: torch.Tensor,
                      rms_weights: Optional[torch.Tensor], status: torch.Tensor, n_layers: int, d_model: int,
-                     d_ff: int, max_blob_bytes: int, cluster_size: int, eps: float = 1e-6,
-                     n_planes: int = 3) -> torch.Tensor:
+                     d_ff: int, max_gate_up_bytes: int, max_down_bytes: int, cluster_size: int,
+                     eps: float = 1e-6, n_planes: int = 3) -> torch.Tensor:
     """``mortar_stack_decode`` on raw tensors (what ``DecodeStack`` holds): in place on x
     [rows, d_model] fp32.  ``rms_weights`` [n_layers, d_model] fp32 serves layers whose blobs do
     not carry their own norm weight."""
@@ -401,7 +407,8 @@ def stack_decode_raw(x: torch.Tensor, blobs: torch.Tensor, blob_table: torch.Ten
         raise ValueError("rms_weights must be contiguous float32 [n_layers, d_model]")
     _lib.check(_lib.lib().mortar_stack_decode(
         _ptr(blobs), _ptr(blob_table), _ptr(app_layer), _ptr(rms_weights), int(app_layer.numel()),
-        int(n_layers), int(d_model), int(d_ff), int(max_blob_bytes), int(cluster_size), _ptr(x), x.stride(0),
+        int(n_layers), int(d_model), int(d_ff), int(max_gate_up_bytes), int(max_down_bytes), int(cluster_size),
+        _ptr(x), x.stride(0),
         x.shape[0], float(eps), int(n_planes), _ptr(status), _stream_ptr()), "mortar_stack_decode")
     _count("stack_decode")
     return x

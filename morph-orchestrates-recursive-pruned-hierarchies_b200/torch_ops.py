@@ -191,16 +191,17 @@ def mlp_prefill_tc_args(gu: SchedMatrix, dn: SchedMatrix):
 @torch.library.custom_op(f"{_LIB}::stack_decode", mutates_args=("x", "status"), device_types="cuda")
 def stack_decode(x: torch.Tensor, blobs: torch.Tensor, blob_table: torch.Tensor, app_layer: torch.Tensor,
                  rms_weights: Optional[torch.Tensor], status: torch.Tensor, n_layers: int, d_model: int,
-                 d_ff: int, max_blob_bytes: int, cluster_size: int, eps: float, n_planes: int) -> None:
+                 d_ff: int, max_gate_up_bytes: int, max_down_bytes: int, cluster_size: int, eps: float,
+                 n_planes: int) -> None:
     """x <- x + MLP_i(rmsnorm_i(x)) for every application listed in ``app_layer``, one launch
     (``ops.stack_decode`` on raw tensors; ``ops.DecodeStack`` builds them)."""
     ops.stack_decode_raw(x, blobs, blob_table, app_layer, rms_weights, status, n_layers, d_model, d_ff,
-                         max_blob_bytes, cluster_size, eps, n_planes)
+                         max_gate_up_bytes, max_down_bytes, cluster_size, eps, n_planes)
 
 
 @stack_decode.register_fake
-def _(x, blobs, blob_table, app_layer, rms_weights, status, n_layers, d_model, d_ff, max_blob_bytes,
-      cluster_size, eps, n_planes):
+def _(x, blobs, blob_table, app_layer, rms_weights, status, n_layers, d_model, d_ff, max_gate_up_bytes,
+      max_down_bytes, cluster_size, eps, n_planes):
     return None
 
 

@@ -143,7 +143,7 @@ def test_stack_decode_takes_norm_weights_as_an_argument(full_stack):
     x0 = mb.synth.make_activations(13, 768, seed=5, dtype=torch.float32) * 1.7
     w = torch.stack(rms[:3]).to(DEV).contiguous()
     x = x0.clone().to(DEV)
-    mb.ops.stack_decode_raw(x, v.blobs, v.table, bare.app_layer, w, bare.status, 3, 768, 2048, v.max_blob, 8)
+    mb.ops.stack_decode_raw(x, v.blobs, v.table, bare.app_layer, w, bare.status, 3, 768, 2048, v.max_a, v.max_b, 8)
     assert bare.error() == 0
     ref = x0.clone()
     for i in [0, 1, 2, 1]:
@@ -151,7 +151,7 @@ def test_stack_decode_takes_norm_weights_as_an_argument(full_stack):
     assert float((x.cpu() - ref).abs().max()) / float(ref.abs().max()) <= 1e-5
     # without weights: no normalisation
     x = x0.clone().to(DEV)
-    mb.ops.stack_decode_raw(x, v.blobs, v.table, bare.app_layer, None, bare.status, 3, 768, 2048, v.max_blob, 8)
+    mb.ops.stack_decode_raw(x, v.blobs, v.table, bare.app_layer, None, bare.status, 3, 768, 2048, v.max_a, v.max_b, 8)
     ref = x0.clone()
     for i in [0, 1, 2, 1]:
         ref = ref + orc.swiglu_mlp(ref, dense[i][0], dense[i][1])
@@ -159,7 +159,7 @@ def test_stack_decode_takes_norm_weights_as_an_argument(full_stack):
     # the registered operator runs the same launch in place
     x = x0.clone().to(DEV)
     torch.ops.mortar_b200.stack_decode(x, v.blobs, v.table, bare.app_layer, None, bare.status, 3, 768, 2048,
-                                       v.max_blob, 8, 1e-6, 3)
+                                       v.max_a, v.max_b, 8, 1e-6, 3)
     assert float((x.cpu() - ref).abs().max()) / float(ref.abs().max()) <= 1e-5
 
 
