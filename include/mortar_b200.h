@@ -71,6 +71,10 @@ typedef struct mortar_stream {
     int32_t tile_rows;       /* R = out_features/16 */
     int32_t tile_cols;       /* C = in_features/16  */
     float scale;
+    const float *row_scale;  /* device fp32[out_features] or NULL.  When given, output row o is scaled
+                                by row_scale[o] instead of `scale`: a stack of ternary matrices with
+                                different scales as ONE matrix, the role of ternary_gemv_rs
+                                (fused_decode_step.py:1754-1791).  Not with MORTAR_FLAG_SWIGLU. */
 } mortar_stream;
 
 const char *mortar_version(void);
@@ -128,8 +132,8 @@ int mortar_act_prep(const void *x, int x_dtype, int64_t rows, int32_t cols, int6
                     void *planes, int32_t n_planes, int64_t plane_stride, int64_t ld_planes,
                     void *stream);
 
-/* out_mode of mortar_linear */
-enum { MORTAR_OUT_F32 = 0, MORTAR_OUT_BF16 = 1, MORTAR_OUT_PLANES = 2 };
+/* out_mode of mortar_linear (MORTAR_OUT_HC is selected by mortar_linear_hc / mortar_mlp_decode_hc) */
+enum { MORTAR_OUT_F32 = 0, MORTAR_OUT_BF16 = 1, MORTAR_OUT_PLANES = 2, MORTAR_OUT_HC = 3 };
 /* flags of mortar_linear */
 enum {
     MORTAR_FLAG_SWIGLU = 1,      /* rows [0,F) are gate, [F,2F) up; out[b, n] = silu(g)*u, F = R/2 */
@@ -178,6 +182,29 @@ int mortar_linear(const mortar_stream *w, const void *planes, int32_t n_planes,
                   const int32_t *row_act, int64_t ld_row_act,
                   const int32_t *col_act, int64_t ld_col_act,
                   void *stream);
+
+/* Hyper-connection POST write fused into the epilogue of a linear / MLP call: instead of storing
+ * its result y[rows, C], the kernel writes the n-stream residual carrier
+ *   out[r][i][c] = sum_j hres[r][i][j] * carrier_in[r][j][c] + hpost_row[r][i] * y[r][c] (+ term[r][c])
+ * which is what the decode engine runs as a separate kernel after the MLP
+ * (morph/inference/engine.py:1001-1060, _hc_post_fwd_kernel
+ * morph/kernels/triton/fused_hyper_connection.py:933-977; `term` is the next block's inject folded
+ * into the same write).  All fp32, device; carrier layout [rows][n_streams][ld_stream] with
+ * ld_stream >= C; carrier_out may be carrier_in (each output element reads its n inputs first). */
+typedef struct mortar_hc_post {
+    const float *hres;        /* [rows][n][n] */
+    const float *hpost_row;   /* [rows][n]    */
+    const float *carrier_in;  /* [rows][n][ld_stream] */
+    float *carrier_out;       /* [rows][n][ld_stream] */
+    const float *term;        /* [rows][ld_stream] or NULL */
+    int32_t n_streams;        /* 1..8 (the reference uses 4) */
+} mortar_hc_post;
+
+/* mortar_linear (fp32 result, no SwiGLU) with the POST write above as its store. */
+int mortar_linear_hc(const mortar_stream *w, const void *planes, int32_t n_planes,
+                     int64_t plane_stride, int64_t ld_planes, int64_t rows,
+                     const mortar_hc_post *hc, int64_t ld_stream, int32_t flags,
+                     const int32_t *col_act, int64_t ld_col_act, void *stream);
 
 /* gates[rows, n_clusters] -> activity flags, fused_decode_step.py:1883-1927: flag = 1 iff
  * either spanned cluster (lo/hi index arrays, device int32) has gate > 0. */
@@ -237,6 +264,17 @@ int mortar_mlp_decode(const mortar_stream *gate_up, const mortar_stream *down,
                       void *y, int y_dtype, int64_t ldy,
                       int32_t n_planes, int32_t flags,
                       void *workspace, int64_t workspace_bytes, void *stream);
+
+/* mortar_mlp_decode whose down projection writes the hyper-connection carrier (see
+ * mortar_hc_post) instead of y: x is the single-stream input the PRE map produced, the n-stream
+ * carrier receives Hres*h + Hpost_row*MLP(x) (+ term) in the same launch.  fp32 semantics only. */
+int mortar_mlp_decode_hc(const mortar_stream *gate_up, const mortar_stream *down,
+                         const void *x, int x_dtype, int64_t ldx, int64_t rows,
+                         const float *rms_weight, float eps,
+                         const float *gates, int64_t ld_gates, int32_t n_clusters,
+                         const mortar_hc_post *hc, int64_t ld_stream,
+                         int32_t n_planes, int32_t flags,
+                         void *workspace, int64_t workspace_bytes, void *stream);
 
 /* mortar_mlp_decode without a caller workspace.  This entry point has no counterpart in the
  * reference.  It exists for callers that cannot hand over device memory of their own: code

@@ -30,7 +30,13 @@ class Stream(C.Structure):
     """mirror of `mortar_stream`"""
     _fields_ = [("grp_codes", C.c_void_p), ("grp_cols", C.c_void_p), ("grp_ptr", C.c_void_p),
                 ("n_groups", C.c_int32), ("tile_rows", C.c_int32), ("tile_cols", C.c_int32),
-                ("scale", C.c_float)]
+                ("scale", C.c_float), ("row_scale", C.c_void_p)]
+
+
+class HcPost(C.Structure):
+    """mirror of `mortar_hc_post`"""
+    _fields_ = [("hres", C.c_void_p), ("hpost_row", C.c_void_p), ("carrier_in", C.c_void_p),
+                ("carrier_out", C.c_void_p), ("term", C.c_void_p), ("n_streams", C.c_int32)]
 
 
 class Sched(C.Structure):
@@ -58,6 +64,10 @@ _SIGNATURES = {
     "mortar_act_prep": (C.c_int, [_vp, C.c_int, _i64, _i32, _i64, _vp, _f32, _vp, _i32, _i64, _i64, _vp]),
     "mortar_linear": (C.c_int, [C.POINTER(Stream), _vp, _i32, _i64, _i64, _i64, _vp, _i32, _i32, _i64,
                                 _i64, _i32, _vp, _i64, _i32, _vp, _i64, _vp, _i64, _vp]),
+    "mortar_linear_hc": (C.c_int, [C.POINTER(Stream), _vp, _i32, _i64, _i64, _i64, C.POINTER(HcPost), _i64, _i32,
+                                   _vp, _i64, _vp]),
+    "mortar_mlp_decode_hc": (C.c_int, [C.POINTER(Stream), C.POINTER(Stream), _vp, C.c_int, _i64, _i64, _vp, _f32,
+                                       _vp, _i64, _i32, C.POINTER(HcPost), _i64, _i32, _i32, _vp, _i64, _vp]),
     "mortar_route_flags": (C.c_int, [_vp, _i64, _i64, _vp, _vp, _i32, _vp, _vp, _i32, _vp, _i64, _vp,
                                      _i64, _vp]),
     "mortar_route_gather": (C.c_int, [_vp, _i64, _i64, _i32, _i32, _vp, _vp, _i64, _vp]),

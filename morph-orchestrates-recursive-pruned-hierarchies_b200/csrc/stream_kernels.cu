@@ -53,6 +53,12 @@ struct LinearParams {
     int units;                         // output tile rows (LINEAR) or hidden tile rows (SWIGLU)
     int fold;                          // >0: the planes are folded into the 8 MMA columns (see below)
     long long real_rows;               // activation rows when fold > 0 (rows = fold * real_rows)
+    const float *row_scale;            // per-output-row scales (replace `scale`) or nullptr
+    // hyper-connection POST write (out_mode == MORTAR_OUT_HC): the result y feeds n carrier streams
+    const float *hc_hres, *hc_hpost, *hc_in, *hc_term;
+    float *hc_out;
+    int hc_n;
+    long long hc_ld;                   // carrier stride between tokens, in floats (n_streams * ld_out)
 };
 
 __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
@@ -94,6 +100,24 @@ __device__ __forceinline__ void store_value(const LinearParams &p, long long row
     } else if (p.out_mode == MORTAR_OUT_BF16) {
         __nv_bfloat16 *o = reinterpret_cast<__nv_bfloat16 *>(p.out) + row * p.ld_out + col;
         *o = __float2bfloat16_rn(p.accumulate ? __bfloat162float(*o) + v : v);
+    } else if (p.out_mode == MORTAR_OUT_HC) {
+        // out[i][col] = sum_j Hres[i][j] * h[j][col] + Hpost_row[i] * y[col] (+ term[col]) for the n
+        // streams of this token (fused_hyper_connection.py:933-977); every h[j][col] is read before
+        // the first write, so the carrier may be updated in place
+        const int n = p.hc_n;
+        const float *hres = p.hc_hres + row * n * n, *hpost = p.hc_hpost + row * n;
+        const float *hin = p.hc_in + row * p.hc_ld + col;
+        float *o = p.hc_out + row * p.hc_ld + col;
+        const float term = p.hc_term != nullptr ? p.hc_term[row * p.ld_out + col] : 0.f;
+        float hj[8];
+        for (int j = 0; j < n; ++j) hj[j] = hin[j * p.ld_out];
+        for (int i = 0; i < n; ++i) {
+            float acc = 0.f;
+            for (int j = 0; j < n; ++j) acc += hres[i * n + j] * hj[j];
+            acc += hpost[i] * v;
+            if (p.hc_term != nullptr) acc += term;
+            o[i * p.ld_out] = acc;
+        }
     } else {
         __nv_bfloat16 *o = reinterpret_cast<__nv_bfloat16 *>(p.out) + row * p.ld_out + col;
         float r = v;
@@ -130,7 +154,7 @@ __device__ __forceinline__ void emit_value(const LinearParams &p, float scale, i
         }
         if (!active || (p.gates != nullptr && !(gate > 0.f))) v = 0.f;
     } else {
-        v = scale * sum_a;
+        v = (p.row_scale != nullptr ? p.row_scale[neuron] : scale) * sum_a;
         if (!active) v = 0.f;
     }
     store_value(p, row, neuron, v);
@@ -770,21 +794,31 @@ extern "C" int mortar_act_prep(const void *x, int x_dtype, int64_t rows, int32_t
     return MORTAR_OK;
 }
 
-extern "C" int mortar_linear(const mortar_stream *w, const void *planes, int32_t n_planes,
-                             int64_t plane_stride, int64_t ld_planes, int64_t rows, void *out,
-                             int32_t out_mode, int32_t n_out_planes, int64_t out_plane_stride,
-                             int64_t ld_out, int32_t flags, const float *gates, int64_t ld_gates,
-                             int32_t cluster_size, const int32_t *row_act, int64_t ld_row_act,
-                             const int32_t *col_act, int64_t ld_col_act, void *stream) {
+static int linear_impl(const mortar_stream *w, const void *planes, int32_t n_planes,
+                       int64_t plane_stride, int64_t ld_planes, int64_t rows, void *out,
+                       int32_t out_mode, int32_t n_out_planes, int64_t out_plane_stride,
+                       int64_t ld_out, int32_t flags, const float *gates, int64_t ld_gates,
+                       int32_t cluster_size, const int32_t *row_act, int64_t ld_row_act,
+                       const int32_t *col_act, int64_t ld_col_act, const mortar_hc_post *hc, void *stream) {
+    if (hc != nullptr) {
+        if (!hc->hres || !hc->hpost_row || !hc->carrier_in || !hc->carrier_out) return MORTAR_ERR_NULL;
+        if (hc->n_streams < 1 || hc->n_streams > 8) return MORTAR_ERR_SHAPE;
+        if (flags & (MORTAR_FLAG_SWIGLU | MORTAR_FLAG_ACCUMULATE)) return MORTAR_ERR_UNSUPPORTED;
+        out = hc->carrier_out;
+        out_mode = MORTAR_OUT_HC;
+    } else if (out_mode == MORTAR_OUT_HC) {
+        return MORTAR_ERR_DTYPE;
+    }
     if (!w || !planes || !out || !w->grp_ptr) return MORTAR_ERR_NULL;
     if (w->n_groups > 0 && (!w->grp_codes || !w->grp_cols)) return MORTAR_ERR_NULL;
     if (w->tile_rows <= 0 || w->tile_cols <= 0 || w->tile_cols > 65534 || rows < 0)
         return MORTAR_ERR_SHAPE;
     if (n_planes < 1 || n_planes > 3) return MORTAR_ERR_DTYPE;
-    if (out_mode < MORTAR_OUT_F32 || out_mode > MORTAR_OUT_PLANES) return MORTAR_ERR_DTYPE;
+    if (out_mode < MORTAR_OUT_F32 || out_mode > MORTAR_OUT_HC) return MORTAR_ERR_DTYPE;
     if (out_mode == MORTAR_OUT_PLANES && (n_out_planes < 1 || n_out_planes > 3)) return MORTAR_ERR_DTYPE;
     const bool swiglu = (flags & MORTAR_FLAG_SWIGLU) != 0;
     if (swiglu && (w->tile_rows % 2)) return MORTAR_ERR_SHAPE;
+    if (swiglu && w->row_scale) return MORTAR_ERR_UNSUPPORTED;
     const int units = swiglu ? w->tile_rows / 2 : w->tile_rows;
     if (ld_planes < (int64_t)w->tile_cols * 16 || ld_out < (int64_t)units * 16) return MORTAR_ERR_SHAPE;
     if (!aligned(planes, 4) || (ld_planes & 1) || (plane_stride & 1)) return MORTAR_ERR_ALIGN;
@@ -818,6 +852,11 @@ extern "C" int mortar_linear(const mortar_stream *w, const void *planes, int32_t
     p.units = units;
     p.fold = 0;
     p.real_rows = rows;
+    p.row_scale = w->row_scale;
+    p.hc_hres = hc ? hc->hres : nullptr; p.hc_hpost = hc ? hc->hpost_row : nullptr;
+    p.hc_in = hc ? hc->carrier_in : nullptr; p.hc_out = hc ? hc->carrier_out : nullptr;
+    p.hc_term = hc ? hc->term : nullptr; p.hc_n = hc ? hc->n_streams : 0;
+    p.hc_ld = hc ? (long long)hc->n_streams * ld_out : 0;
     // Small batches: fold the P exact planes into the 8 columns of one MMA (one MMA and one pair
     // of activation loads per tile instead of P of each).  Needs the planes back to back.
     if (n_planes > 1 && rows * n_planes <= 8 && plane_stride == rows * ld_planes) {
@@ -839,6 +878,27 @@ extern "C" int mortar_linear(const mortar_stream *w, const void *planes, int32_t
         return swiglu ? launch_persistent<true>(p, st) : launch_persistent<false>(p, st);
     const bool bulk = wpr == 4 && path == MORTAR_FLAG_PATH_STAGED;
     return swiglu ? launch_planes<true>(p, wpr, bulk, st) : launch_planes<false>(p, wpr, bulk, st);
+}
+
+extern "C" int mortar_linear(const mortar_stream *w, const void *planes, int32_t n_planes,
+                             int64_t plane_stride, int64_t ld_planes, int64_t rows, void *out,
+                             int32_t out_mode, int32_t n_out_planes, int64_t out_plane_stride,
+                             int64_t ld_out, int32_t flags, const float *gates, int64_t ld_gates,
+                             int32_t cluster_size, const int32_t *row_act, int64_t ld_row_act,
+                             const int32_t *col_act, int64_t ld_col_act, void *stream) {
+    if (out_mode == MORTAR_OUT_HC) return MORTAR_ERR_DTYPE;
+    return linear_impl(w, planes, n_planes, plane_stride, ld_planes, rows, out, out_mode, n_out_planes,
+                       out_plane_stride, ld_out, flags, gates, ld_gates, cluster_size, row_act, ld_row_act,
+                       col_act, ld_col_act, nullptr, stream);
+}
+
+extern "C" int mortar_linear_hc(const mortar_stream *w, const void *planes, int32_t n_planes,
+                                int64_t plane_stride, int64_t ld_planes, int64_t rows,
+                                const mortar_hc_post *hc, int64_t ld_stream, int32_t flags,
+                                const int32_t *col_act, int64_t ld_col_act, void *stream) {
+    if (!hc) return MORTAR_ERR_NULL;
+    return linear_impl(w, planes, n_planes, plane_stride, ld_planes, rows, hc->carrier_out, MORTAR_OUT_HC, 0, 0,
+                       ld_stream, flags, nullptr, 0, 0, nullptr, 0, col_act, ld_col_act, hc, stream);
 }
 
 extern "C" int mortar_route_gather(const float *gates, int64_t rows, int64_t ld_gates, int32_t cluster_size,
@@ -889,6 +949,8 @@ extern "C" int mortar_linear_gathered(const mortar_stream *w, const void *planes
     p.gates_on_input = 0;
     p.row_act = nullptr; p.ld_row_act = 0; p.col_act = nullptr; p.ld_col_act = 0;
     p.units = units; p.fold = 0; p.real_rows = rows;
+    p.row_scale = nullptr;
+    p.hc_hres = p.hc_hpost = p.hc_in = p.hc_term = nullptr; p.hc_out = nullptr; p.hc_n = 0; p.hc_ld = 0;
     const double avg = (double)w->n_groups / (double)units;
     const int wpr = avg >= 3.0 ? 4 : (avg >= 1.5 ? 2 : 1);
     cudaStream_t st = (cudaStream_t)stream;
@@ -937,12 +999,13 @@ extern "C" int64_t mortar_mlp_workspace_bytes(int64_t rows, int32_t d_model, int
            align_up((int64_t)(d_ff / 16) * rows * 4, 256);
 }
 
-extern "C" int mortar_mlp_decode(const mortar_stream *gate_up, const mortar_stream *down,
-                                 const void *x, int x_dtype, int64_t ldx, int64_t rows,
-                                 const float *rms_weight, float eps, const float *gates,
-                                 int64_t ld_gates, int32_t n_clusters, void *y, int y_dtype,
-                                 int64_t ldy, int32_t n_planes, int32_t flags, void *workspace,
-                                 int64_t workspace_bytes, void *stream) {
+static int mlp_decode_impl(const mortar_stream *gate_up, const mortar_stream *down,
+                           const void *x, int x_dtype, int64_t ldx, int64_t rows,
+                           const float *rms_weight, float eps, const float *gates,
+                           int64_t ld_gates, int32_t n_clusters, void *y, int y_dtype,
+                           int64_t ldy, int32_t n_planes, int32_t flags, void *workspace,
+                           int64_t workspace_bytes, const mortar_hc_post *hc, void *stream) {
+    if (hc != nullptr) { y = hc->carrier_out; y_dtype = MORTAR_F32; }
     if (!gate_up || !down || !x || !y || !workspace) return MORTAR_ERR_NULL;
     if (x_dtype != MORTAR_F32 && x_dtype != MORTAR_BF16) return MORTAR_ERR_DTYPE;
     if (y_dtype != MORTAR_F32 && y_dtype != MORTAR_BF16) return MORTAR_ERR_DTYPE;
@@ -994,10 +1057,33 @@ extern "C" int mortar_mlp_decode(const mortar_stream *gate_up, const mortar_stre
                            ld_gates, cs, nullptr, 0, nullptr, 0, stream);
     }
     if (rc != MORTAR_OK) return rc;
-    return mortar_linear(down, hp, h_planes, rows * (int64_t)d_ff, d_ff, rows, y,
-                         y_dtype == MORTAR_F32 ? MORTAR_OUT_F32 : MORTAR_OUT_BF16, 0, 0, ldy,
-                         rb | path | (flags & MORTAR_FLAG_ACCUMULATE) | (gates ? MORTAR_FLAG_GATES_ON_INPUT : 0),
-                         gates, ld_gates, cs, nullptr, 0, nullptr, 0, stream);
+    return linear_impl(down, hp, h_planes, rows * (int64_t)d_ff, d_ff, rows, y,
+                       y_dtype == MORTAR_F32 ? MORTAR_OUT_F32 : MORTAR_OUT_BF16, 0, 0, ldy,
+                       rb | path | (hc ? 0 : (flags & MORTAR_FLAG_ACCUMULATE)) | (gates ? MORTAR_FLAG_GATES_ON_INPUT : 0),
+                       gates, ld_gates, cs, nullptr, 0, nullptr, 0, hc, stream);
+}
+
+extern "C" int mortar_mlp_decode(const mortar_stream *gate_up, const mortar_stream *down,
+                                 const void *x, int x_dtype, int64_t ldx, int64_t rows,
+                                 const float *rms_weight, float eps, const float *gates,
+                                 int64_t ld_gates, int32_t n_clusters, void *y, int y_dtype,
+                                 int64_t ldy, int32_t n_planes, int32_t flags, void *workspace,
+                                 int64_t workspace_bytes, void *stream) {
+    return mlp_decode_impl(gate_up, down, x, x_dtype, ldx, rows, rms_weight, eps, gates, ld_gates, n_clusters, y,
+                           y_dtype, ldy, n_planes, flags, workspace, workspace_bytes, nullptr, stream);
+}
+
+extern "C" int mortar_mlp_decode_hc(const mortar_stream *gate_up, const mortar_stream *down,
+                                    const void *x, int x_dtype, int64_t ldx, int64_t rows,
+                                    const float *rms_weight, float eps, const float *gates,
+                                    int64_t ld_gates, int32_t n_clusters, const mortar_hc_post *hc,
+                                    int64_t ld_stream, int32_t n_planes, int32_t flags, void *workspace,
+                                    int64_t workspace_bytes, void *stream) {
+    if (!hc) return MORTAR_ERR_NULL;
+    if (flags & (MORTAR_FLAG_ROUND_BF16 | MORTAR_FLAG_ACCUMULATE)) return MORTAR_ERR_UNSUPPORTED;
+    return mlp_decode_impl(gate_up, down, x, x_dtype, ldx, rows, rms_weight, eps, gates, ld_gates, n_clusters,
+                           hc->carrier_out, MORTAR_F32, ld_stream, n_planes, flags, workspace, workspace_bytes, hc,
+                           stream);
 }
 
 // ---- MLP application on built-in scratch ---------------------------------------------------

@@ -408,11 +408,12 @@ class StreamMatrix:
     handed to the library borrows their pointers."""
 
     def __init__(self, out_features, in_features, scale, n_groups, nnz, grp_ptr, grp_cols,
-                 grp_codes, algorithmic_bytes):
+                 grp_codes, algorithmic_bytes, row_scale=None):
         self.out_features, self.in_features = int(out_features), int(in_features)
         self.scale, self.n_groups, self.nnz = float(scale), int(n_groups), int(nnz)
         self.grp_ptr, self.grp_cols, self.grp_codes = grp_ptr, grp_cols, grp_codes
         self.algorithmic_bytes = int(algorithmic_bytes)
+        self.row_scale = row_scale          # optional fp32 [out_features] on the device: per-row scales
         self._c = None
 
     @property
@@ -422,11 +423,13 @@ class StreamMatrix:
     def to(self, device) -> "StreamMatrix":
         return StreamMatrix(self.out_features, self.in_features, self.scale, self.n_groups, self.nnz,
                             self.grp_ptr.to(device), self.grp_cols.to(device),
-                            self.grp_codes.to(device), self.algorithmic_bytes)
+                            self.grp_codes.to(device), self.algorithmic_bytes,
+                            None if self.row_scale is None else self.row_scale.to(device))
 
     def c_struct(self) -> _lib.Stream:
         if self._c is None:
             self._c = _lib.Stream(self.grp_codes.data_ptr(), self.grp_cols.data_ptr(),
                                   self.grp_ptr.data_ptr(), self.n_groups,
-                                  self.out_features // TILE, self.in_features // TILE, self.scale)
+                                  self.out_features // TILE, self.in_features // TILE, self.scale,
+                                  None if self.row_scale is None else self.row_scale.data_ptr())
         return self._c

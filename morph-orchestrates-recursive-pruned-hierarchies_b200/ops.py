@@ -392,6 +392,104 @@ def stack_decode(x: torch.Tensor, stack: DecodeStack, *, eps: float = 1e-6, n_pl
     return x
 
 
+def _hc_struct(hres, hpost_row, carrier, out, term, n, C_):
+    for name, t in (("hres", hres), ("hpost_row", hpost_row), ("carrier", carrier), ("out", out), ("term", term)):
+        if t is not None and (t.dtype != torch.float32 or not t.is_cuda or not t.is_contiguous()):
+            raise ValueError(f"{name} must be a contiguous float32 CUDA tensor")
+    rows = carrier.numel() // (n * C_)
+    if hres.numel() != rows * n * n or hpost_row.numel() != rows * n or out.shape != carrier.shape or \
+            (term is not None and term.numel() != rows * C_):
+        raise ValueError("hres [rows,n,n], hpost_row [rows,n], carrier/out [rows,n,C], term [rows,C] expected")
+    return _lib.HcPost(hres.data_ptr(), hpost_row.data_ptr(), carrier.data_ptr(), out.data_ptr(),
+                       None if term is None else term.data_ptr(), n), rows
+
+
+def mlp_decode_hc(x: torch.Tensor, gate_up: StreamMatrix, down: StreamMatrix, hres: torch.Tensor,
+                  hpost_row: torch.Tensor, carrier: torch.Tensor, *, term: Optional[torch.Tensor] = None,
+                  out: Optional[torch.Tensor] = None, rms_weight: Optional[torch.Tensor] = None, eps: float = 1e-6,
+                  gates: Optional[torch.Tensor] = None, n_clusters: int = 0, n_planes: int = 3,
+                  workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The MLP site of the decode engine including the write the engine runs after it
+    (morph/inference/engine.py:1001-1060): x [..., d_model] is the single-stream input the
+    hyper-connection PRE map produced, ``carrier`` [..., n, d_model] the n-stream residual; the down
+    projection's epilogue writes out[..., i, :] = sum_j hres[..., i, j] carrier[..., j, :] +
+    hpost_row[..., i] * MLP(x) (+ term), the arithmetic of ``_hc_post_fwd_kernel``
+    (morph/kernels/triton/fused_hyper_connection.py:933-977).  ``out`` defaults to a new tensor;
+    passing ``carrier`` itself updates the carrier in place."""
+    _require_cuda(x, "x")
+    d_model, d_ff = gate_up.in_features, gate_up.out_features // 2
+    x2 = _rows2d(x, d_model, "x")
+    n = carrier.shape[-2]
+    if carrier.shape[-1] != d_model:
+        raise ValueError("carrier must be [..., n_streams, d_model]")
+    if out is None:
+        out = torch.empty_like(carrier)
+    hc, rows = _hc_struct(hres, hpost_row, carrier, out, term, n, d_model)
+    if rows != x2.shape[0]:
+        raise ValueError("x and carrier disagree on the number of tokens")
+    if rows == 0:
+        return out
+    L = _lib.lib()
+    need = L.mortar_mlp_workspace_bytes(rows, d_model, d_ff, n_planes)
+    if workspace is None:
+        workspace = _workspace(x.device, need)
+    w = None if rms_weight is None else rms_weight.to(device=x.device, dtype=torch.float32).contiguous()
+    g = None
+    if gates is not None:
+        g = gates.to(device=x.device, dtype=torch.float32).reshape(rows, -1).contiguous()
+    gu, dn = gate_up.c_struct(), down.c_struct()
+    _lib.check(L.mortar_mlp_decode_hc(
+        C.byref(gu), C.byref(dn), _ptr(x2), _dtype_code(x2), x2.stride(0), rows, _ptr(w), float(eps), _ptr(g),
+        g.stride(0) if g is not None else 0, int(n_clusters), C.byref(hc), d_model, int(n_planes), 0,
+        _ptr(workspace), workspace.numel(), _stream_ptr()), "mortar_mlp_decode_hc")
+    _count("bcsr_stream", 2)
+    return out
+
+
+class RowScaledPack:
+    """A stack of dense ternary projections with per-row scales in this library's stream layout
+    (what ``ternary_gemv_rs`` consumes; built once per weight stack)."""
+
+    def __init__(self, stream: StreamMatrix, out_features: int):
+        self.stream, self.out_features = stream, int(out_features)
+
+
+def ternary_pack_rs(codes: torch.Tensor, row_scale: torch.Tensor, device="cuda") -> RowScaledPack:
+    """Strip-packed dense ternary rows [O, I/4] uint8 (byte j = columns j, j+I/4, j+I/2, j+3I/4;
+    ``ternary_pack``, fused_decode_step.py:1181-1204) + fp32 row scales [O] -> stream layout.  Rows
+    are padded to a multiple of 16 with zero codes; I must be a multiple of 16."""
+    import numpy as np
+    p = codes.detach().cpu().numpy().astype(np.uint8)
+    O, I4 = p.shape
+    I = 4 * I4
+    if I % TILE:
+        raise ValueError("in_features must be a multiple of 16")
+    dense = np.zeros((O, 4, I4), dtype=np.int8)
+    for st in range(4):
+        dense[:, st] = ((p >> (2 * st)) & 3).astype(np.int8) - 1
+    dense = dense.reshape(O, I)
+    Opad = (O + TILE - 1) // TILE * TILE
+    if Opad != O:
+        dense = np.concatenate([dense, np.zeros((Opad - O, I), dtype=np.int8)])
+    m = MortarMatrix.from_codes(dense, None, 1.0)
+    s = m.to_stream(device)
+    rs = torch.zeros(Opad, dtype=torch.float32)
+    rs[:O] = row_scale.detach().float().cpu().reshape(-1)
+    s.row_scale = rs.to(device)
+    s._c = None
+    return RowScaledPack(s, O)
+
+
+def ternary_gemv_rs(x: torch.Tensor, pack: RowScaledPack) -> torch.Tensor:
+    """Row-scaled dense ternary GEMV, the role of the reference ``ternary_gemv_rs(x, codes,
+    row_scale)`` (fused_decode_step.py:1778-1791): x [B, I] fp32 -> [B, O] fp32 with exact +-x
+    products (three bf16 planes), fp32 accumulation and the row's scale applied after the sum."""
+    _require_cuda(x, "x")
+    planes = act_prep(x.float().reshape(-1, x.shape[-1]), 3)
+    y = linear_planes(pack.stream, planes, out_dtype=torch.float32)
+    return y[:, :pack.out_features]
+
+
 def stack_decode_raw(x: torch.Tensor, blobs: torch.Tensor, blob_table: torch.Tensor, app_layer: torch.Tensor,
                      rms_weights: Optional[torch.Tensor], status: torch.Tensor, n_layers: int, d_model: int,
                      d_ff: int, max_gate_up_bytes: int, max_down_bytes: int, cluster_size: int,

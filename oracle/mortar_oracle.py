@@ -389,3 +389,38 @@ def swiglu_mlp_decode(x: Tensor, codes_gu: Tensor, scale_gu: Tensor, meta_gu,
         cs = h.shape[-1] // n_clusters
         h = h * gates.float().repeat_interleave(cs, dim=-1)
     return F.linear(h, Cdn) * scale_dn.float()
+
+
+# ---------------------------------------------------------------------------------
+# The steps beside the MLP in the decode engine
+# ---------------------------------------------------------------------------------
+
+def hc_post(hres: Tensor, hpost_row: Tensor, h: Tensor, y: Tensor, term: Optional[Tensor] = None) -> Tensor:
+    """Hyper-connection POST write: out[..., i, c] = sum_j Hres[..., i, j] h[..., j, c]
+    + Hpost_row[..., i] y[..., c] (+ term[..., c] on every stream).  Follows
+    morph/kernels/triton/fused_hyper_connection.py:933-977 (_hc_post_fwd_kernel; eager twin
+    hc_post_reference :1426-1433); called after the MLP at morph/inference/engine.py:1001-1060."""
+    out = torch.einsum("...ij,...jc->...ic", hres.float(), h.float()) + hpost_row.float().unsqueeze(-1) * y.float().unsqueeze(-2)
+    if term is not None:
+        out = out + term.float().unsqueeze(-2)
+    return out
+
+
+def unpack_row_strips(codes: np.ndarray) -> np.ndarray:
+    """Strip-packed dense ternary rows [O, I/4] uint8 -> int8 codes [O, I]: byte j of a row holds
+    columns j, j+I/4, j+I/2, j+3I/4 in its four 2-bit fields, stored value = code + 1
+    (ternary_pack, morph/kernels/triton/fused_decode_step.py:1181-1204)."""
+    p = np.asarray(codes, dtype=np.uint8)
+    O, I4 = p.shape
+    out = np.zeros((O, 4, I4), dtype=np.int8)
+    for st in range(4):
+        out[:, st] = ((p >> (2 * st)) & 3).astype(np.int8) - 1
+    return out.reshape(O, 4 * I4)
+
+
+def ternary_gemv_rs(x: np.ndarray, codes: np.ndarray, row_scale: np.ndarray) -> np.ndarray:
+    """out[b, o] = row_scale[o] * sum_i code[o, i] x[b, i]: the row-scaled dense ternary GEMV
+    (_ternary_rs_kernel, morph/kernels/triton/fused_decode_step.py:1754-1791): exact +-x products,
+    fp32 accumulate, the scale applied once after the sum."""
+    w = unpack_row_strips(codes).astype(np.float32)
+    return (np.asarray(x, dtype=np.float32) @ w.T) * np.asarray(row_scale, dtype=np.float32)[None, :]

@@ -153,6 +153,45 @@ def build_case(name, d_model, d_ff, blocking, n_clusters, ratio, x_shape, seed, 
     print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path)} bytes")
 
 
+def decode_sides():
+    """The two steps beside the MLP in the decode engine: the hyper-connection POST write
+    (hc_post_reference, the eager twin of _hc_post_fwd_kernel) and a stack of per-layer ternary
+    projections packed with the reference's ternary_pack for ternary_gemv_rs (the dense
+    product of the dequantised stack is the reference's eager result)."""
+    from morph.kernels.triton.fused_hyper_connection import hc_post_reference
+    from morph.kernels.triton.fused_decode_step import ternary_pack
+    out = {}
+    torch.manual_seed(11)
+    B, S, n, C = 3, 1, 4, 256
+    hres = torch.randn(B, S, n, n) * 0.5
+    hpost = torch.rand(B, S, n)
+    h = torch.randn(B, S, n, C)
+    y = torch.randn(B, S, C) * 0.1
+    term = torch.randn(B, S, C) * 0.05
+    out["hc_hres"], out["hc_hpost_row"], out["hc_h"] = hres.numpy(), hpost.numpy(), h.numpy()
+    out["hc_y"], out["hc_term"] = y.numpy(), term.numpy()
+    out["hc_out"] = hc_post_reference(hres, hpost, h, y, None).numpy()
+    out["hc_out_term"] = hc_post_reference(hres, hpost, h, y, term).numpy()
+    # three ternary layers [48, 128] with their own scales, stacked to one [144, 128] GEMV
+    I, O = 128, 48
+    packs, scales, dense = [], [], []
+    for layer in range(3):
+        gamma = 0.01 * (layer + 1)
+        w = torch.randint(-1, 2, (O, I)).float() * gamma
+        codes, sc = ternary_pack(w)
+        packs.append(codes)
+        scales.append(sc.reshape(1).expand(O).clone())
+        dense.append(w)
+    x = torch.randn(5, I)
+    out["rs_codes"] = torch.cat(packs).numpy()
+    out["rs_row_scale"] = torch.cat(scales).numpy()
+    out["rs_x"] = x.numpy()
+    out["rs_out"] = torch.nn.functional.linear(x, torch.cat(dense)).numpy()
+    path = os.path.join(HERE, "decode_sides.npz")
+    np.savez_compressed(path, **out)
+    print(f"wrote {path}")
+
+
 def known_answers():
     """Tiny known-answer vectors taken from running the reference primitives."""
     from morph.inference.deploy_quant import pack_ternary_codes, unpack_ternary, _ternary_quantize
@@ -181,6 +220,7 @@ def main():
         sys.exit("put the reference checkout on PYTHONPATH to regenerate the fixtures")
     torch.set_num_threads(1)
     known_answers()
+    decode_sides()
     build_case("mlp_tile16_d64", d_model=64, d_ff=128, blocking=16, n_clusters=8, ratio=0.5,
                x_shape=(2, 5), seed=11)
     build_case("mlp_tile16_d128_cs16", d_model=128, d_ff=256, blocking=16, n_clusters=16,

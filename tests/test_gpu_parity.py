@@ -432,3 +432,46 @@ def test_per_token_tile_gather(ncls, k, rows):
     g0[rows // 2] = 0.0
     y0 = mb.ops.mlp_decode(x.to(DEV), gu, dn, gates=g0.to(DEV), n_clusters=ncls, n_planes=3)
     assert float(y0[rows // 2].abs().max()) == 0.0
+
+
+def test_decode_side_steps_fused():
+    """The steps either side of the MLP in the decode engine: the hyper-connection POST write as
+    the down projection's epilogue, and the row-scaled dense ternary GEMV -- against the outputs
+    the reference's eager code produced and against the oracle."""
+    g = load_golden("decode_sides")
+    t = lambda k: torch.from_numpy(g[k]).to(DEV)
+    # row-scaled stack: three ternary layers with their own scales as one product
+    pack = mb.ops.ternary_pack_rs(torch.from_numpy(g["rs_codes"]), torch.from_numpy(g["rs_row_scale"]), DEV)
+    y = mb.ops.ternary_gemv_rs(t("rs_x"), pack)
+    assert y.shape == (5, 144)
+    np.testing.assert_allclose(y.cpu().numpy(), g["rs_out"], rtol=2e-5, atol=1e-6)
+    # O not a multiple of 16 (the reference's ctx_w = 2730 stacks)
+    rng = np.random.default_rng(5)
+    O, I = 2730, 256
+    dense = rng.integers(-1, 2, size=(O, I)).astype(np.int8)
+    st = (dense + 1).astype(np.uint8).reshape(O, 4, I // 4)
+    packed = st[:, 0] | (st[:, 1] << 2) | (st[:, 2] << 4) | (st[:, 3] << 6)
+    rs = rng.random(O).astype(np.float32) * 0.05
+    x = rng.standard_normal((3, I)).astype(np.float32)
+    y = mb.ops.ternary_gemv_rs(torch.from_numpy(x).to(DEV), mb.ops.ternary_pack_rs(torch.from_numpy(packed),
+                                                                                  torch.from_numpy(rs), DEV))
+    ref = orc.ternary_gemv_rs(x, packed, rs)
+    assert y.shape == (3, O)
+    assert float(np.abs(y.cpu().numpy() - ref).max()) <= F32_TOL * float(np.abs(ref).max())
+    # POST write fused behind the MLP: golden mapping tensors, MLP output from the oracle
+    L = mb.synth.make_layer(256, 512, 0.25, seed=1)
+    gu, dn = L.gate_up.to_stream(DEV), L.down.to_stream(DEV)
+    h = t("hc_h")                                            # [3, 1, 4, 256]
+    xbar = h.mean(dim=2)                                     # a single-stream input [3, 1, 256]
+    y_ref = _decode_oracle(xbar.reshape(-1, 256).cpu(), L)
+    for term in (None, t("hc_term")):
+        want = orc.hc_post(t("hc_hres").cpu(), t("hc_hpost_row").cpu(), h.cpu(), y_ref.reshape(3, 1, 256),
+                           None if term is None else term.cpu())
+        out = mb.ops.mlp_decode_hc(xbar, gu, dn, t("hc_hres"), t("hc_hpost_row"), h, term=term)
+        assert out.shape == h.shape
+        assert float((out.cpu() - want).abs().max()) <= F32_TOL * float(want.abs().max())
+    # in place on the carrier, with the MLP replaced by a known y: the reference's own output
+    carrier = h.clone()
+    mb.ops.mlp_decode_hc(xbar, gu, dn, t("hc_hres"), t("hc_hpost_row"), carrier, out=carrier)
+    want = orc.hc_post(t("hc_hres").cpu(), t("hc_hpost_row").cpu(), h.cpu(), y_ref.reshape(3, 1, 256))
+    assert float((carrier.cpu() - want).abs().max()) <= F32_TOL * float(want.abs().max())

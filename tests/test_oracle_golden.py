@@ -179,3 +179,17 @@ def test_oracle_workloads_equal_the_product_generator():
             ref = torch.from_numpy(m.to_dense_codes()).float() * torch.tensor(m.scale)
             assert torch.equal(dense, ref)
     assert torch.equal(wl.activations(5, 64, 3), mb.synth.make_activations(5, 64, 3))
+
+
+def test_decode_side_steps_against_reference_outputs():
+    """hc_post and the row-scaled ternary GEMV restatements against what the reference's eager
+    code produced (hc_post_reference; F.linear on the stack ternary_pack packed)."""
+    from conftest import load_golden
+    g = load_golden("decode_sides")
+    t = lambda k: torch.from_numpy(g[k])
+    out = orc.hc_post(t("hc_hres"), t("hc_hpost_row"), t("hc_h"), t("hc_y"))
+    np.testing.assert_allclose(out.numpy(), g["hc_out"], rtol=1e-6, atol=1e-6)
+    out = orc.hc_post(t("hc_hres"), t("hc_hpost_row"), t("hc_h"), t("hc_y"), t("hc_term"))
+    np.testing.assert_allclose(out.numpy(), g["hc_out_term"], rtol=1e-6, atol=1e-6)
+    y = orc.ternary_gemv_rs(g["rs_x"], g["rs_codes"], g["rs_row_scale"])
+    np.testing.assert_allclose(y, g["rs_out"], rtol=2e-5, atol=1e-6)
