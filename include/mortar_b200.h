@@ -427,6 +427,23 @@ int mortar_router_gates(const float *x, int64_t ldx, int64_t rows, int32_t d_mod
                         int32_t n_groups, int32_t k, float *qv_scratch, float *gates,
                         int64_t ld_gates, void *stream);
 
+/* Weight gradient of the carved linear on its topology (training backward): for every kept tile
+ * (r, c) of the canonical format, out[tile][i][j] = sum_t dy[t][16r+i] * x[t][16c+j] -- the
+ * sampled product the reference's `morph_stk::sdd_at_b` computes (custom_ops.py:68-89;
+ * _sdd_kernel triton_kernels.py:43-78), bf16 operands, fp32 accumulation.  The input gradient
+ * needs no entry point of its own: dx = dy @ W is mortar_linear / mortar_linear_tc on the
+ * transposed matrix (custom_ops.py:112-133).
+ *   dy [rows][ld_dy], x [rows][ld_x]   device bf16, 16-byte aligned, strides multiples of 8
+ *   row_ptr, col_idx                   canonical topology on the device
+ *   item_row, item_first  int32[n_items]  work list: item = up to 8 consecutive kept tiles of one
+ *                         tile row, starting at tile index item_first (built on the host)
+ *   out   [nnz][16][16]   fp32 (MORTAR_F32) or bf16 (MORTAR_BF16)
+ * A functional operator: activations are re-read once per item. */
+int mortar_sdd_tiles(const void *dy, int64_t ld_dy, const void *x, int64_t ld_x, int64_t rows,
+                     const int32_t *row_ptr, const uint16_t *col_idx, int32_t tile_rows,
+                     int32_t tile_cols, const int32_t *item_row, const int32_t *item_first,
+                     int32_t n_items, void *out, int32_t out_dtype, void *stream);
+
 /* Reads (and optionally clears) the error word the staged and persistent paths of
  * mortar_linear set when one of their bounded barrier waits expires: 0 = none, 1 = staged
  * path, 2 = a consumer of the persistent kernel, 3 = one of its producers.  Synchronises.

@@ -88,6 +88,7 @@ _SIGNATURES = {
     "mortar_linear_tc": (C.c_int, [C.POINTER(Sched), _vp, _i64, _i64, _vp, _i64, _vp, _i64, _i32, _vp]),
     "mortar_mlp_prefill": (C.c_int, [C.POINTER(Sched), C.POINTER(Sched), _vp, _i64, _i64, _vp, _i64,
                                      _i32, _vp, _i64, _vp, _i64, _vp]),
+    "mortar_sdd_tiles": (C.c_int, [_vp, _i64, _vp, _i64, _i64, _vp, _vp, _i32, _i32, _vp, _vp, _i32, _vp, _i32, _vp]),
     "mortar_prefill_error": (C.c_int, [_vp, _i32]),
     "mortar_linear_error": (C.c_int, [_vp, _i32]),
     "mortar_router_gates": (C.c_int, [_vp, _i64, _i64, _i32, _vp, _vp, _vp, _vp, _f32, _vp, _vp, _i32, _vp,

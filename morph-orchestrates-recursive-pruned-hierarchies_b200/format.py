@@ -264,6 +264,19 @@ class MortarMatrix:
                             np.ascontiguousarray((self.col_idx[keep] - c0).astype(np.uint16)),
                             np.ascontiguousarray(self.codes[keep]), self.scale)
 
+    def transpose(self) -> "MortarMatrix":
+        """W^T as a canonical matrix [in, out]: tiles transposed one by one and re-sorted by their
+        new row (the matrix the input gradient dx = dy @ W runs the forward kernels on)."""
+        rows = np.repeat(np.arange(self.tile_rows), np.diff(self.row_ptr))
+        cols = self.col_idx.astype(np.int64)
+        order = np.lexsort((rows, cols))                       # by new row (= old column), then new column
+        tiles = unpack_codes_2bit(self.codes).reshape(self.nnz, TILE, TILE).transpose(0, 2, 1)[order]
+        row_ptr = np.zeros(self.tile_cols + 1, dtype=np.int32)
+        np.cumsum(np.bincount(cols, minlength=self.tile_cols), out=row_ptr[1:])
+        return MortarMatrix(self.in_features, self.out_features, row_ptr, rows[order].astype(np.uint16),
+                            np.ascontiguousarray(pack_codes_2bit(tiles.reshape(self.nnz, TILE * TILE))),
+                            self.scale)
+
     def algorithmic_bytes(self) -> int:
         """Bytes a kernel must read to use this matrix once: 64 per tile of codes, 2 per tile of
         column index, 4 per row pointer, 4 of scale."""
@@ -297,6 +310,24 @@ class MortarMatrix:
                             torch.from_numpy(grp_cols.view(np.int16)).to(device),
                             torch.from_numpy(grp_codes).to(device),
                             self.algorithmic_bytes())
+
+
+class TopologyDev:
+    """Canonical topology of a matrix on the device plus the work list of the weight-gradient
+    kernel (items of up to 8 consecutive kept tiles of one tile row)."""
+
+    def __init__(self, m: "MortarMatrix", device="cuda"):
+        self.tile_rows, self.tile_cols, self.nnz = m.tile_rows, m.tile_cols, m.nnz
+        item_row, item_first = [], []
+        for r in range(m.tile_rows):
+            for f in range(int(m.row_ptr[r]), int(m.row_ptr[r + 1]), 8):
+                item_row.append(r)
+                item_first.append(f)
+        t = lambda a, dt: torch.from_numpy(np.ascontiguousarray(np.asarray(a, dtype=dt))).to(device)
+        self.row_ptr = t(m.row_ptr, np.int32)
+        self.col_idx = t(m.col_idx.view(np.int16), np.int16)
+        self.item_row, self.item_first = t(item_row, np.int32), t(item_first, np.int32)
+        self.n_items = len(item_row)
 
 
 PANEL_ROWS, CHUNK_COLS, STEP_TILES = 16, 4, 48

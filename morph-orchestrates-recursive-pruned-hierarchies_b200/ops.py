@@ -11,7 +11,7 @@ from typing import Optional
 import torch
 
 from . import _lib
-from .format import TILE, MortarMatrix, SchedMatrix, StreamMatrix
+from .format import TILE, MortarMatrix, SchedMatrix, StreamMatrix, TopologyDev
 
 _launches = 0      # kernels launched by this module (bench.py reports it)
 _kernel_counts: dict = {}   # the same, per kernel family
@@ -587,6 +587,32 @@ def mlp_prefill_tc(x: torch.Tensor, gate_up: SchedMatrix, down: SchedMatrix, *,
         _ptr(workspace), workspace.numel(), _stream_ptr()), "mortar_mlp_prefill")
     _count("prefill_panel", 2)
     return out.reshape(*lead, d_model)
+
+
+def sdd_tiles(dy: torch.Tensor, x: torch.Tensor, topo: TopologyDev, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """Weight gradient on the topology: [nnz, 16, 16] with tile (r, c) = dy[:, 16r:16r+16]^T @
+    x[:, 16c:16c+16] (bf16 operands, fp32 accumulation) -- ``morph_stk::sdd_at_b`` at tile 16
+    (morph/sparse/stk/backend/custom_ops.py:68-89)."""
+    _require_cuda(dy, "dy")
+    d2 = _rows2d(dy.to(torch.bfloat16), topo.tile_rows * TILE, "dy")
+    x2 = _rows2d(x.to(torch.bfloat16), topo.tile_cols * TILE, "x")
+    if d2.shape[0] != x2.shape[0]:
+        raise ValueError("dy and x disagree on the number of rows")
+    if d2.stride(0) % 8 or d2.data_ptr() % 16:
+        d2 = d2.contiguous()
+    if x2.stride(0) % 8 or x2.data_ptr() % 16:
+        x2 = x2.contiguous()
+    out = torch.empty(topo.nnz, TILE, TILE, device=dy.device, dtype=out_dtype)
+    if topo.nnz == 0:
+        return out
+    if d2.shape[0] == 0:
+        return out.zero_()
+    _lib.check(_lib.lib().mortar_sdd_tiles(
+        _ptr(d2), d2.stride(0), _ptr(x2), x2.stride(0), d2.shape[0], _ptr(topo.row_ptr), _ptr(topo.col_idx),
+        topo.tile_rows, topo.tile_cols, _ptr(topo.item_row), _ptr(topo.item_first), topo.n_items, _ptr(out),
+        _dtype_code(out), _stream_ptr()), "mortar_sdd_tiles")
+    _count("sdd_tiles")
+    return out
 
 
 def linear_error(reset: bool = True) -> int:

@@ -37,7 +37,7 @@ import numpy as np
 import torch
 
 from . import ops
-from .format import MortarMatrix, SchedMatrix, StreamMatrix, matrix_from_stream, pack_codes_2bit
+from .format import MortarMatrix, SchedMatrix, StreamMatrix, TopologyDev, matrix_from_stream, pack_codes_2bit
 
 _LIB = "mortar_b200"
 TC_MIN_ROWS = 128        # bf16 token blocks of at least this many rows run the tcgen05 kernel
@@ -261,15 +261,22 @@ def _ternary_matrix_from_data(data: torch.Tensor, offsets: torch.Tensor, column_
 class _DdsEntry:
     def __init__(self, matrix: MortarMatrix, fingerprint: int, device):
         self.matrix, self.fingerprint, self.device = matrix, fingerprint, device
-        self._stream = None
-        self._sched = None
+        self._stream = self._sched = self._stream_t = self._sched_t = None
 
-    def stream(self):
+    def stream(self, transposed: bool = False):
+        if transposed:
+            if self._stream_t is None:
+                self._stream_t = self.matrix.transpose().to_stream(self.device)
+            return self._stream_t
         if self._stream is None:
             self._stream = self.matrix.to_stream(self.device)
         return self._stream
 
-    def sched(self):
+    def sched(self, transposed: bool = False):
+        if transposed:
+            if self._sched_t is None:
+                self._sched_t = self.matrix.transpose().to_sched(False, self.device)
+            return self._sched_t
         if self._sched is None:
             self._sched = self.matrix.to_sched(False, self.device)
         return self._sched
@@ -278,20 +285,20 @@ class _DdsEntry:
 def stk_dds(lhs: torch.Tensor, data: torch.Tensor, offsets: torch.Tensor, row_indices: torch.Tensor,
             column_indices: torch.Tensor, offsets_t: torch.Tensor, column_indices_t: torch.Tensor,
             block_offsets_t: torch.Tensor, shape0: int, shape1: int, transpose_b: bool = True) -> torch.Tensor:
-    """``torch.ops.morph_stk.dds`` (custom_ops.py:35-56) on the packed kernels:
-    ``out[M, shape1] = lhs[M, shape0] @ W^T`` for the BCSR matrix W[shape1, shape0] whose kept
-    blocks are ``data`` -- the call CMSBlockLinear._forward_mortar makes with
-    ``(in_features, out_features, True)`` (block_sparse.py:956-966).  The transposed metadata is
-    not needed.
+    """``torch.ops.morph_stk.dds`` (custom_ops.py:35-56) on the packed kernels.
+    transpose_b=True: the BCSR matrix W is [shape1, shape0] and the result is ``lhs @ W^T`` -- the
+    call CMSBlockLinear._forward_mortar makes with ``(in_features, out_features, True)``
+    (block_sparse.py:956-966).  transpose_b=False: W is [shape0, shape1] and the result is
+    ``lhs @ W`` -- the input gradient of that forward (custom_ops.py:112-124), served by the same
+    kernels on the transposed matrix.  The reference's transposed metadata is not needed.
     A layer is recognised by its persistent index buffers (``offsets`` / ``column_indices``); its
     converted weights are reused while an exact hash of ``data`` stays the same and converted
     again when it changes (a weight update, a reloaded checkpoint).  ``dds_assume_frozen()`` skips
     the hash for inference."""
-    if not transpose_b:
-        raise ValueError("morph_stk::dds: only the transpose_b=True form of the MLP forward is served")
     if not lhs.is_cuda:
         raise NotImplementedError("morph_stk::dds is a CUDA-only operator (no CPU path)")
-    key = (offsets.data_ptr(), column_indices.data_ptr(), tuple(data.shape), int(shape0), int(shape1))
+    out_f, in_f = (int(shape1), int(shape0)) if transpose_b else (int(shape0), int(shape1))
+    key = (offsets.data_ptr(), column_indices.data_ptr(), tuple(data.shape), out_f, in_f)
     ent = _DDS_CACHE.get(key)
     fp = None
     if ent is not None and not _DDS_ASSUME_FROZEN:
@@ -301,16 +308,94 @@ def stk_dds(lhs: torch.Tensor, data: torch.Tensor, offsets: torch.Tensor, row_in
     if ent is None:
         if fp is None:
             fp = _fingerprint(data)
-        ent = _DdsEntry(_ternary_matrix_from_data(data, offsets, column_indices, int(shape1), int(shape0)),
-                        fp, lhs.device)
+        ent = _DdsEntry(_ternary_matrix_from_data(data, offsets, column_indices, out_f, in_f), fp, lhs.device)
         _DDS_CACHE[key] = ent
         while len(_DDS_CACHE) > _CACHE_MAX:
             _DDS_CACHE.popitem(last=False)
     else:
         _DDS_CACHE.move_to_end(key)
-    if _takes_tc(lhs, int(shape0)):
-        return ops.linear_tc(lhs, ent.sched())
-    return ops.linear(lhs, ent.stream())
+    k_features = in_f if transpose_b else out_f
+    if _takes_tc(lhs, k_features):
+        return ops.linear_tc(lhs, ent.sched(not transpose_b))
+    return ops.linear(lhs, ent.stream(not transpose_b))
+
+
+# topologies (no values) for the weight gradient, keyed by the layer's index buffers
+_TOPO_CACHE: "OrderedDict" = OrderedDict()
+
+
+def _topology(offsets: torch.Tensor, column_indices: torch.Tensor, blk: int, device):
+    key = (offsets.data_ptr(), column_indices.data_ptr(), int(blk))
+    hit = _TOPO_CACHE.get(key)
+    if hit is not None:
+        _TOPO_CACHE.move_to_end(key)
+        return hit
+    off = offsets.detach().cpu().numpy().astype(np.int64)
+    ci = column_indices.detach().cpu().numpy().astype(np.int64)
+    t = blk // 16
+    Rb = len(off) - 1
+    n_cols = int(ci.max(initial=-1)) + 1
+    row_ptr, cols, gather = [0], [], np.zeros((len(ci), t, t), dtype=np.int64)
+    for R in range(Rb):
+        bc = ci[off[R]:off[R + 1]]
+        n_r = len(bc)
+        tile_cols = (bc[:, None] * t + np.arange(t)[None, :]).reshape(-1)
+        for i in range(t):
+            base = row_ptr[-1]
+            cols.append(tile_cols)
+            row_ptr.append(base + n_r * t)
+            # tile (block c of this row, sub-row i, sub-column j) sits at base + c*t + j
+            gather[off[R]:off[R + 1], i, :] = base + np.arange(n_r)[:, None] * t + np.arange(t)[None, :]
+    col_idx = np.concatenate(cols).astype(np.uint16) if cols else np.zeros(0, dtype=np.uint16)
+    m = MortarMatrix(Rb * blk, max(n_cols, 1) * blk, np.asarray(row_ptr, dtype=np.int32), col_idx,
+                     np.zeros((len(col_idx), 64), dtype=np.uint8), 1.0)
+    hit = (TopologyDev(m, device), torch.from_numpy(gather).to(device))
+    _TOPO_CACHE[key] = hit
+    while len(_TOPO_CACHE) > _CACHE_MAX:
+        _TOPO_CACHE.popitem(last=False)
+    return hit
+
+
+def stk_sdd_at_b(a: torch.Tensor, b: torch.Tensor, data: torch.Tensor, offsets: torch.Tensor,
+                 row_indices: torch.Tensor, column_indices: torch.Tensor) -> torch.Tensor:
+    """``torch.ops.morph_stk.sdd_at_b`` (custom_ops.py:68-89): ``a^T @ b`` restricted to the BCSR
+    topology of ``data`` -> [nnz, blk, blk] in the dtype of ``a``; with a = dy [M, out] and
+    b = x [M, in] this is the weight gradient of the carved forward.  ``data`` supplies only the
+    block shape."""
+    if not a.is_cuda:
+        raise NotImplementedError("morph_stk::sdd_at_b is a CUDA-only operator (no CPU path)")
+    nnz, blk, _ = data.shape
+    topo, gather = _topology(offsets, column_indices, blk, a.device)
+    if b.shape[-1] != topo.tile_cols * 16:
+        # the column count of the topology comes from the largest kept column; widen to the operand
+        topo.tile_cols = b.shape[-1] // 16
+    tiles = ops.sdd_tiles(a, b, topo, out_dtype=torch.float32)                    # [nnz16, 16, 16]
+    t = blk // 16
+    blocks = tiles[gather]                                                        # [nnz, t, t, 16, 16]
+    return blocks.permute(0, 1, 3, 2, 4).reshape(nnz, blk, blk).to(a.dtype)
+
+
+def _dds_setup_context(ctx, inputs, output):
+    (lhs, data, offsets, row_indices, column_indices, offsets_t, column_indices_t, block_offsets_t,
+     shape0, shape1, transpose_b) = inputs
+    ctx.save_for_backward(lhs, data, offsets, row_indices, column_indices, offsets_t, column_indices_t,
+                          block_offsets_t)
+    ctx.shape0, ctx.shape1, ctx.transpose_b = shape0, shape1, transpose_b
+
+
+def _dds_backward(ctx, grad):
+    """dlhs = grad @ (W or W^T) -- another dds; ddata = the product of the two dense operands on
+    the topology -- sdd_at_b (the reference's rule, custom_ops.py:91-133)."""
+    (lhs, data, offsets, row_indices, column_indices, offsets_t, column_indices_t, block_offsets_t) = ctx.saved_tensors
+    dy = grad if grad.is_contiguous() else grad.contiguous()
+    dlhs = ddata = None
+    if ctx.needs_input_grad[0]:
+        dlhs = torch.ops.morph_stk.dds(dy, data, offsets, row_indices, column_indices, offsets_t, column_indices_t,
+                                       block_offsets_t, ctx.shape1, ctx.shape0, not ctx.transpose_b)
+    if ctx.needs_input_grad[1]:
+        a, b = (dy, lhs) if ctx.transpose_b else (lhs, dy)
+        ddata = torch.ops.morph_stk.sdd_at_b(a, b, data, offsets, row_indices, column_indices)
+    return (dlhs, ddata, None, None, None, None, None, None, None, None, None)
 
 
 def _dds_fake(lhs, data, offsets, row_indices, column_indices, offsets_t, column_indices_t, block_offsets_t,
@@ -321,15 +406,22 @@ def _dds_fake(lhs, data, offsets, row_indices, column_indices, offsets_t, column
 _DDS_SCHEMA = ("(Tensor lhs, Tensor data, Tensor offsets, Tensor row_indices, Tensor column_indices, "
                "Tensor offsets_t, Tensor column_indices_t, Tensor block_offsets_t, SymInt shape0, "
                "SymInt shape1, bool transpose_b) -> Tensor")
+_SDD_SCHEMA = ("(Tensor a, Tensor b, Tensor data, Tensor offsets, Tensor row_indices, Tensor column_indices) "
+               "-> Tensor")
 _morph_stk_libs = []        # keeps the torch.library.Library objects alive
 
 
+def _sdd_fake(a, b, data, offsets, row_indices, column_indices):
+    return a.new_empty(data.shape)
+
+
 def install_morph_stk_dds() -> str:
-    """Makes ``torch.ops.morph_stk.dds`` run the packed kernels.  When nothing has defined the op
-    yet it is defined here with the reference's schema (custom_ops.py:35-66: CUDA-only,
-    ``mutates_args=()``, a fake kernel for tracing) and "defined" is returned; when the reference
-    package was imported first and owns the definition, its CUDA kernel is replaced and
-    "overridden" is returned.  Idempotent."""
+    """Makes ``torch.ops.morph_stk.dds`` and ``torch.ops.morph_stk.sdd_at_b`` run the packed
+    kernels.  When nothing has defined the ops yet they are defined here with the reference's
+    schemas (custom_ops.py:35-133: CUDA-only, ``mutates_args=()``, fake kernels for tracing, the
+    dds autograd rule) and "defined" is returned; when the reference package was imported first and
+    owns the definitions (and the autograd rule, which calls the two ops), their CUDA kernels are
+    replaced and "overridden" is returned.  Idempotent."""
     if _morph_stk_libs:
         return _morph_stk_libs[0][1]
     try:
@@ -339,12 +431,17 @@ def install_morph_stk_dds() -> str:
     if not have:
         lib = torch.library.Library("morph_stk", "FRAGMENT")
         lib.define("dds" + _DDS_SCHEMA)
+        lib.define("sdd_at_b" + _SDD_SCHEMA)
         lib.impl("dds", stk_dds, "CUDA")
+        lib.impl("sdd_at_b", stk_sdd_at_b, "CUDA")
         torch.library.register_fake("morph_stk::dds", _dds_fake, lib=lib)
+        torch.library.register_fake("morph_stk::sdd_at_b", _sdd_fake, lib=lib)
+        torch.library.register_autograd("morph_stk::dds", _dds_backward, setup_context=_dds_setup_context, lib=lib)
         _morph_stk_libs.append((lib, "defined"))
     else:
         lib = torch.library.Library("morph_stk", "IMPL")
         lib.impl("dds", stk_dds, "CUDA", allow_override=True)
+        lib.impl("sdd_at_b", stk_sdd_at_b, "CUDA", allow_override=True)
         _morph_stk_libs.append((lib, "overridden"))
     return _morph_stk_libs[0][1]
 
