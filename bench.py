@@ -355,6 +355,19 @@ def measured_fp8_peak(device, n: int = 8192, reps: int = 10):
         return {"unavailable": f"{type(e).__name__}: {str(e)[:160]}"}
 
 
+def measured_int8_peak(device, n: int = 8192, reps: int = 10):
+    """Dense int8 tensor-core peak through the library GEMM (torch._int_mm), burst figure: the
+    denominator of the opt-in 8-bit arm.  Bench-only."""
+    try:
+        a = torch.randint(-127, 128, (n, n), device=device, dtype=torch.int8)
+        b = torch.randint(-127, 128, (n, n), device=device, dtype=torch.int8).t()
+        t = time_steps(lambda: torch._int_mm(a, b), reps, 3, None)
+        return {"int8_tops_burst": round(2 * n ** 3 / (min(t) * 1e-3) / 1e12, 1),
+                "how": f"torch._int_mm {n}^3, best of {reps}"}
+    except Exception as e:      # noqa: BLE001
+        return {"unavailable": f"{type(e).__name__}: {str(e)[:160]}"}
+
+
 def tensor_roofline(tf: float, pk: dict, fp8: dict | None = None) -> dict:
     r = {"bound": "tensor", "achieved": round(tf, 2), "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
          "frac": round(tf / pk["bf16_tflops_sustained"], 5), "peak_source": pk["source"] + " (bf16 sustained)"}
@@ -463,7 +476,8 @@ def run_ours(args, rank, world, local_rank):
             prefill["roofline"] = tensor_roofline(prefill["useful_tflops"], pk, fp8)
             extra["prefill_cloud"] = prefill
             for name, fn in (("single_layer_c0", run_single_layer), ("prefill_cloud_blocks128", run_prefill_blocks128),
-                             ("sweep_c3", run_sweep), ("remoe_c4", run_remoe), ("gemv_large_b1", run_gemv_large)):
+                             ("prefill_cloud_i8", run_prefill_i8), ("sweep_c3", run_sweep), ("remoe_c4", run_remoe),
+                             ("gemv_large_b1", run_gemv_large)):
                 with ClockSampler(local_rank) as sc:
                     extra[name] = fn(mb, device, pk, flush)
                 extra[name]["clocks"] = sc.summary()
@@ -592,6 +606,41 @@ def run_prefill_blocks128(mb, device, pk, flush, tokens: int = PREFILL_TOKENS, r
     tf = flops / (ms * 1e-3) / 1e12
     return {"ms_per_application": round(ms, 3), "tokens": tokens, "useful_tflops": round(tf, 2),
             "roofline": tensor_roofline(tf, pk), "device_error_word": mb.ops.prefill_error()}
+
+
+def run_prefill_i8(mb, device, pk, flush, tokens: int = PREFILL_TOKENS, reps: int = 5):
+    """The opt-in 8-bit arm (tcgen05 kind::i8 on per-row quantised activations) beside the bf16 arm on
+    one cloud-shape MLP, single-tile and 128-block topologies: time of the whole MLP (the two
+    quantisation launches included) and its error against the bf16 arm's output -- relative to the
+    output RMS, and the share of elements outside the bf16 element-wise tolerance, which is why the
+    arm is not the default."""
+    d, f = CLOUD["d_model"], CLOUD["d_ff"]
+    x = mb.synth.make_activations(tokens, d, seed=7).to(device)
+    peak = measured_int8_peak(device)
+    out = {"tokens": tokens, "measured_int8_peak": peak, "default_arm": "bf16"}
+    L = mb.synth.make_layer(d, f, DENSITY, seed=CLOUD["seed0"])
+    cases = {"tile16": (L.gate_up, L.down),
+             "blocks128": (mb.synth.make_block_matrix(2 * f, d, DENSITY, seed=11),
+                           mb.synth.make_block_matrix(d, f, DENSITY, seed=12))}
+    for name, (gu_m, dn_m) in cases.items():
+        g16, d16 = gu_m.to_sched(True, device), dn_m.to_sched(False, device)
+        g8, d8 = gu_m.to_sched(True, device, arith="i8"), dn_m.to_sched(False, device, arith="i8")
+        ms16 = statistics.median(time_steps(lambda: mb.ops.mlp_prefill_tc(x, g16, d16), reps, 2, flush))
+        ms8 = statistics.median(time_steps(lambda: mb.ops.mlp_prefill_tc_i8(x, g8, d8), reps, 2, flush))
+        y16 = mb.ops.mlp_prefill_tc(x[:2048], g16, d16).float()
+        y8 = mb.ops.mlp_prefill_tc_i8(x[:2048], g8, d8).float()
+        err = (y8 - y16).abs()
+        flops = 2 * 256 * (gu_m.nnz + dn_m.nnz) * tokens
+        tf8 = flops / (ms8 * 1e-3) / 1e12
+        cell = {"ms_bf16": round(ms16, 3), "ms_i8": round(ms8, 3), "useful_tops_i8": round(tf8, 1),
+                "launches_i8": 4,
+                "rms_error_over_rms_output": round(float(err.pow(2).mean().sqrt() / y16.pow(2).mean().sqrt()), 5),
+                "fraction_outside_1e-2_rel_1e-3_abs": round(float((err > 1e-2 * y16.abs() + 1e-3).float().mean()), 5)}
+        if "int8_tops_burst" in peak:
+            cell["frac_of_measured_int8_burst"] = round(tf8 / peak["int8_tops_burst"], 5)
+        out[name] = cell
+    out["device_error_word"] = mb.ops.prefill_error()
+    return out
 
 
 def run_sweep(mb, device, pk, flush, tokens: int = 8192, reps: int = 3):

@@ -378,6 +378,7 @@ typedef struct mortar_sched {
     int32_t tile_cols;
     int32_t swiglu;                 /* 1: rows [0,R/2) gate, [R/2,R) up, output = silu(g)*u */
     float scale;
+    int32_t arith;                  /* 0: bf16 schedule (mortar_build_sched), 1: int8 (mortar_build_sched_i8) */
 } mortar_sched;
 
 /* Sizes of the schedule of a matrix (host).  swiglu selects the gate/up row pairing. */
@@ -400,6 +401,32 @@ int mortar_build_sched(const int32_t *row_ptr, const uint16_t *col_idx, const ui
 int mortar_linear_tc(const mortar_sched *w, const void *x, int64_t ldx, int64_t rows,
                      void *out, int64_t ld_out, const float *gates, int64_t ld_gates,
                      int32_t cluster_size, void *stream);
+
+/* Opt-in 8-bit arm of the same kernel (not the reference's arithmetic: the activations are
+ * quantised, so results differ from mortar_linear_tc by the quantisation error; with activations
+ * that are exactly representable -- integers in [-127, 127] with a row maximum of 127 -- the two
+ * agree bit for bit).  The schedule pairs horizontally adjacent tiles into slots of 16 x 32 codes
+ * (the int8 MMA's K is 32), a chunk is 128 features, codes are stored one nibble each. */
+int mortar_sched_sizes_i8(const int32_t *row_ptr, const uint16_t *col_idx, int32_t tile_rows,
+                          int32_t tile_cols, int32_t swiglu, int64_t *n_tiles, int64_t *n_runs,
+                          int64_t *n_steps, int32_t *n_panels, int64_t *data_units);
+int mortar_build_sched_i8(const int32_t *row_ptr, const uint16_t *col_idx, const uint8_t *codes,
+                          int32_t tile_rows, int32_t tile_cols, int64_t nnz, int32_t swiglu,
+                          uint8_t *step_data, uint32_t *step_off, uint32_t *step_meta,
+                          int32_t *panel_step_ptr, uint32_t *panel_mask);
+
+/* Per-row symmetric quantisation of bf16 activations: scale[r] = max|x[r]| / 127,
+ * q[r][c] = round(x[r][c] / scale[r]) as int8 (an all-zero row gets scale 0).  cols a multiple
+ * of 8; x 16-byte aligned with ldx a multiple of 8; q 16-byte aligned with ldq a multiple of 16. */
+int mortar_quantize_rows(const void *x, int64_t ldx, int64_t rows, int32_t cols, void *q,
+                         int64_t ldq, float *scale, void *stream);
+
+/* mortar_linear_tc on int8 activations: tcgen05.mma kind::i8 with int32 accumulators; the
+ * epilogue multiplies the sum by x_scale[row] * the bf16-rounded matrix scale and continues as
+ * the bf16 arm does.  w: a schedule with arith == 1.  xq [rows][ldxq] int8, x_scale [rows]. */
+int mortar_linear_tc_i8(const mortar_sched *w, const void *xq, int64_t ldxq, const float *x_scale,
+                        int64_t rows, void *out, int64_t ld_out, const float *gates,
+                        int64_t ld_gates, int32_t cluster_size, void *stream);
 
 /* _SwiGLUMortar.forward on a block of tokens (transformer.py:402-431) as two launches of the
  * kernel above.  workspace: device, 256-byte aligned, rows*d_ff*2 bytes (the hidden block). */

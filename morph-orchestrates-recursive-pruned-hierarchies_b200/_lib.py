@@ -45,7 +45,8 @@ class Sched(C.Structure):
                 ("panel_step_ptr", C.c_void_p), ("panel_mask", C.c_void_p),
                 ("n_tiles", C.c_int64), ("n_runs", C.c_int64), ("n_steps", C.c_int64),
                 ("data_units", C.c_int64), ("n_panels", C.c_int32), ("tile_rows", C.c_int32),
-                ("tile_cols", C.c_int32), ("swiglu", C.c_int32), ("scale", C.c_float)]
+                ("tile_cols", C.c_int32), ("swiglu", C.c_int32), ("scale", C.c_float),
+                ("arith", C.c_int32)]
 
 
 _lib = None
@@ -86,6 +87,10 @@ _SIGNATURES = {
     "mortar_sched_sizes": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp]),
     "mortar_build_sched": (C.c_int, [_vp, _vp, _vp, _i32, _i32, _i64, _i32, _vp, _vp, _vp, _vp, _vp]),
     "mortar_linear_tc": (C.c_int, [C.POINTER(Sched), _vp, _i64, _i64, _vp, _i64, _vp, _i64, _i32, _vp]),
+    "mortar_sched_sizes_i8": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp]),
+    "mortar_build_sched_i8": (C.c_int, [_vp, _vp, _vp, _i32, _i32, _i64, _i32, _vp, _vp, _vp, _vp, _vp]),
+    "mortar_quantize_rows": (C.c_int, [_vp, _i64, _i64, _i32, _vp, _i64, _vp, _vp]),
+    "mortar_linear_tc_i8": (C.c_int, [C.POINTER(Sched), _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _i32, _vp]),
     "mortar_mlp_prefill": (C.c_int, [C.POINTER(Sched), C.POINTER(Sched), _vp, _i64, _i64, _vp, _i64,
                                      _i32, _vp, _i64, _vp, _i64, _vp]),
     "mortar_sdd_tiles": (C.c_int, [_vp, _i64, _vp, _i64, _i64, _vp, _vp, _i32, _i32, _vp, _vp, _i32, _vp, _i32, _vp]),

@@ -9,6 +9,7 @@
 // Geometry of the prefill panel schedule (shared by the host builder and the kernel).
 #define MORTAR_PANEL_ROWS 16   // tile rows per panel = 256 fp32 accumulator columns of tensor memory
 #define MORTAR_CHUNK_COLS 4    // tile columns per chunk = 64 features = one 128-byte swizzle row
+#define MORTAR_STEP_SLOTS_I8 24 // slots (pairs of tiles) per step of the int8 schedule
 #define MORTAR_STEP_TILES 48   // tile slots one B stage of the kernel holds (24 KB of bf16 tiles)
 
 // Records the text of a failed CUDA runtime call for mortar_last_cuda_error().

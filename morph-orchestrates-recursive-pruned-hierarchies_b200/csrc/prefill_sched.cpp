@@ -81,8 +81,13 @@ inline int cover_column(const int32_t *s, int *lo, int *hi) {
 // Panels 2s and 2s+1 are executed side by side on one stream of activation chunks, so both
 // list exactly the same chunks: a panel without tiles on a chunk its partner uses gets an
 // empty step (header only) there.
+// kind 0: bf16 schedule as described above.  kind 1: int8 schedule -- the MMA's K is 32, so a slot
+// is a PAIR of horizontally adjacent tiles (tile columns 2w, 2w+1; a missing half is zero codes), a
+// chunk is 4 such pairs = 128 features, a step holds at most MORTAR_STEP_SLOTS_I8 slots, and a
+// slot's codes are stored one nibble per code (16 rows x 4 words; word k = columns 8k..8k+7 of the
+// pair, stored value = code + 1), the form the kernel's byte-permute expansion reads.
 static int build(const int32_t *row_ptr, const uint16_t *col_idx, const uint8_t *codes, int32_t R,
-                 int32_t C, int32_t swiglu, int64_t *n_tiles_out, int64_t *n_runs_out,
+                 int32_t C, int32_t swiglu, int32_t kind, int64_t *n_tiles_out, int64_t *n_runs_out,
                  int64_t *n_steps_out, int32_t *n_panels_out, int64_t *data_units_out,
                  uint8_t *step_data, uint32_t *step_off, uint32_t *step_meta,
                  int32_t *panel_step_ptr, uint32_t *panel_mask) {
@@ -94,7 +99,10 @@ static int build(const int32_t *row_ptr, const uint16_t *col_idx, const uint8_t 
     const int per_panel = swiglu ? P / 2 : P;
     // panels are executed in pairs: pad to an even count with an all-empty panel
     const int NP = ((units + per_panel - 1) / per_panel + 1) & ~1;
-    const int NC = (C + CC - 1) / CC;
+    if (kind != 0 && kind != 1) return MORTAR_ERR_DTYPE;
+    const int CW = kind ? (C + 1) / 2 : C;          // columns in slot units
+    const int NC = (CW + CC - 1) / CC;
+    const int step_cap = kind ? MORTAR_STEP_SLOTS_I8 : MORTAR_STEP_TILES;
     const bool fill = step_data != nullptr;
 #ifdef MORTAR_SCHED_TUNING
     if (const char *e = getenv("MORTAR_SCHED_FLOOR")) kMmaFloorClk = atoi(e);
@@ -104,6 +112,7 @@ static int build(const int32_t *row_ptr, const uint16_t *col_idx, const uint8_t 
     // bucket tiles by cell: slot[cell][col_local][row_local] = tile index or -1
     const int64_t cells = (int64_t)NP * NC;
     std::vector<int32_t> slot((size_t)cells * CC * P, -1);
+    std::vector<int32_t> slot_b(kind ? (size_t)cells * CC * P : 0, -1);      // right half of a pair (kind 1)
     for (int r = 0; r < R; ++r) {
         if (row_ptr[r + 1] < row_ptr[r]) return MORTAR_ERR_ROWPTR;
         int local;
@@ -111,13 +120,22 @@ static int build(const int32_t *row_ptr, const uint16_t *col_idx, const uint8_t 
         for (int64_t j = row_ptr[r]; j < row_ptr[r + 1]; ++j) {
             const int c = col_idx ? col_idx[j] : 0;
             if (c >= C) return MORTAR_ERR_COLIDX;
-            slot[(((size_t)panel * NC + c / CC) * CC + c % CC) * P + local] = (int32_t)j;
+            const int cw = kind ? c / 2 : c;
+            const size_t at = (((size_t)panel * NC + cw / CC) * CC + cw % CC) * P + local;
+            if (kind && (c & 1)) slot_b[at] = (int32_t)j;
+            else slot[at] = (int32_t)j;
         }
     }
+    // liveness of a slot: either half of the pair holds a tile; -2 marks "right half only"
+    if (kind)
+        for (size_t i = 0; i < slot.size(); ++i)
+            if (slot[i] < 0 && slot_b[i] >= 0) slot[i] = -2;
+    auto live = [&](int32_t v) { return v >= 0 || v == -2; };
     struct Run { int cl, lo, first, len; };
     int64_t nt = 0, nr = 0, ns = 0, units16 = 0, n_gap = 0;
     std::vector<Run> step_runs;
-    std::vector<int32_t> step_tiles;
+    std::vector<int32_t> step_tiles;           // kind 0: tile index or -1; kind 1: position in `slot` or -1
+    const int slot_units = kind ? 16 : 4;      // 16-byte units of codes per slot
     bool step_init = false;            // the step under construction starts with the initialising MMA
     auto flush = [&](int ch, bool reuse, bool last) {
         const int ntile = (int)step_tiles.size(), nrun = (int)step_runs.size();
@@ -136,7 +154,22 @@ static int build(const int32_t *row_ptr, const uint16_t *col_idx, const uint8_t 
                 rr[i] = (uint16_t)(step_runs[i].lo | (step_runs[i].first << 4) | (step_runs[i].cl << 10) |
                                    ((step_runs[i].len - 1) << 12));
             uint32_t *td = reinterpret_cast<uint32_t *>(step_data + (units16 + 1 + run_units) * 16);
-            for (int i = 0; i < ntile; ++i) {
+            for (int i = 0; kind && i < ntile; ++i) {
+                const int32_t pos = step_tiles[i];
+                const int32_t ta = pos >= 0 ? slot[pos] : -1, tb = pos >= 0 ? slot_b[pos] : -1;
+                for (int row = 0; row < 16; ++row) {
+                    uint32_t ca = 0x55555555u, cb = 0x55555555u;      // stored value 1 = code 0
+                    if (ta >= 0) memcpy(&ca, codes + (int64_t)ta * 64 + row * 4, 4);
+                    if (tb >= 0) memcpy(&cb, codes + (int64_t)tb * 64 + row * 4, 4);
+                    for (int k = 0; k < 4; ++k) {
+                        const uint32_t src = k < 2 ? ca : cb;
+                        uint32_t w = 0;
+                        for (int e = 0; e < 8; ++e) w |= ((src >> (2 * ((k & 1) * 8 + e))) & 3u) << (4 * e);
+                        td[(i * 16 + row) * 4 + k] = w;
+                    }
+                }
+            }
+            for (int i = 0; !kind && i < ntile; ++i) {
                 for (int row = 0; row < 16; ++row) {
                     uint32_t canon = 0x55555555u;                        // stored value 1 = code 0
                     if (step_tiles[i] >= 0) memcpy(&canon, codes + (int64_t)step_tiles[i] * 64 + row * 4, 4);
@@ -149,7 +182,7 @@ static int build(const int32_t *row_ptr, const uint16_t *col_idx, const uint8_t 
                 }
             }
         }
-        units16 += 1 + run_units + 4 * (int64_t)ntile;
+        units16 += 1 + run_units + slot_units * (int64_t)ntile;
         nt += ntile; nr += nrun; ++ns;
         step_runs.clear(); step_tiles.clear();
         step_init = false;
@@ -157,7 +190,7 @@ static int build(const int32_t *row_ptr, const uint16_t *col_idx, const uint8_t 
     // which cells hold at least one tile
     std::vector<uint8_t> cell_used((size_t)cells, 0);
     for (size_t i = 0; i < slot.size(); ++i)
-        if (slot[i] >= 0) cell_used[i / ((size_t)CC * P)] = 1;
+        if (live(slot[i])) cell_used[i / ((size_t)CC * P)] = 1;
     for (int p = 0; p < NP; ++p) {
         uint32_t touched = 0;
         bool initialised = false;       // the panel's accumulators hold defined values
@@ -174,7 +207,8 @@ static int build(const int32_t *row_ptr, const uint16_t *col_idx, const uint8_t 
             for (int cl = 0; cl < CC; ++cl) {
                 const int32_t *s = &slot[(cell * CC + cl) * P];
                 int n_live = 0;
-                for (int l = 0; l < P; ++l) n_live += s[l] >= 0;
+                int32_t lv[P];                                           // >= 0 where the slot is live
+                for (int l = 0; l < P; ++l) { lv[l] = live(s[l]) ? 0 : -1; n_live += lv[l] >= 0; }
                 if (n_live == 0) continue;
                 // intervals [lo, hi) of local rows that one MMA each will cover
                 int lo[P], hi[P], n_iv = 0;
@@ -183,11 +217,11 @@ static int build(const int32_t *row_ptr, const uint16_t *col_idx, const uint8_t 
                     // zero tiles), so every later MMA of the item accumulates
                     lo[0] = 0; hi[0] = P; n_iv = 1;
                 } else {
-                    n_iv = cover_column(s, lo, hi);
+                    n_iv = cover_column(lv, lo, hi);
                 }
                 for (int v = 0; v < n_iv; ++v) {
                     const int len = hi[v] - lo[v];
-                    if ((int)step_tiles.size() + len > MORTAR_STEP_TILES) {
+                    if ((int)step_tiles.size() + len > step_cap) {
                         flush(ch, !first_of_chunk, false);
                         first_of_chunk = false;
                     }
@@ -198,8 +232,9 @@ static int build(const int32_t *row_ptr, const uint16_t *col_idx, const uint8_t 
                     if (!initialised) step_init = true;      // always the first run of a fresh step (see below)
                     step_runs.push_back(run);
                     for (int k = lo[v]; k < hi[v]; ++k) {
-                        step_tiles.push_back(s[k]);                      // -1 = zero tile (gap)
-                        if (s[k] >= 0) touched |= 1u << k;
+                        if (kind) step_tiles.push_back(live(s[k]) ? (int32_t)((cell * CC + cl) * P + k) : -1);
+                        else step_tiles.push_back(s[k]);                 // -1 = zero tile (gap)
+                        if (live(s[k])) touched |= 1u << k;
                         else ++n_gap;
                     }
                     initialised = true;
@@ -218,7 +253,7 @@ static int build(const int32_t *row_ptr, const uint16_t *col_idx, const uint8_t 
 extern "C" int mortar_sched_sizes(const int32_t *row_ptr, const uint16_t *col_idx, int32_t R, int32_t C,
                                   int32_t swiglu, int64_t *n_tiles, int64_t *n_runs, int64_t *n_steps,
                                   int32_t *n_panels, int64_t *data_units) {
-    return build(row_ptr, col_idx, nullptr, R, C, swiglu, n_tiles, n_runs, n_steps, n_panels, data_units,
+    return build(row_ptr, col_idx, nullptr, R, C, swiglu, 0, n_tiles, n_runs, n_steps, n_panels, data_units,
                  nullptr, nullptr, nullptr, nullptr, nullptr);
 }
 
@@ -230,6 +265,25 @@ extern "C" int mortar_build_sched(const int32_t *row_ptr, const uint16_t *col_id
     if (v != MORTAR_OK) return v;
     if (!step_data) return MORTAR_ERR_NULL;
     int64_t nt, nr, ns, du; int32_t np;
-    return build(row_ptr, col_idx, codes, R, C, swiglu, &nt, &nr, &ns, &np, &du, step_data, step_off,
+    return build(row_ptr, col_idx, codes, R, C, swiglu, 0, &nt, &nr, &ns, &np, &du, step_data, step_off,
+                 step_meta, panel_step_ptr, panel_mask);
+}
+
+extern "C" int mortar_sched_sizes_i8(const int32_t *row_ptr, const uint16_t *col_idx, int32_t R, int32_t C,
+                                     int32_t swiglu, int64_t *n_tiles, int64_t *n_runs, int64_t *n_steps,
+                                     int32_t *n_panels, int64_t *data_units) {
+    return build(row_ptr, col_idx, nullptr, R, C, swiglu, 1, n_tiles, n_runs, n_steps, n_panels, data_units,
+                 nullptr, nullptr, nullptr, nullptr, nullptr);
+}
+
+extern "C" int mortar_build_sched_i8(const int32_t *row_ptr, const uint16_t *col_idx, const uint8_t *codes,
+                                     int32_t R, int32_t C, int64_t nnz, int32_t swiglu, uint8_t *step_data,
+                                     uint32_t *step_off, uint32_t *step_meta, int32_t *panel_step_ptr,
+                                     uint32_t *panel_mask) {
+    int v = mortar_validate_bcsr(row_ptr, col_idx, codes, R, C, nnz);
+    if (v != MORTAR_OK) return v;
+    if (!step_data) return MORTAR_ERR_NULL;
+    int64_t nt, nr, ns, du; int32_t np;
+    return build(row_ptr, col_idx, codes, R, C, swiglu, 1, &nt, &nr, &ns, &np, &du, step_data, step_off,
                  step_meta, panel_step_ptr, panel_mask);
 }

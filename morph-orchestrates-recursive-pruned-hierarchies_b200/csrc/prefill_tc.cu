@@ -25,6 +25,7 @@
 #include <cuda_bf16.h>
 #include <cstdint>
 #include <mutex>
+#include <type_traits>
 #include "common.h"
 #include "decode.cuh"
 
@@ -49,6 +50,8 @@ constexpr int kEpilogueThreads = 32 * kEpilogueWarps;
 constexpr int kMmaWarp0 = 11, kMmaWarp1 = 15, kTmaWarp = 19, kIdleWarp = 18;
 constexpr int kThreads = 32 * 20;                            // 640
 constexpr int kWordsPerThread = kStepTiles * 16 / kDecodeThreads;   // 6 row words per decoder per step
+constexpr int kStepSlotsI8 = MORTAR_STEP_SLOTS_I8;                  // int8 schedule: 24 slots of 16 x 32 codes
+constexpr int kRowsPerThreadI8 = kStepSlotsI8 * 16 / kDecodeThreads; // 3 row records (16 bytes) per decoder per step
 constexpr int kNumBars = 2 * kAStages + kPipes * 2 * kBStages + 2;
 constexpr int kSmemBytes = kAStages * kAStage + kPipes * kBStages * kBStage + kNumBars * 8 + 1024 /*align*/;
 constexpr uint32_t kWaitLimit = 1u << 22;
@@ -85,6 +88,7 @@ struct PrefillParams {
     __nv_bfloat16 *out;
     long long ld_out;
     float scale;                  // per-matrix scale rounded to bf16
+    const float *x_scale;         // int8 arm: per-row activation scales [rows]
     const float *gates;
     long long ld_gates;
     int cluster_size;
@@ -157,6 +161,16 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint32_t a_lo, uint32_t 
         "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}\n"
         ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate));
 }
+__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                          uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n.reg .b64 da, db;\n"
+        "setp.ne.b32 p, %6, 0;\n"
+        "mov.b64 da, {%1, %2};\n"
+        "mov.b64 db, {%3, %4};\n"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %5, p;\n}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate));
+}
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
                  ::"r"(bar) : "memory");
@@ -226,9 +240,12 @@ struct StepCursor {
 };
 
 // Drains one item's accumulators of one pipe: the epilogue of warp (pipe, quadrant q).
-template <bool SWIGLU, bool GATED>
+template <bool SWIGLU, bool GATED, bool I8>
 __device__ __forceinline__ void epilogue_item(const PrefillParams &p, uint32_t taddr, int panel, long long row,
                                               bool in_range, uint32_t mask) {
+    // int8 arm: the accumulators are int32 sums of (quantised activation x code); the row's
+    // activation scale joins the per-matrix scale
+    const float scale = I8 ? p.scale * (in_range ? __ldg(p.x_scale + row) : 0.f) : p.scale;
     constexpr int units = SWIGLU ? kPanelRows / 2 : kPanelRows;
     const bool tile_gates = GATED && (p.cluster_size % 16 == 0);     // one gate per 16-column tile
 #pragma unroll 1
@@ -253,10 +270,10 @@ __device__ __forceinline__ void epilogue_item(const PrefillParams &p, uint32_t t
                 gate0 = __ldg(p.gates + row * p.ld_gates + (col0 + e) / p.cluster_size);
                 gate1 = __ldg(p.gates + row * p.ld_gates + (col0 + e + 1) / p.cluster_size);
             }
-            packed[e >> 1] = finish2<SWIGLU, GATED>(p.scale, __uint_as_float(a[e]), __uint_as_float(a[e + 1]),
-                                                    SWIGLU ? __uint_as_float(b[e]) : 0.f,
-                                                    SWIGLU ? __uint_as_float(b[e + 1]) : 0.f, live_a, live_b,
-                                                    gate0, gate1);
+            auto val = [](uint32_t bits) { return I8 ? __int2float_rn((int)bits) : __uint_as_float(bits); };
+            packed[e >> 1] = finish2<SWIGLU, GATED>(scale, val(a[e]), val(a[e + 1]),
+                                                    SWIGLU ? val(b[e]) : 0.f, SWIGLU ? val(b[e + 1]) : 0.f,
+                                                    live_a, live_b, gate0, gate1);
         }
         if (in_range) {
             uint4 *dst = reinterpret_cast<uint4 *>(p.out + row * p.ld_out + col0);
@@ -272,6 +289,10 @@ __device__ __forceinline__ void epilogue_item(const PrefillParams &p, uint32_t t
     }
 }
 
+// I8 = false: bf16 activations x ternary codes expanded to bf16 (kind::f16, fp32 accumulators).
+// I8 = true: int8 activations (quantised per row by quantize_rows_kernel) x codes expanded to
+// int8 (kind::i8, int32 accumulators, K = 32 per MMA: a slot is a pair of tiles side by side).
+template <bool I8>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_panel_kernel(const __grid_constant__ CUtensorMap tmap_x, const PrefillParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -328,9 +349,9 @@ prefill_panel_kernel(const __grid_constant__ CUtensorMap tmap_x, const PrefillPa
             PF_ACC(1);
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const uint32_t taddr = tmem + pipe * kAccCols + ((uint32_t)(q * 32) << 16);
-            if (!p.swiglu) epilogue_item<false, false>(p, taddr, panel, row, in_range, mask);
-            else if (p.gates == nullptr) epilogue_item<true, false>(p, taddr, panel, row, in_range, mask);
-            else epilogue_item<true, true>(p, taddr, panel, row, in_range, mask);
+            if (!p.swiglu) epilogue_item<false, false, I8>(p, taddr, panel, row, in_range, mask);
+            else if (p.gates == nullptr) epilogue_item<true, false, I8>(p, taddr, panel, row, in_range, mask);
+            else epilogue_item<true, true, I8>(p, taddr, panel, row, in_range, mask);
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             mbar_arrive(smem_u32(acc_empty));                         // accumulators drained
             PF_ACC(2);
@@ -344,7 +365,9 @@ prefill_panel_kernel(const __grid_constant__ CUtensorMap tmap_x, const PrefillPa
         const uint32_t acc = tmem + pipe * kAccCols;
         // instruction descriptor of an N = 16 MMA: kind::f16, D fp32 (bit 4), A bf16 (bit 7), B bf16
         // (bit 10), both K-major, N>>3 at bit 17, M>>4 at bit 24; a run of len tiles adds (len-1)<<18
-        constexpr uint32_t kIdesc16 = (1u << 4) | (1u << 7) | (1u << 10) | (2u << 17) | ((128u >> 4) << 24);
+        // (kind::i8: D s32 = 2 at bit 4, A and B s8 = 1 at bits 7 and 10)
+        constexpr uint32_t kIdesc16 = I8 ? ((2u << 4) | (1u << 7) | (1u << 10) | (2u << 17) | ((128u >> 4) << 24))
+                                         : ((1u << 4) | (1u << 7) | (1u << 10) | (2u << 17) | ((128u >> 4) << 24));
         int g = 0, ga = -1, it = 0;
         bool ok = true;
         PF_DECL;
@@ -386,10 +409,14 @@ prefill_panel_kernel(const __grid_constant__ CUtensorMap tmap_x, const PrefillPa
 #pragma unroll
                         for (int k = 0; k < 8; ++k) {
                             const uint32_t w = (k & 1) ? (ws[k >> 1] >> 16) : (ws[k >> 1] & 0xffffu);
-                            if (r + k < nrun)
-                                tc_mma(acc + (w & 15u) * 16u, a_lo + ((w >> 10) & 3u) * 2u, a_hi,
-                                       b_lo + ((w >> 4) & 63u) * 32u, b_hi, kIdesc16 + ((w >> 12) << 18),
-                                       (r + k) ? 1u : keep0);
+                            if (r + k < nrun) {
+                                if (I8) tc_mma_i8(acc + (w & 15u) * 16u, a_lo + ((w >> 10) & 3u) * 2u, a_hi,
+                                                  b_lo + ((w >> 4) & 63u) * 32u, b_hi, kIdesc16 + ((w >> 12) << 18),
+                                                  (r + k) ? 1u : keep0);
+                                else tc_mma(acc + (w & 15u) * 16u, a_lo + ((w >> 10) & 3u) * 2u, a_hi,
+                                            b_lo + ((w >> 4) & 63u) * 32u, b_hi, kIdesc16 + ((w >> 12) << 18),
+                                            (r + k) ? 1u : keep0);
+                            }
                         }
                     }
                     PF_ACC(4);
@@ -430,7 +457,7 @@ prefill_panel_kernel(const __grid_constant__ CUtensorMap tmap_x, const PrefillPa
                     "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
                     "[%0], [%1, {%2, %3}], [%4];\n"
                     ::"r"(smem_u32(sA + as * kAStage)), "l"(&tmap_x),
-                      "r"((int)(meta & 0x3fffu) * kChunkCols * 16), "r"(row0), "r"(bar) : "memory");
+                      "r"((int)(meta & 0x3fffu) * (I8 ? 128 : kChunkCols * 16)), "r"(row0), "r"(bar) : "memory");
             }
             __syncwarp();
             ++ga;
@@ -452,25 +479,29 @@ prefill_panel_kernel(const __grid_constant__ CUtensorMap tmap_x, const PrefillPa
             meta = 0; off = 0;
             if (c.valid(p)) { meta = __ldg(p.step_meta + c.s); off = __ldg(p.step_off + c.s); }
         };
-        auto fetch_words = [&](uint32_t meta, uint32_t off, uint32_t (&w)[kWordsPerThread], uint4 &run) {
+        // one row record = the codes of one tile row of a slot: a 32-bit word (bf16 arm: 16 codes)
+        // or 16 bytes (int8 arm: 32 codes as nibbles)
+        using Row = typename std::conditional<I8, uint4, uint32_t>::type;
+        constexpr int kW = I8 ? kRowsPerThreadI8 : kWordsPerThread;
+        auto fetch_words = [&](uint32_t meta, uint32_t off, Row (&w)[kW], uint4 &run) {
             const int ntile = (meta >> 14) & 63, nrun = (meta >> 20) & 63;
             const int run_units = (nrun + 7) >> 3;
             const uint8_t *rec = p.step_data + (size_t)off * 16;
             run = make_uint4(0, 0, 0, 0);
             if (td < run_units) run = __ldg(reinterpret_cast<const uint4 *>(rec + 16) + td);
-            const uint32_t *words = reinterpret_cast<const uint32_t *>(rec + 16 + run_units * 16);
+            const Row *words = reinterpret_cast<const Row *>(rec + 16 + run_units * 16);
 #pragma unroll
-            for (int k = 0; k < kWordsPerThread; ++k) {
+            for (int k = 0; k < kW; ++k) {
                 const int idx = td + k * kDecodeThreads;
-                w[k] = idx < ntile * 16 ? __ldg(words + idx) : 0u;
+                if (idx < ntile * 16) w[k] = __ldg(words + idx);
             }
         };
         // Expands the step (cur, mc) held in (w, run) into its B stage; before that it requests the
         // following step's record (mn, on) into (wn, runn), so those loads are in flight while this
         // step waits for its stage and is expanded.  The two register sets swap roles from call to
         // call (no copy, so nothing waits for the loads before they are used).
-        auto do_step = [&](uint32_t mc, const uint32_t (&w)[kWordsPerThread], const uint4 &run,
-                           bool have_next, uint32_t mn, uint32_t on, uint32_t (&wn)[kWordsPerThread],
+        auto do_step = [&](uint32_t mc, const Row (&w)[kW], const uint4 &run,
+                           bool have_next, uint32_t mn, uint32_t on, Row (&wn)[kW],
                            uint4 &runn) -> bool {
             const int bs = g % kBStages;
             if (have_next) fetch_words(mn, on, wn, runn);
@@ -486,16 +517,26 @@ prefill_panel_kernel(const __grid_constant__ CUtensorMap tmap_x, const PrefillPa
                 *reinterpret_cast<uint4 *>(bdst + kBTiles + kRunBytes) = make_uint4(ntile, nrun, mc, (mc >> 29) & 1u);
             }
 #pragma unroll
-            for (int k = 0; k < kWordsPerThread; ++k) {
+            for (int k = 0; k < kW; ++k) {
                 const int idx = td + k * kDecodeThreads;
                 if (idx < ntile * 16) {
                     const int tile = idx >> 4, row = idx & 15;
                     uint32_t o[8];
+                    if constexpr (I8) {
+                        // a nibble (stored value 0, 1, 2) selects the byte -1, 0, +1 of the table
+                        const uint32_t ws[4] = {w[k].x, w[k].y, w[k].z, w[k].w};
 #pragma unroll
-                    for (int qq = 0; qq < 8; ++qq) o[qq] = mortar_decode_pair(w[k], qq);
+                        for (int qq = 0; qq < 4; ++qq) {
+                            asm("prmt.b32 %0, %1, %2, %3;" : "=r"(o[2 * qq]) : "r"(0x000100ffu), "r"(0u), "r"(ws[qq]));
+                            asm("prmt.b32 %0, %1, %2, %3;" : "=r"(o[2 * qq + 1]) : "r"(0x000100ffu), "r"(0u), "r"(ws[qq] >> 16));
+                        }
+                    } else {
+#pragma unroll
+                        for (int qq = 0; qq < 8; ++qq) o[qq] = mortar_decode_pair(w[k], qq);
+                    }
                     uint8_t *d = bdst + tile * 512 + (row >> 3) * 256 + (row & 7) * 16;
-                    *reinterpret_cast<uint4 *>(d) = make_uint4(o[0], o[1], o[2], o[3]);         // features 0..7
-                    *reinterpret_cast<uint4 *>(d + 128) = make_uint4(o[4], o[5], o[6], o[7]);   // features 8..15
+                    *reinterpret_cast<uint4 *>(d) = make_uint4(o[0], o[1], o[2], o[3]);         // first 16 bytes of K
+                    *reinterpret_cast<uint4 *>(d + 128) = make_uint4(o[4], o[5], o[6], o[7]);   // second 16 bytes of K
                 }
             }
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
@@ -514,7 +555,7 @@ prefill_panel_kernel(const __grid_constant__ CUtensorMap tmap_x, const PrefillPa
             if (c[k].valid(p)) c[k].next(p, n_super, pipe);
             fetch_info(c[k], m[k], o[k]);
         }
-        uint32_t wa[kWordsPerThread], wb[kWordsPerThread];
+        Row wa[kW], wb[kW];
         uint4 runa, runb;
         if (c[0].valid(p)) fetch_words(m[0], o[0], wa, runa);
         auto advance = [&]() {
@@ -568,18 +609,21 @@ int get_encode_fn(EncodeTiledFn *out) {
 
 inline bool aligned_to(const void *ptr, size_t a) { return (reinterpret_cast<uintptr_t>(ptr) % a) == 0; }
 
-}  // namespace
-
-extern "C" int mortar_linear_tc(const mortar_sched *w, const void *x, int64_t ldx, int64_t rows,
-                                void *out, int64_t ld_out, const float *gates, int64_t ld_gates,
-                                int32_t cluster_size, void *stream) {
+// One launch of the panel kernel.  I8: x is int8 [rows][ldx] with per-row scales x_scale.
+template <bool I8>
+int linear_tc_impl(const mortar_sched *w, const void *x, int64_t ldx, int64_t rows, const float *x_scale,
+                   void *out, int64_t ld_out, const float *gates, int64_t ld_gates,
+                   int32_t cluster_size, void *stream) {
     if (!w || !x || !out || !w->panel_step_ptr || !w->panel_mask) return MORTAR_ERR_NULL;
+    if (I8 && !x_scale) return MORTAR_ERR_NULL;
     if (w->n_steps > 0 && (!w->step_data || !w->step_off || !w->step_meta)) return MORTAR_ERR_NULL;
     if (w->tile_rows <= 0 || w->tile_cols <= 0 || w->n_panels <= 0 || rows < 0) return MORTAR_ERR_SHAPE;
+    if (w->arith != (I8 ? 1 : 0)) return MORTAR_ERR_DTYPE;       // schedule built for the other arm
     const int K = w->tile_cols * 16;
     const int units = w->swiglu ? w->tile_rows / 2 : w->tile_rows;
     if (ldx < K || ld_out < (int64_t)units * 16) return MORTAR_ERR_SHAPE;
-    if (!aligned_to(x, 16) || (ldx % 8) || !aligned_to(out, 16) || (ld_out % 8)) return MORTAR_ERR_ALIGN;
+    const int x_elems16 = I8 ? 16 : 8;                          // elements per 16 bytes of x
+    if (!aligned_to(x, 16) || (ldx % x_elems16) || !aligned_to(out, 16) || (ld_out % 8)) return MORTAR_ERR_ALIGN;
     if (!aligned_to(w->step_data, 16)) return MORTAR_ERR_ALIGN;
     if (gates && (cluster_size <= 0 || !w->swiglu)) return MORTAR_ERR_SHAPE;
     if (rows == 0) return MORTAR_OK;
@@ -593,12 +637,13 @@ extern "C" int mortar_linear_tc(const mortar_sched *w, const void *x, int64_t ld
     if (rc != MORTAR_OK) return rc;
     alignas(64) CUtensorMap tmap;
     const cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    const cuuint64_t gstride[1] = {(cuuint64_t)ldx * 2};
-    const cuuint32_t box[2] = {64, (cuuint32_t)kRows};
+    const cuuint64_t gstride[1] = {(cuuint64_t)ldx * (I8 ? 1 : 2)};
+    const cuuint32_t box[2] = {I8 ? 128u : 64u, (cuuint32_t)kRows};    // 128 bytes wide either way
     const cuuint32_t estride[2] = {1, 1};
-    CUresult cr = encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(x), gdim, gstride,
-                         box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult cr = encode(&tmap, I8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                         const_cast<void *>(x), gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (cr != CUDA_SUCCESS) {
         mortar_set_cuda_error("cuTensorMapEncodeTiled", "failed to encode the activation tensor map");
         return MORTAR_ERR_CUDA;
@@ -606,7 +651,7 @@ extern "C" int mortar_linear_tc(const mortar_sched *w, const void *x, int64_t ld
 
     int dev = 0;
     MORTAR_CUDA_CHECK(cudaGetDevice(&dev));
-    static int sm_count[64] = {0};
+    static int sm_count[64] = {0};                               // one table per arm
     if (dev < 0 || dev >= 64) return MORTAR_ERR_CAPACITY;
     int sms = 0;
     {
@@ -614,7 +659,7 @@ extern "C" int mortar_linear_tc(const mortar_sched *w, const void *x, int64_t ld
         if (sm_count[dev] == 0) {
             int v = 0;
             MORTAR_CUDA_CHECK(cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev));
-            MORTAR_CUDA_CHECK(cudaFuncSetAttribute(prefill_panel_kernel,
+            MORTAR_CUDA_CHECK(cudaFuncSetAttribute(prefill_panel_kernel<I8>,
                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
             sm_count[dev] = v;
         }
@@ -634,11 +679,83 @@ extern "C" int mortar_linear_tc(const mortar_sched *w, const void *x, int64_t ld
     p.out = reinterpret_cast<__nv_bfloat16 *>(out);
     p.ld_out = ld_out;
     p.scale = __bfloat162float(__float2bfloat16_rn(w->scale));
+    p.x_scale = x_scale;
     p.gates = gates;
     p.ld_gates = ld_gates;
     p.cluster_size = cluster_size > 0 ? cluster_size : 1;
     const unsigned grid = (unsigned)(n_items < sms ? n_items : sms);
-    prefill_panel_kernel<<<grid, kThreads, kSmemBytes, (cudaStream_t)stream>>>(tmap, p);
+    prefill_panel_kernel<I8><<<grid, kThreads, kSmemBytes, (cudaStream_t)stream>>>(tmap, p);
+    MORTAR_CUDA_CHECK(cudaGetLastError());
+    return MORTAR_OK;
+}
+
+// Per-row symmetric int8 quantisation: scale[r] = max|x[r]| / 127, q = round(x / scale[r]).
+// One CTA per row; the row is read twice (the second time from cache).
+__global__ void __launch_bounds__(256)
+quantize_rows_kernel(const __nv_bfloat16 *__restrict__ x, long long ldx, int cols, int8_t *__restrict__ q,
+                     long long ldq, float *__restrict__ scale) {
+    const long long row = blockIdx.x;
+    const uint4 *src = reinterpret_cast<const uint4 *>(x + row * ldx);      // 8 values per load
+    const int n8 = cols >> 3;
+    float m = 0.f;
+    for (int i = threadIdx.x; i < n8; i += blockDim.x) {
+        const uint4 v = __ldg(src + i);
+        const uint32_t ws[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const __nv_bfloat162 h = __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&ws[k]));
+            m = fmaxf(m, fmaxf(__low2float(h), __high2float(h)));
+        }
+    }
+    __shared__ float red[8];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    m = red[0];
+#pragma unroll
+    for (int k = 1; k < 8; ++k) m = fmaxf(m, red[k]);
+    const float inv = m > 0.f ? 127.f / m : 0.f;
+    if (threadIdx.x == 0) scale[row] = m / 127.f;
+    uint2 *dst = reinterpret_cast<uint2 *>(q + row * ldq);
+    for (int i = threadIdx.x; i < n8; i += blockDim.x) {
+        const uint4 v = __ldg(src + i);
+        const uint32_t ws[4] = {v.x, v.y, v.z, v.w};
+        uint32_t o[2] = {0u, 0u};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162 *>(&ws[k]);
+            const int a = max(-127, min(127, __float2int_rn(__low2float(h) * inv)));
+            const int b = max(-127, min(127, __float2int_rn(__high2float(h) * inv)));
+            o[k >> 1] |= ((uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8)) << ((k & 1) * 16);
+        }
+        dst[i] = make_uint2(o[0], o[1]);
+    }
+}
+
+}  // namespace
+
+extern "C" int mortar_linear_tc(const mortar_sched *w, const void *x, int64_t ldx, int64_t rows,
+                                void *out, int64_t ld_out, const float *gates, int64_t ld_gates,
+                                int32_t cluster_size, void *stream) {
+    return linear_tc_impl<false>(w, x, ldx, rows, nullptr, out, ld_out, gates, ld_gates, cluster_size, stream);
+}
+
+extern "C" int mortar_linear_tc_i8(const mortar_sched *w, const void *xq, int64_t ldxq, const float *x_scale,
+                                   int64_t rows, void *out, int64_t ld_out, const float *gates,
+                                   int64_t ld_gates, int32_t cluster_size, void *stream) {
+    return linear_tc_impl<true>(w, xq, ldxq, rows, x_scale, out, ld_out, gates, ld_gates, cluster_size, stream);
+}
+
+extern "C" int mortar_quantize_rows(const void *x, int64_t ldx, int64_t rows, int32_t cols, void *q,
+                                    int64_t ldq, float *scale, void *stream) {
+    if (!x || !q || !scale) return MORTAR_ERR_NULL;
+    if (rows < 0 || cols <= 0 || (cols % 8) || ldx < cols || ldq < cols || rows > 0x7fffffffLL)
+        return MORTAR_ERR_SHAPE;
+    if (!aligned_to(x, 16) || (ldx % 8) || !aligned_to(q, 16) || (ldq % 16)) return MORTAR_ERR_ALIGN;
+    if (rows == 0) return MORTAR_OK;
+    quantize_rows_kernel<<<(unsigned)rows, 256, 0, (cudaStream_t)stream>>>(
+        reinterpret_cast<const __nv_bfloat16 *>(x), ldx, cols, reinterpret_cast<int8_t *>(q), ldq, scale);
     MORTAR_CUDA_CHECK(cudaGetLastError());
     return MORTAR_OK;
 }

@@ -299,9 +299,10 @@ class MortarMatrix:
                    "mortar_build_stream")
         return grp_ptr, grp_cols, grp_codes, int(G)
 
-    def to_sched(self, swiglu: bool, device="cuda") -> "SchedMatrix":
-        """Prefill (tcgen05) execution layout; `swiglu` pairs gate rows with up rows."""
-        return SchedMatrix(self, swiglu, device)
+    def to_sched(self, swiglu: bool, device="cuda", arith: str = "bf16") -> "SchedMatrix":
+        """Prefill (tcgen05) execution layout; `swiglu` pairs gate rows with up rows;
+        ``arith="i8"`` builds the layout of the opt-in 8-bit arm."""
+        return SchedMatrix(self, swiglu, device, arith)
 
     def to_stream(self, device="cuda") -> "StreamMatrix":
         grp_ptr, grp_cols, grp_codes, G = self.build_stream_host()
@@ -333,25 +334,30 @@ class TopologyDev:
 PANEL_ROWS, CHUNK_COLS, STEP_TILES = 16, 4, 48
 
 
-def build_sched_host(m: "MortarMatrix", swiglu: bool):
-    """Host arrays of the prefill panel schedule of `m` (see ``mortar_sched`` in the header)."""
+def build_sched_host(m: "MortarMatrix", swiglu: bool, arith: str = "bf16"):
+    """Host arrays of the prefill panel schedule of `m` (see ``mortar_sched`` in the header);
+    ``arith="i8"`` builds the paired-tile schedule of the int8 arm."""
+    if arith not in ("bf16", "i8"):
+        raise ValueError(f"unknown schedule arithmetic {arith!r}")
     L = _lib.lib()
+    f_sizes = L.mortar_sched_sizes if arith == "bf16" else L.mortar_sched_sizes_i8
+    f_build = L.mortar_build_sched if arith == "bf16" else L.mortar_build_sched_i8
     rp = np.ascontiguousarray(m.row_ptr)
     ci = np.ascontiguousarray(m.col_idx)
     cd = np.ascontiguousarray(m.codes)
     nt, nr, ns, du = C.c_int64(0), C.c_int64(0), C.c_int64(0), C.c_int64(0)
     npan = C.c_int32(0)
-    _lib.check(L.mortar_sched_sizes(_ptr(rp), _ptr(ci), m.tile_rows, m.tile_cols, int(swiglu),
-                                    C.byref(nt), C.byref(nr), C.byref(ns), C.byref(npan),
-                                    C.byref(du)), "mortar_sched_sizes")
+    _lib.check(f_sizes(_ptr(rp), _ptr(ci), m.tile_rows, m.tile_cols, int(swiglu),
+                       C.byref(nt), C.byref(nr), C.byref(ns), C.byref(npan),
+                       C.byref(du)), "mortar_sched_sizes")
     data = np.zeros(max(du.value, 1) * 16, dtype=np.uint8)
     off = np.zeros(ns.value + 1, dtype=np.uint32)
     meta = np.zeros(max(ns.value, 1), dtype=np.uint32)
     psp = np.zeros(npan.value + 1, dtype=np.int32)
     mask = np.zeros(npan.value, dtype=np.uint32)
-    _lib.check(L.mortar_build_sched(_ptr(rp), _ptr(ci), _ptr(cd), m.tile_rows, m.tile_cols, m.nnz,
-                                    int(swiglu), _ptr(data), _ptr(off), _ptr(meta), _ptr(psp),
-                                    _ptr(mask)), "mortar_build_sched")
+    _lib.check(f_build(_ptr(rp), _ptr(ci), _ptr(cd), m.tile_rows, m.tile_cols, m.nnz,
+                       int(swiglu), _ptr(data), _ptr(off), _ptr(meta), _ptr(psp),
+                       _ptr(mask)), "mortar_build_sched")
     return dict(step_data=data, step_off=off, step_meta=meta, panel_step_ptr=psp, panel_mask=mask,
                 n_tiles=nt.value, n_runs=nr.value, n_steps=ns.value, n_panels=npan.value,
                 data_units=du.value)
@@ -360,8 +366,9 @@ def build_sched_host(m: "MortarMatrix", swiglu: bool):
 class SchedMatrix:
     """Device-resident prefill schedule of one matrix (owns its tensors)."""
 
-    def __init__(self, m: "MortarMatrix", swiglu: bool, device="cuda"):
-        h = build_sched_host(m, swiglu)
+    def __init__(self, m: "MortarMatrix", swiglu: bool, device="cuda", arith: str = "bf16"):
+        h = build_sched_host(m, swiglu, arith)
+        self.arith = arith
         self.out_features, self.in_features = m.out_features, m.in_features
         self.swiglu, self.scale, self.nnz = bool(swiglu), float(m.scale), m.nnz
         self.n_tiles, self.n_runs, self.n_steps = h["n_tiles"], h["n_runs"], h["n_steps"]
@@ -380,6 +387,7 @@ class SchedMatrix:
         """A schedule whose arrays already live on the device (the registered ops pass them as
         tensors); borrows the tensors."""
         self = cls.__new__(cls)
+        self.arith = "bf16"
         self.out_features, self.in_features = int(out_features), int(in_features)
         self.swiglu, self.scale, self.nnz = bool(swiglu), float(scale), 0
         self.n_tiles, self.n_runs, self.n_steps = int(n_tiles), int(n_runs), int(n_steps)
@@ -399,7 +407,8 @@ class SchedMatrix:
                                  self.step_meta.data_ptr(), self.panel_step_ptr.data_ptr(),
                                  self.panel_mask.data_ptr(), self.n_tiles, self.n_runs, self.n_steps,
                                  self.data_units, self.n_panels, self.out_features // TILE,
-                                 self.in_features // TILE, int(self.swiglu), self.scale)
+                                 self.in_features // TILE, int(self.swiglu), self.scale,
+                                 1 if self.arith == "i8" else 0)
         return self._c
 
 

@@ -589,6 +589,65 @@ def mlp_prefill_tc(x: torch.Tensor, gate_up: SchedMatrix, down: SchedMatrix, *,
     return out.reshape(*lead, d_model)
 
 
+def quantize_rows(x: torch.Tensor):
+    """Per-row symmetric int8 quantisation of bf16 activations [rows, cols] on the device:
+    (q int8 [rows, cols], scale fp32 [rows]) with scale = max|row| / 127."""
+    _require_cuda(x, "x")
+    if x.dtype != torch.bfloat16 or x.dim() != 2:
+        raise ValueError("quantize_rows takes a 2-D bfloat16 tensor")
+    if x.stride(1) != 1 or x.stride(0) % 8 or x.data_ptr() % 16:
+        x = x.contiguous()
+    rows, cols = x.shape
+    ldq = (cols + 15) // 16 * 16
+    q = torch.empty(rows, ldq, device=x.device, dtype=torch.int8)
+    scale = torch.empty(rows, device=x.device, dtype=torch.float32)
+    _lib.check(_lib.lib().mortar_quantize_rows(_ptr(x), x.stride(0), rows, cols, _ptr(q), ldq, _ptr(scale),
+                                               _stream_ptr()), "mortar_quantize_rows")
+    _count("quantize_rows")
+    return q[:, :cols], scale
+
+
+def linear_tc_i8(x: torch.Tensor, w: SchedMatrix, *, gates: Optional[torch.Tensor] = None,
+                 cluster_size: int = 0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``linear_tc`` on the 8-bit tensor-core path: the bf16 activations are quantised per row to
+    int8, the products run as tcgen05 kind::i8 with int32 accumulators.  NOT the reference's
+    arithmetic (activation quantisation error of about 1% of an output's typical magnitude);
+    opt-in only.  ``w`` is a ``SchedMatrix(..., arith="i8")``."""
+    _require_cuda(x, "x")
+    if x.dtype != torch.bfloat16:
+        raise ValueError("linear_tc_i8 takes bfloat16 activations")
+    if w.arith != "i8":
+        raise ValueError("linear_tc_i8 needs a schedule built with arith='i8'")
+    lead = x.shape[:-1]
+    x2 = _rows2d(x, w.in_features, "x")
+    rows = x2.shape[0]
+    n_out = w.n_out
+    if out is None:
+        out = torch.empty(rows, n_out, device=x.device, dtype=torch.bfloat16)
+    out2 = out.reshape(rows, n_out)
+    if rows == 0:
+        return out.reshape(*lead, n_out)
+    q, xs = quantize_rows(x2)
+    g = None
+    if gates is not None:
+        g = gates.to(device=x.device, dtype=torch.float32).reshape(rows, -1).contiguous()
+    st = w.c_struct()
+    _lib.check(_lib.lib().mortar_linear_tc_i8(C.byref(st), _ptr(q), q.stride(0), _ptr(xs), rows, _ptr(out2),
+                                              out2.stride(0), _ptr(g), g.stride(0) if g is not None else 0,
+                                              int(cluster_size), _stream_ptr()), "mortar_linear_tc_i8")
+    _count("prefill_panel_i8")
+    return out.reshape(*lead, n_out)
+
+
+def mlp_prefill_tc_i8(x: torch.Tensor, gate_up: SchedMatrix, down: SchedMatrix, *,
+                      gates: Optional[torch.Tensor] = None, n_clusters: int = 0) -> torch.Tensor:
+    """The SwiGLU block on the 8-bit path: quantise x, gate/up product with the SwiGLU epilogue
+    (bf16 hidden block), quantise the hidden block, down product.  Four launches; opt-in."""
+    d_ff = gate_up.out_features // 2
+    h = linear_tc_i8(x, gate_up, gates=gates, cluster_size=(d_ff // n_clusters) if gates is not None else 0)
+    return linear_tc_i8(h, down)
+
+
 def sdd_tiles(dy: torch.Tensor, x: torch.Tensor, topo: TopologyDev, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
     """Weight gradient on the topology: [nnz, 16, 16] with tile (r, c) = dy[:, 16r:16r+16]^T @
     x[:, 16c:16c+16] (bf16 operands, fp32 accumulation) -- ``morph_stk::sdd_at_b`` at tile 16

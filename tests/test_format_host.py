@@ -299,6 +299,60 @@ def test_prefill_schedule_covers_every_tile_once(swiglu, density):
         assert all(((int(w) >> 12) & 15) + 1 == 16 for w in rec0[16:16 + 2 * int(rec0[4:8].view(np.uint32)[0])].view(np.uint16))
 
 
+@pytest.mark.parametrize("swiglu", [False, True])
+@pytest.mark.parametrize("density", [0.35, 1.0])
+def test_prefill_schedule_i8_pairs_tiles(swiglu, density):
+    """The int8 schedule replayed on the host: a slot is a pair of horizontally adjacent tiles
+    (16 rows x 32 columns, one nibble per code, stored value = code + 1), a chunk is four pairs;
+    summing every run's slots rebuilds the dense code matrix, a missing half holds zero codes."""
+    rng = np.random.default_rng(5)
+    R, C = (40, 23) if not swiglu else (48, 23)          # odd column count: the last pair is half empty
+    mask = rng.random((R, C)) < density
+    codes = rng.integers(-1, 2, size=(R * 16, C * 16)).astype(np.int8)
+    m = mb.MortarMatrix.from_codes(codes, mask, 1.0)
+    h = fmt.build_sched_host(m, swiglu, arith="i8")
+    P, CC = fmt.PANEL_ROWS, fmt.CHUNK_COLS
+    dense = np.zeros((R * 16, (C + 1) // 2 * 32), dtype=np.int32)
+    data = h["step_data"]
+    for p in range(h["n_panels"]):
+        started = False
+        for st in range(h["panel_step_ptr"][p], h["panel_step_ptr"][p + 1]):
+            rec = data[int(h["step_off"][st]) * 16:int(h["step_off"][st + 1]) * 16]
+            n_in_step, n_runs, ck, init = (int(v) for v in rec[:16].view(np.uint32))
+            run_units = (n_runs + 7) // 8
+            assert len(rec) == 16 + 16 * run_units + 256 * n_in_step
+            assert n_in_step <= 24
+            ch = ck & 0x3FFF
+            runs = rec[16:16 + 2 * n_runs].view(np.uint16).astype(int)
+            words = rec[16 + 16 * run_units:].view(np.uint32).reshape(n_in_step, 16, 4)
+            nib = np.stack([(words >> (4 * e)) & 15 for e in range(8)], axis=-1)      # [slot,row,word,8]
+            assert nib.max(initial=0) <= 2
+            slots = nib.reshape(n_in_step, 16, 32).astype(np.int32) - 1
+            for r in range(n_runs):
+                w = int(runs[r])
+                l0, first, cl, n = w & 15, (w >> 4) & 63, (w >> 10) & 3, ((w >> 12) & 15) + 1
+                if not started:
+                    assert (l0, n) == (0, P) and init
+                    started = True
+                pair = ch * CC + cl
+                for k in range(n):
+                    l = l0 + k
+                    if swiglu:
+                        half = P // 2
+                        trow = p * half + l if l < half else R // 2 + p * half + (l - half)
+                    else:
+                        trow = p * P + l
+                    t = slots[first + k]
+                    if trow >= R:
+                        assert not t.any()
+                        continue
+                    dense[trow * 16:(trow + 1) * 16, pair * 32:(pair + 1) * 32] += t
+    np.testing.assert_array_equal(dense[:, :C * 16], m.to_dense_codes())
+    assert not dense[:, C * 16:].any()
+    with pytest.raises(ValueError):
+        fmt.build_sched_host(m, swiglu, arith="fp4")
+
+
 @pytest.mark.parametrize("case", GOLDEN_CASES)
 def test_state_dict_ingestion(case):
     """mortar_* checkpoint keys (packed and unpacked flavours) -> canonical matrix."""
