@@ -17,27 +17,49 @@ SOURCES = ["host_pack.cpp", "prefill_sched.cpp", "stream_kernels.cu", "prefill_t
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 
-def _newest_source_mtime() -> float:
-    paths = [os.path.join(CSRC, f) for f in os.listdir(CSRC)]
-    paths.append(os.path.join(ROOT, "include", "mortar_b200.h"))
+OBJ = os.path.join(PKG, "_build")            # per-source objects (ignored by git; only the .so is used)
+
+
+def _deps_mtime(src: str) -> float:
+    """A source is rebuilt when it, any header beside it or the public header is newer than its object."""
+    paths = [os.path.join(CSRC, src), os.path.join(ROOT, "include", "mortar_b200.h")]
+    paths += [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
     return max(os.path.getmtime(p) for p in paths)
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile every source under csrc/ into one shared library; returns its path."""
-    if not force and os.path.exists(LIB) and os.path.getmtime(LIB) >= _newest_source_mtime():
-        return LIB
+    """Compile every source under csrc/ (in parallel, one object each) and link one shared library;
+    returns its path."""
+    from concurrent.futures import ThreadPoolExecutor
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-    cmd = [nvcc, "-O3", "-std=c++17", "-lineinfo", *ARCH, "-shared", "-Xcompiler", "-fPIC",
-           "-I", os.path.join(ROOT, "include"), "-I", CSRC]
+    os.makedirs(OBJ, exist_ok=True)
+    base = [nvcc, "-O3", "-std=c++17", "-lineinfo", *ARCH, "-Xcompiler", "-fPIC",
+            "-I", os.path.join(ROOT, "include"), "-I", CSRC]
     if verbose:
-        cmd += ["-Xptxas", "-v"]
-    cmd += [os.path.join(CSRC, s) for s in SOURCES] + ["-o", LIB]
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if verbose or res.returncode != 0:
-        sys.stderr.write(res.stdout + res.stderr)
-    if res.returncode != 0:
-        raise RuntimeError(f"nvcc failed ({res.returncode}): {' '.join(cmd)}")
+        base += ["-Xptxas", "-v"]
+
+    def compile_one(src: str):
+        obj = os.path.join(OBJ, src + ".o")
+        if not force and os.path.exists(obj) and os.path.getmtime(obj) >= _deps_mtime(src):
+            return obj, False
+        cmd = base + ["-c", os.path.join(CSRC, src), "-o", obj]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if verbose or res.returncode != 0:
+            sys.stderr.write(res.stdout + res.stderr)
+        if res.returncode != 0:
+            raise RuntimeError(f"nvcc failed ({res.returncode}): {' '.join(cmd)}")
+        return obj, True
+
+    with ThreadPoolExecutor(max_workers=len(SOURCES)) as pool:
+        results = list(pool.map(compile_one, SOURCES))
+    objs = [o for o, _ in results]
+    if any(changed for _, changed in results) or not os.path.exists(LIB) or \
+            os.path.getmtime(LIB) < max(os.path.getmtime(o) for o in objs):
+        cmd = [nvcc, *ARCH, "-shared", "-Xcompiler", "-fPIC", *objs, "-o", LIB]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            sys.stderr.write(res.stdout + res.stderr)
+            raise RuntimeError(f"link failed ({res.returncode}): {' '.join(cmd)}")
     return LIB
 
 

@@ -175,13 +175,21 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
                  ::"r"(bar) : "memory");
 }
-// 32 accumulator columns of this thread's tensor-memory lane; waits for the data.
+// 32 accumulator columns of this thread's tensor-memory lane; tc_ld_wait() before the first use.
+// The registers are in-out operands of the wait so that no use of them is scheduled above it.
+__device__ __forceinline__ void tc_ld_wait(uint32_t (&r)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n"
+        : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+          "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+          "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+          "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+        :: "memory");
+}
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
         "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
         "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-        "tcgen05.wait::ld.sync.aligned;\n"
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
           "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
           "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
@@ -253,6 +261,8 @@ __device__ __forceinline__ void epilogue_item(const PrefillParams &p, uint32_t t
         uint32_t a[32], b[32];
         tc_ld32(taddr + j * 16, a);
         if (SWIGLU) tc_ld32(taddr + (units + j) * 16, b);
+        tc_ld_wait(a);                                                  // both loads are in flight before the
+        if (SWIGLU) tc_ld_wait(b);                                      // first wait; the second finds nothing pending
         const long long col0 = ((long long)panel * units + j) * 16;
         float tg[2] = {1.f, 1.f};
         if (GATED && tile_gates && in_range) {
@@ -313,7 +323,7 @@ prefill_panel_kernel(const __grid_constant__ CUtensorMap tmap_x, const PrefillPa
     if (threadIdx.x == 0) {
         abort_s = 0;
         for (int s = 0; s < kAStages; ++s) { mbar_init(smem_u32(&a_full[s]), 1); mbar_init(smem_u32(&a_empty[s]), kPipes); }
-        for (int s = 0; s < kPipes * kBStages; ++s) { mbar_init(smem_u32(&b_full[s]), kDecodeThreads); mbar_init(smem_u32(&b_empty[s]), 1); }
+        for (int s = 0; s < kPipes * kBStages; ++s) { mbar_init(smem_u32(&b_full[s]), kDecodeThreads / 32); mbar_init(smem_u32(&b_empty[s]), 1); }
         mbar_init(smem_u32(acc_full), kPipes);
         mbar_init(smem_u32(acc_empty), kEpilogueThreads);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -539,8 +549,11 @@ prefill_panel_kernel(const __grid_constant__ CUtensorMap tmap_x, const PrefillPa
                     *reinterpret_cast<uint4 *>(d + 128) = make_uint4(o[4], o[5], o[6], o[7]);   // second 16 bytes of K
                 }
             }
+            // every lane orders its own stores before the tensor core's reads; one arrival per warp
+            // (128 arrivals on one barrier word serialise)
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-            mbar_arrive(smem_u32(&bf[bs]));
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bf[bs]));
             PF_ACC(4);
             ++g;
             return true;
