@@ -492,7 +492,7 @@ def run_ours(args, rank, world, local_rank):
         "metric": "MORTAR MLP tokens/s (decode stack, 42 MLP applications per token)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": steps,
         "warmup": warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16 planes x ternary, fp32 accumulate",
+        "scaling": "weak", "vs_baseline": None, "dtype": "two scaled fp16 planes of the fp32 activations x ternary codes, fp32 accumulate",
         "data": "synthetic",
         "config": bench_config(world),
         "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": main["h2d"],
@@ -737,6 +737,15 @@ def run_router(mb, device, reps: int = 20, calls: int = 16):
         t = time_steps(g.replay, reps, 3, None)
         out[f"b{b}_us_per_call"] = round(statistics.median(t) * 1e3 / calls, 2)
     out["launches_per_call"] = 2
+    # prefill scale (configs[4] routing: cloud shape, 352 groups, k = 88, 4096 tokens): the d x d
+    # projection runs as a library GEMM, the rest as the router's second launch
+    big = import_module(mb.__name__ + ".router").TileRouter(352, CLOUD["d_model"], activation_ratio=0.25)
+    big = big.to(device).eval()
+    xb = mb.synth.make_activations(4096, CLOUD["d_model"], seed=9, dtype=torch.float32).to(device)
+    t32 = statistics.median(time_steps(lambda: mb.ops.router_gates(xb, big), 5, 2, None))
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        t16 = statistics.median(time_steps(lambda: mb.ops.router_gates(xb, big), 5, 2, None))
+    out["cloud_4096_tokens_ms"] = {"fp32_projection": round(t32, 3), "bf16_autocast_projection": round(t16, 3)}
     return out
 
 

@@ -326,10 +326,16 @@ int mortar_mlp_decode_static(const mortar_stream *gate_up, const mortar_stream *
  *                carry their own copy of the weight (hdr[6] != 0) uses that copy; otherwise row
  *                `layer` of this array; with neither the application runs without normalisation
  *   x            fp32 [rows][ldx] residual carrier, updated in place
+ *   n_planes     1..3: bf16 planes (3 represent fp32 exactly); MORTAR_PLANES_HALF2: two fp16
+ *                planes with exact power-of-two scaling per activation row -- the residual is
+ *                below 2^-22 of an element, the size of an fp32 rounding, at two thirds of the
+ *                tensor work of 3 bf16 planes.  Norm weights above ~2000 in magnitude overflow
+ *                fp16 and give infinities (use 3 for such a model)
  *   status       device int32, set non-zero if a bounded wait inside the kernel expires
  * Limits: cluster_size 8 (or 16 where the device accepts it), d_ff/16 divisible by cluster_size
  * and d_model by 16*cluster_size, everything of one application's rank share must fit shared memory
  * (MORTAR_ERR_CAPACITY otherwise: use mortar_mlp_decode per application). */
+#define MORTAR_PLANES_HALF2 12
 int mortar_stack_decode(const void *blobs, const int32_t *blob_table, const int32_t *app_layer,
                         const float *rms_weights, int32_t n_apps, int32_t n_layers,
                         int32_t d_model, int32_t d_ff, int32_t max_gate_up_bytes,
@@ -446,7 +452,10 @@ int mortar_mlp_prefill(const mortar_sched *gate_up, const mortar_sched *down, co
  *           cyclically when there are fewer (routing.py:185-204)
  *   gates = relu(logits - k-th largest) * k / max(sum, 1e-6)   (k >= n_groups: no threshold)
  * qv_scratch: device, rows*d_model floats (the projected query between the two launches).
- * Two launches on `stream`; no allocation, no synchronisation. */
+ * Two launches on `stream`; no allocation, no synchronisation.
+ * wq == NULL: qv_scratch already holds x wq^T + iter_vec (a caller that runs the dense d x d
+ * product as a library GEMM for large token blocks); x and iter_vec are ignored and only the
+ * second launch (LayerNorm, logits, gate rule) runs. */
 int mortar_router_gates(const float *x, int64_t ldx, int64_t rows, int32_t d_model,
                         const float *wq, const float *iter_vec, const float *ln_weight,
                         const float *ln_bias, float ln_eps, const float *sub_keys_a,

@@ -1,6 +1,7 @@
 // Device-side decode of the 2-bit stored ternary values of the stream layout.
 #pragma once
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cstdint>
 
 // Two 2-bit stored values s = code + 1 (bits 2q..2q+1 and 16+2q..16+2q+1 of `word`, q = 0..7)
@@ -25,5 +26,20 @@ __device__ __forceinline__ uint32_t mortar_decode_pair(uint32_t word, int q) {
     uint32_t v, r;
     asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(v) : "r"(w), "r"(mask), "r"(base));
     asm("sub.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(v), "r"(bias));
+    return r;
+}
+
+// The same decode into a packed fp16 pair.  fp16 has 10 mantissa bits, so all four 2-bit positions
+// of a byte lie inside the mantissa: the constants are 1024, 256, 64 and 16 (units in the last
+// place 1, 1/4, 1/16, 1/64), the subtrahends those plus one.
+__device__ __forceinline__ uint32_t mortar_decode_pair_h(uint32_t word, int q) {
+    const uint32_t w = (q & 4) ? (word >> 8) : word;
+    const int j = q & 3;
+    const uint32_t mask = 0x00030003u << (2 * j);
+    const uint32_t base = j == 0 ? 0x64006400u : j == 1 ? 0x5C005C00u : j == 2 ? 0x54005400u : 0x4C004C00u;
+    const uint32_t bias = j == 0 ? 0x64016401u : j == 1 ? 0x5C045C04u : j == 2 ? 0x54105410u : 0x4C404C40u;
+    uint32_t v, r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(v) : "r"(w), "r"(mask), "r"(base));
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(r) : "r"(v), "r"(bias));
     return r;
 }

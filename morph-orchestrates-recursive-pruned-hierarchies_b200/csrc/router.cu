@@ -157,9 +157,11 @@ extern "C" int mortar_router_gates(const float *x, int64_t ldx, int64_t rows, in
                                    const float *sub_keys_b, int32_t n_sub_keys, const float *group_bias,
                                    int32_t n_groups, int32_t k, float *qv_scratch, float *gates,
                                    int64_t ld_gates, void *stream) {
-    if (!x || !wq || !ln_weight || !ln_bias || !sub_keys_a || !sub_keys_b || !group_bias || !qv_scratch || !gates)
+    // wq == NULL: qv_scratch already holds the projected query (x wq^T + iter_vec), e.g. from a
+    // library GEMM at prefill scale; only the second launch runs
+    if ((wq && !x) || !ln_weight || !ln_bias || !sub_keys_a || !sub_keys_b || !group_bias || !qv_scratch || !gates)
         return MORTAR_ERR_NULL;
-    if (rows < 0 || d_model <= 0 || (d_model & 1) || ldx < d_model || n_sub_keys <= 0 || n_groups <= 0 ||
+    if (rows < 0 || d_model <= 0 || (d_model & 1) || (wq && ldx < d_model) || n_sub_keys <= 0 || n_groups <= 0 ||
         k <= 0 || ld_gates < n_groups)
         return MORTAR_ERR_SHAPE;
     if (rows == 0) return MORTAR_OK;
@@ -170,9 +172,11 @@ extern "C" int mortar_router_gates(const float *x, int64_t ldx, int64_t rows, in
     dim3 grid((d_model + 7) / 8, (unsigned)((rows + kProjRows - 1) / kProjRows));
     const bool vec = (d_model % 4) == 0 && (ldx % 4) == 0 && (reinterpret_cast<uintptr_t>(x) % 16) == 0 &&
                      (reinterpret_cast<uintptr_t>(wq) % 16) == 0;
-    if (vec) router_project_kernel<true><<<grid, 256, 0, st>>>(x, ldx, rows, d_model, wq, iter_vec, qv_scratch);
-    else router_project_kernel<false><<<grid, 256, 0, st>>>(x, ldx, rows, d_model, wq, iter_vec, qv_scratch);
-    MORTAR_CUDA_CHECK(cudaGetLastError());
+    if (wq) {
+        if (vec) router_project_kernel<true><<<grid, 256, 0, st>>>(x, ldx, rows, d_model, wq, iter_vec, qv_scratch);
+        else router_project_kernel<false><<<grid, 256, 0, st>>>(x, ldx, rows, d_model, wq, iter_vec, qv_scratch);
+        MORTAR_CUDA_CHECK(cudaGetLastError());
+    }
     if (smem > 48 * 1024)
         MORTAR_CUDA_CHECK(cudaFuncSetAttribute(router_tail_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     router_tail_kernel<<<(unsigned)rows, kTailThreads, smem, st>>>(qv_scratch, d_model, ln_weight, ln_bias, ln_eps,

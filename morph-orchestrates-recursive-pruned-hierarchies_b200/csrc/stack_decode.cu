@@ -18,8 +18,17 @@
 // mma.m16n8k16 decoded from 2-bit codes in registers, 8 activation rows as exact bf16 planes as
 // the B operand (one accumulator per plane, so the MMAs of a tile are independent), fp32
 // accumulation, scale after the sum (morph/kernels/triton/fused_decode_step.py:1441-1459).
+//
+// Two representations of the fp32 activations: 1..3 bf16 planes (three are exact), or two fp16
+// planes (H = true).  fp16 carries 11 significant bits, so two planes leave a residual below 2^-22
+// of an element -- the size of an fp32 rounding -- at two thirds of the MMAs and fragment loads.
+// Its narrow exponent range is handled by exact power-of-two scaling per activation row: the
+// normalised rows have unit RMS by construction (rows that skip the RMSNorm are scaled by the
+// power of two next to 1/rms), the hidden rows are scaled so that their largest magnitude lies in
+// [2^13, 2^14); the inverse factors are applied to the fp32 sums.
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cooperative_groups.h>
 #include <cstdint>
 #include <mutex>
@@ -48,6 +57,7 @@ struct StackParams {
     int rows;
     float eps;
     int n_planes;
+    int f16;                       // 1: the planes are fp16 (two of them), 0: bf16
     int *status;
     int x_pitch, h_pitch;          // shared-memory row pitch of the plane buffers (bf16 elements)
     int max_a, max_b;              // bytes reserved for the gate/up part and for the down part of a rank's weights
@@ -65,6 +75,37 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4],
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ void mma_16816_h(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// two fp32 values -> P packed 16-bit pairs (residual split, round to nearest at every level)
+template <int P, bool H>
+__device__ __forceinline__ void split_pair(float a, float b, uint32_t (&out)[P]) {
+#pragma unroll
+    for (int pl = 0; pl < P; ++pl) {
+        if (H) {
+            const __half2 h = __floats2half2_rn(a, b);
+            out[pl] = *reinterpret_cast<const uint32_t *>(&h);
+            a -= __low2float(h); b -= __high2float(h);
+        } else {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+            out[pl] = *reinterpret_cast<const uint32_t *>(&h);
+            a -= __low2float(h); b -= __high2float(h);
+        }
+    }
+}
+
+// 2^k as a float, k clamped to the normal range
+__device__ __forceinline__ float pow2i(int k) {
+    k = k < -126 ? -126 : (k > 127 ? 127 : k);
+    return __int_as_float((k + 127) << 23);
+}
+
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
@@ -79,7 +120,7 @@ __device__ __forceinline__ void lds_bfrag(uint32_t addr, uint32_t &b0, uint32_t 
 // act[pl] = address of plane pl, this lane's row (lane>>2), element 2*(lane&3).  Every plane has
 // its own accumulator (independent MMAs); a group whose last slot is a real tile has no padding
 // and runs without per-slot tests, so its loads and MMAs interleave freely.
-template <int P, bool CHECK>
+template <int P, bool H, bool CHECK>
 __device__ __forceinline__ void tile_group(const uint4 cw, const uint4 cl, const uint32_t (&act)[P],
                                            float (&accp)[P][4]) {
     const uint32_t cws[4] = {cw.x, cw.y, cw.z, cw.w};
@@ -97,9 +138,13 @@ __device__ __forceinline__ void tile_group(const uint4 cw, const uint4 cl, const
         for (int s = 0; s < 8; ++s) {
             uint32_t af[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) af[i] = mortar_decode_pair(cws[s >> 1], (s & 1) * 4 + i);
+            for (int i = 0; i < 4; ++i)
+                af[i] = H ? mortar_decode_pair_h(cws[s >> 1], (s & 1) * 4 + i) : mortar_decode_pair(cws[s >> 1], (s & 1) * 4 + i);
 #pragma unroll
-            for (int pl = 0; pl < P; ++pl) mma_16816(accp[pl], af, b0[s][pl], b1[s][pl]);
+            for (int pl = 0; pl < P; ++pl) {
+                if (H) mma_16816_h(accp[pl], af, b0[s][pl], b1[s][pl]);
+                else mma_16816(accp[pl], af, b0[s][pl], b1[s][pl]);
+            }
         }
         return;
     }
@@ -109,17 +154,21 @@ __device__ __forceinline__ void tile_group(const uint4 cw, const uint4 cl, const
         if (col != 0xffffu) {                                   // padding slots end a row
             uint32_t af[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) af[i] = mortar_decode_pair(cws[s >> 1], (s & 1) * 4 + i);
+            for (int i = 0; i < 4; ++i)
+                af[i] = H ? mortar_decode_pair_h(cws[s >> 1], (s & 1) * 4 + i) : mortar_decode_pair(cws[s >> 1], (s & 1) * 4 + i);
             uint32_t b0[P], b1[P];
 #pragma unroll
             for (int pl = 0; pl < P; ++pl) lds_bfrag(act[pl] + col * 32u, b0[pl], b1[pl]);
 #pragma unroll
-            for (int pl = 0; pl < P; ++pl) mma_16816(accp[pl], af, b0[pl], b1[pl]);
+            for (int pl = 0; pl < P; ++pl) {
+                if (H) mma_16816_h(accp[pl], af, b0[pl], b1[pl]);
+                else mma_16816(accp[pl], af, b0[pl], b1[pl]);
+            }
         }
     }
 }
 
-template <int P>
+template <int P, bool H>
 __device__ __forceinline__ void tile_row(uint32_t grp_ptr, uint32_t cols, uint32_t codes, int trow,
                                          const uint32_t (&act)[P], int lane, float (&acc)[4]) {
     int gbeg, gend;
@@ -134,8 +183,8 @@ __device__ __forceinline__ void tile_row(uint32_t grp_ptr, uint32_t cols, uint32
     for (int grp = gbeg; grp < gend; ++grp, caddr += 512u, laddr += 16u) {
         const uint4 cw = lds128(caddr);
         const uint4 cl = lds128(laddr);
-        if ((cl.w >> 16) != 0xffffu) tile_group<P, false>(cw, cl, act, accp);
-        else tile_group<P, true>(cw, cl, act, accp);
+        if ((cl.w >> 16) != 0xffffu) tile_group<P, H, false>(cw, cl, act, accp);
+        else tile_group<P, H, true>(cw, cl, act, accp);
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -178,7 +227,7 @@ __host__ __device__ inline int align_up_i(int v, int a) { return (v + a - 1) / a
 // followed by the 8 sums of squares of those row slices -- the unit one rank pushes to its peers.
 __host__ __device__ inline int xs_block_floats(int d_model, int cs) { return 8 * (d_model / cs) + 8; }
 
-__host__ __device__ inline SmemLayout smem_layout(int d_model, int d_ff, int cs, int n_planes, int x_pitch,
+__host__ __device__ inline SmemLayout smem_layout(int d_model, int d_ff, int cs, int n_planes, int f16, int x_pitch,
                                                   int h_pitch, int max_a, int max_b) {
     SmemLayout L;
     int off = 0;
@@ -187,13 +236,14 @@ __host__ __device__ inline SmemLayout smem_layout(int d_model, int d_ff, int cs,
     const int xp_bytes = n_planes * 8 * x_pitch * 2, ysend_bytes = cs * 8 * (d_model / cs + 4) * 4;
     off += align_up_i(xp_bytes > ysend_bytes ? xp_bytes : ysend_bytes, 16);
     L.hp = off; off += align_up_i(n_planes * 8 * h_pitch * 2, 16);
-    L.gu = off;                                   // gate and up sums of the hidden slice, fp32: only when a rank has
-    if (d_ff / 16 / cs < kWarps) off += 8 * 2 * (d_ff / cs) * 4;   // fewer hidden tile rows than warps
+    L.gu = off;                                   // gate and up sums of the hidden slice, fp32: when a rank has fewer
+    // hidden tile rows than warps; with fp16 planes always (the fp32 hidden rows wait there for their scale)
+    if (f16 || d_ff / 16 / cs < kWarps) off += 8 * 2 * (d_ff / cs) * 4;
     L.recv = off; off += cs * 8 * (d_model / cs + 4) * 4;   // partial sums of this rank's columns, one block per source rank
     L.xsend = off; off += xs_block_floats(d_model, cs) * 4;
     off = align_up_i(off, 128);
     L.wbuf = off; off += max_a + max_b;           // one buffer per part: a part is refilled as soon as its stage is over
-    L.bars = off; off += 32;
+    L.bars = off; off += 32 + 64;                 // 4 mbarriers, 8 row factors of the x planes, 8 row maxima of the hidden rows
     L.total = off;
     return L;
 }
@@ -211,22 +261,24 @@ __device__ __forceinline__ void push_bulk(uint32_t dst_cluster, uint32_t src_loc
                  ::"r"(dst_cluster), "r"(src_local), "r"(bytes), "r"(bar_cluster) : "memory");
 }
 
-template <int P>
+template <int P, bool H>
 __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = (int)cluster.block_rank();
     const int cs = p.cs;
-    const SmemLayout L = smem_layout(p.d_model, p.d_ff, cs, p.n_planes, p.x_pitch, p.h_pitch, p.max_a, p.max_b);
+    const SmemLayout L = smem_layout(p.d_model, p.d_ff, cs, p.n_planes, p.f16, p.x_pitch, p.h_pitch, p.max_a, p.max_b);
     float *xs = reinterpret_cast<float *>(smem + L.xs);
-    __nv_bfloat16 *xp = reinterpret_cast<__nv_bfloat16 *>(smem + L.xp);
+    uint16_t *xp = reinterpret_cast<uint16_t *>(smem + L.xp);       // planes: bf16 or fp16 bit patterns
     float *ysend = reinterpret_cast<float *>(smem + L.xp);
-    __nv_bfloat16 *hp = reinterpret_cast<__nv_bfloat16 *>(smem + L.hp);
+    uint16_t *hp = reinterpret_cast<uint16_t *>(smem + L.hp);
     float *gu_out = reinterpret_cast<float *>(smem + L.gu);
     float *recv = reinterpret_cast<float *>(smem + L.recv);
     float *xsend = reinterpret_cast<float *>(smem + L.xsend);
     uint8_t *wbuf = smem + L.wbuf;
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + L.bars);     // [0]: gate/up weights, [1]: down weights; [2]: partial sums; [3]: x slices
+    float *xun = reinterpret_cast<float *>(smem + L.bars + 32);       // per row: factor that undoes the scaling of the x planes
+    uint32_t *hmax = reinterpret_cast<uint32_t *>(smem + L.bars + 64); // per row: bits of the largest |hidden| (fp16 planes)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -334,13 +386,22 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
 
         // ---- n = rmsnorm(x) as exact bf16 planes (kWarpsPerRow warps per row) ----
         {
-            const int row = warp / kWarpsPerRow, half = warp % kWarpsPerRow;
-            float inv = 1.f;
-            if (rms_w != nullptr) {
+            const int row = warp / kWarpsPerRow, part = warp % kWarpsPerRow;
+            float inv = 1.f, undo = 1.f;
+            if (rms_w != nullptr || H) {
                 float ss = 0.f;
                 for (int q = 0; q < cs; ++q) ss += xs[q * blk + 8 * OC + row];      // rank order: same sum in every rank
-                inv = 1.f / sqrtf(ss / (float)D + p.eps);
+                if (rms_w != nullptr) {
+                    inv = 1.f / sqrtf(ss / (float)D + p.eps);
+                } else if (ss > 0.f) {
+                    // fp16 planes without a norm: bring the row to unit RMS with the power of two below 1/rms
+                    const int eb = (__float_as_int(rsqrtf(ss / (float)D)) >> 23) & 0xff;
+                    inv = pow2i(eb - 127);
+                    undo = pow2i(127 - eb);
+                }
             }
+            if (part == 0 && lane == 0) xun[row] = undo;
+            if (H && threadIdx.x < 8) hmax[threadIdx.x] = 0u;
             const float inv_oc = 1.f / (float)OC;
             auto plane_split = [&](int c, const float4 wv) {
                 const int q = (int)(((float)c + 0.5f) * inv_oc);                   // c / OC for these small integers
@@ -349,25 +410,23 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
                 if (rms_w != nullptr) {
                     vv[0] = (vv[0] * inv) * wv.x; vv[1] = (vv[1] * inv) * wv.y;
                     vv[2] = (vv[2] * inv) * wv.z; vv[3] = (vv[3] * inv) * wv.w;
+                } else if (H) {
+                    vv[0] *= inv; vv[1] *= inv; vv[2] *= inv; vv[3] *= inv;
                 }
-                for (int pl = 0; pl < P; ++pl) {
-                    // packed conversions (two values per instruction, off the conversion unit)
-                    const __nv_bfloat162 h01 = __floats2bfloat162_rn(vv[0], vv[1]);
-                    const __nv_bfloat162 h23 = __floats2bfloat162_rn(vv[2], vv[3]);
-                    vv[0] -= __low2float(h01); vv[1] -= __high2float(h01);
-                    vv[2] -= __low2float(h23); vv[3] -= __high2float(h23);
-                    uint2 packed;
-                    packed.x = *reinterpret_cast<const uint32_t *>(&h01);
-                    packed.y = *reinterpret_cast<const uint32_t *>(&h23);
-                    *reinterpret_cast<uint2 *>(xp + (size_t)pl * 8 * p.x_pitch + row * p.x_pitch + c) = packed;
-                }
+                // packed conversions (two values per instruction, off the conversion unit)
+                uint32_t lo[P], hi[P];
+                split_pair<P, H>(vv[0], vv[1], lo);
+                split_pair<P, H>(vv[2], vv[3], hi);
+#pragma unroll
+                for (int pl = 0; pl < P; ++pl)
+                    *reinterpret_cast<uint2 *>(xp + (size_t)pl * 8 * p.x_pitch + row * p.x_pitch + c) = make_uint2(lo[pl], hi[pl]);
             };
 #pragma unroll
             for (int k = 0; k < kWPre; ++k) {
-                const int c = half * 128 + lane * 4 + k * kRowStep;
+                const int c = part * 128 + lane * 4 + k * kRowStep;
                 if (c < D) plane_split(c, wpre[k]);
             }
-            for (int c = half * 128 + lane * 4 + kWPre * kRowStep; c < D; c += kRowStep)
+            for (int c = part * 128 + lane * 4 + kWPre * kRowStep; c < D; c += kRowStep)
                 plane_split(c, rms_w != nullptr ? *reinterpret_cast<const float4 *>(rms_w + c) : make_float4(1.f, 1.f, 1.f, 1.f));
         }
         __syncthreads();
@@ -381,38 +440,59 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
                 act[pl] = smem_u32(xp) + (uint32_t)(pl * xplane_w + g * (p.x_pitch / 2) + t) * 4u;
             const int W = 2 * U * 16;                            // gate columns then up columns
             const int HW = U * 16;
+            // the matrix scale times the factor that undoes the row's plane scaling (rows 2t, 2t+1)
+            const float sg[2] = {scale_gu * xun[2 * t], scale_gu * xun[2 * t + 1]};
+            // fp16 planes: the fp32 hidden rows wait in shared memory (row pitch hp32) for the row maxima
+            const int hp32 = U >= kWarps ? HW + 4 : W;
             if (U >= kWarps) {
                 // enough hidden tile rows for every warp: one warp computes the gate and the up
                 // tile row of a hidden tile row and applies SwiGLU in registers
                 for (int hrow = warp; hrow < U; hrow += kWarps) {
                     float ag[4] = {0.f, 0.f, 0.f, 0.f}, au[4] = {0.f, 0.f, 0.f, 0.f};
-                    tile_row<P>(gu_ptr, gu_cols, gu_codes, hrow, act, lane, ag);
-                    tile_row<P>(gu_ptr, gu_cols, gu_codes, U + hrow, act, lane, au);
+                    tile_row<P, H>(gu_ptr, gu_cols, gu_codes, hrow, act, lane, ag);
+                    tile_row<P, H>(gu_ptr, gu_cols, gu_codes, U + hrow, act, lane, au);
+                    float mx[2] = {0.f, 0.f};
 #pragma unroll
                     for (int i = 0; i < 4; i += 2) {             // (neuron g + 8*(i>>1), rows 2t and 2t+1)
                         float hv[2];
 #pragma unroll
                         for (int k = 0; k < 2; ++k) {
-                            const float gv = scale_gu * ag[i + k], uv = scale_gu * au[i + k];
+                            const float gv = sg[k] * ag[i + k], uv = sg[k] * au[i + k];
                             hv[k] = gv * __fdividef(1.f, 1.f + __expf(-gv)) * uv;
                         }
-                        __nv_bfloat16 *o = hp + (2 * t) * p.h_pitch + hrow * 16 + g + 8 * (i >> 1);
+                        const int col = hrow * 16 + g + 8 * (i >> 1);
+                        if (H) {
+                            gu_out[(2 * t) * hp32 + col] = hv[0];
+                            gu_out[(2 * t + 1) * hp32 + col] = hv[1];
+                            mx[0] = fmaxf(mx[0], fabsf(hv[0])); mx[1] = fmaxf(mx[1], fabsf(hv[1]));
+                        } else {
+                            uint32_t pr[P];
+                            split_pair<P, H>(hv[0], hv[1], pr);
+                            uint16_t *o = hp + (2 * t) * p.h_pitch + col;
 #pragma unroll
-                        for (int pl = 0; pl < P; ++pl) {
-                            const __nv_bfloat162 hb = __floats2bfloat162_rn(hv[0], hv[1]);
-                            o[(size_t)pl * 8 * p.h_pitch] = __low2bfloat16(hb);
-                            o[(size_t)pl * 8 * p.h_pitch + p.h_pitch] = __high2bfloat16(hb);
-                            hv[0] -= __low2float(hb); hv[1] -= __high2float(hb);
+                            for (int pl = 0; pl < P; ++pl) {
+                                o[(size_t)pl * 8 * p.h_pitch] = (uint16_t)(pr[pl] & 0xffffu);
+                                o[(size_t)pl * 8 * p.h_pitch + p.h_pitch] = (uint16_t)(pr[pl] >> 16);
+                            }
+                        }
+                    }
+                    if (H) {
+                        // largest |hidden| of rows 2t and 2t+1 over this tile row's 16 neurons (lanes of equal t)
+#pragma unroll
+                        for (int k = 0; k < 2; ++k) {
+#pragma unroll
+                            for (int o = 4; o < 32; o <<= 1) mx[k] = fmaxf(mx[k], __shfl_xor_sync(0xffffffffu, mx[k], o));
+                            if (g == 0) atomicMax(&hmax[2 * t + k], __float_as_uint(mx[k]));
                         }
                     }
                 }
             } else {
                 for (int trow = warp; trow < 2 * U; trow += kWarps) {
                     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-                    tile_row<P>(gu_ptr, gu_cols, gu_codes, trow, act, lane, acc);
+                    tile_row<P, H>(gu_ptr, gu_cols, gu_codes, trow, act, lane, acc);
 #pragma unroll
                     for (int i = 0; i < 4; ++i)                  // (neuron g + 8*(i>>1), row 2t + (i&1))
-                        gu_out[(2 * t + (i & 1)) * W + trow * 16 + g + 8 * (i >> 1)] = scale_gu * acc[i];
+                        gu_out[(2 * t + (i & 1)) * W + trow * 16 + g + 8 * (i >> 1)] = sg[i & 1] * acc[i];
                 }
                 __syncthreads();
                 // silu(gate) * up -> exact bf16 planes of the hidden slice
@@ -420,13 +500,36 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
                 for (int c = (warp % kWarpsPerRow) * 32 + lane; c < HW; c += kWarpsPerRow * 32) {
                     const float gv = gu_out[r * W + c], uv = gu_out[r * W + HW + c];
                     float hv = gv * __fdividef(1.f, 1.f + __expf(-gv)) * uv;
-                    __nv_bfloat16 *o = hp + r * p.h_pitch + c;
+                    if (H) {
+                        gu_out[r * W + c] = hv;                   // in place of the gate sum this thread just read
+                        hv = fabsf(hv);
 #pragma unroll
-                    for (int pl = 0; pl < P; ++pl) {
-                        const __nv_bfloat16 hb = __float2bfloat16_rn(hv);
-                        o[(size_t)pl * 8 * p.h_pitch] = hb;
-                        hv -= __bfloat162float(hb);
+                        for (int o = 1; o < 32; o <<= 1) hv = fmaxf(hv, __shfl_xor_sync(0xffffffffu, hv, o));
+                        if (lane == 0) atomicMax(&hmax[r], __float_as_uint(hv));
+                    } else {
+                        uint16_t *o = hp + r * p.h_pitch + c;
+#pragma unroll
+                        for (int pl = 0; pl < P; ++pl) {
+                            const __nv_bfloat16 hb = __float2bfloat16_rn(hv);
+                            o[(size_t)pl * 8 * p.h_pitch] = __bfloat16_as_ushort(hb);
+                            hv -= __bfloat162float(hb);
+                        }
                     }
+                }
+            }
+            if (H) {
+                // every hidden row scaled so that its largest magnitude lies in [2^13, 2^14), then split
+                __syncthreads();
+                const int r = warp / kWarpsPerRow;
+                const uint32_t mb = hmax[r];
+                const float sc = mb ? pow2i(13 + 127 - (int)(mb >> 23)) : 1.f;
+                for (int c = (warp % kWarpsPerRow) * 64 + lane * 2; c < HW; c += kWarpsPerRow * 64) {
+                    const float2 v = *reinterpret_cast<const float2 *>(gu_out + r * hp32 + c);
+                    uint32_t pr[P];
+                    split_pair<P, H>(v.x * sc, v.y * sc, pr);
+#pragma unroll
+                    for (int pl = 0; pl < P; ++pl)
+                        *reinterpret_cast<uint32_t *>(hp + (size_t)pl * 8 * p.h_pitch + r * p.h_pitch + c) = pr[pl];
                 }
             }
         }
@@ -445,14 +548,22 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
 #pragma unroll
             for (int pl = 0; pl < P; ++pl)
                 act[pl] = smem_u32(hp) + (uint32_t)(pl * hplane_w + g * (p.h_pitch / 2) + t) * 4u;
+            float sd[2] = {scale_dn, scale_dn};                  // times the factor that undoes the hidden rows' scaling
+            if (H) {
+#pragma unroll
+                for (int k = 0; k < 2; ++k) {
+                    const uint32_t mb = hmax[2 * t + k];
+                    if (mb) sd[k] = scale_dn * pow2i((int)(mb >> 23) - 127 - 13);
+                }
+            }
             for (int trow = warp; trow < RD; trow += kWarps) {
                 float acc[4] = {0.f, 0.f, 0.f, 0.f};
-                tile_row<P>(dn_ptr, dn_cols, dn_codes, trow, act, lane, acc);
+                tile_row<P, H>(dn_ptr, dn_cols, dn_codes, trow, act, lane, acc);
                 const int q = trow / TR, cl0 = (trow - q * TR) * 16;
                 float *dst = ysend + (size_t)q * 8 * OCP + cl0;
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
-                    dst[(2 * t + (i & 1)) * OCP + g + 8 * (i >> 1)] = scale_dn * acc[i];
+                    dst[(2 * t + (i & 1)) * OCP + g + 8 * (i >> 1)] = sd[i & 1] * acc[i];
             }
         }
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
@@ -529,6 +640,8 @@ extern "C" int mortar_stack_decode(const void *blobs, const int32_t *blob_table,
         return MORTAR_ERR_SHAPE;
     if (cluster_size != 8 && cluster_size != 16) return MORTAR_ERR_SHAPE;
     if ((d_ff / 16) % cluster_size || d_model % (16 * cluster_size)) return MORTAR_ERR_SHAPE;
+    const int f16 = n_planes == MORTAR_PLANES_HALF2 ? 1 : 0;
+    if (f16) n_planes = 2;
     if (n_planes < 1 || n_planes > 3) return MORTAR_ERR_DTYPE;
     if ((reinterpret_cast<uintptr_t>(blobs) % 16) || (reinterpret_cast<uintptr_t>(x) % 16) || (ldx % 4) ||
         (max_gate_up_bytes % 128) || (max_down_bytes % 128) || max_gate_up_bytes < 128 || max_down_bytes < 128)
@@ -548,7 +661,8 @@ extern "C" int mortar_stack_decode(const void *blobs, const int32_t *blob_table,
         int v = 0;
         MORTAR_CUDA_CHECK(cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
         v -= 256;                                      // room for the kernel's few static shared bytes
-        void (*kernels[3])(const StackParams) = {stack_decode_kernel<1>, stack_decode_kernel<2>, stack_decode_kernel<3>};
+        void (*kernels[4])(const StackParams) = {stack_decode_kernel<1, false>, stack_decode_kernel<2, false>,
+                                                 stack_decode_kernel<3, false>, stack_decode_kernel<2, true>};
         for (auto k : kernels) {
             MORTAR_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, v));
             MORTAR_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
@@ -561,11 +675,11 @@ extern "C" int mortar_stack_decode(const void *blobs, const int32_t *blob_table,
     p.blobs = reinterpret_cast<const uint8_t *>(blobs);
     p.blob_table = blob_table; p.app_layer = app_layer; p.rms = rms_weights;
     p.n_apps = n_apps; p.d_model = d_model; p.d_ff = d_ff; p.cs = cluster_size;
-    p.x = x; p.ldx = ldx; p.rows = (int)rows; p.eps = eps; p.n_planes = n_planes; p.status = status;
+    p.x = x; p.ldx = ldx; p.rows = (int)rows; p.eps = eps; p.n_planes = n_planes; p.f16 = f16; p.status = status;
     p.x_pitch = pitch_for(d_model);
     p.h_pitch = pitch_for(d_ff / cluster_size);
     p.max_a = max_gate_up_bytes; p.max_b = max_down_bytes;
-    const SmemLayout L = smem_layout(d_model, d_ff, cluster_size, n_planes, p.x_pitch, p.h_pitch, max_gate_up_bytes, max_down_bytes);
+    const SmemLayout L = smem_layout(d_model, d_ff, cluster_size, n_planes, f16, p.x_pitch, p.h_pitch, max_gate_up_bytes, max_down_bytes);
     if (L.total > smem_limit) return MORTAR_ERR_CAPACITY;   // a rank's share does not fit shared memory
 
     cudaLaunchConfig_t cfg = {};
@@ -580,8 +694,9 @@ extern "C" int mortar_stack_decode(const void *blobs, const int32_t *blob_table,
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (n_planes == 1) MORTAR_CUDA_CHECK(cudaLaunchKernelEx(&cfg, stack_decode_kernel<1>, p));
-    else if (n_planes == 2) MORTAR_CUDA_CHECK(cudaLaunchKernelEx(&cfg, stack_decode_kernel<2>, p));
-    else MORTAR_CUDA_CHECK(cudaLaunchKernelEx(&cfg, stack_decode_kernel<3>, p));
+    if (f16) MORTAR_CUDA_CHECK(cudaLaunchKernelEx(&cfg, stack_decode_kernel<2, true>, p));
+    else if (n_planes == 1) MORTAR_CUDA_CHECK(cudaLaunchKernelEx(&cfg, stack_decode_kernel<1, false>, p));
+    else if (n_planes == 2) MORTAR_CUDA_CHECK(cudaLaunchKernelEx(&cfg, stack_decode_kernel<2, false>, p));
+    else MORTAR_CUDA_CHECK(cudaLaunchKernelEx(&cfg, stack_decode_kernel<3, false>, p));
     return MORTAR_OK;
 }

@@ -375,10 +375,15 @@ class DecodeStack:
         return v
 
 
-def stack_decode(x: torch.Tensor, stack: DecodeStack, *, eps: float = 1e-6, n_planes: int = 3,
+PLANES_HALF2 = 12      # MORTAR_PLANES_HALF2: two fp16 planes with exact per-row power-of-two scaling
+
+
+def stack_decode(x: torch.Tensor, stack: DecodeStack, *, eps: float = 1e-6, n_planes: int = PLANES_HALF2,
                  cluster_size: Optional[int] = None) -> torch.Tensor:
     """In-place decode step of a whole MLP stack on the fp32 residual carrier x [rows, d_model]:
-    one launch, every block of 8 rows walks all applications inside one thread-block cluster."""
+    one launch, every block of 8 rows walks all applications inside one thread-block cluster.
+    ``n_planes``: 3 = three bf16 planes (fp32 activations represented exactly), ``PLANES_HALF2``
+    (default) = two scaled fp16 planes (residual below 2^-22 of an element; a third fewer MMAs)."""
     _require_cuda(x, "x")
     if x.dtype != torch.float32 or x.dim() != 2 or x.shape[1] != stack.d_model or x.stride(1) != 1:
         raise ValueError("x must be float32 [rows, d_model] with unit inner stride")
@@ -720,6 +725,9 @@ def route_gather(gates: torch.Tensor, cluster_size: int, units: int):
     return cnt, lst
 
 
+ROUTER_GEMM_MIN_ROWS = 256      # token blocks of at least this many rows project through a library GEMM
+
+
 def router_gates(x: torch.Tensor, router, iter_idx: int = 0, out: Optional[torch.Tensor] = None,
                  scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Gates [rows, n_groups] (fp32) of a ReMoE router for activations x[..., d_model]: the
@@ -728,7 +736,11 @@ def router_gates(x: torch.Tensor, router, iter_idx: int = 0, out: Optional[torch
     reference's ``fused_router`` (morph/kernels/triton/fused_router.py:101-139) for any number of
     rows.  ``router`` is anything with the reference router's parameters (``query_proj.weight``,
     ``iter_embed``, ``query_norm``, ``sub_keys_a/b``, ``group_bias``, ``activation_k``,
-    ``n_sub_keys``, ``n_tile_groups``) in fp32 on the device of x."""
+    ``n_sub_keys``, ``n_tile_groups``) in fp32 on the device of x.
+
+    Token blocks of ``ROUTER_GEMM_MIN_ROWS`` rows or more run the dense d x d projection as a
+    plain library GEMM (fp32; bf16 under autocast, as ``nn.Linear`` does in the reference) and
+    only the second launch of the kernel path; smaller batches run both launches."""
     _require_cuda(x, "x")
     d = router.d_model
     x2 = _rows2d(x, d, "x")
@@ -750,13 +762,23 @@ def router_gates(x: torch.Tensor, router, iter_idx: int = 0, out: Optional[torch
         scratch = torch.empty(max(rows, 1) * d, device=x.device, dtype=torch.float32)
     if rows == 0:
         return out
+    wq, n_launch = router.query_proj.weight, 2
+    if rows >= ROUTER_GEMM_MIN_ROWS:
+        with torch.no_grad():
+            if torch.is_autocast_enabled():
+                dt = torch.get_autocast_dtype("cuda")
+                q = torch.nn.functional.linear(x2.to(dt), wq.detach().to(dt)).float()
+                q += router.iter_embed[it]
+            else:
+                q = torch.addmm(router.iter_embed[it], x2, wq.detach().t())
+        scratch, wq, n_launch = q.contiguous(), None, 1
     _lib.check(_lib.lib().mortar_router_gates(
-        _ptr(x2), x2.stride(0), rows, d, _ptr(router.query_proj.weight), _ptr(router.iter_embed[it]),
+        _ptr(x2), x2.stride(0), rows, d, _ptr(wq), _ptr(router.iter_embed[it]),
         _ptr(router.query_norm.weight), _ptr(router.query_norm.bias), float(router.query_norm.eps),
         _ptr(router.sub_keys_a), _ptr(router.sub_keys_b), nsk, _ptr(router.group_bias), G,
         int(router.activation_k), _ptr(scratch), _ptr(out), out.stride(0), _stream_ptr()),
         "mortar_router_gates")
-    _count("router", 2)
+    _count("router", n_launch)
     return out
 
 

@@ -118,14 +118,16 @@ def test_whole_decode_stack_vs_oracle(full_stack, batch):
     layers, rms, order, stack, dense = full_stack
     assert len(order) == 42
     x0 = mb.synth.make_activations(batch, 768, seed=batch, dtype=torch.float32)
-    x = x0.clone().to(DEV)
-    mb.ops.stack_decode(x, stack)
-    assert stack.error() == 0
     ref = x0.clone()
     for i in order:
         ref = ref + orc.swiglu_mlp(orc.rmsnorm_rows(ref, rms[i], 1e-6), dense[i][0], dense[i][1])
-    rel = float((x.cpu() - ref).abs().max()) / float(ref.abs().max())
-    assert rel <= 1e-5, f"batch {batch}: relative error {rel:.2e}"
+    for planes in (mb.ops.PLANES_HALF2, 3):        # the default (two scaled fp16 planes) and three bf16 planes
+        x = x0.clone().to(DEV)
+        mb.ops.stack_decode(x, stack, n_planes=planes)
+        assert stack.error() == 0
+        rel = float((x.cpu() - ref).abs().max()) / float(ref.abs().max())
+        print(f"batch {batch} planes {planes}: max relative error {rel:.2e}")
+        assert rel <= 1e-5, f"batch {batch} planes {planes}: relative error {rel:.2e}"
     # the per-application path on the same chain
     x2 = x0.clone().to(DEV)
     streams = [(L.gate_up.to_stream(DEV), L.down.to_stream(DEV)) for L in layers]

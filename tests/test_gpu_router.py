@@ -75,3 +75,34 @@ def test_router_kernel_rejects_bad_input():
     with pytest.raises(NotImplementedError):
         mb.ops.router_gates(torch.zeros(2, 128), r)
     assert mb.ops.router_gates(torch.zeros(0, 128, device=DEV), r).shape == (0, 16)
+
+
+def test_router_projection_paths_agree(monkeypatch):
+    """Large token blocks project through a library GEMM and run only the second launch; the gates
+    equal the two-launch path's up to summation order, and under autocast the projection runs in
+    bf16 as the reference's nn.Linear does."""
+    torch.manual_seed(5)
+    r = router_mod.TileRouter(352, 2048, activation_ratio=0.25).to(DEV).eval()
+    x = torch.randn(1024, 2048, device=DEV)
+    n0 = mb.ops.kernel_counts().get("router", 0)
+    g_gemm = mb.ops.router_gates(x, r)
+    assert mb.ops.kernel_counts()["router"] - n0 == 1
+    monkeypatch.setattr(mb.ops, "ROUTER_GEMM_MIN_ROWS", 1 << 30)
+    g_two = mb.ops.router_gates(x, r)
+    assert mb.ops.kernel_counts()["router"] - n0 == 3
+    monkeypatch.undo()
+    lg, _ = _oracle_gates(x.cpu(), r)
+    k = r.activation_k
+    kth = np.sort(lg, axis=1)[:, ::-1][:, k - 1][:, None]
+    clear = torch.from_numpy(np.abs(lg - kth) > 1e-4).to(DEV)
+    assert torch.equal((g_gemm > 0)[clear], (g_two > 0)[clear])
+    torch.testing.assert_close(g_gemm, g_two, rtol=2e-3, atol=2e-4)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        g_ac = mb.ops.router_gates(x, r)
+    q = torch.nn.functional.linear(x.bfloat16(), r.query_proj.weight.bfloat16()).float() + r.iter_embed[0]
+    qn = torch.nn.functional.layer_norm(q, (2048,), r.query_norm.weight, r.query_norm.bias, r.query_norm.eps)
+    sa, sb = qn[:, :1024] @ r.sub_keys_a.T, qn[:, 1024:] @ r.sub_keys_b.T
+    prod = (sa.unsqueeze(2) + sb.unsqueeze(1)).reshape(1024, -1)
+    lg_ac = torch.topk(prod, 352, dim=1).values + r.group_bias
+    ref_ac = orc.remoe_gates(lg_ac.detach().cpu(), k).to(DEV)
+    torch.testing.assert_close(g_ac, ref_ac, rtol=5e-3, atol=5e-4)
