@@ -14,7 +14,8 @@ import torch
 import mortar_b200 as mb
 from conftest import GOLDEN_CASES, ROOT, bf16_from_bits, load_golden
 
-REF = "/root/reference"
+# the reference checkout: MORPH_REFERENCE_ROOT, or a `reference` folder beside this repository
+REF = os.environ.get("MORPH_REFERENCE_ROOT", os.path.join(os.path.dirname(ROOT), "reference"))
 have_ref = os.path.isdir(os.path.join(REF, "morph"))
 
 
@@ -129,7 +130,7 @@ def test_reference_model_state_dict_and_op_override():
     CUDA kernel is replaced by ours."""
     code = r'''
 import sys, numpy as np, torch
-sys.path.insert(0, "/root/reference"); sys.path.insert(0, %r)
+sys.path.insert(0, %r); sys.path.insert(0, %r)
 from morph.model.transformer import _SwiGLUMortar
 from morph.inference.deploy_quant import pack_mortar_ternary, _ternary_quantize
 import morph.sparse.stk.backend.custom_ops          # the reference defines morph_stk::dds first
@@ -173,6 +174,6 @@ for packed in (False, True):
     # the attributes reference call sites reach through (deploy_quant.py:462-465, pruning.py:341-347)
     assert mir.gate_up._cms.in_features == d and mir.gate_up._cms.bias is None
 print("OK")
-''' % ROOT
+''' % (REF, ROOT)
     res = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600)
     assert res.returncode == 0 and "OK" in res.stdout, res.stdout + res.stderr
