@@ -476,7 +476,7 @@ def run_ours(args, rank, world, local_rank):
             prefill["roofline"] = tensor_roofline(prefill["useful_tflops"], pk, fp8)
             extra["prefill_cloud"] = prefill
             for name, fn in (("single_layer_c0", run_single_layer), ("prefill_cloud_blocks128", run_prefill_blocks128),
-                             ("prefill_cloud_i8", run_prefill_i8), ("sweep_c3", run_sweep), ("remoe_c4", run_remoe),
+                             ("prefill_cloud_i8", run_prefill_i8), ("backward_gate_up_c0", run_backward), ("sweep_c3", run_sweep), ("remoe_c4", run_remoe),
                              ("gemv_large_b1", run_gemv_large)):
                 with ClockSampler(local_rank) as sc:
                     extra[name] = fn(mb, device, pk, flush)
@@ -640,6 +640,34 @@ def run_prefill_i8(mb, device, pk, flush, tokens: int = PREFILL_TOKENS, reps: in
             cell["frac_of_measured_int8_burst"] = round(tf8 / peak["int8_tops_burst"], 5)
         out[name] = cell
     out["device_error_word"] = mb.ops.prefill_error()
+    return out
+
+
+def run_backward(mb, device, pk, flush, reps: int = 5):
+    """Training backward of the gate/up matrix at the shape the reference profiled (x [16384, 768],
+    W [4096, 768] at 25%; RTX 5090, 128x128 blocks: dW 445.7 us stock / 197 us tuned, dx 180.6 us,
+    .agents/notes/implemented/process/2026-07-03-perf-pass-focus2-bcsr.md:22-46): the weight
+    gradient on the topology (sdd_tiles_kernel) and the input gradient through the transposed
+    matrix on the tensor-memory kernel, for single-tile and 128-block topologies."""
+    d, f, tokens = LOCAL["d_model"], LOCAL["d_ff"], 4 * 4096
+    from importlib import import_module
+    fmt = import_module(mb.__name__ + ".format")
+    out = {"tokens": tokens, "reference_published_us_rtx5090": {"dW_stock": 445.7, "dW_tuned": 197.0, "dx": 180.6}}
+    x = mb.synth.make_activations(tokens, d, seed=5).to(device)
+    dy = mb.synth.make_activations(tokens, 2 * f, seed=6).to(device)
+    cases = {"tile16": mb.synth.make_layer(d, f, DENSITY, seed=0).gate_up,
+             "blocks128": mb.synth.make_block_matrix(2 * f, d, DENSITY, seed=3)}
+    for name, m in cases.items():
+        topo = fmt.TopologyDev(m, device)
+        mt = m.transpose().to_sched(False, device)
+        t_dw = statistics.median(time_steps(lambda: mb.ops.sdd_tiles(dy, x, topo), reps, 2, flush))
+        t_dw_tiles = statistics.median(time_steps(lambda: mb.ops.sdd_tiles(dy, x, topo, path="tiles"), reps, 1, flush))
+        t_dx = statistics.median(time_steps(lambda: mb.ops.linear_tc(dy, mt), reps, 2, flush))
+        flops = 2 * 256 * m.nnz * tokens
+        out[name] = {"dW_us": round(t_dw * 1e3, 1), "dW_tflops": round(flops / (t_dw * 1e-3) / 1e12, 1),
+                     "dW_per_tile_kernel_us": round(t_dw_tiles * 1e3, 1),
+                     "dx_us": round(t_dx * 1e3, 1), "dx_tflops": round(flops / (t_dx * 1e-3) / 1e12, 1)}
+    out["device_error_word"] = mb.ops.prefill_error() or mb.ops.sdd_error()
     return out
 
 

@@ -480,6 +480,26 @@ int mortar_sdd_tiles(const void *dy, int64_t ld_dy, const void *x, int64_t ld_x,
                      int32_t tile_cols, const int32_t *item_row, const int32_t *item_first,
                      int32_t n_items, void *out, int32_t out_dtype, void *stream);
 
+/* The same weight gradient for large token blocks on the tensor-memory path: dW is computed in
+ * whole 128 x 128 blocks (dy[:, 128 outputs]^T @ x[:, 128 inputs], tcgen05.mma over the token
+ * dimension with the activations consumed as they lie in memory) and only kept tiles are stored.
+ *   blk_rc     device int32 [n_blocks][2]   block row and block column (units of 128 features) of
+ *                                           every block that holds at least one kept tile
+ *   blk_tiles  device int32 [n_blocks][64]  index (into out) of the kept tile at tile row i, tile
+ *                                           column j of the block at [8 i + j], or -1
+ *   n_splits   CTAs that share the token dimension of one block (>= 1; fewer are used when the
+ *              token count does not give every split a 64-token stage)
+ *   scratch    device fp32, n_splits * nnz * 256 floats: the splits' partial tiles, added in split
+ *              order by a second launch.  May be NULL when n_splits == 1 and out is fp32.
+ *   out        [nnz][16][16] fp32 or bf16 (out_dtype)
+ * Bounded in-kernel waits report through mortar_sdd_error. */
+int mortar_sdd_blocks(const void *dy, int64_t ld_dy, const void *x, int64_t ld_x, int64_t rows,
+                      int32_t out_features, int32_t in_features, const int32_t *blk_rc,
+                      const int32_t *blk_tiles, int32_t n_blocks, int32_t n_splits, int64_t nnz,
+                      float *scratch, int64_t scratch_floats, void *out, int32_t out_dtype,
+                      void *stream);
+int mortar_sdd_error(int32_t *code, int32_t reset);
+
 /* Reads (and optionally clears) the error word the staged and persistent paths of
  * mortar_linear set when one of their bounded barrier waits expires: 0 = none, 1 = staged
  * path, 2 = a consumer of the persistent kernel, 3 = one of its producers.  Synchronises.

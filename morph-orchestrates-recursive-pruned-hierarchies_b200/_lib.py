@@ -94,6 +94,9 @@ _SIGNATURES = {
     "mortar_mlp_prefill": (C.c_int, [C.POINTER(Sched), C.POINTER(Sched), _vp, _i64, _i64, _vp, _i64,
                                      _i32, _vp, _i64, _vp, _i64, _vp]),
     "mortar_sdd_tiles": (C.c_int, [_vp, _i64, _vp, _i64, _i64, _vp, _vp, _i32, _i32, _vp, _vp, _i32, _vp, _i32, _vp]),
+    "mortar_sdd_blocks": (C.c_int, [_vp, _i64, _vp, _i64, _i64, _i32, _i32, _vp, _vp, _i32, _i32, _i64, _vp, _i64,
+                                    _vp, _i32, _vp]),
+    "mortar_sdd_error": (C.c_int, [_vp, _i32]),
     "mortar_prefill_error": (C.c_int, [_vp, _i32]),
     "mortar_linear_error": (C.c_int, [_vp, _i32]),
     "mortar_router_gates": (C.c_int, [_vp, _i64, _i64, _i32, _vp, _vp, _vp, _vp, _f32, _vp, _vp, _i32, _vp,

@@ -329,6 +329,18 @@ class TopologyDev:
         self.col_idx = t(m.col_idx.view(np.int16), np.int16)
         self.item_row, self.item_first = t(item_row, np.int32), t(item_first, np.int32)
         self.n_items = len(item_row)
+        # work list of the block kernel: every 128 x 128 block with a kept tile, and where its 64
+        # tile positions land in the [nnz] output (-1 = not kept)
+        rows = np.repeat(np.arange(m.tile_rows), np.diff(m.row_ptr)).astype(np.int64)
+        cols = m.col_idx.astype(np.int64)
+        n_bc = (m.tile_cols + 7) // 8
+        key = (rows // 8) * n_bc + cols // 8
+        blocks, inv = np.unique(key, return_inverse=True)
+        tiles = np.full((len(blocks), 64), -1, dtype=np.int32)
+        tiles[inv, (rows % 8) * 8 + cols % 8] = np.arange(m.nnz, dtype=np.int32)
+        self.blk_rc = t(np.stack([blocks // n_bc, blocks % n_bc], axis=1), np.int32)
+        self.blk_tiles = t(tiles, np.int32)
+        self.n_blocks = len(blocks)
 
 
 PANEL_ROWS, CHUNK_COLS, STEP_TILES = 16, 4, 48

@@ -653,10 +653,23 @@ def mlp_prefill_tc_i8(x: torch.Tensor, gate_up: SchedMatrix, down: SchedMatrix, 
     return linear_tc_i8(h, down)
 
 
-def sdd_tiles(dy: torch.Tensor, x: torch.Tensor, topo: TopologyDev, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+SDD_BLOCK_MIN_ROWS = 512      # token blocks of at least this many rows take the tensor-memory block kernel
+
+
+def sdd_error(reset: bool = True) -> int:
+    """Error word of the block weight-gradient kernel (0 = none; synchronises the device)."""
+    code = C.c_int32(0)
+    _lib.check(_lib.lib().mortar_sdd_error(C.byref(code), int(reset)), "mortar_sdd_error")
+    return code.value
+
+
+def sdd_tiles(dy: torch.Tensor, x: torch.Tensor, topo: TopologyDev, out_dtype: torch.dtype = torch.float32,
+              path: Optional[str] = None) -> torch.Tensor:
     """Weight gradient on the topology: [nnz, 16, 16] with tile (r, c) = dy[:, 16r:16r+16]^T @
     x[:, 16c:16c+16] (bf16 operands, fp32 accumulation) -- ``morph_stk::sdd_at_b`` at tile 16
-    (morph/sparse/stk/backend/custom_ops.py:68-89)."""
+    (morph/sparse/stk/backend/custom_ops.py:68-89).  ``path``: "blocks" (whole 128 x 128 blocks on
+    the tensor-memory path, the default from ``SDD_BLOCK_MIN_ROWS`` rows), "tiles" (one kept tile
+    per warp), None = by row count."""
     _require_cuda(dy, "dy")
     d2 = _rows2d(dy.to(torch.bfloat16), topo.tile_rows * TILE, "dy")
     x2 = _rows2d(x.to(torch.bfloat16), topo.tile_cols * TILE, "x")
@@ -671,6 +684,22 @@ def sdd_tiles(dy: torch.Tensor, x: torch.Tensor, topo: TopologyDev, out_dtype: t
         return out
     if d2.shape[0] == 0:
         return out.zero_()
+    rows = d2.shape[0]
+    if path not in (None, "blocks", "tiles"):
+        raise ValueError(f"unknown path {path!r}")
+    if path == "blocks" or (path is None and rows >= SDD_BLOCK_MIN_ROWS):
+        # enough CTAs for two waves of the GPU, each with at least four 64-token stages
+        splits = max(1, min(16, -(-2 * 148 // topo.n_blocks), rows // 256))
+        scratch = None
+        if splits > 1 or out_dtype != torch.float32:
+            scratch = _workspace(dy.device, splits * topo.nnz * 256 * 4)
+        _lib.check(_lib.lib().mortar_sdd_blocks(
+            _ptr(d2), d2.stride(0), _ptr(x2), x2.stride(0), rows, topo.tile_rows * TILE, topo.tile_cols * TILE,
+            _ptr(topo.blk_rc), _ptr(topo.blk_tiles), topo.n_blocks, splits, topo.nnz, _ptr(scratch),
+            scratch.numel() // 4 if scratch is not None else 0, _ptr(out), _dtype_code(out), _stream_ptr()),
+            "mortar_sdd_blocks")
+        _count("sdd_blocks", 1 if scratch is None else 2)
+        return out
     _lib.check(_lib.lib().mortar_sdd_tiles(
         _ptr(d2), d2.stride(0), _ptr(x2), x2.stride(0), d2.shape[0], _ptr(topo.row_ptr), _ptr(topo.col_idx),
         topo.tile_rows, topo.tile_cols, _ptr(topo.item_row), _ptr(topo.item_first), topo.n_items, _ptr(out),

@@ -33,6 +33,40 @@ def test_weight_gradient_tiles(rows):
     assert torch.equal(tb, tiles.to(torch.bfloat16))
 
 
+@pytest.mark.parametrize("rows", [64, 300, 1000, 4096])
+@pytest.mark.parametrize("shape", ["ragged", "local"])
+def test_weight_gradient_blocks(rows, shape):
+    """The tensor-memory block kernel (whole 128 x 128 blocks of dW, kept tiles stored, token
+    dimension split over CTAs) against the per-tile kernel and a float64 product: a ragged
+    topology whose edges are not multiples of 128 features, and the local gate/up shape."""
+    rng = np.random.default_rng(rows)
+    if shape == "ragged":
+        R, C = 21, 13                      # 336 x 208 features: partial blocks on both edges
+        mask = rng.random((R, C)) < 0.4
+        mask[3] = False
+        mask[8:16, 8:13] = False           # a whole block without kept tiles
+        m = mb.MortarMatrix.from_codes(rng.integers(-1, 2, size=(R * 16, C * 16)).astype(np.int8), mask, 0.02)
+    else:
+        m = mb.synth.make_layer(768, 2048, 0.25, seed=7).gate_up
+        R, C = m.tile_rows, m.tile_cols
+    topo = mb.format.TopologyDev(m, DEV)
+    dy = torch.randn(rows, R * 16, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).to(DEV)
+    x = torch.randn(rows, C * 16, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16).to(DEV)
+    blocks = mb.ops.sdd_tiles(dy, x, topo, path="blocks")
+    assert mb.ops.sdd_error() == 0
+    tiles = mb.ops.sdd_tiles(dy, x, topo, path="tiles")
+    scale = max(float(tiles.abs().max()), 1.0)
+    assert float((blocks - tiles).abs().max()) <= 2e-5 * scale
+    if shape == "ragged":
+        full = dy.double().T @ x.double()
+        tr = np.repeat(np.arange(R), np.diff(m.row_ptr))
+        ref = torch.stack([full[r * 16:(r + 1) * 16, c * 16:(c + 1) * 16] for r, c in zip(tr, m.col_idx.astype(int))])
+        assert float((blocks.double() - ref).abs().max()) <= 1e-5 * scale
+    # deterministic, and the bf16 output is the rounded fp32 one
+    assert torch.equal(blocks, mb.ops.sdd_tiles(dy, x, topo, path="blocks"))
+    assert torch.equal(mb.ops.sdd_tiles(dy, x, topo, out_dtype=torch.bfloat16, path="blocks"), blocks.to(torch.bfloat16))
+
+
 @pytest.mark.parametrize("rows", [8, 256])
 @pytest.mark.parametrize("blk", [16, 128])
 def test_autograd_through_the_reference_operator(rows, blk):
