@@ -434,6 +434,41 @@ int mortar_linear_tc_i8(const mortar_sched *w, const void *xq, int64_t ldxq, con
                         int64_t rows, void *out, int64_t ld_out, const float *gates,
                         int64_t ld_gates, int32_t cluster_size, void *stream);
 
+/* ---- prefill, block path: topologies made of (mostly) full 128 x 128 blocks ------------------
+ * The granularity the reference carves at (carve(blocking=128), block_sparse.py:810-907).  Kept
+ * blocks are held expanded -- codes as bf16, [128 outputs][128 inputs] per block, what the
+ * reference keeps as `mortar_data` (block_sparse.py:783-799) without the scale -- so a block is a
+ * plain tensor-core operand; block rows are executed in pairs (SwiGLU: gate block row g with the
+ * up block row of the same hidden columns, which needs d_ff to be a multiple of 128; linear:
+ * block rows 2p and 2p+1).  Same arithmetic and rounding points as mortar_linear_tc.
+ *   data      device bf16 [n_blocks][128][128]; a kept block's tiles that the topology drops, and
+ *             the part of an edge block beyond the matrix, are zeros
+ *   pair_ptr  device int32 [n_pairs + 1]: first step of every pair
+ *   steps     device int32 [n_steps][4] (16-byte aligned): {block column, index into data of the
+ *             first block row's block or -1, of the second's or -1, 0}, ascending block column */
+typedef struct mortar_blocks {
+    const void *data;
+    const int32_t *pair_ptr;
+    const int32_t *steps;
+    int64_t n_blocks;
+    int32_t n_pairs;
+    int32_t n_steps;
+    int32_t out_features;
+    int32_t in_features;
+    int32_t swiglu;
+    float scale;
+} mortar_blocks;
+
+int mortar_linear_blocks(const mortar_blocks *w, const void *x, int64_t ldx, int64_t rows, void *out,
+                         int64_t ld_out, const float *gates, int64_t ld_gates, int32_t cluster_size,
+                         void *stream);
+
+/* mortar_mlp_prefill on the block path (same workspace: rows*d_ff*2 bytes, 256-byte aligned). */
+int mortar_mlp_prefill_blocks(const mortar_blocks *gate_up, const mortar_blocks *down, const void *x,
+                              int64_t ldx, int64_t rows, const float *gates, int64_t ld_gates,
+                              int32_t n_clusters, void *y, int64_t ldy, void *workspace,
+                              int64_t workspace_bytes, void *stream);
+
 /* _SwiGLUMortar.forward on a block of tokens (transformer.py:402-431) as two launches of the
  * kernel above.  workspace: device, 256-byte aligned, rows*d_ff*2 bytes (the hidden block). */
 int mortar_mlp_prefill(const mortar_sched *gate_up, const mortar_sched *down, const void *x,

@@ -49,6 +49,13 @@ class Sched(C.Structure):
                 ("arith", C.c_int32)]
 
 
+class Blocks(C.Structure):
+    """mirror of `mortar_blocks`"""
+    _fields_ = [("data", C.c_void_p), ("pair_ptr", C.c_void_p), ("steps", C.c_void_p), ("n_blocks", C.c_int64),
+                ("n_pairs", C.c_int32), ("n_steps", C.c_int32), ("out_features", C.c_int32),
+                ("in_features", C.c_int32), ("swiglu", C.c_int32), ("scale", C.c_float)]
+
+
 _lib = None
 
 _i32, _i64, _f32, _vp = C.c_int32, C.c_int64, C.c_float, C.c_void_p
@@ -87,6 +94,9 @@ _SIGNATURES = {
     "mortar_sched_sizes": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp]),
     "mortar_build_sched": (C.c_int, [_vp, _vp, _vp, _i32, _i32, _i64, _i32, _vp, _vp, _vp, _vp, _vp]),
     "mortar_linear_tc": (C.c_int, [C.POINTER(Sched), _vp, _i64, _i64, _vp, _i64, _vp, _i64, _i32, _vp]),
+    "mortar_linear_blocks": (C.c_int, [C.POINTER(Blocks), _vp, _i64, _i64, _vp, _i64, _vp, _i64, _i32, _vp]),
+    "mortar_mlp_prefill_blocks": (C.c_int, [C.POINTER(Blocks), C.POINTER(Blocks), _vp, _i64, _i64, _vp, _i64, _i32,
+                                            _vp, _i64, _vp, _i64, _vp]),
     "mortar_sched_sizes_i8": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp]),
     "mortar_build_sched_i8": (C.c_int, [_vp, _vp, _vp, _i32, _i32, _i64, _i32, _vp, _vp, _vp, _vp, _vp]),
     "mortar_quantize_rows": (C.c_int, [_vp, _i64, _i64, _i32, _vp, _i64, _vp, _vp]),

@@ -702,6 +702,268 @@ int linear_tc_impl(const mortar_sched *w, const void *x, int64_t ldx, int64_t ro
     return MORTAR_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Block path: topologies made of (mostly) full 128 x 128 blocks -- the granularity the reference
+// carves at (carve(blocking=128), block_sparse.py:810-907).  The kept blocks are held expanded
+// (codes as bf16, one [128 outputs][128 inputs] block after the other, what the reference keeps as
+// `mortar_data`), so a block is a plain tensor-core operand that TMA brings in: no decode stage,
+// N = 256 MMAs, and 256 accumulator columns per item leave room for two accumulator sets, so the
+// epilogue of an item runs under the MMAs of the next one.
+//
+// Item = 128 activation rows x a PAIR of block rows (SwiGLU: gate block row g and the up block row
+// of the same hidden columns; linear: block rows 2p, 2p+1); the pair's step list names, per block
+// column either of them keeps, the block index of each (or -1).  Per step and half (K = 64): the
+// TMA warp loads the activation chunk [128 x 64] and the present blocks' [128 x 64] halves; the
+// MMA warp issues one N = 256 MMA per 16 features when both blocks are present (they lie back to
+// back in the stage), else N = 128 into the present half.  Eight epilogue warps (two per
+// tensor-memory lane quadrant, each half of the columns) finish as the tile path does.
+constexpr int kBkStages = 4;
+constexpr int kBkA = kRows * 128;                    // [128 rows][64 features] bf16
+constexpr int kBkB = 128 * 128;                      // [128 outputs][64 features] of one block
+constexpr int kBkStage = kBkA + 2 * kBkB;            // 48 KB
+constexpr int kBkEpiWarps = 8;
+constexpr int kBkThreads = 32 * (2 + kBkEpiWarps);   // TMA warp, MMA warp, epilogue warps
+constexpr int kBkMaxSteps = 1024, kBkMaxPairs = 511;   // step lists up to this size are staged in shared memory
+constexpr int kBkSmemBytes = kBkStages * kBkStage + (2 * kBkStages + 4) * 8 + kBkMaxSteps * 16 + (kBkMaxPairs + 1) * 4 +
+                             1024 /*align*/;
+static_assert(kBkSmemBytes <= 227 * 1024, "shared memory budget");
+
+struct BlockParams {
+    const int *pair_ptr;          // [n_pairs + 1] first step of every pair of block rows
+    const int4 *steps;            // [n_steps] {block column, block index of the first row or -1, of the second or -1, 0}
+    int n_pairs;
+    int n_steps;
+    int n_items;                  // n_pairs * row blocks
+    int swiglu;
+    int n_out;                    // output columns: hidden width (SwiGLU) or out_features (linear)
+    long long rows;
+    __nv_bfloat16 *out;
+    long long ld_out;
+    float scale;
+    const float *gates;
+    long long ld_gates;
+    int cluster_size;
+};
+
+// Finishes columns [c0, c0 + 32) of one accumulator set for this thread's row.
+template <bool SWIGLU, bool GATED>
+__device__ __forceinline__ void block_epilogue_chunk(const BlockParams &p, uint32_t taddr, long long row, bool in_range,
+                                                     long long col0, int c0, bool live_a, bool live_b) {
+    uint32_t a[32], b[32];
+    tc_ld32(taddr + c0, a);
+    if (SWIGLU) tc_ld32(taddr + 128 + c0, b);
+    tc_ld_wait(a);
+    if (SWIGLU) tc_ld_wait(b);
+    const bool tile_gates = GATED && (p.cluster_size % 16 == 0);
+    float tg[2] = {1.f, 1.f};
+    if (GATED && tile_gates && in_range) {
+        tg[0] = __ldg(p.gates + row * p.ld_gates + col0 / p.cluster_size);
+        tg[1] = __ldg(p.gates + row * p.ld_gates + (col0 + 16) / p.cluster_size);
+    }
+    uint32_t packed[16];
+#pragma unroll
+    for (int e = 0; e < 32; e += 2) {
+        float gate0 = tg[e >> 4], gate1 = tg[e >> 4];
+        if (GATED && !tile_gates && in_range) {
+            gate0 = __ldg(p.gates + row * p.ld_gates + (col0 + e) / p.cluster_size);
+            gate1 = __ldg(p.gates + row * p.ld_gates + (col0 + e + 1) / p.cluster_size);
+        }
+        packed[e >> 1] = finish2<SWIGLU, GATED>(p.scale, __uint_as_float(a[e]), __uint_as_float(a[e + 1]),
+                                                SWIGLU ? __uint_as_float(b[e]) : 0.f, SWIGLU ? __uint_as_float(b[e + 1]) : 0.f,
+                                                live_a, live_b, gate0, gate1);
+    }
+    if (in_range) {
+        uint4 *dst = reinterpret_cast<uint4 *>(p.out + row * p.ld_out + col0);
+        if (col0 < p.n_out) {
+            dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+        }
+        if (col0 + 16 < p.n_out) {
+            dst[2] = make_uint4(packed[8], packed[9], packed[10], packed[11]);
+            dst[3] = make_uint4(packed[12], packed[13], packed[14], packed[15]);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kBkThreads, 1)
+prefill_blocks_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+                      const BlockParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *stages = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t *full = reinterpret_cast<uint64_t *>(stages + kBkStages * kBkStage), *empty = full + kBkStages;
+    uint64_t *acc_full = empty + kBkStages, *acc_empty = acc_full + 2;
+    int4 *steps_s = reinterpret_cast<int4 *>(acc_empty + 2);
+    int *pairs_s = reinterpret_cast<int *>(steps_s + kBkMaxSteps);
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int abort_s;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // the step lists are read by three roles for every item: keep them in shared memory when they fit
+    const bool cached = p.n_steps <= kBkMaxSteps && p.n_pairs <= kBkMaxPairs;
+    if (cached) {
+        for (int i = threadIdx.x; i < p.n_steps; i += kBkThreads) steps_s[i] = __ldg(p.steps + i);
+        for (int i = threadIdx.x; i <= p.n_pairs; i += kBkThreads) pairs_s[i] = __ldg(p.pair_ptr + i);
+    }
+    const int4 *steps = cached ? steps_s : p.steps;
+    const int *pair_ptr = cached ? pairs_s : p.pair_ptr;
+
+    if (threadIdx.x == 0) {
+        abort_s = 0;
+        for (int s = 0; s < kBkStages; ++s) { mbar_init(smem_u32(&full[s]), 1); mbar_init(smem_u32(&empty[s]), 1); }
+        for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&acc_full[s]), 1); mbar_init(smem_u32(&acc_empty[s]), kBkEpiWarps); }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(smem_u32(&tmem_base_s)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem = tmem_base_s;
+    volatile int *abort_flag = &abort_s;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        int g = 0;
+        bool ok = true;
+        for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
+            const int pair = item % p.n_pairs, row0 = (item / p.n_pairs) * kRows;
+            const int s_end = pair_ptr[pair + 1];
+            for (int st = pair_ptr[pair]; st < s_end && ok; ++st) {
+                const int4 s = steps[st];
+#pragma unroll 1
+                for (int h = 0; h < 2; ++h, ++g) {
+                    const int sg = g % kBkStages;
+                    ok = mbar_wait_relaxed(smem_u32(&empty[sg]), ((g / kBkStages) & 1) ^ 1u, abort_flag, 5);
+                    if (!ok) break;
+                    if (lane == 0) {
+                        const uint32_t bar = smem_u32(&full[sg]);
+                        const uint32_t dst = smem_u32(stages + sg * kBkStage);
+                        mbar_arrive_expect_tx(bar, kBkA + (s.y >= 0 ? kBkB : 0) + (s.z >= 0 ? kBkB : 0));
+                        asm volatile(
+                            "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+                            "[%0], [%1, {%2, %3}], [%4];\n"
+                            ::"r"(dst), "l"(&tmap_x), "r"(s.x * 128 + h * 64), "r"(row0), "r"(bar) : "memory");
+                        if (s.y >= 0)
+                            asm volatile(
+                                "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+                                "[%0], [%1, {%2, %3}], [%4];\n"
+                                ::"r"(dst + kBkA), "l"(&tmap_w), "r"(h * 64), "r"(s.y * 128), "r"(bar) : "memory");
+                        if (s.z >= 0)
+                            asm volatile(
+                                "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+                                "[%0], [%1, {%2, %3}], [%4];\n"
+                                ::"r"(dst + kBkA + kBkB), "l"(&tmap_w), "r"(h * 64), "r"(s.z * 128), "r"(bar) : "memory");
+                    }
+                    __syncwarp();
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issue ----------------
+        // kind::f16, D fp32, A and B bf16, both K-major; N >> 3 at bit 17, M >> 4 at bit 24
+        constexpr uint32_t kIdescBase = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 4) << 24);
+        constexpr uint32_t kIdesc128 = kIdescBase | ((128u >> 3) << 17), kIdesc256 = kIdescBase | ((256u >> 3) << 17);
+        int g = 0, it = 0;
+        bool ok = true;
+        for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++it) {
+            const int pair = item % p.n_pairs, buf = it & 1;
+            ok = mbar_wait_relaxed(smem_u32(&acc_empty[buf]), ((it >> 1) & 1) ^ 1u, abort_flag, 9);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const uint32_t acc = tmem + buf * kAccCols;
+            uint32_t have_a = 0u, have_b = 0u;                 // the halves hold defined values (uniform across the warp)
+            const int s_beg = pair_ptr[pair], s_end = pair_ptr[pair + 1];
+            for (int st = s_beg; st < s_end && ok; ++st) {
+                const int4 s = steps[st];
+#pragma unroll 1
+                for (int h = 0; h < 2; ++h, ++g) {
+                    const int sg = g % kBkStages;
+                    ok = mbar_wait(smem_u32(&full[sg]), (g / kBkStages) & 1, abort_flag, 2);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    if (lane == 0) {
+                        const uint32_t base = smem_u32(stages + sg * kBkStage);
+                        const uint64_t ad = make_smem_desc(base, 16, 1024, 2);
+                        const uint64_t bd = make_smem_desc(base + kBkA, 16, 1024, 2);
+                        const uint32_t a_lo = (uint32_t)ad, a_hi = (uint32_t)(ad >> 32);
+                        const uint32_t b_lo = (uint32_t)bd, b_hi = (uint32_t)(bd >> 32);
+                        uint32_t fa = have_a, fb = have_b;
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk) {       // 16 features = 32 bytes inside the swizzled row
+                            if (s.y >= 0 && s.z >= 0 && fa == fb) {
+                                tc_mma(acc, a_lo + kk * 2, a_hi, b_lo + kk * 2, b_hi, kIdesc256, fa);
+                            } else {
+                                if (s.y >= 0) tc_mma(acc, a_lo + kk * 2, a_hi, b_lo + kk * 2, b_hi, kIdesc128, fa);
+                                if (s.z >= 0) tc_mma(acc + 128, a_lo + kk * 2, a_hi, b_lo + (kBkB >> 4) + kk * 2, b_hi, kIdesc128, fb);
+                            }
+                            if (s.y >= 0) fa = 1u;
+                            if (s.z >= 0) fb = 1u;
+                        }
+                        tc_commit(smem_u32(&empty[sg]));
+                    }
+                    if (s.y >= 0) have_a = 1u;
+                    if (s.z >= 0) have_b = 1u;
+                    __syncwarp();
+                }
+            }
+            if (!ok) break;
+            if (lane == 0) {
+                if (s_end > s_beg) tc_commit(smem_u32(&acc_full[buf]));
+                else mbar_arrive(smem_u32(&acc_full[buf]));
+            }
+            __syncwarp();
+        }
+    } else {
+        // ---------------- epilogue: warps 2..9; lane quadrant = warp % 4, column half = (warp - 2) / 4 ----------------
+        const int q = warp & 3, ch = (warp - 2) >> 2;
+        int it = 0;
+        bool ok = true;
+        for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++it) {
+            const int pair = item % p.n_pairs, buf = it & 1;
+            const long long row = (long long)(item / p.n_pairs) * kRows + q * 32 + lane;
+            const bool in_range = row < p.rows;
+            // which of the two block rows received a block at all
+            bool live_a = false, live_b = false;
+            const int s_end = pair_ptr[pair + 1];
+            for (int st = pair_ptr[pair]; st < s_end; ++st) {
+                const int4 s = steps[st];
+                live_a |= s.y >= 0;
+                live_b |= s.z >= 0;
+            }
+            ok = mbar_wait_relaxed(smem_u32(&acc_full[buf]), (it >> 1) & 1, abort_flag, 8);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const uint32_t taddr = tmem + buf * kAccCols + ((uint32_t)(q * 32) << 16);
+            if (p.swiglu) {
+                // hidden columns [128 pair, +128): gate sums in accumulator columns 0..127, up sums in 128..255
+#pragma unroll 1
+                for (int c0 = ch * 64; c0 < ch * 64 + 64; c0 += 32) {
+                    const long long col0 = (long long)pair * 128 + c0;
+                    if (p.gates == nullptr) block_epilogue_chunk<true, false>(p, taddr, row, in_range, col0, c0, live_a, live_b);
+                    else block_epilogue_chunk<true, true>(p, taddr, row, in_range, col0, c0, live_a, live_b);
+                }
+            } else {
+#pragma unroll 1
+                for (int c0 = ch * 128; c0 < ch * 128 + 128; c0 += 32) {
+                    const long long col0 = (long long)pair * 256 + c0;
+                    block_epilogue_chunk<false, false>(p, taddr, row, in_range, col0, c0, c0 < 128 ? live_a : live_b, true);
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&acc_empty[buf]));
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 1)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(kTmemCols) : "memory");
+}
+
 // Per-row symmetric int8 quantisation: scale[r] = max|x[r]| / 127, q = round(x / scale[r]).
 // One CTA per row; the row is read twice (the second time from cache).
 __global__ void __launch_bounds__(256)
@@ -771,6 +1033,107 @@ extern "C" int mortar_quantize_rows(const void *x, int64_t ldx, int64_t rows, in
         reinterpret_cast<const __nv_bfloat16 *>(x), ldx, cols, reinterpret_cast<int8_t *>(q), ldq, scale);
     MORTAR_CUDA_CHECK(cudaGetLastError());
     return MORTAR_OK;
+}
+
+extern "C" int mortar_linear_blocks(const mortar_blocks *w, const void *x, int64_t ldx, int64_t rows, void *out,
+                                    int64_t ld_out, const float *gates, int64_t ld_gates, int32_t cluster_size,
+                                    void *stream) {
+    if (!w || !x || !out || !w->pair_ptr || (w->n_steps > 0 && (!w->steps || !w->data))) return MORTAR_ERR_NULL;
+    if (w->n_pairs <= 0 || w->n_steps < 0 || w->out_features <= 0 || w->in_features <= 0 || rows < 0 ||
+        (w->out_features % 16) || (w->in_features % 16))
+        return MORTAR_ERR_SHAPE;
+    const int n_out = w->swiglu ? w->out_features / 2 : w->out_features;
+    if (w->swiglu && (n_out % 128)) return MORTAR_ERR_SHAPE;        // gate and up block rows pair up
+    if (ldx < w->in_features || ld_out < n_out) return MORTAR_ERR_SHAPE;
+    if (!aligned_to(x, 16) || (ldx % 8) || !aligned_to(out, 16) || (ld_out % 8) || !aligned_to(w->data, 16) ||
+        !aligned_to(w->steps, 16))
+        return MORTAR_ERR_ALIGN;
+    if (gates && (cluster_size <= 0 || !w->swiglu)) return MORTAR_ERR_SHAPE;
+    if (rows == 0) return MORTAR_OK;
+    const int64_t row_blocks = (rows + kRows - 1) / kRows;
+    const int64_t n_items = row_blocks * w->n_pairs;
+    if (n_items > 0x7fffffffLL || rows > 0x7fffffffLL || w->n_blocks > (0x7fffffffLL >> 7)) return MORTAR_ERR_CAPACITY;
+
+    EncodeTiledFn encode;
+    int rc = get_encode_fn(&encode);
+    if (rc != MORTAR_OK) return rc;
+    alignas(64) CUtensorMap tmap_x, tmap_w;
+    const cuuint32_t box[2] = {64, 128};
+    const cuuint32_t estride[2] = {1, 1};
+    {
+        const cuuint64_t gdim[2] = {(cuuint64_t)w->in_features, (cuuint64_t)rows};
+        const cuuint64_t gstride[1] = {(cuuint64_t)ldx * 2};
+        if (encode(&tmap_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(x), gdim, gstride, box, estride,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+            mortar_set_cuda_error("cuTensorMapEncodeTiled", "failed to encode the activation tensor map");
+            return MORTAR_ERR_CUDA;
+        }
+    }
+    {
+        // the expanded blocks as one [n_blocks * 128][128] matrix (a matrix without blocks never loads from it)
+        const cuuint64_t gdim[2] = {128, (cuuint64_t)(w->n_blocks > 0 ? w->n_blocks : 1) * 128};
+        const cuuint64_t gstride[1] = {256};
+        void *base = w->n_blocks > 0 ? const_cast<void *>(w->data) : const_cast<void *>(x);
+        if (encode(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, gdim, gstride, box, estride,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+            mortar_set_cuda_error("cuTensorMapEncodeTiled", "failed to encode the block tensor map");
+            return MORTAR_ERR_CUDA;
+        }
+    }
+    int dev = 0;
+    MORTAR_CUDA_CHECK(cudaGetDevice(&dev));
+    static int sm_count[64] = {0};
+    if (dev < 0 || dev >= 64) return MORTAR_ERR_CAPACITY;
+    int sms = 0;
+    {
+        std::lock_guard<std::mutex> lock(g_prefill_init_mutex);
+        if (sm_count[dev] == 0) {
+            int v = 0;
+            MORTAR_CUDA_CHECK(cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev));
+            MORTAR_CUDA_CHECK(cudaFuncSetAttribute(prefill_blocks_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   kBkSmemBytes));
+            sm_count[dev] = v;
+        }
+        sms = sm_count[dev];
+    }
+    BlockParams p;
+    p.pair_ptr = w->pair_ptr;
+    p.steps = reinterpret_cast<const int4 *>(w->steps);
+    p.n_pairs = w->n_pairs;
+    p.n_steps = w->n_steps;
+    p.n_items = (int)n_items;
+    p.swiglu = w->swiglu;
+    p.n_out = n_out;
+    p.rows = rows;
+    p.out = reinterpret_cast<__nv_bfloat16 *>(out);
+    p.ld_out = ld_out;
+    p.scale = __bfloat162float(__float2bfloat16_rn(w->scale));
+    p.gates = gates;
+    p.ld_gates = ld_gates;
+    p.cluster_size = cluster_size > 0 ? cluster_size : 1;
+    const unsigned grid = (unsigned)(n_items < sms ? n_items : sms);
+    prefill_blocks_kernel<<<grid, kBkThreads, kBkSmemBytes, (cudaStream_t)stream>>>(tmap_x, tmap_w, p);
+    MORTAR_CUDA_CHECK(cudaGetLastError());
+    return MORTAR_OK;
+}
+
+extern "C" int mortar_mlp_prefill_blocks(const mortar_blocks *gate_up, const mortar_blocks *down, const void *x,
+                                         int64_t ldx, int64_t rows, const float *gates, int64_t ld_gates,
+                                         int32_t n_clusters, void *y, int64_t ldy, void *workspace,
+                                         int64_t workspace_bytes, void *stream) {
+    if (!gate_up || !down || !x || !y || !workspace) return MORTAR_ERR_NULL;
+    if (!gate_up->swiglu || down->swiglu) return MORTAR_ERR_SHAPE;
+    const int d_model = gate_up->in_features, d_ff = gate_up->out_features / 2;
+    if (down->in_features != d_ff || down->out_features != d_model) return MORTAR_ERR_SHAPE;
+    if (gates && (n_clusters <= 0 || d_ff % n_clusters)) return MORTAR_ERR_SHAPE;
+    if (!aligned_to(workspace, 256)) return MORTAR_ERR_ALIGN;
+    if (workspace_bytes < rows * (int64_t)d_ff * 2) return MORTAR_ERR_CAPACITY;
+    int rc = mortar_linear_blocks(gate_up, x, ldx, rows, workspace, d_ff, gates, ld_gates,
+                                  gates ? d_ff / n_clusters : 0, stream);
+    if (rc != MORTAR_OK) return rc;
+    return mortar_linear_blocks(down, workspace, d_ff, rows, y, ldy, nullptr, 0, 0, stream);
 }
 
 extern "C" int mortar_mlp_prefill(const mortar_sched *gate_up, const mortar_sched *down, const void *x,

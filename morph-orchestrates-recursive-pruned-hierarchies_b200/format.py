@@ -304,6 +304,10 @@ class MortarMatrix:
         ``arith="i8"`` builds the layout of the opt-in 8-bit arm."""
         return SchedMatrix(self, swiglu, device, arith)
 
+    def to_blocks(self, swiglu: bool, device="cuda") -> "BlockSched":
+        """Prefill execution layout of the block path (topologies carved at 128 x 128)."""
+        return BlockSched(self, swiglu, device)
+
     def to_stream(self, device="cuda") -> "StreamMatrix":
         grp_ptr, grp_cols, grp_codes, G = self.build_stream_host()
         return StreamMatrix(self.out_features, self.in_features, self.scale, G, self.nnz,
@@ -421,6 +425,71 @@ class SchedMatrix:
                                  self.data_units, self.n_panels, self.out_features // TILE,
                                  self.in_features // TILE, int(self.swiglu), self.scale,
                                  1 if self.arith == "i8" else 0)
+        return self._c
+
+
+BLOCK = 128
+
+
+def block_fill(m: "MortarMatrix") -> float:
+    """Kept tiles / (64 x the number of 128 x 128 blocks that hold a kept tile): 1.0 for a topology
+    carved at 128, about the tile density for a random tile-16 one."""
+    if m.nnz == 0:
+        return 0.0
+    rows = np.repeat(np.arange(m.tile_rows), np.diff(m.row_ptr)).astype(np.int64)
+    key = (rows // 8) * ((m.tile_cols + 7) // 8) + m.col_idx.astype(np.int64) // 8
+    return float(m.nnz) / (64.0 * np.unique(key).size)
+
+
+class BlockSched:
+    """Device-resident layout of one matrix for the block path of the prefill kernels: every
+    128 x 128 block that holds a kept tile, expanded to bf16 codes (dropped tiles inside it are
+    zeros), and the step lists of the pairs of block rows (see ``mortar_blocks`` in the header)."""
+
+    def __init__(self, m: "MortarMatrix", swiglu: bool, device="cuda"):
+        if swiglu and (m.out_features // 2) % BLOCK:
+            raise ValueError("the block path pairs gate and up block rows: d_ff must be a multiple of 128")
+        self.out_features, self.in_features = m.out_features, m.in_features
+        self.swiglu, self.scale, self.nnz = bool(swiglu), float(m.scale), m.nnz
+        Rb, Cb = -(-m.out_features // BLOCK), -(-m.in_features // BLOCK)
+        dense = np.zeros((Rb * BLOCK, Cb * BLOCK), dtype=np.int8)
+        dense[:m.out_features, :m.in_features] = m.to_dense_codes()
+        rows = np.repeat(np.arange(m.tile_rows), np.diff(m.row_ptr)).astype(np.int64)
+        key = np.unique((rows // 8) * Cb + m.col_idx.astype(np.int64) // 8)          # ascending (row, column)
+        brow, bcol = key // Cb, key % Cb
+        blocks = dense.reshape(Rb, BLOCK, Cb, BLOCK).transpose(0, 2, 1, 3)[brow, bcol]   # [nb, 128, 128]
+        self.n_blocks = int(key.size)
+        index = {(int(r), int(c)): i for i, (r, c) in enumerate(zip(brow, bcol))}
+        cols_of = [[] for _ in range(Rb)]
+        for r, c in zip(brow, bcol):
+            cols_of[int(r)].append(int(c))
+        if swiglu:
+            half = Rb // 2
+            pairs = [(g, g + half) for g in range(half)]
+        else:
+            pairs = [(2 * q, 2 * q + 1 if 2 * q + 1 < Rb else -1) for q in range((Rb + 1) // 2)]
+        pair_ptr, steps = [0], []
+        for ra, rb in pairs:
+            ca = set(cols_of[ra])
+            cb = set(cols_of[rb]) if rb >= 0 else set()
+            for c in sorted(ca | cb):
+                steps.append((c, index[(ra, c)] if c in ca else -1, index[(rb, c)] if c in cb else -1, 0))
+            pair_ptr.append(len(steps))
+        self.n_pairs, self.n_steps = len(pairs), len(steps)
+        self.data = torch.from_numpy(np.ascontiguousarray(blocks)).to(device=device, dtype=torch.bfloat16)
+        self.pair_ptr = torch.tensor(pair_ptr, dtype=torch.int32, device=device)
+        self.steps = torch.tensor(steps if steps else [(0, -1, -1, 0)], dtype=torch.int32, device=device).reshape(-1, 4)
+        self._c = None
+
+    @property
+    def n_out(self) -> int:
+        return self.out_features // 2 if self.swiglu else self.out_features
+
+    def c_struct(self) -> _lib.Blocks:
+        if self._c is None:
+            self._c = _lib.Blocks(self.data.data_ptr(), self.pair_ptr.data_ptr(), self.steps.data_ptr(),
+                                  self.n_blocks, self.n_pairs, self.n_steps, self.out_features, self.in_features,
+                                  int(self.swiglu), self.scale)
         return self._c
 
 

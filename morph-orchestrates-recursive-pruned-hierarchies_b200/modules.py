@@ -23,12 +23,13 @@ import torch
 import torch.nn as nn
 
 from . import ops
-from .format import TILE, MortarMatrix, SchedMatrix, StreamMatrix
+from .format import TILE, BlockSched, MortarMatrix, SchedMatrix, StreamMatrix, block_fill
 
 # bf16 token blocks with at least this many rows take the tensor-memory kernel.  Measured on
 # B200 at the 768/2048 and 2048/5632 shapes: the streaming kernel wins below 128 rows, the
 # tcgen05 kernel (whose work item is a block of 128 rows) from 128 rows on.
 TC_MIN_ROWS = 128
+BLOCK_PATH_MIN_FILL = 0.5     # touched 128 x 128 blocks at least this full take the block path of the prefill kernels
 
 
 class CarvedStorage(nn.Module):
@@ -188,6 +189,16 @@ class CarvedStorage(nn.Module):
             self._sched[swiglu] = self.matrix().to_sched(swiglu, self._device)
         return self._sched[swiglu]
 
+    def blocks(self, swiglu: bool) -> Optional[BlockSched]:
+        """Layout of the block path when the topology is made of (mostly) full 128 x 128 blocks
+        (and, for a gate/up matrix, d_ff is a multiple of 128); None otherwise."""
+        key = ("blocks", swiglu)
+        if key not in self._sched:
+            m = self.matrix()
+            ok = block_fill(m) >= BLOCK_PATH_MIN_FILL and not (swiglu and (m.out_features // 2) % 128)
+            self._sched[key] = m.to_blocks(swiglu, self._device) if ok else None
+        return self._sched[key]
+
     # ---- reference API ------------------------------------------------------------------
     def accumulate_scores(self) -> None:
         """No-op: saliency scoring stops at carve time (block_sparse.py:453-493 returns early
@@ -206,7 +217,8 @@ class CarvedStorage(nn.Module):
         if torch.is_autocast_enabled() and x.is_cuda and x.dtype == torch.float32:
             x = x.to(torch.get_autocast_dtype("cuda"))           # as _forward_mortar does (block_sparse.py:947-955)
         if x.dtype == torch.bfloat16 and rows >= TC_MIN_ROWS and x.is_cuda:
-            y = ops.linear_tc(x, self.sched(False))
+            blk = self.blocks(False)
+            y = ops.linear_blocks(x, blk) if blk is not None else ops.linear_tc(x, self.sched(False))
         else:
             y = ops.linear(x, self.stream())
         if self.bias is not None:
@@ -345,6 +357,9 @@ class SwiGLUMortar(nn.Module):
         if x.dtype == torch.bfloat16:
             rows = x.numel() // self.d_model
             if rows >= TC_MIN_ROWS and x.is_cuda:
+                bg, bd = gu.blocks(True), dn.blocks(False)
+                if bg is not None and bd is not None:
+                    return ops.mlp_prefill_blocks(x, bg, bd, gates=gates, n_clusters=self.n_clusters)
                 return ops.mlp_prefill_tc(x, gu.sched(True), dn.sched(False), gates=gates,
                                           n_clusters=self.n_clusters)
             return ops.mlp_prefill(x, gu.stream(), dn.stream(), gates=gates, n_clusters=self.n_clusters)

@@ -11,7 +11,7 @@ from typing import Optional
 import torch
 
 from . import _lib
-from .format import TILE, MortarMatrix, SchedMatrix, StreamMatrix, TopologyDev
+from .format import TILE, BlockSched, MortarMatrix, SchedMatrix, StreamMatrix, TopologyDev
 
 _launches = 0      # kernels launched by this module (bench.py reports it)
 _kernel_counts: dict = {}   # the same, per kernel family
@@ -591,6 +591,71 @@ def mlp_prefill_tc(x: torch.Tensor, gate_up: SchedMatrix, down: SchedMatrix, *,
         g.stride(0) if g is not None else 0, int(n_clusters), _ptr(out2), out2.stride(0),
         _ptr(workspace), workspace.numel(), _stream_ptr()), "mortar_mlp_prefill")
     _count("prefill_panel", 2)
+    return out.reshape(*lead, d_model)
+
+
+def linear_blocks(x: torch.Tensor, w: BlockSched, *, gates: Optional[torch.Tensor] = None,
+                  cluster_size: int = 0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``linear_tc`` on the block path: the matrix as expanded 128 x 128 blocks (``MortarMatrix.to_blocks``),
+    bf16 x[rows, in] -> bf16 [rows, out] (or [rows, out/2] = silu(gate)*up for a swiglu layout), the
+    reference's prefill rounding (stk dds at its own granularity, triton_kernels.py:203-226)."""
+    _require_cuda(x, "x")
+    if x.dtype != torch.bfloat16:
+        raise ValueError("linear_blocks takes bfloat16 activations")
+    lead = x.shape[:-1]
+    x2 = _rows2d(x, w.in_features, "x")
+    rows = x2.shape[0]
+    if x2.stride(0) % 8 or x2.data_ptr() % 16:
+        x2 = x2.contiguous()
+    n_out = w.n_out
+    if out is None:
+        out = torch.empty(rows, n_out, device=x.device, dtype=torch.bfloat16)
+    out2 = out.reshape(rows, n_out)
+    if rows == 0:
+        return out.reshape(*lead, n_out)
+    g = None
+    if gates is not None:
+        g = gates.to(device=x.device, dtype=torch.float32).reshape(rows, -1).contiguous()
+    st = w.c_struct()
+    _lib.check(_lib.lib().mortar_linear_blocks(C.byref(st), _ptr(x2), x2.stride(0), rows, _ptr(out2),
+                                               out2.stride(0), _ptr(g), g.stride(0) if g is not None else 0,
+                                               int(cluster_size), _stream_ptr()), "mortar_linear_blocks")
+    _count("prefill_blocks")
+    return out.reshape(*lead, n_out)
+
+
+def mlp_prefill_blocks(x: torch.Tensor, gate_up: BlockSched, down: BlockSched, *,
+                       gates: Optional[torch.Tensor] = None, n_clusters: int = 0,
+                       out: Optional[torch.Tensor] = None,
+                       workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``_SwiGLUMortar.forward`` on a token block through the block path of the tcgen05 kernels
+    (transformer.py:402-431): bf16 in, bf16 out, the reference's autocast rounding points."""
+    _require_cuda(x, "x")
+    xb = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
+    d_model, d_ff = gate_up.in_features, gate_up.out_features // 2
+    lead = xb.shape[:-1]
+    x2 = _rows2d(xb, d_model, "x")
+    rows = x2.shape[0]
+    if x2.stride(0) % 8 or x2.data_ptr() % 16:
+        x2 = x2.contiguous()
+    if out is None:
+        out = torch.empty(rows, d_model, device=x.device, dtype=torch.bfloat16)
+    out2 = out.reshape(rows, d_model)
+    if rows == 0:
+        return out.reshape(*lead, d_model)
+    if workspace is None:
+        workspace = _workspace(x.device, rows * d_ff * 2)
+    g = None
+    if gates is not None:
+        g = gates.to(device=x.device, dtype=torch.float32).reshape(rows, -1).contiguous()
+        if g.shape[1] != n_clusters:
+            raise ValueError(f"gates have {g.shape[1]} clusters, n_clusters={n_clusters}")
+    gu, dn = gate_up.c_struct(), down.c_struct()
+    _lib.check(_lib.lib().mortar_mlp_prefill_blocks(
+        C.byref(gu), C.byref(dn), _ptr(x2), x2.stride(0), rows, _ptr(g),
+        g.stride(0) if g is not None else 0, int(n_clusters), _ptr(out2), out2.stride(0),
+        _ptr(workspace), workspace.numel(), _stream_ptr()), "mortar_mlp_prefill_blocks")
+    _count("prefill_blocks", 2)
     return out.reshape(*lead, d_model)
 
 

@@ -1,0 +1,103 @@
+"""The block path of the prefill kernels (topologies carved at 128 x 128: expanded blocks as plain
+tensor-core operands, pairs of block rows, two accumulator sets) against the CPU oracle, the tile
+path and the golden fixture made by the reference at blocking 128."""
+import numpy as np
+import pytest
+import torch
+
+import mortar_b200 as mb
+from conftest import bf16_from_bits, load_golden
+from oracle import mortar_oracle as orc
+from test_gpu_parity import _assert_bf16_close, _dense
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _clean():
+    assert mb.ops.prefill_error() == 0, "a bounded wait in the prefill kernel expired"
+
+
+@pytest.mark.parametrize("rows", [1, 100, 128, 300, 1000])
+def test_linear_blocks_ragged(rows):
+    """edges that are not multiples of 128, an empty block row, an odd number of block rows, blocks
+    with dropped tiles inside."""
+    rng = np.random.default_rng(7)
+    R, C = 43, 21                                      # 688 x 336 features: 6 x 3 blocks with ragged edges
+    mask = np.zeros((R, C), dtype=bool)
+    for rb, cb in [(0, 0), (0, 2), (1, 1), (3, 0), (3, 1), (3, 2), (4, 2), (5, 0), (5, 2)]:   # block row 2 is empty
+        mask[rb * 8:(rb + 1) * 8, cb * 8:(cb + 1) * 8] = True
+    mask[1, 2] = False                                 # a dropped tile inside a kept block
+    mask[30:32, 20] = False
+    codes = rng.integers(-1, 2, size=(R * 16, C * 16)).astype(np.int8)
+    m = mb.MortarMatrix.from_codes(codes, mask, 0.0173)
+    x = torch.randn(rows, C * 16, generator=torch.Generator().manual_seed(rows)).to(torch.bfloat16)
+    y = mb.ops.linear_blocks(x.to(DEV), m.to_blocks(False, DEV))
+    _clean()
+    W = torch.from_numpy(m.to_dense_codes()).float() * torch.tensor(0.0173).to(torch.bfloat16).float()
+    ref = torch.nn.functional.linear(x, W.to(torch.bfloat16))
+    _assert_bf16_close(y, ref)
+    assert float(y[:, 256:384].float().abs().max()) == 0.0           # the empty block row
+
+
+@pytest.mark.parametrize("rows", [128, 391, 2048])
+def test_mlp_blocks_cloud_shape_vs_oracle_and_tile_path(rows):
+    d, f = 2048, 5632
+    gu_m = mb.synth.make_block_matrix(2 * f, d, 0.25, seed=11)
+    dn_m = mb.synth.make_block_matrix(d, f, 0.25, seed=12)
+    assert mb.format.block_fill(gu_m) == 1.0
+    x = mb.synth.make_activations(rows, d, seed=rows).to(DEV)
+    bg, bd = gu_m.to_blocks(True, DEV), dn_m.to_blocks(False, DEV)
+    y = mb.ops.mlp_prefill_blocks(x, bg, bd)
+    _clean()
+    ref = orc.swiglu_mlp(x.cpu().float(), _dense(gu_m), _dense(dn_m), dtype=torch.bfloat16)
+    _assert_bf16_close(y, ref, near_zero=1e-2)
+    # exact integer activations: both paths must agree bit for bit (every sum is exact)
+    xi = torch.randint(-3, 4, (rows, d), generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).to(DEV)
+    hb = mb.ops.linear_blocks(xi, gu_m.to_blocks(False, DEV))
+    ht = mb.ops.linear_tc(xi, gu_m.to_sched(False, DEV))
+    assert torch.equal(hb, ht)
+    ncls = f // 16
+    L = type("L", (), {"gate_up": gu_m, "down": dn_m, "d_ff": f, "d_model": d})
+    gates = mb.synth.make_gates(rows, L, ncls, ncls // 4, seed=3).to(DEV)
+    yg = mb.ops.mlp_prefill_blocks(x, bg, bd, gates=gates, n_clusters=ncls)
+    refg = orc.swiglu_mlp(x.cpu().float(), _dense(gu_m), _dense(dn_m), gates.cpu(), ncls, dtype=torch.bfloat16)
+    _assert_bf16_close(yg, refg, near_zero=1e-2)
+    _clean()
+    # token blocks are independent: a 128-row slice gives the same bits
+    if rows >= 256:
+        assert torch.equal(mb.ops.mlp_prefill_blocks(x[128:256], bg, bd), y[128:256])
+
+
+def test_blocks_golden_fixture_and_module_dispatch():
+    """The reference's own 128-blocking carve (fixture made by running it) through the block path, and
+    the module forward choosing that path by itself."""
+    g = load_golden("mlp_blk128_d256")
+    if g is not None:
+        d_model, d_ff, blk, ncls = (int(v) for v in g["meta"])
+        assert blk == 128
+        mats = {}
+        for tag, (O, I) in (("gu", (2 * d_ff, d_model)), ("dn", (d_model, d_ff))):
+            mats[tag] = mb.MortarMatrix.from_reference_bcsr(
+                g[f"{tag}_offsets"], g[f"{tag}_column_indices"], g[f"{tag}_packed"],
+                float(g[f"{tag}_scale"]), blk, O, I)
+        if d_ff % 128 == 0:
+            x = bf16_from_bits(g["x_bf16"])
+            y = mb.ops.mlp_prefill_blocks(x.to(DEV), mats["gu"].to_blocks(True, DEV), mats["dn"].to_blocks(False, DEV))
+            _clean()
+            _assert_bf16_close(y, bf16_from_bits(g["y_bf16"]))
+    gu_m = mb.synth.make_block_matrix(2 * 512, 256, 0.5, seed=1)
+    dn_m = mb.synth.make_block_matrix(256, 512, 0.5, seed=2)
+    mlp = mb.SwiGLUMortar.from_matrices(gu_m, dn_m, device=DEV)
+    x = mb.synth.make_activations(256, 256, seed=4).to(DEV)
+    n0 = mb.ops.kernel_counts().get("prefill_blocks", 0)
+    y = mlp(x)
+    assert mb.ops.kernel_counts()["prefill_blocks"] - n0 == 2
+    ref = orc.swiglu_mlp(x.cpu().float(), _dense(gu_m), _dense(dn_m), dtype=torch.bfloat16)
+    _assert_bf16_close(y, ref, near_zero=1e-2)
+    # a tile-16 topology keeps the tile path
+    L = mb.synth.make_layer(256, 512, 0.25, seed=3)
+    mlp2 = mb.SwiGLUMortar.from_matrices(L.gate_up, L.down, device=DEV)
+    n1 = mb.ops.kernel_counts().get("prefill_panel", 0)
+    mlp2(x)
+    assert mb.ops.kernel_counts()["prefill_panel"] - n1 == 2
