@@ -475,6 +475,11 @@ def run_ours(args, rank, world, local_rank):
                 "checksum": r["checksum"]}
             prefill["roofline"] = tensor_roofline(prefill["useful_tflops"], pk, fp8)
             extra["prefill_cloud"] = prefill
+            with ClockSampler(local_rank) as sc:
+                tp = run_prefill(mb, device, pk, flush, reps=2, tile_path=True)
+            tp["roofline"] = tensor_roofline(tp["useful_tflops"], pk, fp8)
+            tp["clocks"] = sc.summary()
+            extra["prefill_cloud_tile_path"] = tp
             for name, fn in (("single_layer_c0", run_single_layer), ("prefill_cloud_blocks128", run_prefill_blocks128),
                              ("prefill_cloud_i8", run_prefill_i8), ("backward_gate_up_c0", run_backward), ("sweep_c3", run_sweep), ("remoe_c4", run_remoe),
                              ("gemv_large_b1", run_gemv_large)):
@@ -532,7 +537,8 @@ def cloud_modules(mb, device, n_layers=None, mask="topk_l2", density=DENSITY):
     return layers, mods
 
 
-def run_prefill(mb, device, pk, flush, tokens: int = PREFILL_TOKENS, reps: int = 3, seed: int = 7):
+def run_prefill(mb, device, pk, flush, tokens: int = PREFILL_TOKENS, reps: int = 3, seed: int = 7,
+                tile_path: bool = False):
     """Cloud-shape prefill (configs[2]): 16 layers, 72 applications, 16384 tokens per GPU, bf16 with
     the reference's rounding points, through the MODULE forward (``SwiGLUMortar.__call__``, which
     sends token blocks to the tcgen05 / tensor-memory kernels).  Every application reads the same
@@ -545,7 +551,12 @@ def run_prefill(mb, device, pk, flush, tokens: int = PREFILL_TOKENS, reps: int =
     d = cfg["d_model"]
     x0 = mb.synth.make_activations(tokens, d, seed=seed)
     x = x0.to(device)
-    n0 = mb.ops.kernel_counts().get("prefill_panel", 0)
+    # the module picks the kernel by the fill of the touched 128 x 128 blocks (25% random tiles: the
+    # block path); tile_path pins the per-tile kernel for comparison
+    saved_fill = mb.format.BLOCK_PATH_MIN_FILL
+    if tile_path:
+        mb.format.BLOCK_PATH_MIN_FILL = 2.0
+    counts0 = dict(mb.ops.kernel_counts())
     state = {}
 
     def fn():
@@ -553,7 +564,12 @@ def run_prefill(mb, device, pk, flush, tokens: int = PREFILL_TOKENS, reps: int =
             state["y"] = mods[i](x)
     with torch.no_grad():
         t = time_steps(fn, reps, 1, flush)
-        launches = (mb.ops.kernel_counts().get("prefill_panel", 0) - n0) // (reps + 1)
+        mb.format.BLOCK_PATH_MIN_FILL = saved_fill
+        counts = mb.ops.kernel_counts()
+        launched = {k: (counts.get(k, 0) - counts0.get(k, 0)) // (reps + 1) for k in ("prefill_panel", "prefill_blocks")}
+        kernel = "prefill_blocks_kernel (tcgen05, dense 128x128 blocks)" if launched["prefill_blocks"] else \
+            "prefill_panel_kernel (tcgen05, per tile)"
+        launches = launched["prefill_blocks"] or launched["prefill_panel"]
         hx, hy = x0.clone().pin_memory(), torch.empty_like(x0).pin_memory()
         te = time_steps(fn, max(reps - 1, 1), 0, flush, pre=lambda: x.copy_(hx, non_blocking=True),
                         post=lambda: hy.copy_(state["y"], non_blocking=True))
@@ -566,7 +582,7 @@ def run_prefill(mb, device, pk, flush, tokens: int = PREFILL_TOKENS, reps: int =
             "e2e": {"value": round(tokens / (ms_e2e * 1e-3), 1), "unit": "tokens/s",
                     "h2d_bytes_per_step": hx.numel() * 2, "d2h_bytes_per_step": hy.numel() * 2},
             "applications": len(order), "tokens": tokens, "through": "SwiGLUMortar.forward",
-            "kernel": "prefill_panel_kernel (tcgen05)", "prefill_panel_launches_per_pass": launches,
+            "kernel": kernel, "launches_per_pass": launches,
             "useful_tflops": round(tf, 2), "dense_equivalent_tflops": round(tf / DENSITY, 2),
             "checksum": float(hy.double().abs().sum()), "device_error_word": err}
 

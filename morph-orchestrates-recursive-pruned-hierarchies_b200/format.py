@@ -430,6 +430,20 @@ class SchedMatrix:
 
 BLOCK = 128
 
+# Token blocks run the block path of the prefill kernels (every touched 128 x 128 block executed
+# densely, dropped tiles as zeros) when the touched blocks are at least this full.  Measured on the
+# cloud shape: a single 16 x 16 tile is one narrow MMA at the tensor pipe's ~45-cycle floor, so the
+# per-tile path only wins below about 15% fill; 25% random tiles already run faster as dense blocks.
+BLOCK_PATH_MIN_FILL = 0.2
+
+
+def wants_block_path(m: "MortarMatrix", swiglu: bool) -> bool:
+    """Whether token blocks of `m` should take the block path (see BLOCK_PATH_MIN_FILL); a gate/up
+    matrix additionally needs d_ff to be a multiple of 128 so gate and up block rows pair up."""
+    if swiglu and (m.out_features // 2) % BLOCK:
+        return False
+    return block_fill(m) >= BLOCK_PATH_MIN_FILL
+
 
 def block_fill(m: "MortarMatrix") -> float:
     """Kept tiles / (64 x the number of 128 x 128 blocks that hold a kept tile): 1.0 for a topology

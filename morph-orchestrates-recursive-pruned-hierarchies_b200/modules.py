@@ -23,13 +23,12 @@ import torch
 import torch.nn as nn
 
 from . import ops
-from .format import TILE, BlockSched, MortarMatrix, SchedMatrix, StreamMatrix, block_fill
+from .format import TILE, BlockSched, MortarMatrix, SchedMatrix, StreamMatrix, wants_block_path
 
 # bf16 token blocks with at least this many rows take the tensor-memory kernel.  Measured on
 # B200 at the 768/2048 and 2048/5632 shapes: the streaming kernel wins below 128 rows, the
 # tcgen05 kernel (whose work item is a block of 128 rows) from 128 rows on.
 TC_MIN_ROWS = 128
-BLOCK_PATH_MIN_FILL = 0.5     # touched 128 x 128 blocks at least this full take the block path of the prefill kernels
 
 
 class CarvedStorage(nn.Module):
@@ -195,8 +194,7 @@ class CarvedStorage(nn.Module):
         key = ("blocks", swiglu)
         if key not in self._sched:
             m = self.matrix()
-            ok = block_fill(m) >= BLOCK_PATH_MIN_FILL and not (swiglu and (m.out_features // 2) % 128)
-            self._sched[key] = m.to_blocks(swiglu, self._device) if ok else None
+            self._sched[key] = m.to_blocks(swiglu, self._device) if wants_block_path(m, swiglu) else None
         return self._sched[key]
 
     # ---- reference API ------------------------------------------------------------------

@@ -37,7 +37,8 @@ import numpy as np
 import torch
 
 from . import ops
-from .format import MortarMatrix, SchedMatrix, StreamMatrix, TopologyDev, matrix_from_stream, pack_codes_2bit
+from .format import (MortarMatrix, SchedMatrix, StreamMatrix, TopologyDev, matrix_from_stream, pack_codes_2bit,
+                     wants_block_path)
 
 _LIB = "mortar_b200"
 TC_MIN_ROWS = 128        # bf16 token blocks of at least this many rows run the tcgen05 kernel
@@ -262,6 +263,7 @@ class _DdsEntry:
     def __init__(self, matrix: MortarMatrix, fingerprint: int, device):
         self.matrix, self.fingerprint, self.device = matrix, fingerprint, device
         self._stream = self._sched = self._stream_t = self._sched_t = None
+        self._blocks = {}
 
     def stream(self, transposed: bool = False):
         if transposed:
@@ -280,6 +282,14 @@ class _DdsEntry:
         if self._sched is None:
             self._sched = self.matrix.to_sched(False, self.device)
         return self._sched
+
+
+    def blocks(self, transposed: bool = False):
+        """Layout of the block path, or None when the topology is too sparse for it."""
+        if transposed not in self._blocks:
+            m = self.matrix.transpose() if transposed else self.matrix
+            self._blocks[transposed] = m.to_blocks(False, self.device) if wants_block_path(m, False) else None
+        return self._blocks[transposed]
 
 
 def stk_dds(lhs: torch.Tensor, data: torch.Tensor, offsets: torch.Tensor, row_indices: torch.Tensor,
@@ -316,6 +326,9 @@ def stk_dds(lhs: torch.Tensor, data: torch.Tensor, offsets: torch.Tensor, row_in
         _DDS_CACHE.move_to_end(key)
     k_features = in_f if transpose_b else out_f
     if _takes_tc(lhs, k_features):
+        blk = ent.blocks(not transpose_b)
+        if blk is not None:
+            return ops.linear_blocks(lhs, blk)
         return ops.linear_tc(lhs, ent.sched(not transpose_b))
     return ops.linear(lhs, ent.stream(not transpose_b))
 

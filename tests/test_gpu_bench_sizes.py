@@ -27,7 +27,7 @@ def _delta(before, name):
 
 
 @pytest.mark.parametrize("seed", [0, 1, 2])
-def test_single_layer_configuration_full_size(seed):
+def test_single_layer_configuration_full_size(seed, monkeypatch):
     """4 x 4096 tokens, d_model 768, d_ff 2048, top-25% tiles by L2, bf16 RMS-normed input:
     the tensor-memory operator and the module forward against the oracle's bf16 path on every
     one of the 16384 x 768 outputs."""
@@ -38,11 +38,20 @@ def test_single_layer_configuration_full_size(seed):
     _clean()
     assert y.shape == (4, 4096, 768)
     _assert_bf16_close(y, ref, near_zero=1e-2)         # 12.6 million outputs
+    # the module forward: 25% random tiles fill the touched 128 x 128 blocks above the dispatch
+    # threshold, so it takes the block path; pinned to the per-tile path it returns y's bits
     mlp = mb.SwiGLUMortar.from_matrices(L.gate_up, L.down, device=DEV)
     before = mb.ops.kernel_counts()
     y2 = mlp(x.to(DEV))
-    assert _delta(before, "prefill_panel") == 2 and _delta(before, "bcsr_stream") == 0
-    assert torch.equal(y2, y)
+    assert _delta(before, "prefill_blocks") == 2 and _delta(before, "bcsr_stream") == 0
+    _clean()
+    _assert_bf16_close(y2, ref, near_zero=1e-2)
+    monkeypatch.setattr(mb.format, "BLOCK_PATH_MIN_FILL", 2.0)
+    mlp = mb.SwiGLUMortar.from_matrices(L.gate_up, L.down, device=DEV)
+    before = mb.ops.kernel_counts()
+    y3 = mlp(x.to(DEV))
+    assert _delta(before, "prefill_panel") == 2 and _delta(before, "prefill_blocks") == 0
+    assert torch.equal(y3, y)
 
 
 def test_cloud_application_16384_tokens():
@@ -165,10 +174,12 @@ def test_stack_decode_takes_norm_weights_as_an_argument(full_stack):
     assert float((x.cpu() - ref).abs().max()) / float(ref.abs().max()) <= 1e-5
 
 
-def test_module_forward_and_operators_pick_the_kernel_by_row_count():
+def test_module_forward_and_operators_pick_the_kernel_by_row_count(monkeypatch):
     """bf16 token blocks of 128 rows or more run the tcgen05 kernel through every public door
     (module forward, MortarLinear, mortar_b200::mlp_prefill / linear, morph_stk::dds); smaller
-    blocks and fp32 rows run the streaming kernel; results agree with the explicit operators."""
+    blocks and fp32 rows run the streaming kernel; results agree with the explicit operators.
+    (The per-tile path is pinned here; the choice between it and the block path has its own test.)"""
+    monkeypatch.setattr(mb.format, "BLOCK_PATH_MIN_FILL", 2.0)
     L = mb.synth.make_layer(768, 2048, 0.25, seed=100)
     mlp = mb.SwiGLUMortar.from_matrices(L.gate_up, L.down, device=DEV)
     gs, ds = L.gate_up.to_sched(True, DEV), L.down.to_sched(False, DEV)

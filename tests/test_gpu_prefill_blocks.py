@@ -95,9 +95,26 @@ def test_blocks_golden_fixture_and_module_dispatch():
     assert mb.ops.kernel_counts()["prefill_blocks"] - n0 == 2
     ref = orc.swiglu_mlp(x.cpu().float(), _dense(gu_m), _dense(dn_m), dtype=torch.bfloat16)
     _assert_bf16_close(y, ref, near_zero=1e-2)
-    # a tile-16 topology keeps the tile path
-    L = mb.synth.make_layer(256, 512, 0.25, seed=3)
+    # a sparse tile-16 topology keeps the per-tile path
+    L = mb.synth.make_layer(256, 512, 0.1, seed=3)
+    assert mb.format.block_fill(L.gate_up) < mb.format.BLOCK_PATH_MIN_FILL
     mlp2 = mb.SwiGLUMortar.from_matrices(L.gate_up, L.down, device=DEV)
     n1 = mb.ops.kernel_counts().get("prefill_panel", 0)
     mlp2(x)
     assert mb.ops.kernel_counts()["prefill_panel"] - n1 == 2
+    # the reference operator on a 128-carved layer takes the block path too
+    z = torch.zeros(1, dtype=torch.int16, device=DEV)
+    Rb, Cb = 256 // 128, 512 // 128
+    rows = np.repeat(np.arange(dn_m.tile_rows), np.diff(dn_m.row_ptr))
+    kept = np.zeros((Rb, Cb), dtype=bool)
+    kept[rows // 8, dn_m.col_idx.astype(int) // 8] = True
+    idx = np.argwhere(kept)
+    dense = torch.from_numpy(dn_m.to_dense_codes()).float() * torch.tensor(dn_m.scale).to(torch.bfloat16).float()
+    data = torch.stack([dense[r * 128:(r + 1) * 128, c * 128:(c + 1) * 128] for r, c in idx]).to(torch.bfloat16).to(DEV)
+    off = torch.from_numpy(np.concatenate([[0], np.cumsum(kept.sum(1))]).astype(np.int32)).to(DEV)
+    ci = torch.from_numpy(idx[:, 1].astype(np.int16)).to(DEV)
+    hx = mb.synth.make_activations(256, 512, seed=5).to(DEV)
+    n2 = mb.ops.kernel_counts().get("prefill_blocks", 0)
+    yd = torch.ops.morph_stk.dds(hx, data, off, z, ci, z, z, z, 512, 256, True)
+    assert mb.ops.kernel_counts()["prefill_blocks"] - n2 == 1
+    assert torch.equal(yd, mb.ops.linear_blocks(hx, dn_m.to_blocks(False, DEV)))
