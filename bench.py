@@ -753,7 +753,9 @@ def run_remoe(mb, device, pk, flush, reps: int = 10):
     h = torch.empty(tokens, d, device=device, dtype=torch.bfloat16)
     wsp = torch.empty(max(tokens * f * 2, mb._lib.lib().mortar_mlp_workspace_bytes(tokens, d, f, 1)) + 256,
                       device=device, dtype=torch.uint8)
-    for name, fn in (("prefill_tc_gate_multiply", lambda: mb.ops.mlp_prefill_tc(xb, gs, ds, gates=gates, n_clusters=ncls, out=h, workspace=wsp)),
+    bgs, bds = L.gate_up.to_blocks(True, device), L.down.to_blocks(False, device)
+    for name, fn in (("prefill_blocks_gate_multiply", lambda: mb.ops.mlp_prefill_blocks(xb, bgs, bds, gates=gates, n_clusters=ncls, out=h, workspace=wsp)),
+                     ("prefill_tc_gate_multiply", lambda: mb.ops.mlp_prefill_tc(xb, gs, ds, gates=gates, n_clusters=ncls, out=h, workspace=wsp)),
                      ("prefill_tc_unrouted", lambda: mb.ops.mlp_prefill_tc(xb, gs, ds, out=h, workspace=wsp)),
                      ("prefill_stream_gathered", lambda: mb.ops.mlp_decode(xb, gu, dn, gates=gates, n_clusters=ncls, n_planes=1,
                                                                         round_bf16=True, out=h, workspace=wsp))):
