@@ -897,6 +897,16 @@ def run_probe(name: str):
         for _ in range(3):
             mb.ops.linear_tc(x, gu, out=h)
             mb.ops.linear_tc(h, dn, out=y)
+    elif name == "prefill_blocks":   # prefill_blocks_kernel, one cloud-shape MLP carved in 128x128 blocks, 4096 tokens
+        gu_m = mb.synth.make_block_matrix(2 * CLOUD["d_ff"], CLOUD["d_model"], DENSITY, seed=11)
+        dn_m = mb.synth.make_block_matrix(CLOUD["d_model"], CLOUD["d_ff"], DENSITY, seed=12)
+        gu, dn = gu_m.to_blocks(True, device), dn_m.to_blocks(False, device)
+        x = mb.synth.make_activations(4096, CLOUD["d_model"], seed=2).to(device)
+        h = torch.empty(4096, CLOUD["d_ff"], device=device, dtype=torch.bfloat16)
+        y = torch.empty(4096, CLOUD["d_model"], device=device, dtype=torch.bfloat16)
+        for _ in range(3):
+            mb.ops.linear_blocks(x, gu, out=h)
+            mb.ops.linear_blocks(h, dn, out=y)
     else:
         raise SystemExit(f"unknown probe {name}")
     torch.cuda.synchronize()
@@ -910,7 +920,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--quick", action="store_true", help="headline measurement only")
-    ap.add_argument("--probe", default=None, choices=["stack", "decode", "gemv", "prefill"],
+    ap.add_argument("--probe", default=None, choices=["stack", "decode", "gemv", "prefill", "prefill_blocks"],
                     help="run a few untimed launches of one kernel (small case) for a profiler capture")
     args = ap.parse_args()
     if args.probe:
