@@ -495,6 +495,21 @@ class BlockSched:
         self.steps = torch.tensor(steps if steps else [(0, -1, -1, 0)], dtype=torch.int32, device=device).reshape(-1, 4)
         self._c = None
 
+    @classmethod
+    def from_tensors(cls, data, pair_ptr, steps, out_features, in_features, swiglu, scale) -> "BlockSched":
+        """A block layout whose arrays already live on the device (the registered ops pass them as
+        tensors); borrows the tensors."""
+        self = cls.__new__(cls)
+        self.out_features, self.in_features = int(out_features), int(in_features)
+        self.swiglu, self.scale, self.nnz = bool(swiglu), float(scale), 0
+        self.data, self.pair_ptr, self.steps = data, pair_ptr, steps
+        self.n_blocks = int(data.shape[0]) if data.dim() == 3 else int(data.numel() // (BLOCK * BLOCK))
+        self.n_pairs = int(pair_ptr.numel()) - 1
+        # the step list of a matrix without blocks is one placeholder row that no pair points at
+        self.n_steps = int(steps.shape[0]) if self.n_blocks > 0 else 0
+        self._c = None
+        return self
+
     @property
     def n_out(self) -> int:
         return self.out_features // 2 if self.swiglu else self.out_features

@@ -37,7 +37,7 @@ import numpy as np
 import torch
 
 from . import ops
-from .format import (MortarMatrix, SchedMatrix, StreamMatrix, TopologyDev, matrix_from_stream, pack_codes_2bit,
+from .format import (BlockSched, MortarMatrix, SchedMatrix, StreamMatrix, TopologyDev, matrix_from_stream, pack_codes_2bit,
                      wants_block_path)
 
 _LIB = "mortar_b200"
@@ -187,6 +187,44 @@ def mlp_prefill_tc_args(gu: SchedMatrix, dn: SchedMatrix):
     """Arguments between ``x`` and ``gates`` of ``mortar_b200::mlp_prefill_tc`` for two schedules."""
     a, b = sched_args(gu), sched_args(dn)
     return (*a[:12], a[13], *b[:12], b[13])
+
+
+def blocks_args(w: BlockSched):
+    """The tensors and scalars that describe a block layout in the registered ops' argument order."""
+    return (w.data, w.pair_ptr, w.steps, w.out_features, w.in_features, w.swiglu, w.scale)
+
+
+@torch.library.custom_op(f"{_LIB}::linear_blocks", mutates_args=(), device_types="cuda")
+def linear_blocks(x: torch.Tensor, data: torch.Tensor, pair_ptr: torch.Tensor, steps: torch.Tensor,
+                  out_features: int, in_features: int, swiglu: bool, scale: float,
+                  gates: Optional[torch.Tensor], cluster_size: int) -> torch.Tensor:
+    """``ops.linear_blocks`` on raw tensors (``MortarMatrix.to_blocks`` builds them)."""
+    w = BlockSched.from_tensors(data, pair_ptr, steps, out_features, in_features, swiglu, scale)
+    return ops.linear_blocks(x, w, gates=gates, cluster_size=cluster_size)
+
+
+@linear_blocks.register_fake
+def _(x, data, pair_ptr, steps, out_features, in_features, swiglu, scale, gates, cluster_size):
+    return x.new_empty((*x.shape[:-1], out_features // 2 if swiglu else out_features), dtype=torch.bfloat16)
+
+
+@torch.library.custom_op(f"{_LIB}::mlp_prefill_blocks", mutates_args=(), device_types="cuda")
+def mlp_prefill_blocks(x: torch.Tensor,
+                       gu_data: torch.Tensor, gu_pairs: torch.Tensor, gu_steps: torch.Tensor, gu_out: int,
+                       gu_in: int, gu_scale: float,
+                       dn_data: torch.Tensor, dn_pairs: torch.Tensor, dn_steps: torch.Tensor, dn_out: int,
+                       dn_in: int, dn_scale: float,
+                       gates: Optional[torch.Tensor], n_clusters: int) -> torch.Tensor:
+    """``_SwiGLUMortar.forward`` on a token block through the block path of the tcgen05 kernels."""
+    gu = BlockSched.from_tensors(gu_data, gu_pairs, gu_steps, gu_out, gu_in, True, gu_scale)
+    dn = BlockSched.from_tensors(dn_data, dn_pairs, dn_steps, dn_out, dn_in, False, dn_scale)
+    return ops.mlp_prefill_blocks(x, gu, dn, gates=gates, n_clusters=n_clusters)
+
+
+@mlp_prefill_blocks.register_fake
+def _(x, gu_data, gu_pairs, gu_steps, gu_out, gu_in, gu_scale, dn_data, dn_pairs, dn_steps, dn_out, dn_in,
+      dn_scale, gates, n_clusters):
+    return x.new_empty((*x.shape[:-1], dn_out), dtype=torch.bfloat16)
 
 
 @torch.library.custom_op(f"{_LIB}::stack_decode", mutates_args=("x", "status"), device_types="cuda")

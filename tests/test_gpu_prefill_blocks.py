@@ -95,6 +95,18 @@ def test_blocks_golden_fixture_and_module_dispatch():
     assert mb.ops.kernel_counts()["prefill_blocks"] - n0 == 2
     ref = orc.swiglu_mlp(x.cpu().float(), _dense(gu_m), _dense(dn_m), dtype=torch.bfloat16)
     _assert_bf16_close(y, ref, near_zero=1e-2)
+    # the registered operators on raw tensors, eager and through a fake-tensor trace
+    bg, bd = gu_m.to_blocks(True, DEV), dn_m.to_blocks(False, DEV)
+    a, b = mb.torch_ops.blocks_args(bg), mb.torch_ops.blocks_args(bd)
+    y_op = torch.ops.mortar_b200.mlp_prefill_blocks(x, *a[:5], a[6], *b[:5], b[6], None, 0)
+    assert torch.equal(y_op, y)
+    h_op = torch.ops.mortar_b200.linear_blocks(x, *a, None, 0)
+    assert torch.equal(h_op, mb.ops.linear_blocks(x, bg))
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    with FakeTensorMode(allow_non_fake_inputs=True):
+        fy = torch.ops.mortar_b200.mlp_prefill_blocks(torch.empty(300, 256, dtype=torch.bfloat16, device=DEV),
+                                                      *a[:5], a[6], *b[:5], b[6], None, 0)
+    assert tuple(fy.shape) == (300, 256) and fy.dtype == torch.bfloat16
     # a sparse tile-16 topology keeps the per-tile path
     L = mb.synth.make_layer(256, 512, 0.1, seed=3)
     assert mb.format.block_fill(L.gate_up) < mb.format.BLOCK_PATH_MIN_FILL
