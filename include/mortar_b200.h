@@ -298,6 +298,44 @@ int mortar_mlp_decode_static(const mortar_stream *gate_up, const mortar_stream *
                              void *y, int y_dtype, int64_t ldy,
                              int32_t n_planes, int32_t flags, void *stream);
 
+/* ---- decode GEMV for matrices carved in 128 x 128 blocks, on the tensor-memory path ------------
+ * The role of mortar_gemv (fused_decode_step.py:1502-1547) for small batches when every kept tile
+ * belongs to a kept 128 x 128 block: a block's codes are expanded by the kernel straight into
+ * tensor memory as the A operand of tcgen05.mma (M = 128 output rows), the activations are the B
+ * operand (up to 16 columns = rows x exact bf16 planes).  fp32 semantics as mortar_linear with
+ * planes: exact products, fp32 accumulation, scale after the sum, optional SwiGLU of a gate block
+ * row with the up block row of the same hidden features.
+ *   row_words  device uint32 [n_blocks][128 rows][8 tile columns]: the 16 codes of a tile row, even
+ *              columns in bits 0..15 and odd columns in bits 16..31 (2 bits each, stored value = code + 1)
+ *   blk_ptr    device int32 [out_features/128 + 1], blk_col device int32 [n_blocks] (ascending per row)
+ *   items      device int32 [n_items]: the block rows to compute (SwiGLU: the gate block rows),
+ *              ordered by decreasing number of blocks (items are dealt to CTAs round-robin) */
+typedef struct mortar_gemv_pack {
+    const void *row_words;
+    const int32_t *blk_ptr;
+    const int32_t *blk_col;
+    const int32_t *items;
+    int64_t n_blocks;
+    int32_t n_items;
+    int32_t out_features;
+    int32_t in_features;
+    int32_t swiglu;
+    float scale;
+} mortar_gemv_pack;
+
+/* Activation operand of mortar_gemv_blocks from bf16 planes [n_planes][rows][ld_planes]
+ * (rows * n_planes <= 16): xb = in_features/16 tiles of 512 bytes, 128-byte aligned. */
+int mortar_gemv_xprep(const void *planes, int32_t n_planes, int64_t plane_stride, int64_t ld_planes,
+                      int64_t rows, int32_t in_features, void *xb, void *stream);
+
+/* out: MORTAR_OUT_F32 float [rows][ld_out], MORTAR_OUT_BF16, or MORTAR_OUT_PLANES bf16
+ * [n_out_planes][rows][ld_out] (exact residual split, the input of the next product's xprep).
+ * Bounded in-kernel waits report through mortar_gemv_blocks_error. */
+int mortar_gemv_blocks(const mortar_gemv_pack *w, const void *xb, int64_t rows, int32_t n_planes,
+                       void *out, int32_t out_mode, int32_t n_out_planes, int64_t out_plane_stride,
+                       int64_t ld_out, void *stream);
+int mortar_gemv_blocks_error(int32_t *code, int32_t reset);
+
 /* ---- persistent decode of a stack of MLP applications ---------------------------------
  * One launch runs x <- x + MLP_i(rmsnorm_i(x)) for a whole list of MLP applications (the MLP
  * sites of one decode step in StaticDecodeEngine's site order,

@@ -49,6 +49,13 @@ class Sched(C.Structure):
                 ("arith", C.c_int32)]
 
 
+class GemvPack(C.Structure):
+    """mirror of `mortar_gemv_pack`"""
+    _fields_ = [("row_words", C.c_void_p), ("blk_ptr", C.c_void_p), ("blk_col", C.c_void_p), ("items", C.c_void_p),
+                ("n_blocks", C.c_int64), ("n_items", C.c_int32), ("out_features", C.c_int32),
+                ("in_features", C.c_int32), ("swiglu", C.c_int32), ("scale", C.c_float)]
+
+
 class Blocks(C.Structure):
     """mirror of `mortar_blocks`"""
     _fields_ = [("data", C.c_void_p), ("pair_ptr", C.c_void_p), ("steps", C.c_void_p), ("n_blocks", C.c_int64),
@@ -94,6 +101,9 @@ _SIGNATURES = {
     "mortar_sched_sizes": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp]),
     "mortar_build_sched": (C.c_int, [_vp, _vp, _vp, _i32, _i32, _i64, _i32, _vp, _vp, _vp, _vp, _vp]),
     "mortar_linear_tc": (C.c_int, [C.POINTER(Sched), _vp, _i64, _i64, _vp, _i64, _vp, _i64, _i32, _vp]),
+    "mortar_gemv_xprep": (C.c_int, [_vp, _i32, _i64, _i64, _i64, _i32, _vp, _vp]),
+    "mortar_gemv_blocks": (C.c_int, [C.POINTER(GemvPack), _vp, _i64, _i32, _vp, _i32, _i32, _i64, _i64, _vp]),
+    "mortar_gemv_blocks_error": (C.c_int, [_vp, _i32]),
     "mortar_linear_blocks": (C.c_int, [C.POINTER(Blocks), _vp, _i64, _i64, _vp, _i64, _vp, _i64, _i32, _vp]),
     "mortar_mlp_prefill_blocks": (C.c_int, [C.POINTER(Blocks), C.POINTER(Blocks), _vp, _i64, _i64, _vp, _i64, _i32,
                                             _vp, _i64, _vp, _i64, _vp]),

@@ -13,7 +13,7 @@ ROOT = os.path.dirname(PKG)
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libmortar_b200.so")
 SOURCES = ["host_pack.cpp", "prefill_sched.cpp", "stream_kernels.cu", "prefill_tc.cu", "stack_decode.cu",
-           "router.cu", "backward.cu", "backward_tc.cu"]
+           "router.cu", "backward.cu", "backward_tc.cu", "gemv_tc.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

@@ -304,6 +304,10 @@ class MortarMatrix:
         ``arith="i8"`` builds the layout of the opt-in 8-bit arm."""
         return SchedMatrix(self, swiglu, device, arith)
 
+    def to_gemv_blocks(self, swiglu: bool, device="cuda") -> "GemvBlocks":
+        """Layout of the tensor-memory decode GEMV (matrices carved in 128 x 128 blocks)."""
+        return GemvBlocks(self, swiglu, device)
+
     def to_blocks(self, swiglu: bool, device="cuda") -> "BlockSched":
         """Prefill execution layout of the block path (topologies carved at 128 x 128)."""
         return BlockSched(self, swiglu, device)
@@ -519,6 +523,56 @@ class BlockSched:
             self._c = _lib.Blocks(self.data.data_ptr(), self.pair_ptr.data_ptr(), self.steps.data_ptr(),
                                   self.n_blocks, self.n_pairs, self.n_steps, self.out_features, self.in_features,
                                   int(self.swiglu), self.scale)
+        return self._c
+
+
+class GemvBlocks:
+    """Device-resident layout of a matrix carved in 128 x 128 blocks for the tensor-memory decode
+    GEMV (see ``mortar_gemv_pack`` in the header): per kept block 128 rows of 8 permuted row words."""
+
+    def __init__(self, m: "MortarMatrix", swiglu: bool, device="cuda"):
+        if m.out_features % BLOCK or m.in_features % BLOCK or (swiglu and (m.out_features // 2) % BLOCK):
+            raise ValueError("the block GEMV needs feature counts that are multiples of 128")
+        self.out_features, self.in_features = m.out_features, m.in_features
+        self.swiglu, self.scale, self.nnz = bool(swiglu), float(m.scale), m.nnz
+        Rb, Cb = m.out_features // BLOCK, m.in_features // BLOCK
+        rows = np.repeat(np.arange(m.tile_rows), np.diff(m.row_ptr)).astype(np.int64)
+        cols = m.col_idx.astype(np.int64)
+        key = np.unique((rows // 8) * Cb + cols // 8)
+        brow, bcol = key // Cb, key % Cb
+        nb = int(key.size)
+        # canonical row words (code e of a tile row at bits 2e) -> even columns low half, odd columns high half
+        canon = np.ascontiguousarray(m.codes).view(np.uint32).reshape(m.nnz, 16)
+        perm = np.zeros_like(canon)
+        for q in range(8):
+            perm |= ((canon >> np.uint32(4 * q)) & np.uint32(3)) << np.uint32(2 * q)
+            perm |= ((canon >> np.uint32(4 * q + 2)) & np.uint32(3)) << np.uint32(16 + 2 * q)
+        words = np.full((nb, 8, 16, 8), 0x55555555, dtype=np.uint32)          # [block][tile row][row][tile col]
+        blk_of = np.searchsorted(key, (rows // 8) * Cb + cols // 8)
+        words[blk_of, rows % 8, :, cols % 8] = perm
+        blk_ptr = np.concatenate([[0], np.cumsum(np.bincount(brow, minlength=Rb))]).astype(np.int32)
+        per_row = np.diff(blk_ptr)
+        if swiglu:
+            half = Rb // 2
+            size = per_row[:half] + per_row[half:]
+            items = np.argsort(-size, kind="stable").astype(np.int32)
+        else:
+            items = np.argsort(-per_row, kind="stable").astype(np.int32)
+        t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device)
+        self.n_blocks, self.n_items = nb, int(items.size)
+        self.row_words = t(words.reshape(nb, 128, 8).view(np.int32))
+        self.blk_ptr, self.blk_col, self.items = t(blk_ptr), t(bcol.astype(np.int32)), t(items)
+        self._c = None
+
+    @property
+    def n_out(self) -> int:
+        return self.out_features // 2 if self.swiglu else self.out_features
+
+    def c_struct(self) -> _lib.GemvPack:
+        if self._c is None:
+            self._c = _lib.GemvPack(self.row_words.data_ptr(), self.blk_ptr.data_ptr(), self.blk_col.data_ptr(),
+                                    self.items.data_ptr(), self.n_blocks, self.n_items, self.out_features,
+                                    self.in_features, int(self.swiglu), self.scale)
         return self._c
 
 

@@ -11,7 +11,7 @@ from typing import Optional
 import torch
 
 from . import _lib
-from .format import TILE, BlockSched, MortarMatrix, SchedMatrix, StreamMatrix, TopologyDev
+from .format import TILE, BlockSched, GemvBlocks, MortarMatrix, SchedMatrix, StreamMatrix, TopologyDev
 
 _launches = 0      # kernels launched by this module (bench.py reports it)
 _kernel_counts: dict = {}   # the same, per kernel family
@@ -133,6 +133,53 @@ def linear_planes(w: StreamMatrix, planes: torch.Tensor, *, swiglu: bool = False
         "mortar_linear")
     _count("bcsr_stream")
     return out
+
+
+def gemv_xprep(planes: torch.Tensor) -> torch.Tensor:
+    """Activation planes [P, rows, in] (bf16, rows * P <= 16) -> the activation operand of
+    ``gemv_blocks``: in/16 tiles of 512 bytes."""
+    _require_cuda(planes, "planes")
+    if planes.dim() != 3 or planes.dtype != torch.bfloat16 or not planes.is_contiguous():
+        raise ValueError("planes must be a contiguous bfloat16 tensor [P, rows, in_features]")
+    P, rows, cols = planes.shape
+    xb = torch.empty(cols // 16 * 512, device=planes.device, dtype=torch.uint8)
+    _lib.check(_lib.lib().mortar_gemv_xprep(_ptr(planes), P, rows * cols, cols, rows, cols, _ptr(xb), _stream_ptr()),
+               "mortar_gemv_xprep")
+    _count("gemv_xprep")
+    return xb
+
+
+def gemv_blocks(w: GemvBlocks, xb: torch.Tensor, rows: int, n_planes: int, *,
+                out_dtype: torch.dtype = torch.float32, out_planes: int = 0) -> torch.Tensor:
+    """Decode GEMV on the tensor-memory path for a matrix carved in 128 x 128 blocks
+    (``MortarMatrix.to_gemv_blocks``) against an activation operand from ``gemv_xprep``:
+    [rows, out] (or [rows, out/2] = silu(gate)*up for a swiglu layout) as float32 / bfloat16, or
+    with ``out_planes`` > 0 as exact bf16 planes [out_planes, rows, n]."""
+    _require_cuda(xb, "xb")
+    n_out = w.n_out
+    dev = xb.device
+    if xb.numel() != w.in_features // 16 * 512:
+        raise ValueError("activation operand does not match the matrix")
+    if out_planes:
+        out, mode = torch.empty(out_planes, rows, n_out, device=dev, dtype=torch.bfloat16), _lib.OUT_PLANES
+    elif out_dtype == torch.float32:
+        out, mode = torch.empty(rows, n_out, device=dev, dtype=torch.float32), _lib.OUT_F32
+    elif out_dtype == torch.bfloat16:
+        out, mode = torch.empty(rows, n_out, device=dev, dtype=torch.bfloat16), _lib.OUT_BF16
+    else:
+        raise ValueError(f"unsupported out_dtype {out_dtype}")
+    st = w.c_struct()
+    _lib.check(_lib.lib().mortar_gemv_blocks(C.byref(st), _ptr(xb), rows, n_planes, _ptr(out), mode, out_planes,
+                                             rows * n_out, n_out, _stream_ptr()), "mortar_gemv_blocks")
+    _count("gemv_tc")
+    return out
+
+
+def gemv_blocks_error(reset: bool = True) -> int:
+    """Error word of the tensor-memory decode GEMV (0 = none; synchronises the device)."""
+    code = C.c_int32(0)
+    _lib.check(_lib.lib().mortar_gemv_blocks_error(C.byref(code), int(reset)), "mortar_gemv_blocks_error")
+    return code.value
 
 
 def linear(x: torch.Tensor, w: StreamMatrix, *, n_planes: Optional[int] = None,
