@@ -328,6 +328,12 @@ typedef struct mortar_gemv_pack {
 int mortar_gemv_xprep(const void *planes, int32_t n_planes, int64_t plane_stride, int64_t ld_planes,
                       int64_t rows, int32_t in_features, void *xb, void *stream);
 
+/* The activation operand of the down product from the fp32 result of an unfused gate/up product
+ * [rows][ld] (gate columns, then up columns): silu(gate) * up split into n_planes exact bf16 planes.
+ * For gate/up matrices whose d_ff is not a multiple of 128 (gate and up block rows do not pair up). */
+int mortar_gemv_xprep_swiglu(const float *gate_up, int64_t ld, int64_t rows, int32_t d_ff, int32_t n_planes,
+                             void *xb, void *stream);
+
 /* out: MORTAR_OUT_F32 float [rows][ld_out], MORTAR_OUT_BF16, or MORTAR_OUT_PLANES bf16
  * [n_out_planes][rows][ld_out] (exact residual split, the input of the next product's xprep).
  * Bounded in-kernel waits report through mortar_gemv_blocks_error. */

@@ -102,6 +102,7 @@ _SIGNATURES = {
     "mortar_build_sched": (C.c_int, [_vp, _vp, _vp, _i32, _i32, _i64, _i32, _vp, _vp, _vp, _vp, _vp]),
     "mortar_linear_tc": (C.c_int, [C.POINTER(Sched), _vp, _i64, _i64, _vp, _i64, _vp, _i64, _i32, _vp]),
     "mortar_gemv_xprep": (C.c_int, [_vp, _i32, _i64, _i64, _i64, _i32, _vp, _vp]),
+    "mortar_gemv_xprep_swiglu": (C.c_int, [_vp, _i64, _i64, _i32, _i32, _vp, _vp]),
     "mortar_gemv_blocks": (C.c_int, [C.POINTER(GemvPack), _vp, _i64, _i32, _vp, _i32, _i32, _i64, _i64, _vp]),
     "mortar_gemv_blocks_error": (C.c_int, [_vp, _i32]),
     "mortar_linear_blocks": (C.c_int, [C.POINTER(Blocks), _vp, _i64, _i64, _vp, _i64, _vp, _i64, _i32, _vp]),

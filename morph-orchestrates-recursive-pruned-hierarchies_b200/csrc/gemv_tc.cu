@@ -322,6 +322,34 @@ __global__ void gemv_xprep_kernel(const __nv_bfloat16 *planes, int n_planes, lon
     *reinterpret_cast<uint4 *>(xb + (size_t)tile * 512 + (chunk >> 4) * 256 + kh * 128 + (chunk & 7) * 16) = v;
 }
 
+// The same operand from the fp32 result of a gate/up product [rows][2 d_ff] (gate columns, then up
+// columns): h = silu(gate) * up, split into n_planes exact bf16 planes on the way -- the SwiGLU of a
+// gate/up matrix whose d_ff is not a multiple of 128, where gate and up block rows do not pair up.
+__global__ void gemv_xprep_swiglu_kernel(const float *gu, long long ld, int rows, int d_ff, int n_planes, uint8_t *xb) {
+    const int tile = blockIdx.x;
+    const int chunk = threadIdx.x;
+    const int n = (chunk >> 4) * 8 + (chunk & 7), kh = (chunk >> 3) & 1;
+    uint32_t packed[4] = {0u, 0u, 0u, 0u};
+    if (n < n_planes * rows) {
+        const int pl = n / rows, r = n - pl * rows;
+        const float *g = gu + r * ld + tile * 16 + kh * 8, *u = g + d_ff;
+#pragma unroll
+        for (int k = 0; k < 8; k += 2) {
+            float v[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const float gv = g[k + e];
+                v[e] = gv * (1.f / (1.f + expf(-gv))) * u[k + e];
+                for (int q = 0; q < pl; ++q) v[e] -= __bfloat162float(__float2bfloat16_rn(v[e]));   // peel the planes before this one
+            }
+            const __nv_bfloat162 h = __floats2bfloat162_rn(v[0], v[1]);
+            packed[k >> 1] = *reinterpret_cast<const uint32_t *>(&h);
+        }
+    }
+    *reinterpret_cast<uint4 *>(xb + (size_t)tile * 512 + (chunk >> 4) * 256 + kh * 128 + (chunk & 7) * 16) =
+        make_uint4(packed[0], packed[1], packed[2], packed[3]);
+}
+
 std::mutex g_gemv_tc_mutex;
 
 }  // namespace
@@ -338,6 +366,18 @@ extern "C" int mortar_gemv_xprep(const void *planes, int32_t n_planes, int64_t p
     gemv_xprep_kernel<<<(unsigned)(in_features / 16), 32, 0, (cudaStream_t)stream>>>(
         reinterpret_cast<const __nv_bfloat16 *>(planes), n_planes, plane_stride, ld_planes, (int)rows, in_features,
         reinterpret_cast<uint8_t *>(xb));
+    MORTAR_CUDA_CHECK(cudaGetLastError());
+    return MORTAR_OK;
+}
+
+extern "C" int mortar_gemv_xprep_swiglu(const float *gate_up, int64_t ld, int64_t rows, int32_t d_ff, int32_t n_planes,
+                                        void *xb, void *stream) {
+    if (!gate_up || !xb) return MORTAR_ERR_NULL;
+    if (n_planes < 1 || n_planes > 3 || rows < 1 || n_planes * rows > 16 || d_ff <= 0 || (d_ff % 16) || ld < 2 * (int64_t)d_ff)
+        return MORTAR_ERR_SHAPE;
+    if (reinterpret_cast<uintptr_t>(xb) % 128) return MORTAR_ERR_ALIGN;
+    gemv_xprep_swiglu_kernel<<<(unsigned)(d_ff / 16), 32, 0, (cudaStream_t)stream>>>(gate_up, ld, (int)rows, d_ff, n_planes,
+                                                                                   reinterpret_cast<uint8_t *>(xb));
     MORTAR_CUDA_CHECK(cudaGetLastError());
     return MORTAR_OK;
 }

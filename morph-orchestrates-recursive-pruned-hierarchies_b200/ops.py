@@ -149,6 +149,20 @@ def gemv_xprep(planes: torch.Tensor) -> torch.Tensor:
     return xb
 
 
+def gemv_xprep_swiglu(gate_up: torch.Tensor, n_planes: int = 3) -> torch.Tensor:
+    """fp32 result of an unfused gate/up product [rows, 2 d_ff] -> activation operand of the down
+    product: silu(gate) * up as ``n_planes`` exact bf16 planes in the layout of ``gemv_xprep``."""
+    _require_cuda(gate_up, "gate_up")
+    if gate_up.dim() != 2 or gate_up.dtype != torch.float32 or gate_up.stride(1) != 1:
+        raise ValueError("gate_up must be float32 [rows, 2 d_ff] with unit inner stride")
+    rows, two_f = gate_up.shape
+    xb = torch.empty(two_f // 2 // 16 * 512, device=gate_up.device, dtype=torch.uint8)
+    _lib.check(_lib.lib().mortar_gemv_xprep_swiglu(_ptr(gate_up), gate_up.stride(0), rows, two_f // 2, n_planes,
+                                                   _ptr(xb), _stream_ptr()), "mortar_gemv_xprep_swiglu")
+    _count("gemv_xprep")
+    return xb
+
+
 def gemv_blocks(w: GemvBlocks, xb: torch.Tensor, rows: int, n_planes: int, *,
                 out_dtype: torch.dtype = torch.float32, out_planes: int = 0) -> torch.Tensor:
     """Decode GEMV on the tensor-memory path for a matrix carved in 128 x 128 blocks

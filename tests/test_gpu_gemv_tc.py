@@ -42,6 +42,29 @@ def test_gemv_blocks_matches_float64(rows, planes, swiglu):
     assert float((yp.float().sum(0) - y).abs().max()) <= 1e-6 * float(y.abs().max())
 
 
+def test_gemv_blocks_unfused_swiglu_for_unaligned_d_ff():
+    """d_ff = 64 mod 128 (the published 30B shape has it): gate/up as a plain product, SwiGLU in the
+    operand preparation of the down product."""
+    d, f = 1024, 1984                                  # 1984 = 15.5 x 128
+    gu_m = mb.synth.make_block_matrix(2 * f, d, 0.3, seed=4)
+    dn_m = mb.synth.make_block_matrix(d, f + 64, 0.3, seed=5)      # in_features padded to a multiple of 128
+    x = mb.synth.make_activations(2, d, seed=6, dtype=torch.float32).to(DEV)
+    xp = mb.ops.act_prep(x, 3)
+    gu32 = mb.ops.gemv_blocks(gu_m.to_gemv_blocks(False, DEV), mb.ops.gemv_xprep(xp), 2, 3)
+    hb = mb.ops.gemv_xprep_swiglu(gu32, 3)
+    hs = mb.ops.linear_planes(gu_m.to_stream(DEV), xp, swiglu=True, out_planes=3)
+    ref_b = mb.ops.gemv_xprep(hs)
+    hb_f = hb.view(torch.bfloat16).float().reshape(-1, 2, 2, 8, 8)      # [tile][col group][k half][col][k]
+    rb_f = ref_b.view(torch.bfloat16).float().reshape(-1, 2, 2, 8, 8)
+    # sums over the three planes (columns 2p + r) agree
+    def total(t):
+        cols = t.permute(0, 1, 3, 2, 4).reshape(-1, 16, 16)              # [tile][column][k]
+        return cols[:, 0:6].reshape(-1, 3, 2, 16).sum(1)
+    assert float((total(hb_f) - total(rb_f)).abs().max()) <= 1e-5 * float(total(rb_f).abs().max())
+    with pytest.raises(ValueError):
+        gu_m.to_gemv_blocks(True, DEV)                 # gate and up block rows do not pair up
+
+
 def test_gemv_blocks_chain_large_shape():
     """gate/up with SwiGLU then down at an eighth of the published 30B shape, chained through planes."""
     d, f = 2048, 5632 - 5632 % 128 + 128 if 5632 % 128 else 5632
