@@ -39,6 +39,18 @@ constexpr uint32_t kWaitLimit = 1u << 22;
 
 __device__ int g_gemv_tc_error;
 
+#ifdef MORTAR_GEMV_TIMING
+__device__ unsigned long long g_gemv_ticks[24];
+#define GT_DECL long long tk[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long tprev = clock64()
+#define GT_ACC(i) do { const long long tn_ = clock64(); tk[i] += tn_ - tprev; tprev = tn_; } while (0)
+#define GT_PUT(base, cond) do { if ((cond) && blockIdx.x == 0) for (int i_ = 0; i_ < 8; ++i_) \
+        atomicAdd(&g_gemv_ticks[(base) + i_], (unsigned long long)tk[i_]); } while (0)
+#else
+#define GT_DECL
+#define GT_ACC(i)
+#define GT_PUT(base, cond)
+#endif
+
 struct GemvTcParams {
     const uint8_t *words;        // [n_blocks][128 rows][8] permuted row words (32 bytes per row)
     const uint8_t *xb;           // activation operand [in/16][512 B]
@@ -158,9 +170,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(const GemvTcParams
         // ---------------- producer: codes and activation slice of every block ----------------
         BlockWalk w;
         int n = 0;
+        GT_DECL;
         for (w.start(p); w.valid(p); w.next(p), ++n) {
             const int s = n % kStages;
+            GT_ACC(0);
             if (!tc::mbar_wait(tc::smem_u32(&raw_empty[s]), ((n / kStages) & 1) ^ 1u, abort_flag, &g_gemv_tc_error, 1, kWaitLimit)) break;
+            GT_ACC(1);
             if (lane == 0) {
                 const uint32_t bar = tc::smem_u32(&raw_full[s]);
                 const uint32_t dst = tc::smem_u32(stages + s * kRawBytes);
@@ -174,6 +189,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(const GemvTcParams
             }
             __syncwarp();
         }
+        GT_PUT(0, lane == 0);
     } else if (warp == 1) {
         // ---------------- MMA issue ----------------
         // kind::f16, D fp32 (bit 4), A and B bf16 (bits 7, 10), both K-major, N = 16 (>> 3 at bit 17), M = 128 (>> 4 at bit 24)
@@ -181,7 +197,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(const GemvTcParams
         BlockWalk w;
         int n = 0, it = -1, cur_item = -1, cur_sub = -1;
         bool ok = true;
+        GT_DECL;
         for (w.start(p); w.valid(p) && ok; w.next(p), ++n) {
+            GT_ACC(0);
             if (w.item != cur_item) {
                 // the previous item is complete once its MMAs retire
                 if (cur_item >= 0 && lane == 0) tc::commit(tc::smem_u32(&acc_full[it & 1]));
@@ -194,10 +212,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(const GemvTcParams
             const bool first = w.sub != cur_sub;                     // first block of this block row: overwrite
             cur_sub = w.sub;
             const int s = n % kStages, ab = n % kABufs;
+            GT_ACC(1);
             ok = tc::mbar_wait(tc::smem_u32(&raw_full[s]), (n / kStages) & 1, abort_flag, &g_gemv_tc_error, 2, kWaitLimit);
             if (!ok) break;
+            GT_ACC(2);
             ok = tc::mbar_wait(tc::smem_u32(&a_full[ab]), (n / kABufs) & 1, abort_flag, &g_gemv_tc_error, 3, kWaitLimit);
             if (!ok) break;
+            GT_ACC(3);
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             if (lane == 0) {
                 const uint32_t acc = tmem + kAccCol + (it & 1) * 32 + w.sub * 16;
@@ -209,22 +230,28 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(const GemvTcParams
                     const uint64_t bd = tc::make_smem_desc(b0 + kk * 512, 128, 256, 0);
                     mma_a_tmem(acc, a0 + kk * 8, bd, kIdesc, (first && kk == 0) ? 0u : 1u);
                 }
+                GT_ACC(4);
                 tc::commit(tc::smem_u32(&a_empty[ab]));
                 tc::commit(tc::smem_u32(&raw_empty[s]));
+                GT_ACC(5);
             }
             __syncwarp();
         }
         if (ok && cur_item >= 0 && lane == 0) tc::commit(tc::smem_u32(&acc_full[it & 1]));
         __syncwarp();
+        GT_PUT(8, lane == 0);
     } else if (warp < 2 + kDecodeWarps) {
         // ---------------- decode: codes -> bf16 rows of the A operand in tensor memory ----------------
         const int quad = warp & 3, kh = (warp - 2) >> 2;              // lane quadrant (fixed by the warp id), input half
         const int m = quad * 32 + lane;                               // output row of the block
         BlockWalk w;
         int n = 0;
+        GT_DECL;
         for (w.start(p); w.valid(p); w.next(p), ++n) {
             const int s = n % kStages, ab = n % kABufs;
+            GT_ACC(0);
             if (!tc::mbar_wait(tc::smem_u32(&raw_full[s]), (n / kStages) & 1, abort_flag, &g_gemv_tc_error, 4, kWaitLimit)) break;
+            GT_ACC(1);
             const uint4 wv = *reinterpret_cast<const uint4 *>(stages + s * kRawBytes + m * 32 + kh * 16);
             const uint32_t ws[4] = {wv.x, wv.y, wv.z, wv.w};
             uint32_t r[32];
@@ -232,7 +259,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(const GemvTcParams
             for (int tcl = 0; tcl < 4; ++tcl)
 #pragma unroll
                 for (int q = 0; q < 8; ++q) r[tcl * 8 + q] = mortar_decode_pair(ws[tcl], q);
+            GT_ACC(2);
             if (!tc::mbar_wait(tc::smem_u32(&a_empty[ab]), ((n / kABufs) & 1) ^ 1u, abort_flag, &g_gemv_tc_error, 5, kWaitLimit)) break;
+            GT_ACC(3);
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             st32(tmem + kACol + ab * 64 + kh * 32 + ((uint32_t)(quad * 32) << 16), r);
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -241,7 +270,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tc_kernel(const GemvTcParams
                 arrive(tc::smem_u32(&a_full[ab]));
                 arrive(tc::smem_u32(&raw_empty[s]));
             }
+            GT_ACC(4);
         }
+        GT_PUT(16, warp == 2 && lane == 0);
     } else {
         // ---------------- epilogue: one item = 128 output features ----------------
         const int quad = warp & 3;
@@ -427,6 +458,15 @@ extern "C" int mortar_gemv_blocks(const mortar_gemv_pack *w, const void *xb, int
     MORTAR_CUDA_CHECK(cudaGetLastError());
     return MORTAR_OK;
 }
+
+#ifdef MORTAR_GEMV_TIMING
+extern "C" int mortar_gemv_ticks(unsigned long long *out) {
+    MORTAR_CUDA_CHECK(cudaMemcpyFromSymbol(out, g_gemv_ticks, sizeof(unsigned long long) * 24));
+    static const unsigned long long zeros[24] = {0};
+    MORTAR_CUDA_CHECK(cudaMemcpyToSymbol(g_gemv_ticks, zeros, sizeof(zeros)));
+    return MORTAR_OK;
+}
+#endif
 
 extern "C" int mortar_gemv_blocks_error(int32_t *code, int32_t reset) {
     if (!code) return MORTAR_ERR_NULL;
