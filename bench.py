@@ -824,6 +824,22 @@ def run_gemv_large(mb, device, pk, flush, reps: int = 20, copies: int = 8):
         out[name] = {"us": round(us, 2), "algorithmic_mb": round(m.algorithmic_bytes() / 1e6, 2),
                      "gb_per_s": round(gbs, 1), "frac_of_measured_hbm": round(gbs / pk["hbm_gbs"], 4),
                      "frac_of_8tbs_spec": round(gbs / 8000.0, 4)}
+    # the tensor-memory GEMV (codes expanded straight into tensor memory; opt-in, not selected): same
+    # matrices, gate/up as a plain product with the SwiGLU in the operand preparation of the down product
+    dn_pad = mb.synth.make_block_matrix(d, f + 64, DENSITY, seed=2)      # hidden width padded to a multiple of 128
+    tg = [gu_m.to_gemv_blocks(False, device) for _ in range(copies)]
+    td = [dn_pad.to_gemv_blocks(False, device) for _ in range(copies)]
+    xb = mb.ops.gemv_xprep(xp)
+    g32 = mb.ops.gemv_blocks(tg[0], xb, 1, 3)
+    hb = torch.zeros((f + 64) // 16 * 512, device=device, dtype=torch.uint8)
+    hb[:f // 16 * 512] = mb.ops.gemv_xprep_swiglu(g32, 3)
+    tm = {}
+    for name, ws, call in (("gate_up", tg, lambda w: mb.ops.gemv_blocks(w, xb, 1, 3)),
+                           ("down", td, lambda w: mb.ops.gemv_blocks(w, hb, 1, 3))):
+        g = capture(lambda: [call(w) for w in ws])
+        tm[name + "_us"] = round(statistics.median(time_steps(g.replay, reps, 3, flush)) * 1e3 / copies, 2)
+    tm["device_error_word"] = mb.ops.gemv_blocks_error()
+    out["tensor_memory_path_not_selected"] = tm
     out["reference_published_us_rtx5090"] = {"gate_up": 43.3, "down": 38.9}
     out["note"] = (f"kernel bcsr_stream_kernel; one CUDA graph of {copies} launches over {copies} "
                    f"distinct weight copies, L2 flushed before each replay; per-launch time = "
