@@ -356,11 +356,7 @@ int mortar_gemv_blocks_error(int32_t *code, int32_t reset);
  *
  * Weights come per (layer, cluster rank) in two parts built on the host (16-byte aligned), each
  *   int32 hdr[8] = { n_groups, byte offsets of grp_ptr, grp_cols, grp_codes, scale bits, part
- *                    bytes, byte offset of an fp32[d_model] rmsnorm weight inside the part or 0,
- *                    byte offset of a row assignment or 0 }
- * Row assignment (optional, used with MORTAR_PLANES_HALF2): int32 [16][ceil(rows of the part / 16)],
- * the tile rows of the part each of the kernel's 16 warps computes (-1 = none), e.g. dealt out by
- * decreasing tile count so the warps finish together; without it warp w takes rows w, w + 16, ...
+ *                    bytes, byte offset of an fp32[d_model] rmsnorm weight inside the part or 0, 0 }
  * followed by the arrays: rank c's gate/up part is the stream layout of gate tile rows [cU,(c+1)U)
  * followed by the matching up tile rows (U = d_ff/16/cluster_size); its down part is the stream
  * layout of all output tile rows restricted to hidden tile columns [cU,(c+1)U) (column indices

@@ -238,7 +238,7 @@ __host__ __device__ inline SmemLayout smem_layout(int d_model, int d_ff, int cs,
     L.hp = off; off += align_up_i(n_planes * 8 * h_pitch * 2, 16);
     L.gu = off;                                   // gate and up sums of the hidden slice, fp32: when a rank has fewer
     // hidden tile rows than warps; with fp16 planes always (the fp32 hidden rows wait there for their scale)
-    if (f16 || d_ff / 16 / cs < kWarps) off += 8 * (2 * (d_ff / cs) + 4) * 4;   // row pitch 2 d_ff / cs + 4 floats
+    if (f16 || d_ff / 16 / cs < kWarps) off += 8 * 2 * (d_ff / cs) * 4;
     L.recv = off; off += cs * 8 * (d_model / cs + 4) * 4;   // partial sums of this rank's columns, one block per source rank
     L.xsend = off; off += xs_block_floats(d_model, cs) * 4;
     off = align_up_i(off, 128);
@@ -356,7 +356,7 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
         wait(smem_u32(&bars[0]), a & 1);
         ST_ACC(1);
         // part header: int32 {n_groups, offsets of grp_ptr, grp_cols, grp_codes, scale bits, bytes,
-        // offset of an fp32[d_model] rmsnorm weight or 0, offset of the warps' row assignment or 0}
+        // offset of an fp32[d_model] rmsnorm weight or 0, 0}
         const uint8_t *part_a = wbuf, *part_b = wbuf + p.max_a;
         const int *ha = reinterpret_cast<const int *>(part_a);
         const uint32_t gu_ptr = smem_u32(part_a) + ha[1], gu_cols = smem_u32(part_a) + ha[2], gu_codes = smem_u32(part_a) + ha[3];
@@ -440,17 +440,11 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
                 act[pl] = smem_u32(xp) + (uint32_t)(pl * xplane_w + g * (p.x_pitch / 2) + t) * 4u;
             const int W = 2 * U * 16;                            // gate columns then up columns
             const int HW = U * 16;
-            const int WP = W + 4;                                // row pitch of the fp32 sums: the four row pairs a warp stores fall into different banks
-            // optional assignment of the part's 2U tile rows to the warps (balanced by tile count when the
-            // weights were packed): ceil(2U / kWarps) entries per warp, -1 = none
-            const int *asg_a = ha[7] ? reinterpret_cast<const int *>(part_a + ha[7]) : nullptr;
-            const int na = (2 * U + kWarps - 1) / kWarps;
             // the matrix scale times the factor that undoes the row's plane scaling (rows 2t, 2t+1)
             const float sg[2] = {scale_gu * xun[2 * t], scale_gu * xun[2 * t + 1]};
             // fp16 planes: the fp32 hidden rows wait in shared memory (row pitch hp32) for the row maxima
-            const bool in_registers = U >= kWarps && !(H && asg_a != nullptr);
-            const int hp32 = in_registers ? HW + 4 : WP;
-            if (in_registers) {
+            const int hp32 = U >= kWarps ? HW + 4 : W;
+            if (U >= kWarps) {
                 // enough hidden tile rows for every warp: one warp computes the gate and the up
                 // tile row of a hidden tile row and applies SwiGLU in registers
                 for (int hrow = warp; hrow < U; hrow += kWarps) {
@@ -493,23 +487,21 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
                     }
                 }
             } else {
-                for (int i = 0; i < na; ++i) {
-                    const int trow = asg_a != nullptr ? asg_a[warp * na + i] : warp + i * kWarps;
-                    if (trow < 0 || trow >= 2 * U) continue;
+                for (int trow = warp; trow < 2 * U; trow += kWarps) {
                     float acc[4] = {0.f, 0.f, 0.f, 0.f};
                     tile_row<P, H>(gu_ptr, gu_cols, gu_codes, trow, act, lane, acc);
 #pragma unroll
-                    for (int e = 0; e < 4; ++e)                  // (neuron g + 8*(e>>1), row 2t + (e&1))
-                        gu_out[(2 * t + (e & 1)) * WP + trow * 16 + g + 8 * (e >> 1)] = sg[e & 1] * acc[e];
+                    for (int i = 0; i < 4; ++i)                  // (neuron g + 8*(i>>1), row 2t + (i&1))
+                        gu_out[(2 * t + (i & 1)) * W + trow * 16 + g + 8 * (i >> 1)] = sg[i & 1] * acc[i];
                 }
                 __syncthreads();
                 // silu(gate) * up -> exact bf16 planes of the hidden slice
                 const int r = warp / kWarpsPerRow;               // kWarpsPerRow warps per activation row
                 for (int c = (warp % kWarpsPerRow) * 32 + lane; c < HW; c += kWarpsPerRow * 32) {
-                    const float gv = gu_out[r * WP + c], uv = gu_out[r * WP + HW + c];
+                    const float gv = gu_out[r * W + c], uv = gu_out[r * W + HW + c];
                     float hv = gv * __fdividef(1.f, 1.f + __expf(-gv)) * uv;
                     if (H) {
-                        gu_out[r * WP + c] = hv;                  // in place of the gate sum this thread just read
+                        gu_out[r * W + c] = hv;                   // in place of the gate sum this thread just read
                         hv = fabsf(hv);
 #pragma unroll
                         for (int o = 1; o < 32; o <<= 1) hv = fmaxf(hv, __shfl_xor_sync(0xffffffffu, hv, o));
@@ -564,19 +556,14 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
                     if (mb) sd[k] = scale_dn * pow2i((int)(mb >> 23) - 127 - 13);
                 }
             }
-            // optional assignment of the RD output tile rows to the warps, as for the gate/up part
-            const int *asg_b = hb[7] ? reinterpret_cast<const int *>(part_b + hb[7]) : nullptr;
-            const int nb = (RD + kWarps - 1) / kWarps;
-            for (int i = 0; i < nb; ++i) {
-                const int trow = asg_b != nullptr ? asg_b[warp * nb + i] : warp + i * kWarps;
-                if (trow < 0 || trow >= RD) continue;
+            for (int trow = warp; trow < RD; trow += kWarps) {
                 float acc[4] = {0.f, 0.f, 0.f, 0.f};
                 tile_row<P, H>(dn_ptr, dn_cols, dn_codes, trow, act, lane, acc);
                 const int q = trow / TR, cl0 = (trow - q * TR) * 16;
                 float *dst = ysend + (size_t)q * 8 * OCP + cl0;
 #pragma unroll
-                for (int e = 0; e < 4; ++e)
-                    dst[(2 * t + (e & 1)) * OCP + g + 8 * (e >> 1)] = sd[e & 1] * acc[e];
+                for (int i = 0; i < 4; ++i)
+                    dst[(2 * t + (i & 1)) * OCP + g + 8 * (i >> 1)] = sd[i & 1] * acc[i];
             }
         }
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");

@@ -340,28 +340,6 @@ def mlp_decode_static(x: torch.Tensor, gate_up: StreamMatrix, down: StreamMatrix
     return out
 
 
-STACK_WARPS = 16        # warps of stack_decode_kernel: the row assignments in the blobs are made for them
-
-
-def _balanced_rows(tiles_per_row) -> "np.ndarray":
-    """Tile rows of one weight part dealt to the stack kernel's warps so that they finish together:
-    int32 [STACK_WARPS][ceil(rows / STACK_WARPS)], -1 = none.  A row costs its tiles plus a fixed
-    amount per group of 8; rows go, heaviest first, to the least loaded warp that has a slot left."""
-    import numpy as np
-    n = np.asarray(tiles_per_row, dtype=np.int64)
-    cost = n + 2 * ((n + 7) // 8)
-    per = -(-len(n) // STACK_WARPS)
-    table = np.full((STACK_WARPS, per), -1, dtype=np.int32)
-    load, used = np.zeros(STACK_WARPS, dtype=np.int64), np.zeros(STACK_WARPS, dtype=np.int64)
-    for r in np.argsort(-cost, kind="stable"):
-        free = np.where(used < per)[0]
-        w = free[np.argmin(load[free])]
-        table[w, used[w]] = r
-        used[w] += 1
-        load[w] += cost[r]
-    return table
-
-
 class _StackBlobs:
     """Per-(layer, cluster rank) weights of a stack for one cluster size, in two parts per rank:
     the stream layout of the rank's gate/up tile rows, and the stream layout of the matching
@@ -382,15 +360,16 @@ class _StackBlobs:
                 subs = (gu.slice_tile_rows(rows), dn.slice_tile_cols(c * U, (c + 1) * U))
                 for part, sub in enumerate(subs):
                     gp, gc, gcd, G = sub.build_stream_host()
-                    arrays = [gp.tobytes(), gc[:max(G, 1) * 8].tobytes(), gcd[:max(G, 1) * 512].tobytes(),
-                              wb if part == 0 else b"", _balanced_rows(np.diff(sub.row_ptr)).tobytes()]
+                    arrays = [gp.tobytes(), gc[:max(G, 1) * 8].tobytes(), gcd[:max(G, 1) * 512].tobytes()]
+                    if part == 0:
+                        arrays.append(wb)
                     hdr = np.zeros(8, dtype=np.int32)
                     body, pos = [], 32
                     for k, raw in enumerate(arrays):
                         if k < 3:
                             hdr[1 + k] = pos
                         else:
-                            hdr[3 + k] = pos if raw else 0          # [6]: norm weight, [7]: row assignment
+                            hdr[6] = pos if raw else 0
                         pad = (-len(raw)) % 16
                         body.append(raw + b"\0" * pad)
                         pos += len(raw) + pad
