@@ -111,13 +111,20 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
     return v;
 }
+// Activation planes keep the 8 element pairs of a 16-column tile in fragment order: pair j sits
+// at 32-bit word (j & 3) * 2 + (j >> 2), so the two words a lane feeds to one MMA (pairs t and
+// t + 4) are adjacent and come with one 64-bit load.
+__device__ __forceinline__ int plane_word(int c) {             // 32-bit word of column c's pair within its row
+    const int j = (c & 15) >> 1;
+    return (c >> 4) * 8 + (j & 3) * 2 + (j >> 2);
+}
 __device__ __forceinline__ void lds_bfrag(uint32_t addr, uint32_t &b0, uint32_t &b1) {
-    asm volatile("ld.shared.u32 %0, [%2];\n\tld.shared.u32 %1, [%2+16];\n" : "=r"(b0), "=r"(b1) : "r"(addr));
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(b0), "=r"(b1) : "r"(addr));
 }
 
 // All groups of one tile row of a stream-format matrix held in shared memory, against the 8
 // staged activation rows.  Everything is addressed in the shared window (32-bit addresses):
-// act[pl] = address of plane pl, this lane's row (lane>>2), element 2*(lane&3).  Every plane has
+// act[pl] = address of plane pl, this lane's row (lane>>2), word 2*(lane&3) of tile 0.  Every plane has
 // its own accumulator (independent MMAs); a group whose last slot is a real tile has no padding
 // and runs without per-slot tests, so its loads and MMAs interleave freely.
 template <int P, bool H, bool CHECK>
@@ -417,9 +424,12 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
                 uint32_t lo[P], hi[P];
                 split_pair<P, H>(vv[0], vv[1], lo);
                 split_pair<P, H>(vv[2], vv[3], hi);
+                uint32_t *o = reinterpret_cast<uint32_t *>(xp + row * p.x_pitch) + plane_word(c);
 #pragma unroll
-                for (int pl = 0; pl < P; ++pl)
-                    *reinterpret_cast<uint2 *>(xp + (size_t)pl * 8 * p.x_pitch + row * p.x_pitch + c) = make_uint2(lo[pl], hi[pl]);
+                for (int pl = 0; pl < P; ++pl) {                // pairs (c, c+1) and (c+2, c+3): two words apart
+                    o[pl * xplane_w] = lo[pl];
+                    o[pl * xplane_w + 2] = hi[pl];
+                }
             };
 #pragma unroll
             for (int k = 0; k < kWPre; ++k) {
@@ -437,7 +447,7 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
             uint32_t act[P];
 #pragma unroll
             for (int pl = 0; pl < P; ++pl)
-                act[pl] = smem_u32(xp) + (uint32_t)(pl * xplane_w + g * (p.x_pitch / 2) + t) * 4u;
+                act[pl] = smem_u32(xp) + (uint32_t)(pl * xplane_w + g * (p.x_pitch / 2) + 2 * t) * 4u;
             const int W = 2 * U * 16;                            // gate columns then up columns
             const int HW = U * 16;
             // the matrix scale times the factor that undoes the row's plane scaling (rows 2t, 2t+1)
@@ -468,7 +478,7 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
                         } else {
                             uint32_t pr[P];
                             split_pair<P, H>(hv[0], hv[1], pr);
-                            uint16_t *o = hp + (2 * t) * p.h_pitch + col;
+                            uint16_t *o = hp + (2 * t) * p.h_pitch + plane_word(col) * 2 + (col & 1);
 #pragma unroll
                             for (int pl = 0; pl < P; ++pl) {
                                 o[(size_t)pl * 8 * p.h_pitch] = (uint16_t)(pr[pl] & 0xffffu);
@@ -507,7 +517,7 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
                         for (int o = 1; o < 32; o <<= 1) hv = fmaxf(hv, __shfl_xor_sync(0xffffffffu, hv, o));
                         if (lane == 0) atomicMax(&hmax[r], __float_as_uint(hv));
                     } else {
-                        uint16_t *o = hp + r * p.h_pitch + c;
+                        uint16_t *o = hp + r * p.h_pitch + plane_word(c) * 2 + (c & 1);
 #pragma unroll
                         for (int pl = 0; pl < P; ++pl) {
                             const __nv_bfloat16 hb = __float2bfloat16_rn(hv);
@@ -529,7 +539,7 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
                     split_pair<P, H>(v.x * sc, v.y * sc, pr);
 #pragma unroll
                     for (int pl = 0; pl < P; ++pl)
-                        *reinterpret_cast<uint32_t *>(hp + (size_t)pl * 8 * p.h_pitch + r * p.h_pitch + c) = pr[pl];
+                        reinterpret_cast<uint32_t *>(hp + r * p.h_pitch)[pl * hplane_w + plane_word(c)] = pr[pl];
                 }
             }
         }
@@ -547,7 +557,7 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
             uint32_t act[P];
 #pragma unroll
             for (int pl = 0; pl < P; ++pl)
-                act[pl] = smem_u32(hp) + (uint32_t)(pl * hplane_w + g * (p.h_pitch / 2) + t) * 4u;
+                act[pl] = smem_u32(hp) + (uint32_t)(pl * hplane_w + g * (p.h_pitch / 2) + 2 * t) * 4u;
             float sd[2] = {scale_dn, scale_dn};                  // times the factor that undoes the hidden rows' scaling
             if (H) {
 #pragma unroll
@@ -610,10 +620,10 @@ __global__ void __launch_bounds__(kThreads, 1) stack_decode_kernel(const StackPa
 }
 
 inline int pitch_for(int features) {
-    // row pitch (bf16 elements) whose 32-bit word count is 4 mod 32: the 8 rows x 4 lanes of a
-    // B-fragment load then hit 32 different banks
+    // row pitch (bf16 elements) whose 32-bit word count is 8 mod 32: the 4 rows x 4 lanes of each
+    // half of a 64-bit B-fragment load then hit 32 different banks
     const int words = features / 2;
-    const int pad = ((4 - words % 32) % 32 + 32) % 32;
+    const int pad = ((8 - words % 32) % 32 + 32) % 32;
     return (words + pad) * 2;
 }
 
