@@ -489,7 +489,11 @@ int mortar_linear_tc_i8(const mortar_sched *w, const void *xq, int64_t ldxq, con
  *             the part of an edge block beyond the matrix, are zeros
  *   pair_ptr  device int32 [n_pairs + 1]: first step of every pair
  *   steps     device int32 [n_steps][4] (16-byte aligned): {block column, index into data of the
- *             first block row's block or -1, of the second's or -1, 0}, ascending block column */
+ *             first block row's block or -1, of the second's or -1, 0}; the block columns of a pair
+ *             may come in any order (listing those both rows keep first lets every such step run
+ *             as one N = 256 MMA)
+ * With more than 128 rows the kernel runs on CTA pairs (tcgen05 cta_group::2): 256 rows per work
+ * item, every block half in each CTA's shared memory. */
 typedef struct mortar_blocks {
     const void *data;
     const int32_t *pair_ptr;
@@ -506,6 +510,11 @@ typedef struct mortar_blocks {
 int mortar_linear_blocks(const mortar_blocks *w, const void *x, int64_t ldx, int64_t rows, void *out,
                          int64_t ld_out, const float *gates, int64_t ld_gates, int32_t cluster_size,
                          void *stream);
+
+/* Which kernel the block path launches, process-wide: 0 = by row count (the default), 1 = single
+ * CTAs, 2 = CTA pairs.  Returns the previous mode, or MORTAR_ERR_SHAPE for an unknown mode.  For
+ * measurements and tests; the results of the kernels agree to the accumulation order. */
+int mortar_linear_blocks_mode(int32_t mode);
 
 /* mortar_mlp_prefill on the block path (same workspace: rows*d_ff*2 bytes, 256-byte aligned). */
 int mortar_mlp_prefill_blocks(const mortar_blocks *gate_up, const mortar_blocks *down, const void *x,

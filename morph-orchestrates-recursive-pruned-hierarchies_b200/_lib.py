@@ -106,6 +106,7 @@ _SIGNATURES = {
     "mortar_gemv_blocks": (C.c_int, [C.POINTER(GemvPack), _vp, _i64, _i32, _vp, _i32, _i32, _i64, _i64, _vp]),
     "mortar_gemv_blocks_error": (C.c_int, [_vp, _i32]),
     "mortar_linear_blocks": (C.c_int, [C.POINTER(Blocks), _vp, _i64, _i64, _vp, _i64, _vp, _i64, _i32, _vp]),
+    "mortar_linear_blocks_mode": (C.c_int, [_i32]),
     "mortar_mlp_prefill_blocks": (C.c_int, [C.POINTER(Blocks), C.POINTER(Blocks), _vp, _i64, _i64, _vp, _i64, _i32,
                                             _vp, _i64, _vp, _i64, _vp]),
     "mortar_sched_sizes_i8": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp]),

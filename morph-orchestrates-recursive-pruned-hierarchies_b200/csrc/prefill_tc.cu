@@ -24,6 +24,7 @@
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <cstdint>
+#include <atomic>
 #include <mutex>
 #include <type_traits>
 #include "common.h"
@@ -602,6 +603,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   CUtensorMapFloatOOBfill);
 
 std::mutex g_prefill_init_mutex;   // guards the first-use initialisation below
+std::atomic<int> g_blocks_mode{0};  // block path: 0 = choose by row count, 1 = single CTAs, 2 = CTA pairs
 
 int get_encode_fn(EncodeTiledFn *out) {
     static EncodeTiledFn cached = nullptr;
@@ -964,6 +966,260 @@ prefill_blocks_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(kTmemCols) : "memory");
 }
 
+// ---------------------------------------------------------------------------------------------
+// Block path on CTA pairs (tcgen05 cta_group::2).  A cluster of two CTAs works on 256 activation
+// rows (128 each) against one pair of block rows: the MMA has M = 256 and its B operand is split
+// between the two CTAs' shared memories, so each CTA stages and reads only half of every block.
+// A single-CTA MMA is bound by shared-memory bandwidth (operand reads plus the TMA writes that
+// refill the stages); halving the B traffic per SM lifts that bound.
+//
+// Per step (one block column of the pair) and half (K = 64) each CTA loads its own [128 x 64]
+// activation chunk and its share of the B operand:
+//   both blocks present and in the same accumulate state: one N = 256 MMA per 16 features whose
+//     B rows 0..127 are the first block (held by CTA 0) and 128..255 the second (held by CTA 1);
+//   otherwise one N = 128 MMA per present block, whose B rows 0..63 are held by CTA 0 and 64..127
+//     by CTA 1: every CTA loads 64 rows of each present block (first block at offset 0, second at
+//     8 KB of the B region).
+// All loads of a stage complete on CTA 0's `full` barrier (its producer posts the byte count of
+// both CTAs); CTA 0's MMA warp issues for the pair and commits to the `empty` and accumulator
+// barriers of both CTAs; the epilogue warps of both CTAs release an accumulator set on CTA 0's
+// barrier.  Every wait is bounded as in the single-CTA kernel.
+constexpr int kB2Stages = 6;
+constexpr int kB2B = 128 * 128;                      // this CTA's share of the step's B operand
+constexpr int kB2Stage = kBkA + kB2B;                // 32 KB
+constexpr int kB2SmemBytes = kB2Stages * kB2Stage + (2 * kB2Stages + 4) * 8 + kBkMaxSteps * 16 + (kBkMaxPairs + 1) * 4 +
+                             1024 /*align*/;
+static_assert(kB2SmemBytes <= 227 * 1024, "shared memory budget");
+
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+// shared::cluster address of the same shared-memory offset in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                            uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n.reg .b64 da, db;\n"
+        "setp.ne.b32 p, %6, 0;\n"
+        "mov.b64 da, {%1, %2};\n"
+        "mov.b64 db, {%3, %4};\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate));
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t cluster_bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
+                 ::"r"(cluster_bar) : "memory");
+}
+// TMA tile load into this CTA's shared memory that completes on a barrier of either CTA of the pair
+__device__ __forceinline__ void tma_load_pair(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t cluster_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3}], [%4];\n"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(cluster_bar) : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kBkThreads, 1)
+prefill_blocks_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+                           const __grid_constant__ CUtensorMap tmap_wh, const BlockParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *stages = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t *full = reinterpret_cast<uint64_t *>(stages + kB2Stages * kB2Stage), *empty = full + kB2Stages;
+    uint64_t *acc_full = empty + kB2Stages, *acc_empty = acc_full + 2;
+    int4 *steps_s = reinterpret_cast<int4 *>(acc_empty + 2);
+    int *pairs_s = reinterpret_cast<int *>(steps_s + kBkMaxSteps);
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int abort_s;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_cta_rank();
+    const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+
+    const bool cached = p.n_steps <= kBkMaxSteps && p.n_pairs <= kBkMaxPairs;
+    if (cached) {
+        for (int i = threadIdx.x; i < p.n_steps; i += kBkThreads) steps_s[i] = __ldg(p.steps + i);
+        for (int i = threadIdx.x; i <= p.n_pairs; i += kBkThreads) pairs_s[i] = __ldg(p.pair_ptr + i);
+    }
+    const int4 *steps = cached ? steps_s : p.steps;
+    const int *pair_ptr = cached ? pairs_s : p.pair_ptr;
+
+    if (threadIdx.x == 0) {
+        abort_s = 0;
+        for (int s = 0; s < kB2Stages; ++s) { mbar_init(smem_u32(&full[s]), 1); mbar_init(smem_u32(&empty[s]), 1); }
+        for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&acc_full[s]), 1); mbar_init(smem_u32(&acc_empty[s]), 2 * kBkEpiWarps); }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        // the same warp of both CTAs allocates (and later frees) the pair's tensor memory
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(smem_u32(&tmem_base_s)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();                                        // barriers of both CTAs are initialised
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem = tmem_base_s;
+    volatile int *abort_flag = &abort_s;
+
+    if (warp == 0) {
+        // ---------------- TMA producer (both CTAs) ----------------
+        int g = 0;
+        bool ok = true;
+        for (int item = cluster_id; item < p.n_items && ok; item += n_clusters) {
+            const int pair = item % p.n_pairs, row0 = (item / p.n_pairs) * (2 * kRows) + (int)rank * kRows;
+            bool have_a = false, have_b = false;
+            const int s_end = pair_ptr[pair + 1];
+            for (int st = pair_ptr[pair]; st < s_end && ok; ++st) {
+                const int4 s = steps[st];
+                const bool wide = s.y >= 0 && s.z >= 0 && have_a == have_b;
+                const uint32_t b_bytes = wide ? (uint32_t)kB2B : (uint32_t)((s.y >= 0) + (s.z >= 0)) * (kB2B / 2);
+#pragma unroll 1
+                for (int h = 0; h < 2; ++h, ++g) {
+                    const int sg = g % kB2Stages;
+                    ok = mbar_wait_relaxed(smem_u32(&empty[sg]), ((g / kB2Stages) & 1) ^ 1u, abort_flag, 5);
+                    if (!ok) break;
+                    if (lane == 0) {
+                        const uint32_t bar = map_to_cta(smem_u32(&full[sg]), 0);
+                        const uint32_t dst = smem_u32(stages + sg * kB2Stage);
+                        if (rank == 0) mbar_arrive_expect_tx(smem_u32(&full[sg]), 2u * (kBkA + b_bytes));
+                        tma_load_pair(dst, &tmap_x, s.x * 128 + h * 64, row0, bar);
+                        if (wide) {
+                            tma_load_pair(dst + kBkA, &tmap_w, h * 64, (rank == 0 ? s.y : s.z) * 128, bar);
+                        } else {
+                            if (s.y >= 0) tma_load_pair(dst + kBkA, &tmap_wh, h * 64, s.y * 128 + (int)rank * 64, bar);
+                            if (s.z >= 0) tma_load_pair(dst + kBkA + kB2B / 2, &tmap_wh, h * 64, s.z * 128 + (int)rank * 64, bar);
+                        }
+                    }
+                    __syncwarp();
+                }
+                have_a |= s.y >= 0;
+                have_b |= s.z >= 0;
+            }
+        }
+    } else if (warp == 1) {
+        if (rank == 0) {
+            // ---------------- MMA issue (CTA 0 for the pair) ----------------
+            // kind::f16, D fp32, A and B bf16, both K-major; N >> 3 at bit 17, M >> 4 at bit 24 (M = 256 over the pair)
+            constexpr uint32_t kIdescBase = (1u << 4) | (1u << 7) | (1u << 10) | ((256u >> 4) << 24);
+            constexpr uint32_t kIdesc128 = kIdescBase | ((128u >> 3) << 17), kIdesc256 = kIdescBase | ((256u >> 3) << 17);
+            int g = 0, it = 0;
+            bool ok = true;
+            for (int item = cluster_id; item < p.n_items && ok; item += n_clusters, ++it) {
+                const int pair = item % p.n_pairs, buf = it & 1;
+                ok = mbar_wait_relaxed(smem_u32(&acc_empty[buf]), ((it >> 1) & 1) ^ 1u, abort_flag, 9);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint32_t acc = tmem + buf * kAccCols;
+                uint32_t have_a = 0u, have_b = 0u;
+                const int s_beg = pair_ptr[pair], s_end = pair_ptr[pair + 1];
+                for (int st = s_beg; st < s_end && ok; ++st) {
+                    const int4 s = steps[st];
+                    const bool wide = s.y >= 0 && s.z >= 0 && have_a == have_b;
+#pragma unroll 1
+                    for (int h = 0; h < 2; ++h, ++g) {
+                        const int sg = g % kB2Stages;
+                        ok = mbar_wait(smem_u32(&full[sg]), (g / kB2Stages) & 1, abort_flag, 2);
+                        if (!ok) break;
+                        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                        if (lane == 0) {
+                            const uint32_t base = smem_u32(stages + sg * kB2Stage);
+                            const uint64_t ad = make_smem_desc(base, 16, 1024, 2);
+                            const uint64_t bd = make_smem_desc(base + kBkA, 16, 1024, 2);
+                            const uint32_t a_lo = (uint32_t)ad, a_hi = (uint32_t)(ad >> 32);
+                            const uint32_t b_lo = (uint32_t)bd, b_hi = (uint32_t)(bd >> 32);
+                            uint32_t fa = have_a, fb = have_b;
+#pragma unroll
+                            for (int kk = 0; kk < 4; ++kk) {
+                                if (wide) {
+                                    tc_mma_pair(acc, a_lo + kk * 2, a_hi, b_lo + kk * 2, b_hi, kIdesc256, fa);
+                                } else {
+                                    if (s.y >= 0) tc_mma_pair(acc, a_lo + kk * 2, a_hi, b_lo + kk * 2, b_hi, kIdesc128, fa);
+                                    if (s.z >= 0) tc_mma_pair(acc + 128, a_lo + kk * 2, a_hi, b_lo + (kB2B >> 5) + kk * 2, b_hi, kIdesc128, fb);
+                                }
+                                if (s.y >= 0) fa = 1u;
+                                if (s.z >= 0) fb = 1u;
+                            }
+                            tc_commit_pair(smem_u32(&empty[sg]));
+                            tc_commit_pair(map_to_cta(smem_u32(&empty[sg]), 1));
+                        }
+                        if (s.y >= 0) have_a = 1u;
+                        if (s.z >= 0) have_b = 1u;
+                        __syncwarp();
+                    }
+                }
+                if (!ok) break;
+                if (lane == 0) {
+                    if (s_end > s_beg) {
+                        tc_commit_pair(smem_u32(&acc_full[buf]));
+                        tc_commit_pair(map_to_cta(smem_u32(&acc_full[buf]), 1));
+                    } else {
+                        mbar_arrive(smem_u32(&acc_full[buf]));
+                        mbar_arrive_cluster(map_to_cta(smem_u32(&acc_full[buf]), 1));
+                    }
+                }
+                __syncwarp();
+            }
+        }
+    } else {
+        // ---------------- epilogue (both CTAs, each for its own 128 rows) ----------------
+        const int q = warp & 3, ch = (warp - 2) >> 2;
+        int it = 0;
+        bool ok = true;
+        for (int item = cluster_id; item < p.n_items && ok; item += n_clusters, ++it) {
+            const int pair = item % p.n_pairs, buf = it & 1;
+            const long long row = (long long)(item / p.n_pairs) * (2 * kRows) + (long long)rank * kRows + q * 32 + lane;
+            const bool in_range = row < p.rows;
+            bool live_a = false, live_b = false;
+            const int s_end = pair_ptr[pair + 1];
+            for (int st = pair_ptr[pair]; st < s_end; ++st) {
+                const int4 s = steps[st];
+                live_a |= s.y >= 0;
+                live_b |= s.z >= 0;
+            }
+            ok = mbar_wait_relaxed(smem_u32(&acc_full[buf]), (it >> 1) & 1, abort_flag, 8);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const uint32_t taddr = tmem + buf * kAccCols + ((uint32_t)(q * 32) << 16);
+            if (p.swiglu) {
+#pragma unroll 1
+                for (int c0 = ch * 64; c0 < ch * 64 + 64; c0 += 32) {
+                    const long long col0 = (long long)pair * 128 + c0;
+                    if (p.gates == nullptr) block_epilogue_chunk<true, false>(p, taddr, row, in_range, col0, c0, live_a, live_b);
+                    else block_epilogue_chunk<true, true>(p, taddr, row, in_range, col0, c0, live_a, live_b);
+                }
+            } else {
+#pragma unroll 1
+                for (int c0 = ch * 128; c0 < ch * 128 + 128; c0 += 32) {
+                    const long long col0 = (long long)pair * 256 + c0;
+                    block_epilogue_chunk<false, false>(p, taddr, row, in_range, col0, c0, c0 < 128 ? live_a : live_b, true);
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0));
+        }
+    }
+
+    // neither CTA may leave (or free tensor memory) while its peer can still read its shared
+    // memory or signal its barriers
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1)
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(kTmemCols) : "memory");
+}
+
 // Per-row symmetric int8 quantisation: scale[r] = max|x[r]| / 127, q = round(x / scale[r]).
 // One CTA per row; the row is read twice (the second time from cache).
 __global__ void __launch_bounds__(256)
@@ -1035,6 +1291,11 @@ extern "C" int mortar_quantize_rows(const void *x, int64_t ldx, int64_t rows, in
     return MORTAR_OK;
 }
 
+extern "C" int mortar_linear_blocks_mode(int32_t mode) {
+    if (mode < 0 || mode > 2) return MORTAR_ERR_SHAPE;
+    return g_blocks_mode.exchange(mode, std::memory_order_relaxed);
+}
+
 extern "C" int mortar_linear_blocks(const mortar_blocks *w, const void *x, int64_t ldx, int64_t rows, void *out,
                                     int64_t ld_out, const float *gates, int64_t ld_gates, int32_t cluster_size,
                                     void *stream) {
@@ -1050,15 +1311,21 @@ extern "C" int mortar_linear_blocks(const mortar_blocks *w, const void *x, int64
         return MORTAR_ERR_ALIGN;
     if (gates && (cluster_size <= 0 || !w->swiglu)) return MORTAR_ERR_SHAPE;
     if (rows == 0) return MORTAR_OK;
-    const int64_t row_blocks = (rows + kRows - 1) / kRows;
+    // more than one block of rows: CTA pairs share every block (unless the single-CTA kernel is forced)
+    const int mode = g_blocks_mode.load(std::memory_order_relaxed);
+    const bool pairs = mode == 2 || (mode == 0 && rows > kRows);
+    const int item_rows = pairs ? 2 * kRows : kRows;
+    const int64_t row_blocks = (rows + item_rows - 1) / item_rows;
     const int64_t n_items = row_blocks * w->n_pairs;
-    if (n_items > 0x7fffffffLL || rows > 0x7fffffffLL || w->n_blocks > (0x7fffffffLL >> 7)) return MORTAR_ERR_CAPACITY;
+    if (n_items > 0x7fffffffLL || rows > 0x7fffffffLL - item_rows || w->n_blocks > (0x7fffffffLL >> 7))
+        return MORTAR_ERR_CAPACITY;
 
     EncodeTiledFn encode;
     int rc = get_encode_fn(&encode);
     if (rc != MORTAR_OK) return rc;
-    alignas(64) CUtensorMap tmap_x, tmap_w;
+    alignas(64) CUtensorMap tmap_x, tmap_w, tmap_wh;
     const cuuint32_t box[2] = {64, 128};
+    const cuuint32_t box_half[2] = {64, 64};
     const cuuint32_t estride[2] = {1, 1};
     {
         const cuuint64_t gdim[2] = {(cuuint64_t)w->in_features, (cuuint64_t)rows};
@@ -1081,6 +1348,13 @@ extern "C" int mortar_linear_blocks(const mortar_blocks *w, const void *x, int64
             mortar_set_cuda_error("cuTensorMapEncodeTiled", "failed to encode the block tensor map");
             return MORTAR_ERR_CUDA;
         }
+        // the same matrix in boxes of 64 block rows: the share of a block one CTA of a pair holds
+        if (pairs && encode(&tmap_wh, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, gdim, gstride, box_half, estride,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+            mortar_set_cuda_error("cuTensorMapEncodeTiled", "failed to encode the half-block tensor map");
+            return MORTAR_ERR_CUDA;
+        }
     }
     int dev = 0;
     MORTAR_CUDA_CHECK(cudaGetDevice(&dev));
@@ -1094,6 +1368,8 @@ extern "C" int mortar_linear_blocks(const mortar_blocks *w, const void *x, int64
             MORTAR_CUDA_CHECK(cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev));
             MORTAR_CUDA_CHECK(cudaFuncSetAttribute(prefill_blocks_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                    kBkSmemBytes));
+            MORTAR_CUDA_CHECK(cudaFuncSetAttribute(prefill_blocks_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   kB2SmemBytes));
             sm_count[dev] = v;
         }
         sms = sm_count[dev];
@@ -1113,8 +1389,15 @@ extern "C" int mortar_linear_blocks(const mortar_blocks *w, const void *x, int64
     p.gates = gates;
     p.ld_gates = ld_gates;
     p.cluster_size = cluster_size > 0 ? cluster_size : 1;
-    const unsigned grid = (unsigned)(n_items < sms ? n_items : sms);
-    prefill_blocks_kernel<<<grid, kBkThreads, kBkSmemBytes, (cudaStream_t)stream>>>(tmap_x, tmap_w, p);
+    if (pairs) {
+        const int64_t n_clusters = n_items < sms / 2 ? n_items : sms / 2;
+        if (n_clusters < 1) return MORTAR_ERR_CAPACITY;
+        prefill_blocks_pair_kernel<<<(unsigned)(2 * n_clusters), kBkThreads, kB2SmemBytes, (cudaStream_t)stream>>>(
+            tmap_x, tmap_w, tmap_wh, p);
+    } else {
+        const unsigned grid = (unsigned)(n_items < sms ? n_items : sms);
+        prefill_blocks_kernel<<<grid, kBkThreads, kBkSmemBytes, (cudaStream_t)stream>>>(tmap_x, tmap_w, p);
+    }
     MORTAR_CUDA_CHECK(cudaGetLastError());
     return MORTAR_OK;
 }

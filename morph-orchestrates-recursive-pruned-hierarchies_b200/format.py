@@ -490,7 +490,9 @@ class BlockSched:
         for ra, rb in pairs:
             ca = set(cols_of[ra])
             cb = set(cols_of[rb]) if rb >= 0 else set()
-            for c in sorted(ca | cb):
+            # block columns both rows keep first: from then on both accumulators are in the same
+            # state and every such step is one N = 256 MMA
+            for c in sorted(ca | cb, key=lambda c: (not (c in ca and c in cb), c)):
                 steps.append((c, index[(ra, c)] if c in ca else -1, index[(rb, c)] if c in cb else -1, 0))
             pair_ptr.append(len(steps))
         self.n_pairs, self.n_steps = len(pairs), len(steps)

@@ -655,6 +655,17 @@ def mlp_prefill_tc(x: torch.Tensor, gate_up: SchedMatrix, down: SchedMatrix, *,
     return out.reshape(*lead, d_model)
 
 
+BLOCKS_MODES = {"auto": 0, "single": 1, "pairs": 2}
+
+
+def linear_blocks_mode(mode: str) -> str:
+    """Chooses the kernel of the block path process-wide: "auto" (CTA pairs from 129 rows on),
+    "single" or "pairs".  Returns the previous mode."""
+    prev = _lib.lib().mortar_linear_blocks_mode(BLOCKS_MODES[mode])
+    _lib.check(min(prev, 0), "mortar_linear_blocks_mode")
+    return {v: k for k, v in BLOCKS_MODES.items()}[prev]
+
+
 def linear_blocks(x: torch.Tensor, w: BlockSched, *, gates: Optional[torch.Tensor] = None,
                   cluster_size: int = 0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``linear_tc`` on the block path: the matrix as expanded 128 x 128 blocks (``MortarMatrix.to_blocks``),

@@ -18,8 +18,16 @@ def _clean():
     assert mb.ops.prefill_error() == 0, "a bounded wait in the prefill kernel expired"
 
 
+@pytest.fixture(params=["single", "pairs"])
+def kernel_mode(request):
+    """Both kernels of the block path at every size (by default the row count chooses)."""
+    prev = mb.ops.linear_blocks_mode(request.param)
+    yield request.param
+    mb.ops.linear_blocks_mode(prev)
+
+
 @pytest.mark.parametrize("rows", [1, 100, 128, 300, 1000])
-def test_linear_blocks_ragged(rows):
+def test_linear_blocks_ragged(rows, kernel_mode):
     """edges that are not multiples of 128, an empty block row, an odd number of block rows, blocks
     with dropped tiles inside."""
     rng = np.random.default_rng(7)
@@ -41,7 +49,7 @@ def test_linear_blocks_ragged(rows):
 
 
 @pytest.mark.parametrize("rows", [128, 391, 2048])
-def test_mlp_blocks_cloud_shape_vs_oracle_and_tile_path(rows):
+def test_mlp_blocks_cloud_shape_vs_oracle_and_tile_path(rows, kernel_mode):
     d, f = 2048, 5632
     gu_m = mb.synth.make_block_matrix(2 * f, d, 0.25, seed=11)
     dn_m = mb.synth.make_block_matrix(d, f, 0.25, seed=12)
@@ -64,9 +72,13 @@ def test_mlp_blocks_cloud_shape_vs_oracle_and_tile_path(rows):
     refg = orc.swiglu_mlp(x.cpu().float(), _dense(gu_m), _dense(dn_m), gates.cpu(), ncls, dtype=torch.bfloat16)
     _assert_bf16_close(yg, refg, near_zero=1e-2)
     _clean()
-    # token blocks are independent: a 128-row slice gives the same bits
+    # token blocks are independent: a 128-row slice gives the same bits, from either kernel
     if rows >= 256:
         assert torch.equal(mb.ops.mlp_prefill_blocks(x[128:256], bg, bd), y[128:256])
+        mb.ops.linear_blocks_mode("pairs" if kernel_mode == "single" else "single")
+        assert torch.equal(mb.ops.mlp_prefill_blocks(x[128:256], bg, bd), y[128:256])
+        assert torch.equal(mb.ops.mlp_prefill_blocks(x, bg, bd), y)
+        mb.ops.linear_blocks_mode(kernel_mode)
 
 
 def test_blocks_golden_fixture_and_module_dispatch():
