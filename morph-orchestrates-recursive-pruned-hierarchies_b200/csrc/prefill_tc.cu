@@ -864,59 +864,62 @@ prefill_blocks_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
             }
         }
     } else if (warp == 1) {
-        // ---------------- MMA issue ----------------
+        // ---------------- MMA issue: one thread ----------------
+        // The issuing thread's own instruction stream is the critical path (the MMA queue holds only
+        // two or three instructions, so every cycle the thread spends between MMAs beyond that is a
+        // cycle the tensor pipe idles): everything a step decides is decided once per step, the
+        // four MMAs of a stage are straight-line code, and the other lanes stay out of the loop.
         // kind::f16, D fp32, A and B bf16, both K-major; N >> 3 at bit 17, M >> 4 at bit 24
         constexpr uint32_t kIdescBase = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 4) << 24);
         constexpr uint32_t kIdesc128 = kIdescBase | ((128u >> 3) << 17), kIdesc256 = kIdescBase | ((256u >> 3) << 17);
-        int g = 0, it = 0;
-        bool ok = true;
-        for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++it) {
-            const int pair = item % p.n_pairs, buf = it & 1;
-            ok = mbar_wait_relaxed(smem_u32(&acc_empty[buf]), ((it >> 1) & 1) ^ 1u, abort_flag, 9);
-            if (!ok) break;
-            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            const uint32_t acc = tmem + buf * kAccCols;
-            uint32_t have_a = 0u, have_b = 0u;                 // the halves hold defined values (uniform across the warp)
-            const int s_beg = pair_ptr[pair], s_end = pair_ptr[pair + 1];
-            for (int st = s_beg; st < s_end && ok; ++st) {
-                const int4 s = steps[st];
-#pragma unroll 1
-                for (int h = 0; h < 2; ++h, ++g) {
-                    const int sg = g % kBkStages;
-                    ok = mbar_wait(smem_u32(&full[sg]), (g / kBkStages) & 1, abort_flag, 2);
-                    if (!ok) break;
-                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                    if (lane == 0) {
-                        const uint32_t base = smem_u32(stages + sg * kBkStage);
-                        const uint64_t ad = make_smem_desc(base, 16, 1024, 2);
-                        const uint64_t bd = make_smem_desc(base + kBkA, 16, 1024, 2);
-                        const uint32_t a_lo = (uint32_t)ad, a_hi = (uint32_t)(ad >> 32);
-                        const uint32_t b_lo = (uint32_t)bd, b_hi = (uint32_t)(bd >> 32);
-                        uint32_t fa = have_a, fb = have_b;
+        if (lane == 0) {
+            const uint64_t d0 = make_smem_desc(smem_u32(stages), 16, 1024, 2);
+            const uint32_t a_lo0 = (uint32_t)d0, d_hi = (uint32_t)(d0 >> 32);   // stage 0; only the address field changes
+            const uint32_t full0 = smem_u32(&full[0]), empty0 = smem_u32(&empty[0]);
+            int g = 0, it = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++it) {
+                const int pair = item % p.n_pairs, buf = it & 1;
+                ok = mbar_wait_relaxed(smem_u32(&acc_empty[buf]), ((it >> 1) & 1) ^ 1u, abort_flag, 9);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint32_t acc = tmem + buf * kAccCols;
+                bool have_a = false, have_b = false;           // the halves hold defined values
+                const int s_beg = pair_ptr[pair], s_end = pair_ptr[pair + 1];
+                for (int st = s_beg; st < s_end && ok; ++st) {
+                    const int4 s = steps[st];
+                    const bool ya = s.y >= 0, zb = s.z >= 0;
+                    const bool wide = ya && zb && have_a == have_b;       // one N = 256 MMA covers both blocks
+                    const bool two = ya && zb && !wide;                    // different accumulate states: two N = 128 MMAs
+                    const uint32_t d1 = acc + (ya ? 0u : 128u);
+                    const uint32_t b_off1 = (kBkA >> 4) + (ya ? 0u : (uint32_t)(kBkB >> 4));
+                    const uint32_t idesc1 = wide ? kIdesc256 : kIdesc128;
+                    uint32_t f1 = (ya ? have_a : have_b) ? 1u : 0u, f2 = have_b ? 1u : 0u;
+#pragma unroll
+                    for (int h = 0; h < 2; ++h, ++g) {
+                        const uint32_t sg = (uint32_t)g % kBkStages;
+                        ok = mbar_wait(full0 + sg * 8u, ((uint32_t)g / kBkStages) & 1u, abort_flag, 2);
+                        if (!ok) break;
+                        const uint32_t a_lo = a_lo0 + sg * (uint32_t)(kBkStage >> 4);
+                        const uint32_t b_lo = a_lo + b_off1;
 #pragma unroll
                         for (int kk = 0; kk < 4; ++kk) {       // 16 features = 32 bytes inside the swizzled row
-                            if (s.y >= 0 && s.z >= 0 && fa == fb) {
-                                tc_mma(acc, a_lo + kk * 2, a_hi, b_lo + kk * 2, b_hi, kIdesc256, fa);
-                            } else {
-                                if (s.y >= 0) tc_mma(acc, a_lo + kk * 2, a_hi, b_lo + kk * 2, b_hi, kIdesc128, fa);
-                                if (s.z >= 0) tc_mma(acc + 128, a_lo + kk * 2, a_hi, b_lo + (kBkB >> 4) + kk * 2, b_hi, kIdesc128, fb);
+                            tc_mma(d1, a_lo + kk * 2, d_hi, b_lo + kk * 2, d_hi, idesc1, f1);
+                            f1 = 1u;
+                            if (two) {
+                                tc_mma(acc + 128, a_lo + kk * 2, d_hi, a_lo + (uint32_t)((kBkA + kBkB) >> 4) + kk * 2, d_hi, kIdesc128, f2);
+                                f2 = 1u;
                             }
-                            if (s.y >= 0) fa = 1u;
-                            if (s.z >= 0) fb = 1u;
                         }
-                        tc_commit(smem_u32(&empty[sg]));
+                        tc_commit(empty0 + sg * 8u);
                     }
-                    if (s.y >= 0) have_a = 1u;
-                    if (s.z >= 0) have_b = 1u;
-                    __syncwarp();
+                    have_a |= ya;
+                    have_b |= zb;
                 }
-            }
-            if (!ok) break;
-            if (lane == 0) {
+                if (!ok) break;
                 if (s_end > s_beg) tc_commit(smem_u32(&acc_full[buf]));
                 else mbar_arrive(smem_u32(&acc_full[buf]));
             }
-            __syncwarp();
         }
     } else {
         // ---------------- epilogue: warps 2..9; lane quadrant = warp % 4, column half = (warp - 2) / 4 ----------------
@@ -1108,11 +1111,15 @@ prefill_blocks_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
             }
         }
     } else if (warp == 1) {
-        if (rank == 0) {
-            // ---------------- MMA issue (CTA 0 for the pair) ----------------
+        if (rank == 0 && lane == 0) {
+            // ---------------- MMA issue: one thread of CTA 0 for the pair ----------------
             // kind::f16, D fp32, A and B bf16, both K-major; N >> 3 at bit 17, M >> 4 at bit 24 (M = 256 over the pair)
             constexpr uint32_t kIdescBase = (1u << 4) | (1u << 7) | (1u << 10) | ((256u >> 4) << 24);
             constexpr uint32_t kIdesc128 = kIdescBase | ((128u >> 3) << 17), kIdesc256 = kIdescBase | ((256u >> 3) << 17);
+            const uint64_t d0 = make_smem_desc(smem_u32(stages), 16, 1024, 2);
+            const uint32_t a_lo0 = (uint32_t)d0, d_hi = (uint32_t)(d0 >> 32);
+            const uint32_t full0 = smem_u32(&full[0]), empty0 = smem_u32(&empty[0]);
+            const uint32_t empty0_peer = map_to_cta(empty0, 1);
             int g = 0, it = 0;
             bool ok = true;
             for (int item = cluster_id; item < p.n_items && ok; item += n_clusters, ++it) {
@@ -1121,54 +1128,48 @@ prefill_blocks_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 const uint32_t acc = tmem + buf * kAccCols;
-                uint32_t have_a = 0u, have_b = 0u;
+                bool have_a = false, have_b = false;
                 const int s_beg = pair_ptr[pair], s_end = pair_ptr[pair + 1];
                 for (int st = s_beg; st < s_end && ok; ++st) {
                     const int4 s = steps[st];
-                    const bool wide = s.y >= 0 && s.z >= 0 && have_a == have_b;
-#pragma unroll 1
-                    for (int h = 0; h < 2; ++h, ++g) {
-                        const int sg = g % kB2Stages;
-                        ok = mbar_wait(smem_u32(&full[sg]), (g / kB2Stages) & 1, abort_flag, 2);
-                        if (!ok) break;
-                        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                        if (lane == 0) {
-                            const uint32_t base = smem_u32(stages + sg * kB2Stage);
-                            const uint64_t ad = make_smem_desc(base, 16, 1024, 2);
-                            const uint64_t bd = make_smem_desc(base + kBkA, 16, 1024, 2);
-                            const uint32_t a_lo = (uint32_t)ad, a_hi = (uint32_t)(ad >> 32);
-                            const uint32_t b_lo = (uint32_t)bd, b_hi = (uint32_t)(bd >> 32);
-                            uint32_t fa = have_a, fb = have_b;
+                    const bool ya = s.y >= 0, zb = s.z >= 0;
+                    const bool wide = ya && zb && have_a == have_b;
+                    const bool two = ya && zb && !wide;
+                    // N = 128: the first block's share lies at the start of the B region, the second's 8 KB in
+                    const uint32_t d1 = acc + (ya ? 0u : 128u);
+                    const uint32_t b_off1 = (uint32_t)(kBkA >> 4) + (ya ? 0u : (uint32_t)(kB2B >> 5));
+                    const uint32_t idesc1 = wide ? kIdesc256 : kIdesc128;
+                    uint32_t f1 = (ya ? have_a : have_b) ? 1u : 0u, f2 = have_b ? 1u : 0u;
 #pragma unroll
-                            for (int kk = 0; kk < 4; ++kk) {
-                                if (wide) {
-                                    tc_mma_pair(acc, a_lo + kk * 2, a_hi, b_lo + kk * 2, b_hi, kIdesc256, fa);
-                                } else {
-                                    if (s.y >= 0) tc_mma_pair(acc, a_lo + kk * 2, a_hi, b_lo + kk * 2, b_hi, kIdesc128, fa);
-                                    if (s.z >= 0) tc_mma_pair(acc + 128, a_lo + kk * 2, a_hi, b_lo + (kB2B >> 5) + kk * 2, b_hi, kIdesc128, fb);
-                                }
-                                if (s.y >= 0) fa = 1u;
-                                if (s.z >= 0) fb = 1u;
+                    for (int h = 0; h < 2; ++h, ++g) {
+                        const uint32_t sg = (uint32_t)g % kB2Stages;
+                        ok = mbar_wait(full0 + sg * 8u, ((uint32_t)g / kB2Stages) & 1u, abort_flag, 2);
+                        if (!ok) break;
+                        const uint32_t a_lo = a_lo0 + sg * (uint32_t)(kB2Stage >> 4);
+                        const uint32_t b_lo = a_lo + b_off1;
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk) {
+                            tc_mma_pair(d1, a_lo + kk * 2, d_hi, b_lo + kk * 2, d_hi, idesc1, f1);
+                            f1 = 1u;
+                            if (two) {
+                                tc_mma_pair(acc + 128, a_lo + kk * 2, d_hi, a_lo + (uint32_t)((kBkA >> 4) + (kB2B >> 5)) + kk * 2, d_hi, kIdesc128, f2);
+                                f2 = 1u;
                             }
-                            tc_commit_pair(smem_u32(&empty[sg]));
-                            tc_commit_pair(map_to_cta(smem_u32(&empty[sg]), 1));
                         }
-                        if (s.y >= 0) have_a = 1u;
-                        if (s.z >= 0) have_b = 1u;
-                        __syncwarp();
+                        tc_commit_pair(empty0 + sg * 8u);
+                        tc_commit_pair(empty0_peer + sg * 8u);
                     }
+                    have_a |= ya;
+                    have_b |= zb;
                 }
                 if (!ok) break;
-                if (lane == 0) {
-                    if (s_end > s_beg) {
-                        tc_commit_pair(smem_u32(&acc_full[buf]));
-                        tc_commit_pair(map_to_cta(smem_u32(&acc_full[buf]), 1));
-                    } else {
-                        mbar_arrive(smem_u32(&acc_full[buf]));
-                        mbar_arrive_cluster(map_to_cta(smem_u32(&acc_full[buf]), 1));
-                    }
+                if (s_end > s_beg) {
+                    tc_commit_pair(smem_u32(&acc_full[buf]));
+                    tc_commit_pair(map_to_cta(smem_u32(&acc_full[buf]), 1));
+                } else {
+                    mbar_arrive(smem_u32(&acc_full[buf]));
+                    mbar_arrive_cluster(map_to_cta(smem_u32(&acc_full[buf]), 1));
                 }
-                __syncwarp();
             }
         }
     } else {
