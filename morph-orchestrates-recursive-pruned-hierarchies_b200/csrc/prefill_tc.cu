@@ -878,16 +878,22 @@ prefill_blocks_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
             const uint32_t full0 = smem_u32(&full[0]), empty0 = smem_u32(&empty[0]);
             int g = 0, it = 0;
             bool ok = true;
+            // The poll of a stage's barrier is issued one stage ahead, so its latency runs under the
+            // MMAs of the stage before; a first poll that fails falls back to the bounded wait.
+            bool ready = mbar_try_wait(full0, 0u);
             for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++it) {
                 const int pair = item % p.n_pairs, buf = it & 1;
-                ok = mbar_wait_relaxed(smem_u32(&acc_empty[buf]), ((it >> 1) & 1) ^ 1u, abort_flag, 9);
+                if (!mbar_try_wait(smem_u32(&acc_empty[buf]), ((it >> 1) & 1) ^ 1u))
+                    ok = mbar_wait_relaxed(smem_u32(&acc_empty[buf]), ((it >> 1) & 1) ^ 1u, abort_flag, 9);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 const uint32_t acc = tmem + buf * kAccCols;
                 bool have_a = false, have_b = false;           // the halves hold defined values
                 const int s_beg = pair_ptr[pair], s_end = pair_ptr[pair + 1];
+                int4 s_next = steps[s_beg < s_end ? s_beg : 0];
                 for (int st = s_beg; st < s_end && ok; ++st) {
-                    const int4 s = steps[st];
+                    const int4 s = s_next;
+                    s_next = steps[st + 1 < s_end ? st + 1 : st];          // the next step's record, ahead of its use
                     const bool ya = s.y >= 0, zb = s.z >= 0;
                     const bool wide = ya && zb && have_a == have_b;       // one N = 256 MMA covers both blocks
                     const bool two = ya && zb && !wide;                    // different accumulate states: two N = 128 MMAs
@@ -898,8 +904,10 @@ prefill_blocks_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
 #pragma unroll
                     for (int h = 0; h < 2; ++h, ++g) {
                         const uint32_t sg = (uint32_t)g % kBkStages;
-                        ok = mbar_wait(full0 + sg * 8u, ((uint32_t)g / kBkStages) & 1u, abort_flag, 2);
+                        if (!ready) ok = mbar_wait(full0 + sg * 8u, ((uint32_t)g / kBkStages) & 1u, abort_flag, 2);
                         if (!ok) break;
+                        const uint32_t gn = (uint32_t)g + 1u;
+                        ready = mbar_try_wait(full0 + (gn % kBkStages) * 8u, (gn / kBkStages) & 1u);
                         const uint32_t a_lo = a_lo0 + sg * (uint32_t)(kBkStage >> 4);
                         const uint32_t b_lo = a_lo + b_off1;
 #pragma unroll
