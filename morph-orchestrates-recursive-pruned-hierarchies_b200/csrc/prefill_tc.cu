@@ -162,6 +162,18 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint32_t a_lo, uint32_t 
         "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}\n"
         ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate));
 }
+// The same with the accumulate flag fixed at compile time (no predicate to compute per instruction).
+template <bool ACC>
+__device__ __forceinline__ void tc_mma_lit(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                           uint32_t b_hi, uint32_t idesc) {
+    asm volatile(
+        "{\n.reg .pred p;\n.reg .b64 da, db;\n"
+        "setp.eq.u32 p, %6, 1;\n"
+        "mov.b64 da, {%1, %2};\n"
+        "mov.b64 db, {%3, %4};\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "n"(ACC ? 1 : 0));
+}
 __device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
                                           uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
@@ -603,7 +615,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   CUtensorMapFloatOOBfill);
 
 std::mutex g_prefill_init_mutex;   // guards the first-use initialisation below
-std::atomic<int> g_blocks_mode{0};  // block path: 0 = choose by row count, 1 = single CTAs, 2 = CTA pairs
+std::atomic<int> g_blocks_mode{0};  // block path: 0 = default (single CTAs), 1 = single CTAs, 2 = CTA pairs
 
 int get_encode_fn(EncodeTiledFn *out) {
     static EncodeTiledFn cached = nullptr;
@@ -891,36 +903,58 @@ prefill_blocks_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
                 bool have_a = false, have_b = false;           // the halves hold defined values
                 const int s_beg = pair_ptr[pair], s_end = pair_ptr[pair + 1];
                 int4 s_next = steps[s_beg < s_end ? s_beg : 0];
-                for (int st = s_beg; st < s_end && ok; ++st) {
+                for (int st = s_beg; st < s_end && ok; ++st, g += 2) {
                     const int4 s = s_next;
                     s_next = steps[st + 1 < s_end ? st + 1 : st];          // the next step's record, ahead of its use
                     const bool ya = s.y >= 0, zb = s.z >= 0;
                     const bool wide = ya && zb && have_a == have_b;       // one N = 256 MMA covers both blocks
                     const bool two = ya && zb && !wide;                    // different accumulate states: two N = 128 MMAs
                     const uint32_t d1 = acc + (ya ? 0u : 128u);
-                    const uint32_t b_off1 = (kBkA >> 4) + (ya ? 0u : (uint32_t)(kBkB >> 4));
                     const uint32_t idesc1 = wide ? kIdesc256 : kIdesc128;
-                    uint32_t f1 = (ya ? have_a : have_b) ? 1u : 0u, f2 = have_b ? 1u : 0u;
+                    const bool fresh = !(ya ? have_a : have_b);
+                    // a step takes two consecutive stages, the first of them stage 0 or 2
+                    const uint32_t odd = ((uint32_t)g >> 1) & 1u, parity = ((uint32_t)g >> 2) & 1u;
+                    const uint32_t bar_f = full0 + odd * 16u, bar_e = empty0 + odd * 16u;
+                    const uint32_t a_lo = a_lo0 + odd * (uint32_t)(2 * kBkStage >> 4);
+                    const uint32_t b_lo = a_lo + (kBkA >> 4) + (ya ? 0u : (uint32_t)(kBkB >> 4));
+                    constexpr uint32_t kS = kBkStage >> 4;
+                    // first half
+                    if (!ready) ok = mbar_wait(bar_f, parity, abort_flag, 2);
+                    if (!ok) break;
+                    ready = mbar_try_wait(bar_f + 8u, parity);
+                    if (!two) {
+                        if (fresh) tc_mma_lit<false>(d1, a_lo, d_hi, b_lo, d_hi, idesc1);
+                        else tc_mma_lit<true>(d1, a_lo, d_hi, b_lo, d_hi, idesc1);
+                        tc_mma_lit<true>(d1, a_lo + 2, d_hi, b_lo + 2, d_hi, idesc1);
+                        tc_mma_lit<true>(d1, a_lo + 4, d_hi, b_lo + 4, d_hi, idesc1);
+                        tc_mma_lit<true>(d1, a_lo + 6, d_hi, b_lo + 6, d_hi, idesc1);
+                    } else {
+                        uint32_t f1 = have_a ? 1u : 0u, f2 = have_b ? 1u : 0u;
 #pragma unroll
-                    for (int h = 0; h < 2; ++h, ++g) {
-                        const uint32_t sg = (uint32_t)g % kBkStages;
-                        if (!ready) ok = mbar_wait(full0 + sg * 8u, ((uint32_t)g / kBkStages) & 1u, abort_flag, 2);
-                        if (!ok) break;
-                        const uint32_t gn = (uint32_t)g + 1u;
-                        ready = mbar_try_wait(full0 + (gn % kBkStages) * 8u, (gn / kBkStages) & 1u);
-                        const uint32_t a_lo = a_lo0 + sg * (uint32_t)(kBkStage >> 4);
-                        const uint32_t b_lo = a_lo + b_off1;
-#pragma unroll
-                        for (int kk = 0; kk < 4; ++kk) {       // 16 features = 32 bytes inside the swizzled row
-                            tc_mma(d1, a_lo + kk * 2, d_hi, b_lo + kk * 2, d_hi, idesc1, f1);
-                            f1 = 1u;
-                            if (two) {
-                                tc_mma(acc + 128, a_lo + kk * 2, d_hi, a_lo + (uint32_t)((kBkA + kBkB) >> 4) + kk * 2, d_hi, kIdesc128, f2);
-                                f2 = 1u;
-                            }
+                        for (int kk = 0; kk < 4; ++kk) {
+                            tc_mma(acc, a_lo + kk * 2, d_hi, b_lo + kk * 2, d_hi, kIdesc128, f1);
+                            tc_mma(acc + 128, a_lo + kk * 2, d_hi, b_lo + (uint32_t)(kBkB >> 4) + kk * 2, d_hi, kIdesc128, f2);
+                            f1 = f2 = 1u;
                         }
-                        tc_commit(empty0 + sg * 8u);
                     }
+                    tc_commit(bar_e);
+                    // second half: the next stage; the poll after it goes to the stage the next step starts with
+                    if (!ready) ok = mbar_wait(bar_f + 8u, parity, abort_flag, 2);
+                    if (!ok) break;
+                    ready = mbar_try_wait(full0 + (odd ^ 1u) * 16u, parity ^ odd);
+                    if (!two) {
+                        tc_mma_lit<true>(d1, a_lo + kS, d_hi, b_lo + kS, d_hi, idesc1);
+                        tc_mma_lit<true>(d1, a_lo + kS + 2, d_hi, b_lo + kS + 2, d_hi, idesc1);
+                        tc_mma_lit<true>(d1, a_lo + kS + 4, d_hi, b_lo + kS + 4, d_hi, idesc1);
+                        tc_mma_lit<true>(d1, a_lo + kS + 6, d_hi, b_lo + kS + 6, d_hi, idesc1);
+                    } else {
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk) {
+                            tc_mma_lit<true>(acc, a_lo + kS + kk * 2, d_hi, b_lo + kS + kk * 2, d_hi, kIdesc128);
+                            tc_mma_lit<true>(acc + 128, a_lo + kS + kk * 2, d_hi, b_lo + kS + (uint32_t)(kBkB >> 4) + kk * 2, d_hi, kIdesc128);
+                        }
+                    }
+                    tc_commit(bar_e + 8u);
                     have_a |= ya;
                     have_b |= zb;
                 }
@@ -1320,9 +1354,10 @@ extern "C" int mortar_linear_blocks(const mortar_blocks *w, const void *x, int64
         return MORTAR_ERR_ALIGN;
     if (gates && (cluster_size <= 0 || !w->swiglu)) return MORTAR_ERR_SHAPE;
     if (rows == 0) return MORTAR_OK;
-    // more than one block of rows: CTA pairs share every block (unless the single-CTA kernel is forced)
+    // CTA pairs only on request: both kernels are bound by how fast one thread issues MMAs, not by
+    // the shared-memory traffic the pairs halve
     const int mode = g_blocks_mode.load(std::memory_order_relaxed);
-    const bool pairs = mode == 2 || (mode == 0 && rows > kRows);
+    const bool pairs = mode == 2;
     const int item_rows = pairs ? 2 * kRows : kRows;
     const int64_t row_blocks = (rows + item_rows - 1) / item_rows;
     const int64_t n_items = row_blocks * w->n_pairs;
