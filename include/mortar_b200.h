@@ -493,7 +493,8 @@ int mortar_linear_tc_i8(const mortar_sched *w, const void *xq, int64_t ldxq, con
  *             may come in any order (listing those both rows keep first lets every such step run
  *             as one N = 256 MMA)
  * A second kernel runs the same items on CTA pairs (tcgen05 cta_group::2: 256 rows per work
- * item, half of every block in each CTA's shared memory); it measured no faster and is opt-in. */
+ * item, half of every block in each CTA's shared memory); it is chosen for more than 128 rows when
+ * at least 90% of the steps hold both blocks (n_blocks >= 1.9 n_steps), where it measured faster. */
 typedef struct mortar_blocks {
     const void *data;
     const int32_t *pair_ptr;
@@ -511,7 +512,7 @@ int mortar_linear_blocks(const mortar_blocks *w, const void *x, int64_t ldx, int
                          int64_t ld_out, const float *gates, int64_t ld_gates, int32_t cluster_size,
                          void *stream);
 
-/* Which kernel the block path launches, process-wide: 0 = the default (single CTAs), 1 = single
+/* Which kernel the block path launches, process-wide: 0 = chosen per call (the default), 1 = single
  * CTAs, 2 = CTA pairs.  Returns the previous mode, or MORTAR_ERR_SHAPE for an unknown mode.  For
  * measurements and tests; the results of the kernels agree to the accumulation order. */
 int mortar_linear_blocks_mode(int32_t mode);

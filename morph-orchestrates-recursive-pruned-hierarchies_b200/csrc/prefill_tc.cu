@@ -615,7 +615,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   CUtensorMapFloatOOBfill);
 
 std::mutex g_prefill_init_mutex;   // guards the first-use initialisation below
-std::atomic<int> g_blocks_mode{0};  // block path: 0 = default (single CTAs), 1 = single CTAs, 2 = CTA pairs
+std::atomic<int> g_blocks_mode{0};  // block path: 0 = chosen per call, 1 = single CTAs, 2 = CTA pairs
 
 int get_encode_fn(EncodeTiledFn *out) {
     static EncodeTiledFn cached = nullptr;
@@ -1063,6 +1063,17 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint32_t a_lo, uint
         "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n}\n"
         ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate));
 }
+template <bool ACC>
+__device__ __forceinline__ void tc_mma_pair_lit(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                                uint32_t b_hi, uint32_t idesc) {
+    asm volatile(
+        "{\n.reg .pred p;\n.reg .b64 da, db;\n"
+        "setp.eq.u32 p, %6, 1;\n"
+        "mov.b64 da, {%1, %2};\n"
+        "mov.b64 db, {%3, %4};\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "n"(ACC ? 1 : 0));
+}
 __device__ __forceinline__ void tc_commit_pair(uint32_t cluster_bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
                  ::"r"(cluster_bar) : "memory");
@@ -1162,45 +1173,76 @@ prefill_blocks_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
             const uint32_t a_lo0 = (uint32_t)d0, d_hi = (uint32_t)(d0 >> 32);
             const uint32_t full0 = smem_u32(&full[0]), empty0 = smem_u32(&empty[0]);
             const uint32_t empty0_peer = map_to_cta(empty0, 1);
-            int g = 0, it = 0;
+            int it = 0;
+            uint32_t sp = 0u, parity = 0u;                     // stage pair (stages 2sp, 2sp+1) and its phase
             bool ok = true;
+            bool ready = mbar_try_wait(full0, 0u);             // polls run one stage ahead, as in the single-CTA kernel
             for (int item = cluster_id; item < p.n_items && ok; item += n_clusters, ++it) {
                 const int pair = item % p.n_pairs, buf = it & 1;
-                ok = mbar_wait_relaxed(smem_u32(&acc_empty[buf]), ((it >> 1) & 1) ^ 1u, abort_flag, 9);
+                if (!mbar_try_wait(smem_u32(&acc_empty[buf]), ((it >> 1) & 1) ^ 1u))
+                    ok = mbar_wait_relaxed(smem_u32(&acc_empty[buf]), ((it >> 1) & 1) ^ 1u, abort_flag, 9);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 const uint32_t acc = tmem + buf * kAccCols;
                 bool have_a = false, have_b = false;
                 const int s_beg = pair_ptr[pair], s_end = pair_ptr[pair + 1];
+                int4 s_next = steps[s_beg < s_end ? s_beg : 0];
                 for (int st = s_beg; st < s_end && ok; ++st) {
-                    const int4 s = steps[st];
+                    const int4 s = s_next;
+                    s_next = steps[st + 1 < s_end ? st + 1 : st];
                     const bool ya = s.y >= 0, zb = s.z >= 0;
                     const bool wide = ya && zb && have_a == have_b;
                     const bool two = ya && zb && !wide;
                     // N = 128: the first block's share lies at the start of the B region, the second's 8 KB in
                     const uint32_t d1 = acc + (ya ? 0u : 128u);
-                    const uint32_t b_off1 = (uint32_t)(kBkA >> 4) + (ya ? 0u : (uint32_t)(kB2B >> 5));
                     const uint32_t idesc1 = wide ? kIdesc256 : kIdesc128;
-                    uint32_t f1 = (ya ? have_a : have_b) ? 1u : 0u, f2 = have_b ? 1u : 0u;
-#pragma unroll
-                    for (int h = 0; h < 2; ++h, ++g) {
-                        const uint32_t sg = (uint32_t)g % kB2Stages;
-                        ok = mbar_wait(full0 + sg * 8u, ((uint32_t)g / kB2Stages) & 1u, abort_flag, 2);
-                        if (!ok) break;
-                        const uint32_t a_lo = a_lo0 + sg * (uint32_t)(kB2Stage >> 4);
-                        const uint32_t b_lo = a_lo + b_off1;
+                    const bool fresh = !(ya ? have_a : have_b);
+                    const uint32_t bar_f = full0 + sp * 16u, bar_e = empty0 + sp * 16u, bar_ep = empty0_peer + sp * 16u;
+                    const uint32_t a_lo = a_lo0 + sp * (uint32_t)(2 * kB2Stage >> 4);
+                    const uint32_t b_lo = a_lo + (uint32_t)(kBkA >> 4) + (ya ? 0u : (uint32_t)(kB2B >> 5));
+                    constexpr uint32_t kS = kB2Stage >> 4, kZ = kB2B >> 5;
+                    const uint32_t sp_next = sp == 2u ? 0u : sp + 1u, parity_next = sp == 2u ? parity ^ 1u : parity;
+                    // first half
+                    if (!ready) ok = mbar_wait(bar_f, parity, abort_flag, 2);
+                    if (!ok) break;
+                    ready = mbar_try_wait(bar_f + 8u, parity);
+                    if (!two) {
+                        if (fresh) tc_mma_pair_lit<false>(d1, a_lo, d_hi, b_lo, d_hi, idesc1);
+                        else tc_mma_pair_lit<true>(d1, a_lo, d_hi, b_lo, d_hi, idesc1);
+                        tc_mma_pair_lit<true>(d1, a_lo + 2, d_hi, b_lo + 2, d_hi, idesc1);
+                        tc_mma_pair_lit<true>(d1, a_lo + 4, d_hi, b_lo + 4, d_hi, idesc1);
+                        tc_mma_pair_lit<true>(d1, a_lo + 6, d_hi, b_lo + 6, d_hi, idesc1);
+                    } else {
+                        uint32_t f1 = have_a ? 1u : 0u, f2 = have_b ? 1u : 0u;
 #pragma unroll
                         for (int kk = 0; kk < 4; ++kk) {
-                            tc_mma_pair(d1, a_lo + kk * 2, d_hi, b_lo + kk * 2, d_hi, idesc1, f1);
-                            f1 = 1u;
-                            if (two) {
-                                tc_mma_pair(acc + 128, a_lo + kk * 2, d_hi, a_lo + (uint32_t)((kBkA >> 4) + (kB2B >> 5)) + kk * 2, d_hi, kIdesc128, f2);
-                                f2 = 1u;
-                            }
+                            tc_mma_pair(acc, a_lo + kk * 2, d_hi, b_lo + kk * 2, d_hi, kIdesc128, f1);
+                            tc_mma_pair(acc + 128, a_lo + kk * 2, d_hi, b_lo + kZ + kk * 2, d_hi, kIdesc128, f2);
+                            f1 = f2 = 1u;
                         }
-                        tc_commit_pair(empty0 + sg * 8u);
-                        tc_commit_pair(empty0_peer + sg * 8u);
                     }
+                    tc_commit_pair(bar_e);
+                    tc_commit_pair(bar_ep);
+                    // second half
+                    if (!ready) ok = mbar_wait(bar_f + 8u, parity, abort_flag, 2);
+                    if (!ok) break;
+                    ready = mbar_try_wait(full0 + sp_next * 16u, parity_next);
+                    if (!two) {
+                        tc_mma_pair_lit<true>(d1, a_lo + kS, d_hi, b_lo + kS, d_hi, idesc1);
+                        tc_mma_pair_lit<true>(d1, a_lo + kS + 2, d_hi, b_lo + kS + 2, d_hi, idesc1);
+                        tc_mma_pair_lit<true>(d1, a_lo + kS + 4, d_hi, b_lo + kS + 4, d_hi, idesc1);
+                        tc_mma_pair_lit<true>(d1, a_lo + kS + 6, d_hi, b_lo + kS + 6, d_hi, idesc1);
+                    } else {
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk) {
+                            tc_mma_pair_lit<true>(acc, a_lo + kS + kk * 2, d_hi, b_lo + kS + kk * 2, d_hi, kIdesc128);
+                            tc_mma_pair_lit<true>(acc + 128, a_lo + kS + kk * 2, d_hi, b_lo + kS + kZ + kk * 2, d_hi, kIdesc128);
+                        }
+                    }
+                    tc_commit_pair(bar_e + 8u);
+                    tc_commit_pair(bar_ep + 8u);
+                    sp = sp_next;
+                    parity = parity_next;
                     have_a |= ya;
                     have_b |= zb;
                 }
@@ -1354,10 +1396,11 @@ extern "C" int mortar_linear_blocks(const mortar_blocks *w, const void *x, int64
         return MORTAR_ERR_ALIGN;
     if (gates && (cluster_size <= 0 || !w->swiglu)) return MORTAR_ERR_SHAPE;
     if (rows == 0) return MORTAR_OK;
-    // CTA pairs only on request: both kernels are bound by how fast one thread issues MMAs, not by
-    // the shared-memory traffic the pairs halve
+    // CTA pairs pay where nearly every step holds both blocks (N = 256 MMAs, bound by the tensor pipe
+    // and the shared-memory traffic the pairs halve); steps with one block are bound by how fast one
+    // thread issues MMAs, and there the single CTAs measured faster
     const int mode = g_blocks_mode.load(std::memory_order_relaxed);
-    const bool pairs = mode == 2;
+    const bool pairs = mode == 2 || (mode == 0 && rows > kRows && w->n_blocks * 10 >= (int64_t)w->n_steps * 19);
     const int item_rows = pairs ? 2 * kRows : kRows;
     const int64_t row_blocks = (rows + item_rows - 1) / item_rows;
     const int64_t n_items = row_blocks * w->n_pairs;
