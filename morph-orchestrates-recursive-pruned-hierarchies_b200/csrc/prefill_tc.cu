@@ -839,39 +839,51 @@ prefill_blocks_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
     volatile int *abort_flag = &abort_s;
 
     if (warp == 0) {
-        // ---------------- TMA producer ----------------
-        int g = 0;
-        bool ok = true;
-        for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
-            const int pair = item % p.n_pairs, row0 = (item / p.n_pairs) * kRows;
-            const int s_end = pair_ptr[pair + 1];
-            for (int st = pair_ptr[pair]; st < s_end && ok; ++st) {
-                const int4 s = steps[st];
-#pragma unroll 1
-                for (int h = 0; h < 2; ++h, ++g) {
-                    const int sg = g % kBkStages;
-                    ok = mbar_wait_relaxed(smem_u32(&empty[sg]), ((g / kBkStages) & 1) ^ 1u, abort_flag, 5);
-                    if (!ok) break;
-                    if (lane == 0) {
-                        const uint32_t bar = smem_u32(&full[sg]);
-                        const uint32_t dst = smem_u32(stages + sg * kBkStage);
-                        mbar_arrive_expect_tx(bar, kBkA + (s.y >= 0 ? kBkB : 0) + (s.z >= 0 ? kBkB : 0));
+        // ---------------- TMA producer: one thread ----------------
+        // Same shape as the MMA role: per-step values hoisted, the poll of the next stage's `empty`
+        // barrier issued before the loads of the current one.
+        if (lane == 0) {
+            const uint32_t full0 = smem_u32(&full[0]), empty0 = smem_u32(&empty[0]), stage0 = smem_u32(stages);
+            int g = 0;
+            bool ok = true;
+            bool ready = mbar_try_wait(empty0, 1u);
+            for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
+                const int pair = item % p.n_pairs, row0 = (item / p.n_pairs) * kRows;
+                const int s_beg = pair_ptr[pair], s_end = pair_ptr[pair + 1];
+                int4 s_next = steps[s_beg < s_end ? s_beg : 0];
+                for (int st = s_beg; st < s_end && ok; ++st, g += 2) {
+                    const int4 s = s_next;
+                    s_next = steps[st + 1 < s_end ? st + 1 : st];
+                    const uint32_t bytes = kBkA + (s.y >= 0 ? kBkB : 0) + (s.z >= 0 ? kBkB : 0);
+                    const uint32_t odd = ((uint32_t)g >> 1) & 1u, parity = (((uint32_t)g >> 2) & 1u) ^ 1u;
+                    const int xcol = s.x * 128, yrow = s.y * 128, zrow = s.z * 128;
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const uint32_t sg = odd * 2u + (uint32_t)h;
+                        if (!ready) ok = mbar_wait_relaxed(empty0 + sg * 8u, parity, abort_flag, 5);
+                        if (!ok) break;
+                        // next stage: the pair's second stage, or the first stage of the other pair (whose phase
+                        // flips when this pair is the second one)
+                        ready = h == 0 ? mbar_try_wait(empty0 + (sg + 1u) * 8u, parity)
+                                       : mbar_try_wait(empty0 + (odd ^ 1u) * 16u, parity ^ odd);
+                        const uint32_t bar = full0 + sg * 8u;
+                        const uint32_t dst = stage0 + sg * (uint32_t)kBkStage;
+                        mbar_arrive_expect_tx(bar, bytes);
                         asm volatile(
                             "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
                             "[%0], [%1, {%2, %3}], [%4];\n"
-                            ::"r"(dst), "l"(&tmap_x), "r"(s.x * 128 + h * 64), "r"(row0), "r"(bar) : "memory");
+                            ::"r"(dst), "l"(&tmap_x), "r"(xcol + h * 64), "r"(row0), "r"(bar) : "memory");
                         if (s.y >= 0)
                             asm volatile(
                                 "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
                                 "[%0], [%1, {%2, %3}], [%4];\n"
-                                ::"r"(dst + kBkA), "l"(&tmap_w), "r"(h * 64), "r"(s.y * 128), "r"(bar) : "memory");
+                                ::"r"(dst + kBkA), "l"(&tmap_w), "r"(h * 64), "r"(yrow), "r"(bar) : "memory");
                         if (s.z >= 0)
                             asm volatile(
                                 "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
                                 "[%0], [%1, {%2, %3}], [%4];\n"
-                                ::"r"(dst + kBkA + kBkB), "l"(&tmap_w), "r"(h * 64), "r"(s.z * 128), "r"(bar) : "memory");
+                                ::"r"(dst + kBkA + kBkB), "l"(&tmap_w), "r"(h * 64), "r"(zrow), "r"(bar) : "memory");
                     }
-                    __syncwarp();
                 }
             }
         }
