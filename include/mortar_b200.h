@@ -492,9 +492,8 @@ int mortar_linear_tc_i8(const mortar_sched *w, const void *xq, int64_t ldxq, con
  *             first block row's block or -1, of the second's or -1, 0}; the block columns of a pair
  *             may come in any order (listing those both rows keep first lets every such step run
  *             as one N = 256 MMA)
- * A second kernel runs the same items on CTA pairs (tcgen05 cta_group::2: 256 rows per work
- * item, half of every block in each CTA's shared memory); it is chosen for more than 128 rows when
- * at least 90% of the steps hold both blocks (n_blocks >= 1.9 n_steps), where it measured faster. */
+ * With more than 128 rows the kernel runs on CTA pairs (tcgen05 cta_group::2: 256 rows per work
+ * item, half of every block in each CTA's shared memory). */
 typedef struct mortar_blocks {
     const void *data;
     const int32_t *pair_ptr;

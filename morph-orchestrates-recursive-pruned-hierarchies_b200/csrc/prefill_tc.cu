@@ -1141,38 +1141,51 @@ prefill_blocks_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
     volatile int *abort_flag = &abort_s;
 
     if (warp == 0) {
-        // ---------------- TMA producer (both CTAs) ----------------
-        int g = 0;
-        bool ok = true;
-        for (int item = cluster_id; item < p.n_items && ok; item += n_clusters) {
-            const int pair = item % p.n_pairs, row0 = (item / p.n_pairs) * (2 * kRows) + (int)rank * kRows;
-            bool have_a = false, have_b = false;
-            const int s_end = pair_ptr[pair + 1];
-            for (int st = pair_ptr[pair]; st < s_end && ok; ++st) {
-                const int4 s = steps[st];
-                const bool wide = s.y >= 0 && s.z >= 0 && have_a == have_b;
-                const uint32_t b_bytes = wide ? (uint32_t)kB2B : (uint32_t)((s.y >= 0) + (s.z >= 0)) * (kB2B / 2);
-#pragma unroll 1
-                for (int h = 0; h < 2; ++h, ++g) {
-                    const int sg = g % kB2Stages;
-                    ok = mbar_wait_relaxed(smem_u32(&empty[sg]), ((g / kB2Stages) & 1) ^ 1u, abort_flag, 5);
-                    if (!ok) break;
-                    if (lane == 0) {
-                        const uint32_t bar = map_to_cta(smem_u32(&full[sg]), 0);
-                        const uint32_t dst = smem_u32(stages + sg * kB2Stage);
-                        if (rank == 0) mbar_arrive_expect_tx(smem_u32(&full[sg]), 2u * (kBkA + b_bytes));
-                        tma_load_pair(dst, &tmap_x, s.x * 128 + h * 64, row0, bar);
+        // ---------------- TMA producer: one thread in each CTA ----------------
+        if (lane == 0) {
+            const uint32_t full0 = smem_u32(&full[0]), full0_lead = map_to_cta(full0, 0);
+            const uint32_t empty0 = smem_u32(&empty[0]), stage0 = smem_u32(stages);
+            uint32_t sp = 0u, parity = 1u;                     // stage pair and the phase its `empty` barriers are waited in
+            bool ok = true;
+            bool ready = mbar_try_wait(empty0, 1u);
+            for (int item = cluster_id; item < p.n_items && ok; item += n_clusters) {
+                const int pair = item % p.n_pairs, row0 = (item / p.n_pairs) * (2 * kRows) + (int)rank * kRows;
+                bool have_a = false, have_b = false;
+                const int s_beg = pair_ptr[pair], s_end = pair_ptr[pair + 1];
+                int4 s_next = steps[s_beg < s_end ? s_beg : 0];
+                for (int st = s_beg; st < s_end && ok; ++st) {
+                    const int4 s = s_next;
+                    s_next = steps[st + 1 < s_end ? st + 1 : st];
+                    const bool ya = s.y >= 0, zb = s.z >= 0;
+                    const bool wide = ya && zb && have_a == have_b;
+                    const uint32_t b_bytes = wide ? (uint32_t)kB2B : (uint32_t)(ya + zb) * (kB2B / 2);
+                    const int xcol = s.x * 128;
+                    const int yrow = wide ? (rank == 0 ? s.y : s.z) * 128 : s.y * 128 + (int)rank * 64;
+                    const int zrow = s.z * 128 + (int)rank * 64;
+                    const uint32_t sp_next = sp == 2u ? 0u : sp + 1u, parity_next = sp == 2u ? parity ^ 1u : parity;
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const uint32_t sg = sp * 2u + (uint32_t)h;
+                        if (!ready) ok = mbar_wait_relaxed(empty0 + sg * 8u, parity, abort_flag, 5);
+                        if (!ok) break;
+                        ready = h == 0 ? mbar_try_wait(empty0 + (sg + 1u) * 8u, parity)
+                                       : mbar_try_wait(empty0 + sp_next * 16u, parity_next);
+                        const uint32_t bar = full0_lead + sg * 8u;
+                        const uint32_t dst = stage0 + sg * (uint32_t)kB2Stage;
+                        if (rank == 0) mbar_arrive_expect_tx(full0 + sg * 8u, 2u * (kBkA + b_bytes));
+                        tma_load_pair(dst, &tmap_x, xcol + h * 64, row0, bar);
                         if (wide) {
-                            tma_load_pair(dst + kBkA, &tmap_w, h * 64, (rank == 0 ? s.y : s.z) * 128, bar);
+                            tma_load_pair(dst + kBkA, &tmap_w, h * 64, yrow, bar);
                         } else {
-                            if (s.y >= 0) tma_load_pair(dst + kBkA, &tmap_wh, h * 64, s.y * 128 + (int)rank * 64, bar);
-                            if (s.z >= 0) tma_load_pair(dst + kBkA + kB2B / 2, &tmap_wh, h * 64, s.z * 128 + (int)rank * 64, bar);
+                            if (ya) tma_load_pair(dst + kBkA, &tmap_wh, h * 64, yrow, bar);
+                            if (zb) tma_load_pair(dst + kBkA + kB2B / 2, &tmap_wh, h * 64, zrow, bar);
                         }
                     }
-                    __syncwarp();
+                    sp = sp_next;
+                    parity = parity_next;
+                    have_a |= ya;
+                    have_b |= zb;
                 }
-                have_a |= s.y >= 0;
-                have_b |= s.z >= 0;
             }
         }
     } else if (warp == 1) {
@@ -1408,11 +1421,10 @@ extern "C" int mortar_linear_blocks(const mortar_blocks *w, const void *x, int64
         return MORTAR_ERR_ALIGN;
     if (gates && (cluster_size <= 0 || !w->swiglu)) return MORTAR_ERR_SHAPE;
     if (rows == 0) return MORTAR_OK;
-    // CTA pairs pay where nearly every step holds both blocks (N = 256 MMAs, bound by the tensor pipe
-    // and the shared-memory traffic the pairs halve); steps with one block are bound by how fast one
-    // thread issues MMAs, and there the single CTAs measured faster
+    // more than one block of rows: CTA pairs (never slower in measurements, a few percent faster where
+    // most steps hold both blocks and the tensor pipe and shared-memory traffic bound the kernel)
     const int mode = g_blocks_mode.load(std::memory_order_relaxed);
-    const bool pairs = mode == 2 || (mode == 0 && rows > kRows && w->n_blocks * 10 >= (int64_t)w->n_steps * 19);
+    const bool pairs = mode == 2 || (mode == 0 && rows > kRows);
     const int item_rows = pairs ? 2 * kRows : kRows;
     const int64_t row_blocks = (rows + item_rows - 1) / item_rows;
     const int64_t n_items = row_blocks * w->n_pairs;

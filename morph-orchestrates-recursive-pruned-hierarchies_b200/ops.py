@@ -659,9 +659,8 @@ BLOCKS_MODES = {"auto": 0, "single": 1, "pairs": 2}
 
 
 def linear_blocks_mode(mode: str) -> str:
-    """Chooses the kernel of the block path process-wide: "auto" (the default: CTA pairs where nearly
-    every step holds both blocks, else single CTAs), "single" or "pairs" (tcgen05 cta_group::2).
-    Returns the previous mode."""
+    """Chooses the kernel of the block path process-wide: "auto" (the default: CTA pairs, tcgen05
+    cta_group::2, from 129 rows on), "single" or "pairs".  Returns the previous mode."""
     prev = _lib.lib().mortar_linear_blocks_mode(BLOCKS_MODES[mode])
     _lib.check(min(prev, 0), "mortar_linear_blocks_mode")
     return {v: k for k, v in BLOCKS_MODES.items()}[prev]
