@@ -436,9 +436,13 @@ BLOCK = 128
 
 # Token blocks run the block path of the prefill kernels (every touched 128 x 128 block executed
 # densely, dropped tiles as zeros) when the touched blocks are at least this full.  Measured on the
-# cloud shape: a single 16 x 16 tile is one narrow MMA at the tensor pipe's ~45-cycle floor, so the
-# per-tile path only wins below about 15% fill; 25% random tiles already run faster as dense blocks.
-BLOCK_PATH_MIN_FILL = 0.2
+# cloud shape the dense blocks run at the tensor pipe's rate whatever their fill, while the per-tile
+# path pays a narrow MMA per tile and a fixed cost per panel: the block path was faster down to 3%
+# random tiles (0.38 ms against 0.41 ms per MLP at 8192 tokens; 187 against 147 TFLOP/s useful at
+# 12.5%).  The price is memory: the expanded blocks take 2 bytes per element of every touched
+# block, built on the first forward with 128 rows or more.  Below this fill that price buys
+# little, and the per-tile path keeps the packed footprint.
+BLOCK_PATH_MIN_FILL = 0.05
 
 
 def wants_block_path(m: "MortarMatrix", swiglu: bool) -> bool:

@@ -120,11 +120,11 @@ def test_blocks_golden_fixture_and_module_dispatch():
                                                       *a[:5], a[6], *b[:5], b[6], None, 0)
     assert tuple(fy.shape) == (300, 256) and fy.dtype == torch.bfloat16
     # a sparse tile-16 topology keeps the per-tile path
-    L = mb.synth.make_layer(256, 512, 0.1, seed=3)
-    assert mb.format.block_fill(L.gate_up) < mb.format.BLOCK_PATH_MIN_FILL
+    L = mb.synth.make_layer(1024, 512, 0.02, seed=3)
+    assert max(mb.format.block_fill(L.gate_up), mb.format.block_fill(L.down)) < mb.format.BLOCK_PATH_MIN_FILL
     mlp2 = mb.SwiGLUMortar.from_matrices(L.gate_up, L.down, device=DEV)
     n1 = mb.ops.kernel_counts().get("prefill_panel", 0)
-    mlp2(x)
+    mlp2(mb.synth.make_activations(256, 1024, seed=6).to(DEV))
     assert mb.ops.kernel_counts()["prefill_panel"] - n1 == 2
     # the reference operator on a 128-carved layer takes the block path too
     z = torch.zeros(1, dtype=torch.int16, device=DEV)
