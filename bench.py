@@ -675,14 +675,23 @@ def run_backward(mb, device, pk, flush, reps: int = 5):
              "blocks128": mb.synth.make_block_matrix(2 * f, d, DENSITY, seed=3)}
     for name, m in cases.items():
         topo = fmt.TopologyDev(m, device)
-        mt = m.transpose().to_sched(False, device)
+        # dx the way the registered operator's backward runs it: the transposed matrix on the block
+        # path when its touched blocks are full enough, else per tile
+        mT = m.transpose()
+        if fmt.wants_block_path(mT, False):
+            mt, dx_path = mT.to_blocks(False, device), "prefill_blocks_kernel"
+            dx = lambda: mb.ops.linear_blocks(dy, mt)
+        else:
+            mt, dx_path = mT.to_sched(False, device), "prefill_panel_kernel"
+            dx = lambda: mb.ops.linear_tc(dy, mt)
         t_dw = statistics.median(time_steps(lambda: mb.ops.sdd_tiles(dy, x, topo), reps, 2, flush))
         t_dw_tiles = statistics.median(time_steps(lambda: mb.ops.sdd_tiles(dy, x, topo, path="tiles"), reps, 1, flush))
-        t_dx = statistics.median(time_steps(lambda: mb.ops.linear_tc(dy, mt), reps, 2, flush))
+        t_dx = statistics.median(time_steps(dx, reps, 2, flush))
         flops = 2 * 256 * m.nnz * tokens
         out[name] = {"dW_us": round(t_dw * 1e3, 1), "dW_tflops": round(flops / (t_dw * 1e-3) / 1e12, 1),
                      "dW_per_tile_kernel_us": round(t_dw_tiles * 1e3, 1),
-                     "dx_us": round(t_dx * 1e3, 1), "dx_tflops": round(flops / (t_dx * 1e-3) / 1e12, 1)}
+                     "dx_us": round(t_dx * 1e3, 1), "dx_tflops": round(flops / (t_dx * 1e-3) / 1e12, 1),
+                     "dx_kernel": dx_path}
     out["device_error_word"] = mb.ops.prefill_error() or mb.ops.sdd_error()
     return out
 
