@@ -174,6 +174,39 @@ __device__ __forceinline__ void tc_mma_lit(uint32_t d_tmem, uint32_t a_lo, uint3
         "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}\n"
         ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "n"(ACC ? 1 : 0));
 }
+// One stage of a step: the poll of the NEXT stage's barrier and this stage's four MMAs (16 features
+// each, descriptor addresses 2 units apart) as one instruction sequence, so that the poll's result
+// is first read after the MMAs have issued and its latency runs under them.  PAIR selects
+// cta_group::2.  Returns whether the polled phase had completed.
+template <bool FIRST_ACC, bool PAIR>
+__device__ __forceinline__ bool tc_poll_mma4(uint32_t next_bar, uint32_t next_parity, uint32_t d_tmem, uint32_t a_lo,
+                                             uint32_t b_lo, uint32_t d_hi, uint32_t idesc) {
+    uint32_t ready;
+#define MORTAR_MMA4_BODY(GROUP)                                                                      \
+    asm volatile(                                                                                    \
+        "{\n.reg .pred q, p0, p1;\n.reg .b64 da, db;\n"                                              \
+        "mbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2;\n"                                    \
+        "setp.eq.u32 p0, %12, 1;\n"                                                                  \
+        "setp.eq.u32 p1, 1, 1;\n"                                                                    \
+        "mov.b64 da, {%4, %11};\n mov.b64 db, {%8, %11};\n"                                          \
+        "tcgen05.mma.cta_group::" GROUP ".kind::f16 [%3], da, db, %13, p0;\n"                        \
+        "mov.b64 da, {%5, %11};\n mov.b64 db, {%9, %11};\n"                                          \
+        "tcgen05.mma.cta_group::" GROUP ".kind::f16 [%3], da, db, %13, p1;\n"                        \
+        "mov.b64 da, {%6, %11};\n mov.b64 db, {%10, %11};\n"                                         \
+        "tcgen05.mma.cta_group::" GROUP ".kind::f16 [%3], da, db, %13, p1;\n"                        \
+        "mov.b64 da, {%7, %11};\n mov.b64 db, {%14, %11};\n"                                         \
+        "tcgen05.mma.cta_group::" GROUP ".kind::f16 [%3], da, db, %13, p1;\n"                        \
+        "selp.b32 %0, 1, 0, q;\n}\n"                                                                 \
+        : "=r"(ready)                                                                                \
+        : "r"(next_bar), "r"(next_parity), "r"(d_tmem), "r"(a_lo), "r"(a_lo + 2), "r"(a_lo + 4),    \
+          "r"(a_lo + 6), "r"(b_lo), "r"(b_lo + 2), "r"(b_lo + 4), "r"(d_hi), "n"(FIRST_ACC ? 1 : 0), \
+          "r"(idesc), "r"(b_lo + 6)                                                                  \
+        : "memory")
+    if (PAIR) MORTAR_MMA4_BODY("2");
+    else MORTAR_MMA4_BODY("1");
+#undef MORTAR_MMA4_BODY
+    return ready != 0;
+}
 __device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
                                           uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
@@ -933,14 +966,11 @@ prefill_blocks_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
                     // first half
                     if (!ready) ok = mbar_wait(bar_f, parity, abort_flag, 2);
                     if (!ok) break;
-                    ready = mbar_try_wait(bar_f + 8u, parity);
                     if (!two) {
-                        if (fresh) tc_mma_lit<false>(d1, a_lo, d_hi, b_lo, d_hi, idesc1);
-                        else tc_mma_lit<true>(d1, a_lo, d_hi, b_lo, d_hi, idesc1);
-                        tc_mma_lit<true>(d1, a_lo + 2, d_hi, b_lo + 2, d_hi, idesc1);
-                        tc_mma_lit<true>(d1, a_lo + 4, d_hi, b_lo + 4, d_hi, idesc1);
-                        tc_mma_lit<true>(d1, a_lo + 6, d_hi, b_lo + 6, d_hi, idesc1);
+                        ready = fresh ? tc_poll_mma4<false, false>(bar_f + 8u, parity, d1, a_lo, b_lo, d_hi, idesc1)
+                                      : tc_poll_mma4<true, false>(bar_f + 8u, parity, d1, a_lo, b_lo, d_hi, idesc1);
                     } else {
+                        ready = mbar_try_wait(bar_f + 8u, parity);
                         uint32_t f1 = have_a ? 1u : 0u, f2 = have_b ? 1u : 0u;
 #pragma unroll
                         for (int kk = 0; kk < 4; ++kk) {
@@ -953,13 +983,10 @@ prefill_blocks_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
                     // second half: the next stage; the poll after it goes to the stage the next step starts with
                     if (!ready) ok = mbar_wait(bar_f + 8u, parity, abort_flag, 2);
                     if (!ok) break;
-                    ready = mbar_try_wait(full0 + (odd ^ 1u) * 16u, parity ^ odd);
                     if (!two) {
-                        tc_mma_lit<true>(d1, a_lo + kS, d_hi, b_lo + kS, d_hi, idesc1);
-                        tc_mma_lit<true>(d1, a_lo + kS + 2, d_hi, b_lo + kS + 2, d_hi, idesc1);
-                        tc_mma_lit<true>(d1, a_lo + kS + 4, d_hi, b_lo + kS + 4, d_hi, idesc1);
-                        tc_mma_lit<true>(d1, a_lo + kS + 6, d_hi, b_lo + kS + 6, d_hi, idesc1);
+                        ready = tc_poll_mma4<true, false>(full0 + (odd ^ 1u) * 16u, parity ^ odd, d1, a_lo + kS, b_lo + kS, d_hi, idesc1);
                     } else {
+                        ready = mbar_try_wait(full0 + (odd ^ 1u) * 16u, parity ^ odd);
 #pragma unroll
                         for (int kk = 0; kk < 4; ++kk) {
                             tc_mma_lit<true>(acc, a_lo + kS + kk * 2, d_hi, b_lo + kS + kk * 2, d_hi, kIdesc128);
@@ -1230,14 +1257,11 @@ prefill_blocks_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                     // first half
                     if (!ready) ok = mbar_wait(bar_f, parity, abort_flag, 2);
                     if (!ok) break;
-                    ready = mbar_try_wait(bar_f + 8u, parity);
                     if (!two) {
-                        if (fresh) tc_mma_pair_lit<false>(d1, a_lo, d_hi, b_lo, d_hi, idesc1);
-                        else tc_mma_pair_lit<true>(d1, a_lo, d_hi, b_lo, d_hi, idesc1);
-                        tc_mma_pair_lit<true>(d1, a_lo + 2, d_hi, b_lo + 2, d_hi, idesc1);
-                        tc_mma_pair_lit<true>(d1, a_lo + 4, d_hi, b_lo + 4, d_hi, idesc1);
-                        tc_mma_pair_lit<true>(d1, a_lo + 6, d_hi, b_lo + 6, d_hi, idesc1);
+                        ready = fresh ? tc_poll_mma4<false, true>(bar_f + 8u, parity, d1, a_lo, b_lo, d_hi, idesc1)
+                                      : tc_poll_mma4<true, true>(bar_f + 8u, parity, d1, a_lo, b_lo, d_hi, idesc1);
                     } else {
+                        ready = mbar_try_wait(bar_f + 8u, parity);
                         uint32_t f1 = have_a ? 1u : 0u, f2 = have_b ? 1u : 0u;
 #pragma unroll
                         for (int kk = 0; kk < 4; ++kk) {
@@ -1251,13 +1275,10 @@ prefill_blocks_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                     // second half
                     if (!ready) ok = mbar_wait(bar_f + 8u, parity, abort_flag, 2);
                     if (!ok) break;
-                    ready = mbar_try_wait(full0 + sp_next * 16u, parity_next);
                     if (!two) {
-                        tc_mma_pair_lit<true>(d1, a_lo + kS, d_hi, b_lo + kS, d_hi, idesc1);
-                        tc_mma_pair_lit<true>(d1, a_lo + kS + 2, d_hi, b_lo + kS + 2, d_hi, idesc1);
-                        tc_mma_pair_lit<true>(d1, a_lo + kS + 4, d_hi, b_lo + kS + 4, d_hi, idesc1);
-                        tc_mma_pair_lit<true>(d1, a_lo + kS + 6, d_hi, b_lo + kS + 6, d_hi, idesc1);
+                        ready = tc_poll_mma4<true, true>(full0 + sp_next * 16u, parity_next, d1, a_lo + kS, b_lo + kS, d_hi, idesc1);
                     } else {
+                        ready = mbar_try_wait(full0 + sp_next * 16u, parity_next);
 #pragma unroll
                         for (int kk = 0; kk < 4; ++kk) {
                             tc_mma_pair_lit<true>(acc, a_lo + kS + kk * 2, d_hi, b_lo + kS + kk * 2, d_hi, kIdesc128);
