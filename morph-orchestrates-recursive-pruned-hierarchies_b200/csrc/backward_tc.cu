@@ -45,15 +45,6 @@ struct SddParams {
     long long split_stride;   // floats between splits
 };
 
-template <bool ACC>
-__device__ __forceinline__ void mma_lit(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "setp.eq.u32 p, %4, 1;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "n"(ACC ? 1 : 0));
-}
-
 __global__ void __launch_bounds__(kThreads, 1)
 sdd_blocks_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant__ CUtensorMap tmap_x,
                   const SddParams p) {
@@ -88,25 +79,17 @@ sdd_blocks_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_cons
     const uint32_t tmem = tmem_base_s;
     volatile int *abort_flag = &abort_s;
 
-    // The producer and the MMA role are one thread each: what such a thread spends between the MMAs
-    // of two stages (polls, commits, address arithmetic) is time the tensor pipe drains, so the poll
-    // of the next stage's barrier is issued before the work of the current one and the accumulate
-    // flag is a compile-time constant.
     if (warp == 0) {
         // ---------------- TMA producer ----------------
-        if (lane == 0) {
-            const int out0 = p.blk_rc[2 * b] * 128, in0 = p.blk_rc[2 * b + 1] * 128;
-            const uint32_t full0 = tc::smem_u32(&full[0]), empty0 = tc::smem_u32(&empty[0]), stage0 = tc::smem_u32(stages);
-            bool ready = tc::mbar_try_wait(empty0, 1u);
-            for (int it = 0; it < n_it; ++it) {
-                const uint32_t s = (uint32_t)it % kStages;
-                if (!ready && !tc::mbar_wait(empty0 + s * 8u, (((uint32_t)it / kStages) & 1u) ^ 1u, abort_flag, &g_sdd_error, 1)) break;
-                const uint32_t nx = (uint32_t)it + 1u;
-                ready = tc::mbar_try_wait(empty0 + (nx % kStages) * 8u, ((nx / kStages) & 1u) ^ 1u);
-                const uint32_t bar = full0 + s * 8u;
+        const int out0 = p.blk_rc[2 * b] * 128, in0 = p.blk_rc[2 * b + 1] * 128;
+        for (int it = 0; it < n_it; ++it) {
+            const int s = it % kStages;
+            if (!tc::mbar_wait(tc::smem_u32(&empty[s]), ((it / kStages) & 1) ^ 1u, abort_flag, &g_sdd_error, 1)) break;
+            if (lane == 0) {
+                const uint32_t bar = tc::smem_u32(&full[s]);
                 tc::mbar_arrive_expect_tx(bar, kStageBytes);
                 const int tok = (int)(k_begin + (long long)it * kTok);
-                const uint32_t dst = stage0 + s * (uint32_t)kStageBytes;
+                const uint32_t dst = tc::smem_u32(stages + s * kStageBytes);
 #pragma unroll
                 for (int h = 0; h < 4; ++h) {
                     const CUtensorMap *map = h < 2 ? &tmap_dy : &tmap_x;
@@ -117,6 +100,7 @@ sdd_blocks_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_cons
                         ::"r"(dst + h * kBox), "l"(map), "r"(feat), "r"(tok), "r"(bar) : "memory");
                 }
             }
+            __syncwarp();
         }
     } else if (warp == 1) {
         // ---------------- MMA issue ----------------
@@ -124,40 +108,36 @@ sdd_blocks_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_cons
         // (bits 15, 16), N >> 3 at bit 17, M >> 4 at bit 24
         constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) |
                                     ((128u >> 3) << 17) | ((128u >> 4) << 24);
-        if (lane == 0) {
-            // M/N-major, 128-byte swizzle: a token is a 128-byte row of 64 features, 8 tokens are one
-            // 1024-byte atom (stride byte offset), the second half of the 128 features lies one box
-            // further (leading byte offset); 16 tokens per MMA = two atoms (2048 bytes).  Only the
-            // address field of the descriptors changes between MMAs and stages.
-            const uint64_t ad0 = tc::make_smem_desc(tc::smem_u32(stages), kBox, 1024, 2);
-            const uint64_t bd0 = tc::make_smem_desc(tc::smem_u32(stages) + 2 * kBox, kBox, 1024, 2);
-            const uint32_t full0 = tc::smem_u32(&full[0]), empty0 = tc::smem_u32(&empty[0]);
-            bool ok = true;
-            bool ready = tc::mbar_try_wait(full0, 0u);
-            for (int it = 0; it < n_it; ++it) {
-                const uint32_t s = (uint32_t)it % kStages;
-                if (!ready) ok = tc::mbar_wait(full0 + s * 8u, ((uint32_t)it / kStages) & 1u, abort_flag, &g_sdd_error, 2);
-                if (!ok) break;
-                const uint32_t nx = (uint32_t)it + 1u;
-                ready = tc::mbar_try_wait(full0 + (nx % kStages) * 8u, (nx / kStages) & 1u);
-                const uint64_t ad = ad0 + (uint64_t)(s * (uint32_t)(kStageBytes >> 4));
-                const uint64_t bd = bd0 + (uint64_t)(s * (uint32_t)(kStageBytes >> 4));
-                if (it == 0) mma_lit<false>(tmem, ad, bd, kIdesc);
-                else mma_lit<true>(tmem, ad, bd, kIdesc);
+        bool ok = true;
+        for (int it = 0; it < n_it && ok; ++it) {
+            const int s = it % kStages;
+            ok = tc::mbar_wait(tc::smem_u32(&full[s]), (it / kStages) & 1, abort_flag, &g_sdd_error, 2);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            if (lane == 0) {
+                const uint32_t a0 = tc::smem_u32(stages + s * kStageBytes), b0 = a0 + 2 * kBox;
 #pragma unroll
-                for (int kk = 1; kk < kTok / 16; ++kk)
-                    mma_lit<true>(tmem, ad + (uint64_t)(kk * (2048 >> 4)), bd + (uint64_t)(kk * (2048 >> 4)), kIdesc);
-                tc::commit(empty0 + s * 8u);
+                for (int kk = 0; kk < kTok / 16; ++kk) {
+                    // M/N-major, 128-byte swizzle: a token is a 128-byte row of 64 features, 8 tokens
+                    // are one 1024-byte atom (stride byte offset), the second half of the 128 features
+                    // lies one box further (leading byte offset); 16 tokens per MMA = two atoms
+                    const uint64_t ad = tc::make_smem_desc(a0 + kk * 2048, kBox, 1024, 2);
+                    const uint64_t bd = tc::make_smem_desc(b0 + kk * 2048, kBox, 1024, 2);
+                    tc::mma_f16(tmem, ad, bd, kIdesc, (it | kk) ? 1u : 0u);
+                }
+                tc::commit(tc::smem_u32(&empty[s]));
             }
-            if (ok) {
-                if (n_it > 0) tc::commit(tc::smem_u32(acc_full));
-                else asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(tc::smem_u32(acc_full)) : "memory");
-            }
+            __syncwarp();
         }
+        if (ok && lane == 0) {
+            if (n_it > 0) tc::commit(tc::smem_u32(acc_full));
+            else asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(tc::smem_u32(acc_full)) : "memory");
+        }
+        __syncwarp();
     } else {
         // ---------------- epilogue: warp w reads tensor-memory lanes 32 (w % 4) .. +31 ----------------
         const int q = warp & 3;
-        if (tc::mbar_wait_warp_relaxed(tc::smem_u32(acc_full), 0, abort_flag, &g_sdd_error, 3, 1u << 24)) {
+        if (tc::mbar_wait(tc::smem_u32(acc_full), 0, abort_flag, &g_sdd_error, 3, 1u << 26)) {
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const int m = q * 32 + lane;                       // output feature of the block = accumulator lane
             const int tr = m >> 4;

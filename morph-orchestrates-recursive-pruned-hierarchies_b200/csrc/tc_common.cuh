@@ -41,26 +41,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     return false;
 }
 
-// The same for a whole warp that is off the critical path: lane 0 polls with a pause between
-// polls (a spinning warp takes issue slots and barrier-unit time from the roles that feed the
-// tensor pipe), the result goes to every lane.
-__device__ __forceinline__ bool mbar_wait_warp_relaxed(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                                       int *error_word, int code, uint32_t limit = 1u << 22) {
-    bool ok = true;
-    if ((threadIdx.x & 31) == 0) {
-        ok = false;
-        for (uint32_t i = 0; i < limit; ++i) {
-            if (mbar_try_wait(bar, parity)) { ok = true; break; }
-            __nanosleep(128);
-            if ((i & 255u) == 255u && *abort_flag) break;
-            if (i + 1 == limit) { *abort_flag = 1; atomicCAS(error_word, 0, code); }
-        }
-    }
-    ok = __shfl_sync(0xffffffffu, ok, 0);
-    __syncwarp();
-    return ok;
-}
-
 // Shared-memory matrix descriptor: start address, leading and stride byte offsets (all in
 // 16-byte units), descriptor version 1, layout type (0 = no swizzle, 2 = 128-byte swizzle).
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo, uint32_t layout) {
