@@ -850,6 +850,9 @@ def run_gemv_large(mb, device, pk, flush, reps: int = 20, copies: int = 8):
     tm["device_error_word"] = mb.ops.gemv_blocks_error()
     out["tensor_memory_path_not_selected"] = tm
     out["reference_published_us_rtx5090"] = {"gate_up": 43.3, "down": 38.9}
+    # the reference's own Triton GEMV on this GPU: its source tree is not present on the machine this
+    # benchmark runs on and may not be copied into this repository, so there is nothing to launch
+    out["reference_triton_us_b200"] = {"unavailable": "the reference's Triton kernel source is not on this machine"}
     out["note"] = (f"kernel bcsr_stream_kernel; one CUDA graph of {copies} launches over {copies} "
                    f"distinct weight copies, L2 flushed before each replay; per-launch time = "
                    f"graph time / {copies} (includes the launch gaps inside the graph)")
