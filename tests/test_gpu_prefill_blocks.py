@@ -81,6 +81,20 @@ def test_mlp_blocks_cloud_shape_vs_oracle_and_tile_path(rows, kernel_mode):
         mb.ops.linear_blocks_mode(kernel_mode)
 
 
+def test_step_list_larger_than_the_shared_memory_cache(kernel_mode):
+    """More than 1024 steps: the roles read the step list from global memory instead of the copy in
+    shared memory."""
+    m = mb.synth.make_block_matrix(16384, 2176, 1.0, seed=21)
+    b = m.to_blocks(False, DEV)
+    assert b.n_steps > 1024
+    x = mb.synth.make_activations(256, 2176, seed=9).to(DEV)
+    y = mb.ops.linear_blocks(x, b)
+    _clean()
+    W = torch.from_numpy(m.to_dense_codes()).float() * torch.tensor(m.scale).to(torch.bfloat16).float()
+    ref = torch.nn.functional.linear(x.cpu(), W.to(torch.bfloat16))
+    _assert_bf16_close(y, ref)
+
+
 def test_blocks_golden_fixture_and_module_dispatch():
     """The reference's own 128-blocking carve (fixture made by running it) through the block path, and
     the module forward choosing that path by itself."""
