@@ -482,9 +482,10 @@ int mortar_linear_tc_i8(const mortar_sched *w, const void *xq, int64_t ldxq, con
  * The granularity the reference carves at (carve(blocking=128), block_sparse.py:810-907).  Kept
  * blocks are held expanded -- codes as bf16, [128 outputs][128 inputs] per block, what the
  * reference keeps as `mortar_data` (block_sparse.py:783-799) without the scale -- so a block is a
- * plain tensor-core operand; block rows are executed in pairs (SwiGLU: gate block row g with the
- * up block row of the same hidden columns, which needs d_ff to be a multiple of 128; linear:
- * block rows 2p and 2p+1).  Same arithmetic and rounding points as mortar_linear_tc.
+ * plain tensor-core operand; block rows are executed in pairs (SwiGLU: block row g of the gate
+ * half with block row g of the up half, both halves cut into blocks from their own first row, so
+ * a d_ff that is not a multiple of 128 only leaves the last block row of each half partly empty;
+ * linear: block rows 2p and 2p+1).  Same arithmetic and rounding points as mortar_linear_tc.
  *   data      device bf16 [n_blocks][128][128]; a kept block's tiles that the topology drops, and
  *             the part of an edge block beyond the matrix, are zeros
  *   pair_ptr  device int32 [n_pairs + 1]: first step of every pair

@@ -803,15 +803,15 @@ __device__ __forceinline__ void block_epilogue_chunk(const BlockParams &p, uint3
     if (SWIGLU) tc_ld_wait(b);
     const bool tile_gates = GATED && (p.cluster_size % 16 == 0);
     float tg[2] = {1.f, 1.f};
-    if (GATED && tile_gates && in_range) {
-        tg[0] = __ldg(p.gates + row * p.ld_gates + col0 / p.cluster_size);
-        tg[1] = __ldg(p.gates + row * p.ld_gates + (col0 + 16) / p.cluster_size);
+    if (GATED && tile_gates && in_range) {       // columns past the hidden width (a padded last pair) have no gate
+        if (col0 < p.n_out) tg[0] = __ldg(p.gates + row * p.ld_gates + col0 / p.cluster_size);
+        if (col0 + 16 < p.n_out) tg[1] = __ldg(p.gates + row * p.ld_gates + (col0 + 16) / p.cluster_size);
     }
     uint32_t packed[16];
 #pragma unroll
     for (int e = 0; e < 32; e += 2) {
         float gate0 = tg[e >> 4], gate1 = tg[e >> 4];
-        if (GATED && !tile_gates && in_range) {
+        if (GATED && !tile_gates && in_range && col0 + e + 1 < p.n_out) {
             gate0 = __ldg(p.gates + row * p.ld_gates + (col0 + e) / p.cluster_size);
             gate1 = __ldg(p.gates + row * p.ld_gates + (col0 + e + 1) / p.cluster_size);
         }
@@ -1428,7 +1428,9 @@ extern "C" int mortar_linear_blocks(const mortar_blocks *w, const void *x, int64
         (w->out_features % 16) || (w->in_features % 16))
         return MORTAR_ERR_SHAPE;
     const int n_out = w->swiglu ? w->out_features / 2 : w->out_features;
-    if (w->swiglu && (n_out % 128)) return MORTAR_ERR_SHAPE;        // gate and up block rows pair up
+    // every output column belongs to a pair (SwiGLU: 128 hidden columns per pair, the last pair may be
+    // padded; linear: 256 output columns per pair)
+    if ((int64_t)w->n_pairs * (w->swiglu ? 128 : 256) < n_out) return MORTAR_ERR_SHAPE;
     if (ldx < w->in_features || ld_out < n_out) return MORTAR_ERR_SHAPE;
     if (!aligned_to(x, 16) || (ldx % 8) || !aligned_to(out, 16) || (ld_out % 8) || !aligned_to(w->data, 16) ||
         !aligned_to(w->steps, 16))

@@ -446,10 +446,7 @@ BLOCK_PATH_MIN_FILL = 0.05
 
 
 def wants_block_path(m: "MortarMatrix", swiglu: bool) -> bool:
-    """Whether token blocks of `m` should take the block path (see BLOCK_PATH_MIN_FILL); a gate/up
-    matrix additionally needs d_ff to be a multiple of 128 so gate and up block rows pair up."""
-    if swiglu and (m.out_features // 2) % BLOCK:
-        return False
+    """Whether token blocks of `m` should take the block path (see BLOCK_PATH_MIN_FILL)."""
     return block_fill(m) >= BLOCK_PATH_MIN_FILL
 
 
@@ -469,15 +466,29 @@ class BlockSched:
     zeros), and the step lists of the pairs of block rows (see ``mortar_blocks`` in the header)."""
 
     def __init__(self, m: "MortarMatrix", swiglu: bool, device="cuda"):
-        if swiglu and (m.out_features // 2) % BLOCK:
-            raise ValueError("the block path pairs gate and up block rows: d_ff must be a multiple of 128")
         self.out_features, self.in_features = m.out_features, m.in_features
         self.swiglu, self.scale, self.nnz = bool(swiglu), float(m.scale), m.nnz
-        Rb, Cb = -(-m.out_features // BLOCK), -(-m.in_features // BLOCK)
-        dense = np.zeros((Rb * BLOCK, Cb * BLOCK), dtype=np.int8)
-        dense[:m.out_features, :m.in_features] = m.to_dense_codes()
+        Cb = -(-m.in_features // BLOCK)
         rows = np.repeat(np.arange(m.tile_rows), np.diff(m.row_ptr)).astype(np.int64)
-        key = np.unique((rows // 8) * Cb + m.col_idx.astype(np.int64) // 8)          # ascending (row, column)
+        codes = m.to_dense_codes()
+        if swiglu:
+            # gate rows and up rows each start on a block boundary, so that block row g of the gate
+            # half and block row g of the up half cover the same hidden columns whatever d_ff is
+            # (a d_ff that is not a multiple of 128 leaves the last block row of each half partly empty)
+            d_ff = m.out_features // 2
+            Hb = -(-d_ff // BLOCK)
+            Rb = 2 * Hb
+            dense = np.zeros((Rb * BLOCK, Cb * BLOCK), dtype=np.int8)
+            dense[:d_ff, :m.in_features] = codes[:d_ff]
+            dense[Hb * BLOCK:Hb * BLOCK + d_ff, :m.in_features] = codes[d_ff:]
+            ht = d_ff // TILE
+            brow_of_tile = np.where(rows < ht, rows // 8, (rows - ht) // 8 + Hb)
+        else:
+            Rb = -(-m.out_features // BLOCK)
+            dense = np.zeros((Rb * BLOCK, Cb * BLOCK), dtype=np.int8)
+            dense[:m.out_features, :m.in_features] = codes
+            brow_of_tile = rows // 8
+        key = np.unique(brow_of_tile * Cb + m.col_idx.astype(np.int64) // 8)          # ascending (row, column)
         brow, bcol = key // Cb, key % Cb
         blocks = dense.reshape(Rb, BLOCK, Cb, BLOCK).transpose(0, 2, 1, 3)[brow, bcol]   # [nb, 128, 128]
         self.n_blocks = int(key.size)

@@ -189,8 +189,8 @@ class CarvedStorage(nn.Module):
         return self._sched[swiglu]
 
     def blocks(self, swiglu: bool) -> Optional[BlockSched]:
-        """Layout of the block path when the topology is made of (mostly) full 128 x 128 blocks
-        (and, for a gate/up matrix, d_ff is a multiple of 128); None otherwise."""
+        """Layout of the block path when the touched 128 x 128 blocks are full enough
+        (format.BLOCK_PATH_MIN_FILL); None otherwise."""
         key = ("blocks", swiglu)
         if key not in self._sched:
             m = self.matrix()

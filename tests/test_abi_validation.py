@@ -28,7 +28,7 @@ def test_block_path_entry_points_validate():
     assert f(C.byref(blk), C.c_void_p(p.value + 2), 256, 8, p, 256, None, 0, 0, None) == ALIGN
     assert f(C.byref(blk), p, 256, 8, p, 256, p, 4, 16, None) == SHAPE             # gates without a swiglu layout
     assert f(C.byref(blk), p, 256, 0, p, 256, None, 0, 0, None) == 0               # no rows: nothing to do
-    sw = mb._lib.Blocks(p, p, p, 1, 1, 1, 2 * 192, 256, 1, 1.0)                    # d_ff = 192 is not a multiple of 128
+    sw = mb._lib.Blocks(p, p, p, 1, 1, 1, 2 * 192, 256, 1, 1.0)                    # one pair of block rows cannot hold 192 hidden columns
     assert f(C.byref(sw), p, 256, 8, p, 192, None, 0, 0, None) == SHAPE
     g = L.mortar_mlp_prefill_blocks
     assert g(C.byref(blk), C.byref(blk), p, 256, 8, None, 0, 0, p, 256, p, 1 << 20, None) == SHAPE   # first must be swiglu

@@ -81,6 +81,31 @@ def test_mlp_blocks_cloud_shape_vs_oracle_and_tile_path(rows, kernel_mode):
         mb.ops.linear_blocks_mode(kernel_mode)
 
 
+@pytest.mark.parametrize("rows", [130, 300])
+def test_mlp_blocks_hidden_width_not_a_multiple_of_128(rows, kernel_mode):
+    """d_ff = 448: the gate and the up half are cut into blocks from their own first rows, the last
+    block row of each half is half empty, and so is the last block column of the down matrix."""
+    d, f = 256, 448
+    L = mb.synth.make_layer(d, f, 0.3, seed=13)
+    x = mb.synth.make_activations(rows, d, seed=rows).to(DEV)
+    bg, bd = L.gate_up.to_blocks(True, DEV), L.down.to_blocks(False, DEV)
+    assert bg.n_pairs == 4 and bg.n_out == f
+    y = mb.ops.mlp_prefill_blocks(x, bg, bd)
+    _clean()
+    ref = orc.swiglu_mlp(x.cpu().float(), _dense(L.gate_up), _dense(L.down), dtype=torch.bfloat16)
+    _assert_bf16_close(y, ref, near_zero=1e-2)
+    ncls = f // 16
+    gates = mb.synth.make_gates(rows, L, ncls, ncls // 4, seed=3).to(DEV)
+    yg = mb.ops.mlp_prefill_blocks(x, bg, bd, gates=gates, n_clusters=ncls)
+    refg = orc.swiglu_mlp(x.cpu().float(), _dense(L.gate_up), _dense(L.down), gates.cpu(), ncls, dtype=torch.bfloat16)
+    _assert_bf16_close(yg, refg, near_zero=1e-2)
+    # the hidden block itself, against the per-tile path bit for bit on exact integer activations
+    xi = torch.randint(-3, 4, (rows, d), generator=torch.Generator().manual_seed(2)).to(torch.bfloat16).to(DEV)
+    assert torch.equal(mb.ops.linear_blocks(xi, L.gate_up.to_blocks(False, DEV)),
+                       mb.ops.linear_tc(xi, L.gate_up.to_sched(False, DEV)))
+    _clean()
+
+
 def test_step_list_larger_than_the_shared_memory_cache(kernel_mode):
     """More than 1024 steps: the roles read the step list from global memory instead of the copy in
     shared memory."""
