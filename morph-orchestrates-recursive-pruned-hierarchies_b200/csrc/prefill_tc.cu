@@ -1053,9 +1053,12 @@ prefill_blocks_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
 // ---------------------------------------------------------------------------------------------
 // Block path on CTA pairs (tcgen05 cta_group::2).  A cluster of two CTAs works on 256 activation
 // rows (128 each) against one pair of block rows: the MMA has M = 256 and its B operand is split
-// between the two CTAs' shared memories, so each CTA stages and reads only half of every block.
-// A single-CTA MMA is bound by shared-memory bandwidth (operand reads plus the TMA writes that
-// refill the stages); halving the B traffic per SM lifts that bound.
+// between the two CTAs' shared memories, so each CTA stages and reads only half of every block
+// (a quarter less traffic from L2 and through shared memory per FLOP) and one instruction drives
+// both SMs' tensor cores (half the MMA instructions per FLOP for the one issuing thread).  The
+// smaller stages leave room for six, three steps in flight, which lets a step hang on ONE pair of
+// barriers.  Measured against the single-CTA kernel: 8% faster on a dense topology, 7% on ragged
+// 128-blocks.
 //
 // Per step (one block column of the pair) and half (K = 64) each CTA loads its own [128 x 64]
 // activation chunk and its share of the B operand:
@@ -1064,9 +1067,9 @@ prefill_blocks_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
 //   otherwise one N = 128 MMA per present block, whose B rows 0..63 are held by CTA 0 and 64..127
 //     by CTA 1: every CTA loads 64 rows of each present block (first block at offset 0, second at
 //     8 KB of the B region).
-// All loads of a stage complete on CTA 0's `full` barrier (its producer posts the byte count of
-// both CTAs); CTA 0's MMA warp issues for the pair and commits to the `empty` and accumulator
-// barriers of both CTAs; the epilogue warps of both CTAs release an accumulator set on CTA 0's
+// All loads of a step complete on CTA 0's `full` barrier of the stage pair (its producer posts the
+// byte count of both CTAs and both halves); one thread of CTA 0 issues for the pair and commits to
+// the `empty` and accumulator barriers of both CTAs; the epilogue warps of both CTAs release an accumulator set on CTA 0's
 // barrier.  Every wait is bounded as in the single-CTA kernel.
 constexpr int kB2Stages = 6;
 constexpr int kB2B = 128 * 128;                      // this CTA's share of the step's B operand
