@@ -106,6 +106,33 @@ def test_mlp_blocks_hidden_width_not_a_multiple_of_128(rows, kernel_mode):
     _clean()
 
 
+def test_blocks_at_the_large_model_shape_match_the_tile_path():
+    """The shape of the reference's large-model decode bench (d_model 8192, d_ff 21824 -- not a
+    multiple of 128 --, 25% ragged 128-blocks): step lists beyond the shared-memory cache, padded last
+    block rows, 5456 blocks.  On exact integer activations every sum is exact, so the block path and
+    the per-tile path (itself checked against the oracle at small sizes) must agree bit for bit."""
+    d, f, rows = 8192, 21824, 256
+    gu_m = mb.synth.make_block_matrix(2 * f, d, 0.25, seed=1)
+    dn_m = mb.synth.make_block_matrix(d, f, 0.25, seed=2)
+    xi = torch.randint(-2, 3, (rows, d), generator=torch.Generator().manual_seed(4)).to(torch.bfloat16).to(DEV)
+    bg = gu_m.to_blocks(False, DEV)
+    assert bg.n_steps > 1024
+    g_blocks = mb.ops.linear_blocks(xi, bg)
+    g_tiles = mb.ops.linear_tc(xi, gu_m.to_sched(False, DEV))
+    _clean()
+    assert torch.equal(g_blocks, g_tiles)
+    del bg, g_blocks, g_tiles
+    hi = torch.randint(-2, 3, (rows, f), generator=torch.Generator().manual_seed(5)).to(torch.bfloat16).to(DEV)
+    assert torch.equal(mb.ops.linear_blocks(hi, dn_m.to_blocks(False, DEV)), mb.ops.linear_tc(hi, dn_m.to_sched(False, DEV)))
+    _clean()
+    # the fused MLP: SwiGLU pairing with the padded last block row of each half
+    x = mb.synth.make_activations(rows, d, seed=6).to(DEV)
+    yb = mb.ops.mlp_prefill_blocks(x, gu_m.to_blocks(True, DEV), dn_m.to_blocks(False, DEV))
+    yt = mb.ops.mlp_prefill_tc(x, gu_m.to_sched(True, DEV), dn_m.to_sched(False, DEV))
+    _clean()
+    _assert_bf16_close(yb, yt.cpu(), near_zero=1e-2)
+
+
 def test_step_list_larger_than_the_shared_memory_cache(kernel_mode):
     """More than 1024 steps: the roles read the step list from global memory instead of the copy in
     shared memory."""
