@@ -849,6 +849,19 @@ def run_gemv_large(mb, device, pk, flush, reps: int = 20, copies: int = 8):
         tm[name + "_us"] = round(statistics.median(time_steps(g.replay, reps, 3, flush)) * 1e3 / copies, 2)
     tm["device_error_word"] = mb.ops.gemv_blocks_error()
     out["tensor_memory_path_not_selected"] = tm
+    del tg, td, gus, dns
+    # the same layer as a token block (block path; d_ff = 21824 is not a multiple of 128, the step
+    # lists exceed the kernel's shared-memory cache): one MLP over 4096 tokens
+    tokens = 4096
+    bg, bd = gu_m.to_blocks(True, device), dn_m.to_blocks(False, device)
+    xt = mb.synth.make_activations(tokens, d, seed=4).to(device)
+    yt = torch.empty(tokens, d, device=device, dtype=torch.bfloat16)
+    wsp = torch.empty(tokens * f * 2 + 256, device=device, dtype=torch.uint8)
+    t_pf = statistics.median(time_steps(lambda: mb.ops.mlp_prefill_blocks(xt, bg, bd, out=yt, workspace=wsp), 5, 2, flush))
+    flops = 2.0 * 256 * (gu_m.nnz + dn_m.nnz) * tokens
+    out["prefill_blocks_4096_tokens"] = {"ms": round(t_pf, 3), "useful_tflops": round(flops / (t_pf * 1e-3) / 1e12, 1),
+                                         "frac_of_measured_bf16_sustained": round(flops / (t_pf * 1e-3) / 1e12 / pk["bf16_tflops_sustained"], 4),
+                                         "device_error_word": mb.ops.prefill_error()}
     out["reference_published_us_rtx5090"] = {"gate_up": 43.3, "down": 38.9}
     # the reference's own Triton GEMV on this GPU: its source tree is not present on the machine this
     # benchmark runs on and may not be copied into this repository, so there is nothing to launch
