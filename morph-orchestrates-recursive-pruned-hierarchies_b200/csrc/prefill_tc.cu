@@ -796,9 +796,23 @@ struct BlockParams {
 template <bool SWIGLU, bool GATED>
 __device__ __forceinline__ void block_epilogue_chunk(const BlockParams &p, uint32_t taddr, long long row, bool in_range,
                                                      long long col0, int c0, bool live_a, bool live_b) {
+    // an accumulator half that received no block holds undefined values: zeros stand in for it, so the
+    // arithmetic below needs no per-element select
     uint32_t a[32], b[32];
-    tc_ld32(taddr + c0, a);
-    if (SWIGLU) tc_ld32(taddr + 128 + c0, b);
+    if (live_a) {
+        tc_ld32(taddr + c0, a);
+    } else {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) a[e] = 0u;
+    }
+    if (SWIGLU) {
+        if (live_b) {
+            tc_ld32(taddr + 128 + c0, b);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) b[e] = 0u;
+        }
+    }
     tc_ld_wait(a);
     if (SWIGLU) tc_ld_wait(b);
     const bool tile_gates = GATED && (p.cluster_size % 16 == 0);
@@ -817,7 +831,7 @@ __device__ __forceinline__ void block_epilogue_chunk(const BlockParams &p, uint3
         }
         packed[e >> 1] = finish2<SWIGLU, GATED>(p.scale, __uint_as_float(a[e]), __uint_as_float(a[e + 1]),
                                                 SWIGLU ? __uint_as_float(b[e]) : 0.f, SWIGLU ? __uint_as_float(b[e + 1]) : 0.f,
-                                                live_a, live_b, gate0, gate1);
+                                                true, true, gate0, gate1);
     }
     if (in_range) {
         uint4 *dst = reinterpret_cast<uint4 *>(p.out + row * p.ld_out + col0);
